@@ -1,0 +1,409 @@
+/*
+ * tpb_oracle.c -- CPU restatement of TensorPencil's quantized-linear path.
+ *
+ * TEST INFRASTRUCTURE ONLY (see tpb_oracle.h).  Compile with
+ * -ffp-contract=off: the reference's Zig code fuses a multiply-add only where
+ * it says @mulAdd, and this file does the same with explicit FMA intrinsics.
+ */
+#include "tpb_oracle.h"
+
+#include <immintrin.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int tpo_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------------ */
+/* ConvRot rotation -- src/ops/convrot.zig                                   */
+/* ------------------------------------------------------------------------ */
+
+/* 4x4 regular-Hadamard block, convrot.zig:19-25. */
+static const float H4[4][4] = {
+    {1, 1, 1, -1},
+    {1, 1, -1, 1},
+    {1, -1, 1, 1},
+    {-1, 1, 1, 1},
+};
+
+void tpo_hadamard256(float *out) {
+    /* convrot.zig:30-47: product over the four base-4 digits, then /16. */
+    for (int i = 0; i < TPO_GROUP; i++) {
+        for (int j = 0; j < TPO_GROUP; j++) {
+            float p = 1.0f;
+            int ii = i, jj = j;
+            for (int d = 0; d < 4; d++) {
+                p *= H4[ii % 4][jj % 4];
+                ii /= 4;
+                jj /= 4;
+            }
+            out[i * TPO_GROUP + j] = p / 16.0f;
+        }
+    }
+}
+
+/* convrot.zig:56-78.  The add order is the reference's, left to right:
+ * ((a+b)+c)-d, ((a+b)-c)+d, ((a-b)+c)+d, ((-a+b)+c)+d. */
+static void rotate_group(float *v) {
+    static const size_t strides[4] = {1, 4, 16, 64};
+    for (int si = 0; si < 4; si++) {
+        const size_t s = strides[si];
+        for (size_t base = 0; base < TPO_GROUP; base += s * 4) {
+            for (size_t o = 0; o < s; o++) {
+                const size_t p = base + o;
+                const float a = v[p];
+                const float b = v[p + s];
+                const float c = v[p + 2 * s];
+                const float d = v[p + 3 * s];
+                v[p] = a + b + c - d;
+                v[p + s] = a + b - c + d;
+                v[p + 2 * s] = a - b + c + d;
+                v[p + 3 * s] = -a + b + c + d;
+            }
+        }
+    }
+    for (size_t i = 0; i < TPO_GROUP; i++) v[i] /= 16.0f;
+}
+
+void tpo_convrot_rotate(float *data, size_t n) {
+    for (size_t off = 0; off + TPO_GROUP <= n; off += TPO_GROUP)
+        rotate_group(data + off);
+}
+
+/* ------------------------------------------------------------------------ */
+/* Storage layouts -- src/core/dtype.zig                                     */
+/* ------------------------------------------------------------------------ */
+
+int8_t tpo_nibble_i4(uint8_t byte, int idx) {
+    /* dtype.zig:146-149: take the nibble, reinterpret as a signed 4-bit value. */
+    const uint8_t nib = (uint8_t)((byte >> (idx ? 4 : 0)) & 0xF);
+    return (int8_t)((nib & 0x8) ? (int)nib - 16 : (int)nib);
+}
+
+void tpo_unpack_i4(const uint8_t *packed, size_t n_elems, int8_t *out) {
+    for (size_t e = 0; e < n_elems; e++)
+        out[e] = tpo_nibble_i4(packed[e / 2], (int)(e & 1));
+}
+
+void tpo_pack_i4(const int8_t *vals, size_t n_elems, uint8_t *packed) {
+    for (size_t i = 0; i < n_elems / 2; i++)
+        packed[i] = (uint8_t)(((uint8_t)vals[2 * i] & 0xF) |
+                              (((uint8_t)vals[2 * i + 1] & 0xF) << 4));
+}
+
+void tpo_i4_convrot_dequant(const uint8_t *packed, const float *row_scale,
+                            size_t rows, size_t cols, float *out) {
+    for (size_t r = 0; r < rows; r++) {
+        const uint8_t *rb = packed + r * cols / 2;
+        float *row = out + r * cols;
+        for (size_t k = 0; k < cols; k++)
+            row[k] = (float)tpo_nibble_i4(rb[k / 2], (int)(k & 1)) * row_scale[r];
+        tpo_convrot_rotate(row, cols);
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Integer-domain replica -- src/gpu/cuda/kernels.zig:2638-2677, :2487-2523  */
+/* ------------------------------------------------------------------------ */
+
+void tpo_convrot_prep(const float *x, size_t m, size_t k, int bits, int8_t *q,
+                      float *act_scale, float *xr_out) {
+    const float maxq = bits == 4 ? 7.0f : 127.0f;
+    const int lo = bits == 4 ? -8 : -127;
+    const int hi = bits == 4 ? 7 : 127;
+#pragma omp parallel
+    {
+        float *tmp = (float *)malloc(k * sizeof(float));
+#pragma omp for schedule(static)
+        for (long long i = 0; i < (long long)m; i++) {
+            float *xr = xr_out ? xr_out + (size_t)i * k : tmp;
+            memcpy(xr, x + (size_t)i * k, k * sizeof(float));
+            tpo_convrot_rotate(xr, k);
+            float amax = 0.0f;
+            for (size_t c = 0; c < k; c++) {
+                const float a = fabsf(xr[c]);
+                amax = a > amax ? a : amax; /* @max(amax, @abs(v)) */
+            }
+            float s = amax / maxq;
+            s = s > 1e-12f ? s : 1e-12f; /* @max(amax / maxq, 1e-12) */
+            act_scale[i] = s;
+            for (size_t c = 0; c < k; c++) {
+                int qi = (int)roundf(xr[c] / s); /* @round: half away from zero */
+                qi = qi < lo ? lo : (qi > hi ? hi : qi);
+                q[(size_t)i * k + c] = (int8_t)qi;
+            }
+        }
+        free(tmp);
+    }
+}
+
+void tpo_igemm_s32(const int8_t *a, const int8_t *w, size_t m, size_t n,
+                   size_t k, int32_t *acc) {
+#pragma omp parallel for schedule(dynamic, 4)
+    for (long long i = 0; i < (long long)m; i++) {
+        const int8_t *ar = a + (size_t)i * k;
+        for (size_t j = 0; j < n; j++) {
+            const int8_t *wr = w + j * k;
+            int32_t s = 0;
+            for (size_t c = 0; c < k; c++) s += (int32_t)ar[c] * (int32_t)wr[c];
+            acc[(size_t)i * n + j] = s;
+        }
+    }
+}
+
+void tpo_dequant_sim(const int32_t *acc, const float *act_scale,
+                     const float *w_scale, size_t m, size_t n, double *y) {
+    for (size_t i = 0; i < m; i++)
+        for (size_t j = 0; j < n; j++)
+            y[i * n + j] = (double)acc[i * n + j] * (double)act_scale[i] * (double)w_scale[j];
+}
+
+void tpo_linear_truth(const float *xr, const int8_t *w, const float *w_scale,
+                      size_t m, size_t n, size_t k, double *y) {
+#pragma omp parallel for schedule(dynamic, 4)
+    for (long long i = 0; i < (long long)m; i++) {
+        for (size_t j = 0; j < n; j++) {
+            double t = 0.0;
+            for (size_t c = 0; c < k; c++)
+                t += (double)xr[(size_t)i * k + c] *
+                     ((double)w[j * k + c] * (double)w_scale[j]);
+            y[(size_t)i * n + j] = t;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* `--backend cpu` float path -- src/ops/matmul.zig                          */
+/* ------------------------------------------------------------------------ */
+
+enum { MR = 6, NR = 16, KC = 512 }; /* matmul.zig:69-71 (vlen 8 => NR 16) */
+
+/* matmul.zig:580-639: MRC x NR register tile, one FMA per (row, k) in k order,
+ * continuing from y when this is not the first k block. */
+static void micro_kernel(int mrc, float *y, const float *x, const float *sub,
+                         size_t t0, size_t col0, size_t rows, size_t cols,
+                         size_t kc0, size_t kl, const float *bias, int accumulate) {
+    const int full = col0 + NR <= rows;
+    __m256 acc[MR][2];
+    for (int mi = 0; mi < mrc; mi++) {
+        float tmp[NR];
+        memset(tmp, 0, sizeof tmp);
+        if (accumulate) {
+            const size_t lim = full ? NR : rows - col0;
+            for (size_t c = 0; c < lim; c++) tmp[c] = y[(t0 + mi) * rows + col0 + c];
+        } else if (bias) {
+            const size_t lim = full ? NR : rows - col0;
+            for (size_t c = 0; c < lim; c++) tmp[c] = bias[col0 + c];
+        }
+        acc[mi][0] = _mm256_loadu_ps(tmp);
+        acc[mi][1] = _mm256_loadu_ps(tmp + 8);
+    }
+    for (size_t k = 0; k < kl; k++) {
+        const __m256 b0 = _mm256_loadu_ps(sub + k * NR);
+        const __m256 b1 = _mm256_loadu_ps(sub + k * NR + 8);
+        for (int mi = 0; mi < mrc; mi++) {
+            const __m256 a = _mm256_set1_ps(x[(t0 + mi) * cols + kc0 + k]);
+            acc[mi][0] = _mm256_fmadd_ps(a, b0, acc[mi][0]);
+            acc[mi][1] = _mm256_fmadd_ps(a, b1, acc[mi][1]);
+        }
+    }
+    for (int mi = 0; mi < mrc; mi++) {
+        float tmp[NR];
+        _mm256_storeu_ps(tmp, acc[mi][0]);
+        _mm256_storeu_ps(tmp + 8, acc[mi][1]);
+        const size_t lim = full ? NR : rows - col0;
+        for (size_t c = 0; c < lim; c++) y[(t0 + mi) * rows + col0 + c] = tmp[c];
+    }
+}
+
+/* matmul.zig:408-484 (.i8) and :502-563 (.i4): per KC-wide k block, dequantise
+ * each weight row of the chunk (q * row_scale), un-rotate, scatter k-major into
+ * NR-wide subpanels, then sweep the microkernel over all activation rows. */
+static void packed_task(float *y, const float *x, size_t m, const void *w,
+                        int w_bits, const float *row_scale, size_t rows,
+                        size_t cols, int convrot, const float *bias,
+                        size_t row_start, size_t row_end, float *panel) {
+    const size_t n_nr = (row_end - row_start + NR - 1) / NR;
+    for (size_t kc0 = 0; kc0 < cols; kc0 += KC) {
+        const size_t kl = cols - kc0 < KC ? cols - kc0 : KC;
+        for (size_t nr = 0; nr < n_nr; nr++) {
+            float *sub = panel + nr * KC * NR;
+            for (size_t j = 0; j < NR; j++) {
+                const size_t row = row_start + nr * NR + j;
+                if (row >= rows) {
+                    for (size_t k = 0; k < kl; k++) sub[k * NR + j] = 0.0f;
+                    continue;
+                }
+                float tmp[KC];
+                const float rs = row_scale[row];
+                if (w_bits == 8) {
+                    const int8_t *src = (const int8_t *)w + row * cols + kc0;
+                    for (size_t k = 0; k < kl; k++) tmp[k] = (float)src[k] * rs;
+                } else {
+                    const uint8_t *src = (const uint8_t *)w + (row * cols + kc0) / 2;
+                    for (size_t k = 0; k < kl; k++)
+                        tmp[k] = (float)tpo_nibble_i4(src[k / 2], (int)(k & 1)) * rs;
+                }
+                if (convrot) tpo_convrot_rotate(tmp, kl);
+                for (size_t k = 0; k < kl; k++) sub[k * NR + j] = tmp[k];
+            }
+        }
+        for (size_t t0 = 0; t0 < m; t0 += MR) {
+            const int mr = (int)(m - t0 < MR ? m - t0 : MR);
+            for (size_t nr = 0; nr < n_nr; nr++)
+                micro_kernel(mr, y, x, panel + nr * KC * NR, t0, row_start + nr * NR,
+                             rows, cols, kc0, kl, kc0 == 0 ? bias : NULL, kc0 != 0);
+        }
+    }
+}
+
+void tpo_linear_cpu_backend(const float *x, size_t m, const void *w, int w_bits,
+                            const float *row_scale, size_t n, size_t k,
+                            int convrot, const float *bias, float *y,
+                            int nthreads) {
+    if (m == 0 || n == 0) return;
+    int nt = nthreads > 0 ? nthreads : tpo_num_threads();
+    /* matmul.zig:206-211: 4 x ncpu row chunks, rounded up to whole NR panels. */
+    const size_t want = nt == 1 ? 1 : (size_t)4 * (size_t)nt;
+    size_t per = (n + want - 1) / want;
+    if (per < NR) per = NR;
+    const size_t chunk = (per + NR - 1) / NR * NR;
+    const size_t n_tasks = (n + chunk - 1) / chunk;
+    const size_t stride = (chunk / NR) * KC * NR;
+#pragma omp parallel num_threads(nt)
+    {
+        float *panel = (float *)aligned_alloc(64, stride * sizeof(float));
+#pragma omp for schedule(dynamic, 1)
+        for (long long t = 0; t < (long long)n_tasks; t++) {
+            const size_t r0 = (size_t)t * chunk;
+            const size_t r1 = r0 + chunk < n ? r0 + chunk : n;
+            packed_task(y, x, m, w, w_bits, row_scale, n, k, convrot, bias, r0, r1, panel);
+        }
+        free(panel);
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* GGUF Q8_0                                                                  */
+/* ------------------------------------------------------------------------ */
+
+float tpo_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else { /* subnormal: renormalise */
+            int e = -1;
+            do {
+                man <<= 1;
+                e++;
+            } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+uint16_t tpo_f32_to_f16(float f) {
+    /* round to nearest even, via the F16C conversion instruction */
+    const __m128 v = _mm_set_ss(f);
+    const __m128i h = _mm_cvtps_ph(v, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+    return (uint16_t)_mm_extract_epi16(h, 0);
+}
+
+void tpo_q8_0_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t b = 0; b < k / 32; b++) {
+        const uint8_t *blk = blocks + b * TPO_Q8_0_BLOCK_BYTES;
+        uint16_t dh;
+        memcpy(&dh, blk, 2);
+        const float d = tpo_f16_to_f32(dh);
+        const int8_t *qs = (const int8_t *)(blk + 2);
+        for (int e = 0; e < 32; e++) out[b * 32 + e] = (float)qs[e] * d;
+    }
+}
+
+void tpo_q8_1_quantize(const float *x, size_t n, int tie_mode, float *d, int8_t *qs) {
+    for (size_t b = 0; b < n / 32; b++) {
+        float amax = 0.0f;
+        for (int e = 0; e < 32; e++) {
+            const float a = fabsf(x[b * 32 + e]);
+            amax = a > amax ? a : amax;
+        }
+        d[b] = amax / 127.0f;
+        const float inv = amax == 0.0f ? 0.0f : 127.0f / amax;
+        for (int e = 0; e < 32; e++) {
+            const float v = x[b * 32 + e] * inv;
+            const float r = tie_mode ? roundf(v) : nearbyintf(v);
+            qs[b * 32 + e] = (int8_t)(int)r;
+        }
+    }
+}
+
+void tpo_q8_0_gemv_f64(const uint8_t *w, size_t n, size_t k, const float *x,
+                       size_t m, float scale, float *y) {
+    const size_t row_bytes = k / 32 * TPO_Q8_0_BLOCK_BYTES;
+#pragma omp parallel
+    {
+        float *row = (float *)malloc(k * sizeof(float));
+#pragma omp for schedule(static)
+        for (long long r = 0; r < (long long)n; r++) {
+            tpo_q8_0_dequant_row(w + (size_t)r * row_bytes, k, row);
+            for (size_t t = 0; t < m; t++) {
+                double acc = 0.0;
+                for (size_t c = 0; c < k; c++) acc += (double)row[c] * (double)x[t * k + c];
+                y[t * n + (size_t)r] = (float)(acc * (double)scale);
+            }
+        }
+        free(row);
+    }
+}
+
+void tpo_q8_0_gemv_q8(const uint8_t *w, size_t n, size_t k, const float *x,
+                      size_t m, float scale, int tie_mode, float *y) {
+    float *xq = (float *)malloc(m * k * sizeof(float));
+    float *d = (float *)malloc(m * k / 32 * sizeof(float));
+    int8_t *qs = (int8_t *)malloc(m * k);
+    tpo_q8_1_quantize(x, m * k, tie_mode, d, qs);
+    for (size_t i = 0; i < m * k; i++) xq[i] = d[i / 32] * (float)qs[i];
+    tpo_q8_0_gemv_f64(w, n, k, xq, m, scale, y);
+    free(xq);
+    free(d);
+    free(qs);
+}
+
+void tpo_q8_0_block_sumi(const uint8_t *w, size_t n, size_t k, const int8_t *xq,
+                         size_t m, int32_t *sumi) {
+    const size_t nblk = k / 32;
+    const size_t row_bytes = nblk * TPO_Q8_0_BLOCK_BYTES;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < (long long)n; r++) {
+        for (size_t t = 0; t < m; t++) {
+            for (size_t b = 0; b < nblk; b++) {
+                const int8_t *qw = (const int8_t *)(w + (size_t)r * row_bytes +
+                                                    b * TPO_Q8_0_BLOCK_BYTES + 2);
+                const int8_t *qx = xq + t * k + b * 32;
+                int32_t s = 0;
+                for (int e = 0; e < 32; e++) s += (int32_t)qw[e] * (int32_t)qx[e];
+                sumi[(t * n + (size_t)r) * nblk + b] = s;
+            }
+        }
+    }
+}

@@ -1,0 +1,263 @@
+"""Pins the CPU oracle against the reference's own golden vectors and
+known-answer tests for the quantized-linear path.  No GPU needed.
+
+Mirrors: src/ops/convrot.zig:91-192 (Hadamard properties + ComfyUI int4
+fixture), src/core/dtype.zig:264-280 (nibble decode), src/core/quants.zig:118-120
+(Q8_0 golden bits), src/ops/matmul.zig:932-1070 (ConvRot matmul vs naive f64).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tensorpencil_b200 import synth
+
+
+# -- Hadamard / rotation (convrot.zig:91-139) ---------------------------------
+
+def test_hadamard_symmetric():
+    h = oracle.hadamard256()
+    assert np.array_equal(h, h.T)
+
+
+def test_hadamard_orthonormal():
+    h = oracle.hadamard256()
+    assert np.allclose(h @ h, np.eye(256, dtype=np.float32), atol=1e-5)
+
+
+def test_rotation_self_inverse():
+    rng = np.random.default_rng(7)
+    v = rng.standard_normal(256).astype(np.float32)
+    assert np.allclose(oracle.rotate(oracle.rotate(v)), v, atol=1e-4)
+
+
+def test_rotation_matches_matvec_multi_group():
+    rng = np.random.default_rng(11)
+    data = rng.standard_normal(512).astype(np.float32)
+    got = oracle.rotate(data)
+    h = oracle.hadamard256()
+    for g in range(2):
+        want = h @ data[g * 256:(g + 1) * 256]
+        assert np.allclose(got[g * 256:(g + 1) * 256], want, atol=1e-4)
+
+
+def test_rotation_add_order_is_the_reference_one():
+    """One radix-4 pass on values where float association matters: the four
+    outputs must be ((a+b)+c)-d, ((a+b)-c)+d, ((a-b)+c)+d, ((-a+b)+c)+d
+    (src/ops/convrot.zig:68-71)."""
+    rng = np.random.default_rng(3)
+    v = (rng.standard_normal(256) * np.array([1e4, 1.0, 1e-3, 37.0] * 64)).astype(np.float32)
+    w = v.copy()
+    f = np.float32
+    for s in (1, 4, 16, 64):
+        nxt = w.copy()
+        for base in range(0, 256, 4 * s):
+            for o in range(s):
+                p = base + o
+                a, b, c, d = f(w[p]), f(w[p + s]), f(w[p + 2 * s]), f(w[p + 3 * s])
+                nxt[p] = f(f(f(a + b) + c) - d)
+                nxt[p + s] = f(f(f(a + b) - c) + d)
+                nxt[p + 2 * s] = f(f(f(a - b) + c) + d)
+                nxt[p + 3 * s] = f(f(f(-a + b) + c) + d)
+        w = nxt
+    w = (w / f(16.0)).astype(np.float32)
+    assert np.array_equal(oracle.rotate(v).view(np.uint32), w.view(np.uint32))
+
+
+# -- nibble decode (dtype.zig:264-280) -----------------------------------------
+
+def test_nibble_known_answers():
+    assert oracle.nibble_i4(0xF7, 0) == 7
+    assert oracle.nibble_i4(0xF7, 1) == -1
+    assert oracle.nibble_i4(0x80, 0) == 0
+    assert oracle.nibble_i4(0x80, 1) == -8
+
+
+def test_pack_unpack_round_trip():
+    rng = np.random.default_rng(5)
+    v = rng.integers(-8, 8, size=(3, 64), dtype=np.int8)
+    p = oracle.pack_i4(v)
+    assert np.array_equal(p, synth.pack_i4(v))
+    assert np.array_equal(oracle.unpack_i4(p), v)
+    assert np.array_equal(synth.unpack_i4(p), v)
+
+
+# -- ComfyUI int4 ConvRot fixture (convrot.zig:148-192) -------------------------
+
+def test_int4_convrot_fixture(golden_dir):
+    rows, cols = 16, 6144
+    packed = np.fromfile(os.path.join(golden_dir, "int4_convrot_weight.u8"), np.uint8)
+    scale = np.fromfile(os.path.join(golden_dir, "int4_convrot_scale.f32"), np.float32)
+    expected = np.fromfile(os.path.join(golden_dir, "int4_convrot_expected.f32"), np.float32)
+    assert packed.size == rows * cols // 2 and scale.size == rows and expected.size == rows * cols
+    got = oracle.i4_convrot_dequant(packed, scale, rows, cols).astype(np.float64).ravel()
+    rel = np.sqrt(np.sum((expected - got) ** 2) / np.sum(expected.astype(np.float64) ** 2))
+    assert rel < 1e-4, rel  # the reference's gate
+
+
+# -- Q8_0 golden block (quants_fixtures.zig:6-15) --------------------------------
+
+def test_q8_0_golden_bits(golden_dir):
+    g = json.load(open(os.path.join(golden_dir, "q8_0_block.json")))
+    blk = np.array(g["block_bytes"], np.uint8)
+    assert blk.size == 34
+    got = oracle.q8_0_dequant_row(blk, 32)
+    want = np.array(g["expected_f32_bits"], np.uint32)
+    assert np.array_equal(got.view(np.uint32), want)
+
+
+def test_f16_conversion_matches_numpy():
+    hs = np.arange(0, 65536, 7, dtype=np.uint16)
+    want = hs.view(np.float16).astype(np.float32)
+    got = np.array([oracle.f16_to_f32(int(h)) for h in hs], np.float32)
+    ok = np.isnan(want) | (got.view(np.uint32) == want.view(np.uint32))
+    assert ok.all()
+
+
+# -- replica vs committed oracle vectors ----------------------------------------
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_replica_matches_committed_vectors(golden_dir, bits):
+    g = np.load(os.path.join(golden_dir, "oracle_vectors.npz"))
+    q, s, acc, y = oracle.convrot_linear_sim(g[f"i{bits}_x"], g[f"i{bits}_w"], g[f"i{bits}_ws"], bits)
+    assert np.array_equal(q, g[f"i{bits}_q"])
+    assert np.array_equal(s.view(np.uint32), g[f"i{bits}_as"].view(np.uint32))
+    assert np.array_equal(acc, g[f"i{bits}_acc"])
+    assert np.array_equal(y, g[f"i{bits}_y"])
+
+
+def test_replica_quantiser_definition():
+    """q = clamp(round_half_away(xr / s)), s = max(amax/maxq, 1e-12), in f32
+    (src/gpu/cuda/kernels.zig:2638-2653)."""
+    x = synth.activations(4, 768, seed=9)
+    for bits, maxq, lo in ((8, 127.0, -127), (4, 7.0, -8)):
+        q, s, xr = oracle.convrot_prep(x, bits, want_rotated=True)
+        assert np.array_equal(xr.view(np.uint32), oracle.rotate(x).view(np.uint32))
+        amax = np.abs(xr).max(axis=1)
+        s_want = np.maximum(amax / np.float32(maxq), np.float32(1e-12)).astype(np.float32)
+        assert np.array_equal(s.view(np.uint32), s_want.view(np.uint32))
+        r = (xr / s_want[:, None]).astype(np.float32)
+        q_want = np.clip(np.sign(r) * np.floor(np.abs(r) + np.float32(0.5)), lo, int(maxq))
+        assert np.array_equal(q, q_want.astype(np.int8))
+        assert np.abs(q).max() == int(maxq)  # absmax element hits full scale
+
+
+def test_prep_all_zero_row_uses_floor_scale():
+    x = np.zeros((2, 256), np.float32)
+    q, s = oracle.convrot_prep(x, 8)
+    assert np.all(q == 0) and np.all(s == np.float32(1e-12))
+
+
+def test_igemm_exact_vs_numpy():
+    rng = np.random.default_rng(7)
+    for m, n, k in ((16, 8, 32), (64, 256, 128), (48, 72, 320)):  # kernels.zig:2208-2231, :2327-2333
+        a = rng.integers(-128, 128, size=(m, k), dtype=np.int8)
+        w = rng.integers(-128, 128, size=(n, k), dtype=np.int8)
+        want = a.astype(np.int32) @ w.astype(np.int32).T
+        assert np.array_equal(oracle.igemm_s32(a, w), want)
+
+
+# -- `--backend cpu` float path (matmul.zig:932-1070) ----------------------------
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 16, 256), (7, 33, 512), (13, 40, 768), (20, 64, 1024)])
+def test_cpu_backend_matches_naive_f64(bits, m, n, k):
+    c = synth.convrot_linear(m, n, k, bits, seed=100 + m)
+    w = c["w_packed"] if bits == 4 else c["w_i8"]
+    y = oracle.linear_cpu_backend(c["x"], w, bits, c["w_scale"], n, k)
+    # naive f64 over the un-rotated weight
+    wd = oracle.rotate((c["w_i8"].astype(np.float32) * c["w_scale"][:, None]).astype(np.float32))
+    e = c["x"].astype(np.float64) @ wd.astype(np.float64).T
+    tol = 1e-3 + 1e-5 * np.abs(e) * np.sqrt(k)
+    assert np.all(np.abs(y - e) <= tol)
+
+
+def test_cpu_backend_is_a_sequential_fma_chain():
+    """The packed path accumulates one FMA per k, k ascending, per output
+    (matmul.zig:611-619), whatever the k-blocking or thread split."""
+    c = synth.convrot_linear(3, 16, 1024, 8, seed=77)
+    y = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024)
+    y1 = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024, nthreads=1)
+    assert np.array_equal(y, y1)
+    wd = oracle.rotate((c["w_i8"].astype(np.float32) * c["w_scale"][:, None]).astype(np.float32))
+    import math
+    for i in range(3):
+        for j in (0, 5, 15):
+            acc = np.float32(0)
+            for kk in range(1024):
+                # fma(a, b, acc) rounded once: evaluate exactly in f64 then round
+                acc = np.float32(math.fma(float(c["x"][i, kk]), float(wd[j, kk]), float(acc))) \
+                    if hasattr(math, "fma") else np.float32(np.float64(c["x"][i, kk]) * np.float64(wd[j, kk]) + np.float64(acc))
+            assert abs(float(acc) - float(y[i, j])) <= 2e-6 * max(1.0, abs(float(acc)))
+
+
+def test_cpu_backend_bias_and_no_convrot():
+    rng = np.random.default_rng(2)
+    c = synth.convrot_linear(4, 24, 256, 8, seed=5)
+    b = rng.standard_normal(24).astype(np.float32)
+    y = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 24, 256, convrot=0, bias=b)
+    e = c["x"].astype(np.float64) @ (c["w_i8"].astype(np.float64) * c["w_scale"][:, None]).T + b
+    assert np.allclose(y, e, rtol=1e-4, atol=1e-3)
+
+
+def test_int_path_close_to_float_path_int8():
+    """Activation-quantisation noise of the integer replica against the float
+    path stays within the reference's accuracy gate (rel-L2 <= 0.03,
+    kernels.zig:2700)."""
+    c = synth.convrot_linear(32, 64, 1024, 8, seed=31)
+    _, _, _, y_int = oracle.convrot_linear_sim(c["x"], c["w_i8"], c["w_scale"], 8)
+    y_f = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 64, 1024)
+    rel = np.sqrt(np.sum((y_int - y_f) ** 2) / np.sum(y_f.astype(np.float64) ** 2))
+    assert rel < 0.03, rel
+
+
+# -- Q8_0 GEMV ---------------------------------------------------------------------
+
+def test_q8_1_quantise_definition():
+    rng = np.random.default_rng(1337)
+    x = (rng.random(512, dtype=np.float32) * 2 - 1).astype(np.float32)
+    x[32:64] = 0  # amax == 0 block -> d = 0, q = 0
+    d, qs = oracle.q8_1_quantize(x)
+    amax = np.abs(x.reshape(-1, 32)).max(axis=1)
+    assert np.array_equal(d, (amax / np.float32(127.0)).astype(np.float32))
+    assert np.all(qs[32:64] == 0) and d[1] == 0
+    inv = np.where(amax == 0, 0, np.float32(127.0) / np.where(amax == 0, 1, amax)).astype(np.float32)
+    want = np.rint((x.reshape(-1, 32) * inv[:, None]).astype(np.float32)).astype(np.int8).ravel()
+    assert np.array_equal(qs, want)
+    assert np.abs(qs.reshape(-1, 32)).max(axis=1)[0] == 127
+
+
+def test_q8_0_gemv_f64_matches_numpy():
+    g = synth.q8_0_gemv(3, 16, 512, seed=4242)
+    y = oracle.q8_0_gemv_f64(g["w"], 16, 512, g["x"], scale=0.5)
+    wf = np.stack([oracle.q8_0_dequant_row(g["w"][r], 512) for r in range(16)])
+    want = 0.5 * (g["x"].astype(np.float64) @ wf.astype(np.float64).T)
+    assert np.allclose(y, want, rtol=1e-6, atol=1e-6)
+
+
+def test_q8_0_gemv_q8_close_to_f64():
+    # same relation the reference tests rely on (matmul.zig:1138-1165: rel-L2 < 0.05)
+    g = synth.q8_0_gemv(2, 24, 512, seed=271)
+    y64 = oracle.q8_0_gemv_f64(g["w"], 24, 512, g["x"])
+    yq = oracle.q8_0_gemv_q8(g["w"], 24, 512, g["x"])
+    rel = np.sqrt(np.sum((y64 - yq) ** 2) / np.sum(y64 ** 2))
+    assert rel < 0.05, rel
+
+
+def test_q8_0_block_sumi():
+    g = synth.q8_0_gemv(2, 8, 256, seed=12)
+    _, xq = oracle.q8_1_quantize(g["x"])
+    s = oracle.q8_0_block_sumi(g["w"], 8, 256, xq)
+    qw = g["w"].reshape(8, 8, 34)[:, :, 2:].view(np.int8).astype(np.int32)
+    want = np.einsum("rbe,tbe->trb", qw, xq.reshape(2, 8, 32).astype(np.int32))
+    assert np.array_equal(s, want)
+
+
+def test_committed_q8_vectors(golden_dir):
+    g = np.load(os.path.join(golden_dir, "oracle_vectors.npz"))
+    assert np.array_equal(oracle.q8_0_gemv_f64(g["q8_w"], 16, 512, g["q8_x"]), g["q8_y_f64"])
+    assert np.array_equal(oracle.q8_0_gemv_q8(g["q8_w"], 16, 512, g["q8_x"]), g["q8_y_q8"])
+    d, qs = oracle.q8_1_quantize(g["q8_x"])
+    assert np.array_equal(d, g["q8_act_d"]) and np.array_equal(qs, g["q8_act_qs"])
