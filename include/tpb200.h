@@ -1,0 +1,185 @@
+/*
+ * tpb200.h -- C ABI of libtpb200.so, the B200-native (sm_100a) implementation
+ * of TensorPencil's quantized-linear path.
+ *
+ * Each entry point names the TensorPencil interface it stands in for
+ * (path:line within that project).  The reference binds its GPU libraries by
+ * dlopen + symbol table (src/gpu/cuda/cu.zig:252-345); this header is what such
+ * a table would list.
+ *
+ * Conventions
+ *   - plain C linkage, plain pointers and sizes; no CUDA or C++ types in the
+ *     signatures.  `stream` is a CUstream / cudaStream_t passed as void*.
+ *   - every call returns 0 (TPB_OK) or a negative tpb_status; the text of the
+ *     last failure on a handle is available from tpb_last_error().
+ *   - the library never creates a CUDA context: tpb_create() binds to the
+ *     device's primary context / whatever context is current, and all work is
+ *     enqueued on the caller's stream.  No entry point synchronises unless its
+ *     comment says so.
+ *   - a handle is thread-compatible, not thread-safe: one thread at a time.
+ *   - there is no CPU fallback anywhere behind this interface.
+ */
+#ifndef TPB200_H
+#define TPB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tpb_handle_s *tpb_handle_t;
+typedef struct tpb_streamer_s *tpb_streamer_t;
+typedef void *tpb_stream_t; /* CUstream / cudaStream_t */
+
+typedef enum tpb_status {
+    TPB_OK = 0,
+    TPB_ERR_INVALID_ARG = -1, /* bad pointer, shape, alignment or enum */
+    TPB_ERR_CUDA = -2,        /* a CUDA call failed (reference: error.CudaError) */
+    TPB_ERR_OOM = -3,         /* device or pinned-host allocation failed (error.DeviceOutOfMemory / OutOfMemory) */
+    TPB_ERR_TIMEOUT = -4,     /* a bounded device-side wait ran out; see tpb_status_poll */
+    TPB_ERR_STATE = -5,       /* call order violated (e.g. acquire of an unregistered layer) */
+    TPB_ERR_NO_DEVICE = -6    /* no usable sm_100 device (error.NoSuitableDevice) */
+} tpb_status;
+
+typedef enum tpb_dtype {
+    TPB_F32 = 0,
+    TPB_BF16 = 1,
+    TPB_F16 = 2,
+    TPB_S32 = 3 /* raw int32 accumulators; output only */
+} tpb_dtype;
+
+/* ---- lifetime ------------------------------------------------------------
+ * Stands in for cuda.Backend.init / deinit (src/gpu/cuda/backend.zig:196,
+ * src/gpu/cuda/context.zig:103-116) for this path only. */
+int tpb_version(void);
+int tpb_create(tpb_handle_t *out, int device_ordinal);
+int tpb_destroy(tpb_handle_t h);
+const char *tpb_last_error(tpb_handle_t h);
+const char *tpb_status_string(int status);
+
+/* Reads (and clears) the device status word that bounded waits inside the
+ * kernels write when they give up.  Synchronises `stream` first.  Returns
+ * TPB_OK or TPB_ERR_TIMEOUT; *detail (optional) receives the raw word:
+ * (role << 24) | stage, role 1 = tile loader, 2 = MMA issuer, 3 = epilogue. */
+int tpb_status_poll(tpb_handle_t h, tpb_stream_t stream, uint32_t *detail);
+
+/* Device facts the host side sizes its work with. */
+int tpb_device_sm_count(tpb_handle_t h);
+
+/* ---- ConvRot activation prep ----------------------------------------------
+ * Replaces Backend.opI8Prep / opI4Prep + kernels.buildPrep
+ * (src/gpu/cuda/backend.zig:2454-2480, :2532-2553; src/gpu/cuda/kernels.zig:971-1212).
+ *
+ * Per row of x[m][k]: rotate every 256-group with the regular Hadamard
+ * (src/ops/convrot.zig:56-87, same add order), take the row absmax,
+ * scale = max(absmax / maxq, 1e-12), q = clamp(round-half-away(v / scale)).
+ * bits = 8: maxq 127, clamp [-127,127].  bits = 4: maxq 7, clamp [-8,7].
+ *
+ * Outputs (device, caller-owned; they replace the reference's hidden
+ * i8_x / i8_scale backend scratch):
+ *   q         int8 [m][k]   one value per byte for both widths
+ *   act_scale f32  [m]
+ *   act_sum   int32 [m]     sum of the row's q values; required when bits = 4
+ *                           (the int4 GEMM consumes it), optional (NULL) for 8.
+ * x_dtype: TPB_F32, TPB_F16 or TPB_BF16 (the reference's in_f16 switch).
+ * k must be a multiple of 256 and at most 32768; x and q 16-byte aligned. */
+int tpb_convrot_prep(tpb_handle_t h, tpb_stream_t stream, const void *x, int x_dtype,
+                     int64_t m, int64_t k, int bits, int8_t *q, float *act_scale,
+                     int32_t *act_sum);
+
+/* ---- ConvRot GEMM + fused dequant ------------------------------------------
+ * Replaces Backend.opI8Gemm / opI4Gemm + kernels.buildIgemmPipe(fuse) and the
+ * irescale pass (src/gpu/cuda/backend.zig:2484-2501, :2558-2573, :2427-2450;
+ * src/gpu/cuda/kernels.zig:557-958, :1216-1328).
+ *
+ *   y[i][j] = (float(sum_k q[i][k] * w[j][k]) * act_scale[i]) * w_scale[j]
+ *
+ * q int8 [m][k] and act_scale from tpb_convrot_prep.  w_bits = 8: w is int8
+ * [n][k].  w_bits = 4: w is [n][k/2] bytes, element 2j in the low nibble
+ * (src/core/dtype.zig:146-149), q holds int4-range values and act_sum is
+ * required.  w_scale is one f32 per output row [n] for both widths
+ * (src/ops/matmul.zig:82-89).  y is [m][ldy] with ldy >= n elements;
+ * y_dtype TPB_F32 or TPB_BF16, or TPB_S32 to store the raw int32 accumulators
+ * (scales ignored) for exact integer checks.
+ * Requirements: k % 256 == 0, n % 16 == 0, all pointers 16-byte aligned, ldy
+ * a multiple of 4 elements (8 for bf16).  Any m >= 1: no padding of m to 128
+ * is needed (out-of-range rows are never read or written). */
+int tpb_convrot_gemm(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, int64_t ldy,
+                     const int8_t *q, const float *act_scale, const int32_t *act_sum,
+                     const void *w, int w_bits, const float *w_scale,
+                     int64_t m, int64_t n, int64_t k);
+
+/* Bytes of the int8 expansion of an [n][k] int4 weight. */
+size_t tpb_convrot_w4_expanded_bytes(int64_t n, int64_t k);
+
+/* Expands a packed int4 weight [n][k/2] into int8 [n][k] (device to device), so
+ * a resident weight can be expanded once and then used with w_bits = 8.  No
+ * counterpart in the reference, whose int4 kernel always reads packed nibbles. */
+int tpb_convrot_w4_expand(tpb_handle_t h, tpb_stream_t stream, const void *w4, int64_t n,
+                          int64_t k, int8_t *w8);
+
+/* ---- GGUF Q8_0 decode GEMV ---------------------------------------------------
+ * Q8_0 row = k/32 blocks of 34 bytes: f16 d, then 32 int8 (src/core/dtype.zig:93,
+ * src/gpu/cuda/elt.zig:666-669).
+ *
+ * tpb_q8_1_quantize replaces Backend.opGemvQuantizeX + elt.quantize_q8_1
+ * (src/gpu/cuda/backend.zig:1687-1695, src/gpu/cuda/elt.zig:1226-1269): per
+ * 32-element block d = amax/127, q = round-to-nearest-even(x * (127/amax)),
+ * 0 when amax == 0.  xq layout is the reference's: f32 d[n_elems/32] followed
+ * by int8 qs[n_elems]; xq must hold n_elems/32*4 + n_elems bytes, 16-byte aligned,
+ * n_elems % 32 == 0. */
+int tpb_q8_1_quantize(tpb_handle_t h, tpb_stream_t stream, const float *x, int64_t n_elems,
+                      void *xq);
+
+/* Replaces Backend.opGemvQuantQ8N(.q8_0) + elt.gemv_q8_0_q8n
+ * (src/gpu/cuda/backend.zig:1719-1735, src/gpu/cuda/elt.zig:1926-2006):
+ *   y[i*rows + r] = scale * sum_b float(sum_e qw*qx) * (d_w * d_x),  i < ng <= 8
+ * against activation rows row_off .. row_off+ng-1 of an xq buffer that holds
+ * n_total rows of `cols` elements.  The weight streams from HBM once for all
+ * ng rows.  cols % 32 == 0; w 16-byte aligned. */
+int tpb_q8_0_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, float *y, const void *w, float scale,
+                      int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
+                      int n_total);
+
+/* Replaces Backend.opGemvQuant(.q8_0) + elt.gemv_q8_0
+ * (src/gpu/cuda/backend.zig:1660-1681, src/gpu/cuda/elt.zig:671-727): the M = 1
+ * GEMV in f32 arithmetic on un-quantised activations,
+ *   y[r] = scale * sum_k (q_w * d_w) * x[k]. */
+int tpb_q8_0_gemv_f32(tpb_handle_t h, tpb_stream_t stream, float *y, const float *x,
+                      const void *w, float scale, int64_t rows, int64_t cols);
+
+/* ---- weight streaming ---------------------------------------------------------
+ * Replaces the diffusion weight cache's streaming half: Backend.prefetchWeight,
+ * cachedWeight's wait on a prefetch, the deferred free behind a compute-stream
+ * event and Context.uploadStaged (src/gpu/cuda/backend.zig:617-736, :954-961,
+ * :1376-1429; src/gpu/cuda/context.zig:151-187).
+ *
+ * A streamer owns n_slots device buffers of slot_bytes each (n_slots *
+ * slot_bytes <= budget_bytes, the `--vram-budget` of src/main.zig:1454-1464) and
+ * one transfer stream.  Layers are registered once with their pinned host
+ * image.  prefetch(layer) copies host -> slot on the transfer stream as soon as
+ * the slot's previous user has released it; acquire(layer) makes the compute
+ * stream wait for that copy and returns the device address; release(layer)
+ * records, on the compute stream, the point after which the slot may be
+ * overwritten.  Nothing here blocks the host.  Calls for one streamer come from
+ * one thread. */
+int tpb_stream_open(tpb_handle_t h, size_t budget_bytes, size_t slot_bytes, int n_slots,
+                    tpb_streamer_t *out);
+int tpb_stream_close(tpb_streamer_t s);
+int tpb_stream_register(tpb_streamer_t s, int layer_id, const void *pinned_host, size_t bytes);
+int tpb_stream_prefetch(tpb_streamer_t s, int layer_id);
+int tpb_stream_acquire(tpb_streamer_t s, int layer_id, tpb_stream_t compute, void **dev_ptr);
+int tpb_stream_release(tpb_streamer_t s, int layer_id, tpb_stream_t compute);
+/* Bytes copied host -> device since open (for the achieved-H2D-bandwidth figure). */
+uint64_t tpb_stream_bytes_copied(tpb_streamer_t s);
+
+/* Pinned host memory for weight images (cuMemHostAlloc in src/gpu/cuda/context.zig:151-160). */
+int tpb_host_alloc(tpb_handle_t h, size_t bytes, void **out);
+int tpb_host_free(tpb_handle_t h, void *p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPB200_H */

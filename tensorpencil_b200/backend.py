@@ -1,0 +1,251 @@
+"""Host-side mirror of TensorPencil's ``cuda.Backend`` op surface for the
+quantized-linear path (src/gpu/cuda/backend.zig:196), on top of the C ABI of
+``libtpb200.so``.
+
+Method names, argument meaning and the hidden prep -> GEMM state follow the
+reference so its orchestrators' call sequences carry over unchanged:
+
+    opI8Prep / opI8Gemm / opI4Prep / opI4Gemm      backend.zig:2454-2573
+    opGemvQuant / opGemvQuantizeX / opGemvQuantQ8N backend.zig:1660-1735
+    prefetchWeight / cachedWeight                  backend.zig:689, :1376-1429
+    tensorCreate / tensorUpload / tensorDownload   backend.zig:740, :1257-1269
+    beginBatch / endBatch                          backend.zig:1449-1455
+
+Device buffers are ``torch`` CUDA tensors (the reference's ``DeviceBuffer`` is a
+raw device pointer + size); weights arrive as host ``numpy`` arrays, as the
+reference passes mmap'd checkpoint slices, and are resolved to device copies
+through a cache keyed by the host address.
+
+Nothing here computes on the CPU: every op raises if the CUDA library or a
+device is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import TPB_BF16, TPB_F16, TPB_F32, TPB_OK, TPB_S32, TpbError
+
+_TORCH_TO_TPB = {torch.float32: TPB_F32, torch.bfloat16: TPB_BF16, torch.float16: TPB_F16,
+                 torch.int32: TPB_S32}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class Backend:
+    """One device, one compute stream (the caller's current torch stream)."""
+
+    def __init__(self, device: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("tensorpencil_b200.Backend needs a CUDA device; there is no CPU path")
+        self.lib = _lib.load()
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        torch.cuda.init()
+        torch.zeros(1, device=self.device)  # make sure the primary context exists
+        h = C.c_void_p()
+        rc = self.lib.tpb_create(C.byref(h), device)
+        if rc != TPB_OK:
+            raise TpbError(rc, self.lib.tpb_status_string(rc).decode())
+        self.h = h
+        # prep -> GEMM state (backend.zig:336-341)
+        self.i8_x: Optional[torch.Tensor] = None
+        self.i8_scale: Optional[torch.Tensor] = None
+        self.i8_sum: Optional[torch.Tensor] = None
+        self.i8_m = 0
+        self.i8_cols = 0
+        self.i8_bits = 0
+        # q8_1 activation scratch of the GEMV path (backend.zig:1691)
+        self.q8_act: Optional[torch.Tensor] = None
+        # host-pointer-keyed weight cache (backend.zig:1376-1378)
+        self._wcache: Dict[Tuple[int, int], Tuple[torch.Tensor, np.ndarray]] = {}
+        self.launches = 0  # kernels launched through this backend (bench accounting)
+
+    # -- plumbing -----------------------------------------------------------------
+    def close(self):
+        if getattr(self, "h", None):
+            torch.cuda.synchronize(self.device)
+            self.lib.tpb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _check(self, rc: int):
+        if rc != TPB_OK:
+            raise TpbError(rc, self.lib.tpb_last_error(self.h).decode())
+
+    def status_poll(self) -> int:
+        """Synchronises and raises TpbError(TPB_ERR_TIMEOUT) if a bounded
+        device-side wait gave up."""
+        detail = C.c_uint32(0)
+        rc = self.lib.tpb_status_poll(self.h, self._stream(), C.byref(detail))
+        self._check(rc)
+        return int(detail.value)
+
+    def sm_count(self) -> int:
+        return int(self.lib.tpb_device_sm_count(self.h))
+
+    # -- tensors (backend.zig:740, :1257-1269) ---------------------------------------
+    def tensorCreate(self, nbytes: int) -> torch.Tensor:
+        return torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+
+    def tensorUpload(self, dst: torch.Tensor, host: np.ndarray):
+        src = torch.from_numpy(np.ascontiguousarray(host)).view(torch.uint8).reshape(-1)
+        dst.view(torch.uint8).reshape(-1)[: src.numel()].copy_(src, non_blocking=True)
+
+    def tensorDownload(self, src: torch.Tensor) -> np.ndarray:
+        return src.detach().cpu().numpy()
+
+    def beginBatch(self):
+        pass
+
+    def endBatch(self):
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def cachedWeight(self, host: np.ndarray) -> torch.Tensor:
+        """Device copy of a host weight slice, keyed by its address and size."""
+        key = (host.__array_interface__["data"][0], host.nbytes)
+        hit = self._wcache.get(key)
+        if hit is not None:
+            return hit[0]
+        dev = torch.from_numpy(np.ascontiguousarray(host)).to(self.device, non_blocking=False)
+        self._wcache[key] = (dev, host)  # keep the host array alive: the key is its address
+        return dev
+
+    def prefetchWeight(self, host: np.ndarray):
+        self.cachedWeight(host)
+
+    def dropWeights(self):
+        self._wcache.clear()
+
+    # -- ConvRot linear ---------------------------------------------------------------
+    def _prep(self, x: torch.Tensor, m: int, cols: int, bits: int):
+        assert x.is_cuda and x.is_contiguous()
+        if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise TypeError("prep input must be f32, f16 or bf16")
+        assert x.numel() >= m * cols
+        if self.i8_x is None or self.i8_x.numel() < m * cols:
+            self.i8_x = torch.empty(max(m * cols, 1), dtype=torch.int8, device=self.device)
+        if self.i8_scale is None or self.i8_scale.numel() < m:
+            self.i8_scale = torch.empty(max(m, 1), dtype=torch.float32, device=self.device)
+            self.i8_sum = torch.empty(max(m, 1), dtype=torch.int32, device=self.device)
+        rc = self.lib.tpb_convrot_prep(self.h, self._stream(), x.data_ptr(), _TORCH_TO_TPB[x.dtype],
+                                       m, cols, bits, self.i8_x.data_ptr(),
+                                       self.i8_scale.data_ptr(), self.i8_sum.data_ptr())
+        self._check(rc)
+        self.launches += 1
+        self.i8_m, self.i8_cols, self.i8_bits = m, cols, bits
+
+    def opI8Prep(self, x: torch.Tensor, m: int, cols: int, in_f16: bool = False):
+        """Rotate + per-row quantise x[m][cols] into the backend's prepped
+        activation (backend.zig:2454-2480).  ``in_f16`` is implied by x.dtype."""
+        self._prep(x, m, cols, 8)
+
+    def opI4Prep(self, x: torch.Tensor, m: int, cols: int):
+        """int4 (W4A4) analogue of opI8Prep (backend.zig:2532-2553)."""
+        self._prep(x, m, cols, 4)
+
+    def _gemm(self, y: torch.Tensor, w_bytes: np.ndarray, weight_scale: np.ndarray, rows: int,
+              w_bits: int, ldy: Optional[int] = None):
+        assert self.i8_bits == w_bits, "opI{8,4}Gemm must follow the matching prep"
+        w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
+        ws_dev = self.cachedWeight(weight_scale) if isinstance(weight_scale, np.ndarray) else weight_scale
+        ydt = _TORCH_TO_TPB[y.dtype]
+        rc = self.lib.tpb_convrot_gemm(self.h, self._stream(), y.data_ptr(), ydt,
+                                       ldy if ldy is not None else rows,
+                                       self.i8_x.data_ptr(), self.i8_scale.data_ptr(),
+                                       self.i8_sum.data_ptr() if w_bits == 4 else None,
+                                       w_dev.data_ptr(), w_bits, _ptr(ws_dev),
+                                       self.i8_m, rows, self.i8_cols)
+        self._check(rc)
+        self.launches += 2 if w_bits == 4 else 1
+
+    def opI8Gemm(self, y: torch.Tensor, w_bytes, weight_scale, rows: int, c_h16: bool = False):
+        """y[m][rows] = prepped @ W^T * act_scale[row] * weight_scale[col]
+        (backend.zig:2484-2501).  The output type is y.dtype (f32 or bf16; int32
+        stores the raw accumulators)."""
+        self._gemm(y, w_bytes, weight_scale, rows, 8)
+
+    def opI4Gemm(self, y: torch.Tensor, w_bytes, weight_scale, rows: int):
+        """int4 GEMM + fused rescale against the last opI4Prep; ``w_bytes`` is the
+        packed weight [rows][cols/2] (backend.zig:2558-2573)."""
+        self._gemm(y, w_bytes, weight_scale, rows, 4)
+
+    # -- Q8_0 GEMV ------------------------------------------------------------------------
+    def opGemvQuantizeX(self, x: torch.Tensor, cols: int):
+        """Quantise f32 activations (cols = total element count, a multiple of
+        32) into the shared q8 scratch: f32 d[cols/32] then int8 qs[cols]
+        (backend.zig:1687-1695)."""
+        assert x.dtype == torch.float32 and x.is_cuda and cols % 32 == 0
+        need = cols // 32 * 4 + cols
+        if self.q8_act is None or self.q8_act.numel() < need:
+            self.q8_act = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self._q8_total = cols
+        rc = self.lib.tpb_q8_1_quantize(self.h, self._stream(), x.data_ptr(), cols, self.q8_act.data_ptr())
+        self._check(rc)
+        self.launches += 1
+
+    def opGemvQuantQ8N(self, dt: str, y: torch.Tensor, w_bytes, scale: float, rows: int, cols: int,
+                       ng: int, row_off: int, n_total: int):
+        """Grouped dp4a GEMV: y[i][rows] = scale * (W @ x_hat[row_off+i]) for i < ng <= 8
+        against the activations staged by ONE opGemvQuantizeX(x, n_total*cols)
+        (backend.zig:1719-1735)."""
+        if dt != "q8_0":
+            raise NotImplementedError(f"GEMV weight format {dt!r} is outside this library's scope")
+        assert self.q8_act is not None and self._q8_total == n_total * cols
+        w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
+        rc = self.lib.tpb_q8_0_gemv_q8n(self.h, self._stream(), y.data_ptr(), w_dev.data_ptr(),
+                                        float(scale), rows, cols, self.q8_act.data_ptr(), ng,
+                                        row_off, n_total)
+        self._check(rc)
+        self.launches += 1
+
+    def opGemvQuant(self, dt: str, y: torch.Tensor, x: torch.Tensor, w_bytes, scale: float, rows: int,
+                    cols: int):
+        """M = 1 GEMV in f32 arithmetic on un-quantised x (backend.zig:1660-1681)."""
+        if dt != "q8_0":
+            raise NotImplementedError(f"GEMV weight format {dt!r} is outside this library's scope")
+        w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
+        rc = self.lib.tpb_q8_0_gemv_f32(self.h, self._stream(), y.data_ptr(), x.data_ptr(),
+                                        w_dev.data_ptr(), float(scale), rows, cols)
+        self._check(rc)
+        self.launches += 1
+
+    # -- composites the harness uses -----------------------------------------------------
+    def convrot_linear(self, x: torch.Tensor, w, w_scale, n: int, bits: int,
+                       out_dtype=torch.float32) -> torch.Tensor:
+        """prep + GEMM for one linear; x is [m][k] on the device."""
+        m, k = x.shape
+        y = torch.empty((m, n), dtype=out_dtype, device=self.device)
+        if bits == 8:
+            self.opI8Prep(x, m, k)
+            self.opI8Gemm(y, w, w_scale, n)
+        else:
+            self.opI4Prep(x, m, k)
+            self.opI4Gemm(y, w, w_scale, n)
+        return y
+
+    def q8_0_linear(self, x: torch.Tensor, w, n: int, k: int, scale: float = 1.0) -> torch.Tensor:
+        """Decode linear the way the reference's steppers dispatch it
+        (src/models/qwen3_cuda.zig:1497-1517): quantise all rows once, then one
+        grouped GEMV per 8 activation rows."""
+        m = x.shape[0]
+        y = torch.empty((m, n), dtype=torch.float32, device=self.device)
+        self.opGemvQuantizeX(x, m * k)
+        for r0 in range(0, m, 8):
+            ng = min(8, m - r0)
+            self.opGemvQuantQ8N("q8_0", y[r0:], w, scale, n, k, ng, r0, m)
+        return y

@@ -1,0 +1,485 @@
+// ConvRot int8 GEMM with fused dequant epilogue for sm_100a.
+//
+//   y[i][j] = (float(sum_k q[i][k] * w[j][k]) * act_scale[i]) * w_scale[j]
+//
+// Both operands are K-major (q is [m][k], w is [n][k]) so neither is transposed.
+// One persistent CTA per SM walks output tiles of 128 x BN:
+//   warp 0      : TMA producer -- 128-byte-swizzled tiles of q and w, K block of
+//                 128 bytes per pipeline stage, completion on an mbarrier;
+//   warp 1      : allocates TMEM and issues tcgen05.mma.kind::i8 (M=128, N=BN,
+//                 K=32) from one thread; int32 accumulators live in TMEM, two
+//                 buffers so the epilogue of tile t overlaps the main loop of t+1;
+//   warps 2..5  : epilogue -- tcgen05.ld the accumulator rows, apply the two
+//                 scales, convert and store.
+// Every wait on an mbarrier is bounded: on expiry the kernel records a status
+// word, every role leaves its loop, TMEM is released and the kernel returns.
+// No TMA load here uses cluster multicast.
+#include <cuda_bf16.h>
+
+#include "tpb_internal.h"
+
+namespace {
+
+constexpr int BM = 128;            // rows of q per tile (= UMMA M)
+constexpr int BK = 128;            // int8 elements (= bytes) of K per stage: one 128B swizzle row
+constexpr int UMMA_K = 32;         // K of one tcgen05.mma.kind::i8
+constexpr int kThreads = 192;      // 6 warps
+constexpr int kEpiWarp0 = 2;
+constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
+
+enum OutKind { OUT_F32 = 0, OUT_BF16 = 1, OUT_S32 = 2 };
+
+template <int BN>
+struct TileCfg {
+    static constexpr int kStageBytesA = BM * BK;
+    static constexpr int kStageBytesB = BN * BK;
+    static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
+    // tiles + barriers (full/empty per stage, full/empty per accumulator) + TMEM
+    // base slot + abort flag, plus 1 KB slack to align the tiles to 1024 bytes.
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+struct GemmParams {
+    void *y;
+    long long ldy;
+    const float *act_scale;
+    const float *w_scale;
+    const int32_t *act_sum;  // non-null: subtract 8 * act_sum[row] (unsigned-nibble weights)
+    int m, n, k;
+    uint32_t *status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out or another role already
+// gave up; the caller then leaves its loop.  `code` identifies the waiter.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                            uint32_t *status, uint32_t code) {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicCAS(status, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint32_t *status, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets row (lane
+// base + t), registers 0..31 = columns col..col+31.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle
+// layout TMA writes: rows of 128 bytes, 8-row groups 1024 bytes apart.
+//   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (unused here)
+//   bits 32-45 stride byte offset >> 4 (1024)   bits 46-47 descriptor version (1)
+//   bits 61-63 layout (2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::i8: int32 accumulate, A signed int8, B signed or
+// unsigned int8, both K-major, N at bits 17-22 (N/8), M at bits 24-28 (M/16).
+template <int BN>
+__device__ __forceinline__ uint32_t make_idesc_i8(bool b_unsigned) {
+    uint32_t d = 0;
+    d |= 2u << 4;                       // accumulator format S32
+    d |= 1u << 7;                       // A: signed 8-bit
+    d |= (b_unsigned ? 0u : 1u) << 10;  // B: signed / unsigned 8-bit
+    d |= (uint32_t)(BN >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+// ---- the kernel ---------------------------------------------------------------
+
+template <int BN, int OUT>
+__global__ void __launch_bounds__(kThreads, 1)
+convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
+                    const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
+                    const int b_unsigned) {
+    using Cfg = TileCfg<BN>;
+    constexpr int S = Cfg::kStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // layout: [S x (A tile | B tile)] [barriers] [tmem slot] [abort flag]
+    const uint32_t bars = smem_base + S * Cfg::kStageBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * S + 2 + a); };
+    uint8_t *tail = smem_gen + S * Cfg::kStageBytes + 8 * (2 * S + 4);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tail + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int m_tiles = (p.m + BM - 1) / BM;
+    const int n_tiles = (p.n + BN - 1) / BN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int k_blocks = p.k / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32((const void *)tmem_slot)),
+                     "r"(Cfg::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM;
+                const int n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | s);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
+                    tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m0);
+                    tma_load_2d(a_dst + Cfg::kStageBytesA, &tma_b, full_bar(s), kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_i8<BN>(b_unsigned != 0);
+            uint32_t it = 0, t_it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, t_it++) {
+                const int acc = t_it & 1;
+                const uint32_t acc_ph = (t_it >> 1) & 1u;
+                ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, (2u << 24) | 0x100u | acc);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, (2u << 24) | s);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + Cfg::kStageBytesA);
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; kk++) {
+                        // advancing 32 bytes inside the 128-byte swizzle row = +2 in the
+                        // (address >> 4) field of the descriptor
+                        tc_mma_i8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc,
+                                  (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));  // stage reusable once these MMAs have read it
+                }
+                if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+        uint32_t t_it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, t_it++) {
+            const int m0 = (tile % m_tiles) * BM;
+            const int n0 = (tile / m_tiles) * BN;
+            const int acc = t_it & 1;
+            const uint32_t acc_ph = (t_it >> 1) & 1u;
+            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | acc);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            float as = 0.0f;
+            int corr = 0;
+            if (OUT != OUT_S32 && row_ok) as = __ldg(p.act_scale + row);
+            if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t r[32];
+                tc_ld_32x32(t_row + (uint32_t)(c * 32), r);
+                tc_wait_ld();
+                const int col0 = n0 + c * 32;
+                if (!row_ok || col0 >= p.n) continue;
+                if (OUT == OUT_S32) {
+                    int32_t *dst = reinterpret_cast<int32_t *>(p.y) + (size_t)row * p.ldy + col0;
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        if (col0 + 4 * g < p.n) {
+                            int4 v = make_int4((int)r[4 * g] - corr, (int)r[4 * g + 1] - corr,
+                                               (int)r[4 * g + 2] - corr, (int)r[4 * g + 3] - corr);
+                            *reinterpret_cast<int4 *>(dst + 4 * g) = v;
+                        }
+                    }
+                } else if (OUT == OUT_F32) {
+                    float *dst = reinterpret_cast<float *>(p.y) + (size_t)row * p.ldy + col0;
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        if (col0 + 4 * g < p.n) {
+                            const float4 ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                            float4 v;
+                            v.x = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g] - corr), as), ws.x);
+                            v.y = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 1] - corr), as), ws.y);
+                            v.z = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 2] - corr), as), ws.z);
+                            v.w = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 3] - corr), as), ws.w);
+                            *reinterpret_cast<float4 *>(dst + 4 * g) = v;
+                        }
+                    }
+                } else {
+                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.ldy + col0;
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        if (col0 + 8 * g < p.n) {
+                            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g));
+                            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g + 4));
+                            const float wsv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float lo = __fmul_rn(__fmul_rn(__int2float_rn((int)r[8 * g + 2 * e] - corr), as), wsv[2 * e]);
+                                const float hi = __fmul_rn(__fmul_rn(__int2float_rn((int)r[8 * g + 2 * e + 1] - corr), as), wsv[2 * e + 1]);
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                                pk[e] = *reinterpret_cast<const uint32_t *>(&b2);
+                            }
+                            *reinterpret_cast<uint4 *>(dst + 8 * g) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        }
+                    }
+                }
+            }
+            // all of this warp's TMEM reads are complete: hand the buffer back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // A role gave up.  Give copies and MMAs still in flight time to land
+        // before shared memory and TMEM are released.
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(Cfg::kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D uint8 tensor [rows][k] (k contiguous), box = 128 bytes x box_rows, 128B swizzle,
+// out-of-range rows read as zero.
+int make_kmajor_map(tpb_handle_t h, CUtensorMap *map, const void *base, int64_t rows, int64_t k,
+                    int box_rows) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)k};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld", (int)r,
+                        (long long)rows, (long long)k);
+    return TPB_OK;
+}
+
+template <int BN, int OUT>
+int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+               bool b_unsigned) {
+    using Cfg = TileCfg<BN>;
+    CUtensorMap ma, mb;
+    int rc = make_kmajor_map(h, &ma, q, p.m, p.k, BM);
+    if (rc != TPB_OK) return rc;
+    rc = make_kmajor_map(h, &mb, w8, p.n, p.k, BN);
+    if (rc != TPB_OK) return rc;
+    auto kern = convrot_gemm_kernel<BN, OUT>;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+    const int grid = tiles < h->sm_count ? tiles : h->sm_count;
+    kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(ma, mb, p, b_unsigned ? 1 : 0);
+    TPB_CUDA(h, cudaGetLastError());
+    return TPB_OK;
+}
+
+template <int OUT>
+int launch_out(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+               bool b_unsigned) {
+    // Widest tile that still gives every SM work; narrow tiles for small problems.
+    const int m_tiles = (p.m + BM - 1) / BM;
+    auto tiles = [&](int bn) { return m_tiles * ((p.n + bn - 1) / bn); };
+    if (tiles(256) >= h->sm_count || p.n % 256 == 0 && tiles(128) > 2 * h->sm_count)
+        return launch_cfg<256, OUT>(h, st, p, q, w8, b_unsigned);
+    if (tiles(128) >= h->sm_count) return launch_cfg<128, OUT>(h, st, p, q, w8, b_unsigned);
+    return launch_cfg<64, OUT>(h, st, p, q, w8, b_unsigned);
+}
+
+}  // namespace
+
+// Scratch for the int8 expansion of an int4 weight (grown on demand, owned by
+// the handle).  Keyed by nothing: the expansion is redone on every call.
+struct W4Scratch {
+    int8_t *buf = nullptr;
+    size_t bytes = 0;
+};
+static W4Scratch g_w4_scratch[64];  // per device ordinal
+
+int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
+                    const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *w,
+                    int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k) {
+    GemmParams p;
+    p.y = y;
+    p.ldy = ldy;
+    p.act_scale = act_scale;
+    p.w_scale = w_scale;
+    p.act_sum = nullptr;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.status = h->d_status;
+    const void *w8 = w;
+    if (w_bits == 4) {
+        W4Scratch &s = g_w4_scratch[h->device & 63];
+        const size_t need = (size_t)n * (size_t)k;
+        if (s.bytes < need) {
+            if (s.buf) TPB_CUDA(h, cudaFree(s.buf));
+            s.buf = nullptr;
+            s.bytes = 0;
+            TPB_CUDA(h, cudaMalloc(&s.buf, need));
+            s.bytes = need;
+        }
+        const int rc = tpb_launch_w4_expand(h, st, w, n, k, s.buf);
+        if (rc != TPB_OK) return rc;
+        w8 = s.buf;
+    }
+    switch (y_dtype) {
+        case TPB_F32: return launch_out<OUT_F32>(h, st, p, q, w8, false);
+        case TPB_BF16: return launch_out<OUT_BF16>(h, st, p, q, w8, false);
+        case TPB_S32: return launch_out<OUT_S32>(h, st, p, q, w8, false);
+    }
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm: unsupported y_dtype %d", y_dtype);
+}

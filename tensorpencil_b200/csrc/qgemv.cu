@@ -1,0 +1,432 @@
+// GGUF Q8_0 decode GEMV family for sm_100a (CUDA cores, dp4a + warp reductions;
+// HBM-bound: the weight matrix streams once for up to 8 activation rows).
+//
+// A Q8_0 row is k/32 blocks of 34 bytes (f16 d, then 32 int8); blocks are only
+// 2-byte aligned, which is what makes per-lane global loads of them expensive.
+// Here the weight never goes through the load/store unit on its way in: each
+// warp streams its rows into a private shared-memory ring with 1-D bulk async
+// copies (cp.async.bulk, completion on an mbarrier, no multicast), several
+// stages ahead of the arithmetic.  A lane then takes a PAIR of adjacent blocks
+// (68 bytes = 17 aligned words, lane stride 17 words => no bank conflicts): the
+// second block's quants are already word-aligned, the first block's need one
+// funnel shift per word.  Activations (int8 + per-block scale, the q8_1 form)
+// sit in shared memory for the whole kernel and are reused across the R rows a
+// warp handles at once.
+//
+// Arithmetic follows the reference kernel (src/gpu/cuda/elt.zig:1926-2006,
+// :1663-1709): per block sumi = sum of 32 int8 products (exact), then
+// acc += float(sumi) * (d_w * d_x) in f32, a butterfly reduction across the
+// warp, and y = acc * scale.
+#include <cuda_fp16.h>
+
+#include "tpb_internal.h"
+
+namespace {
+
+constexpr int kBlockBytes = 34;
+constexpr int kRows = 4;                           // weight rows a warp processes together
+constexpr int kPairsPerChunk = 32;                 // one block pair per lane
+constexpr int kChunkBlocks = 2 * kPairsPerChunk;   // 64 blocks
+constexpr int kChunkBytes = kChunkBlocks * kBlockBytes;  // 2176 per row (multiple of 16)
+constexpr int kStageBytes = kRows * kChunkBytes + 16;    // +16: the last lane over-reads one word
+constexpr long long kWaitLimitCycles = 2000000000ll;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the limit ran out (status word written).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && clock64() - t0 > kWaitLimitCycles) {
+            atomicCAS(status, 0u, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+struct GemvParams {
+    float *y;
+    const uint8_t *w;
+    const float *xd;   // activation block scales, row 0 of the group: [ng][nblk] with stride nblk
+    const int8_t *xq;  // activation quants: [ng][cols]
+    float scale;
+    int rows, cols, nblk;
+    uint32_t *status;
+};
+
+// M activation rows (compile time).  ACT_SMEM: activations staged in shared memory.
+template <int M, bool ACT_SMEM>
+__global__ void __launch_bounds__(256, 1)
+q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5;
+    const int nblk = p.nblk;
+    const int cols = p.cols;
+    const size_t row_bytes = (size_t)nblk * kBlockBytes;
+
+    // shared layout: [act q: M*cols][act d: M*nblk f32][per-warp: stages*kStageBytes][barriers]
+    int8_t *s_q = reinterpret_cast<int8_t *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (ACT_SMEM ? (size_t)M * cols : 0));
+    uint8_t *ring0 = smem + (ACT_SMEM ? (size_t)M * cols + (size_t)M * nblk * 4 : 0);
+    uint8_t *ring = ring0 + (size_t)warp * stages * kStageBytes;
+    const uint32_t bars = smem_u32(ring0 + (size_t)n_warps * stages * kStageBytes) + warp * stages * 8;
+
+    if (ACT_SMEM) {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        int4 *sq = reinterpret_cast<int4 *>(s_q);
+        for (int i = threadIdx.x; i < M * cols / 16; i += blockDim.x) sq[i] = __ldg(gq + i);
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+    }
+    if (lane == 0) {
+        for (int s = 0; s < stages; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * s), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int cpr = (nblk + kChunkBlocks - 1) / kChunkBlocks;  // chunks per row
+    const int n_rg = (p.rows + kRows - 1) / kRows;             // row groups
+    const int gw = blockIdx.x * n_warps + warp;
+    const int GW = gridDim.x * n_warps;
+    const int my_rg = gw < n_rg ? (n_rg - gw + GW - 1) / GW : 0;
+    const int total = my_rg * cpr;
+
+    auto issue = [&](int i) {
+        // lane 0 only: start the copies of iteration i into its stage
+        const int rg = gw + (i / cpr) * GW;
+        const int c = i % cpr;
+        const int st = i % stages;
+        const int row0 = rg * kRows;
+        const int nrow = min(kRows, p.rows - row0);
+        const int blocks = min(kChunkBlocks, nblk - c * kChunkBlocks);
+        const uint32_t bytes = (uint32_t)blocks * kBlockBytes;
+        const uint32_t bar = bars + 8 * st;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                     "r"(bytes * (uint32_t)nrow)
+                     : "memory");
+        const uint32_t dst = smem_u32(ring + (size_t)st * kStageBytes);
+        for (int r = 0; r < nrow; r++)
+            bulk_g2s(dst + r * kChunkBytes, p.w + (size_t)(row0 + r) * row_bytes + (size_t)c * kChunkBytes,
+                     bytes, bar);
+    };
+
+    if (lane == 0)
+        for (int i = 0; i < stages - 1 && i < total; i++) issue(i);
+
+    float acc[kRows][M];
+#pragma unroll
+    for (int r = 0; r < kRows; r++)
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < total && ok; i++) {
+        // the stage refilled here was consumed in iteration i-1 (warp-synchronous)
+        if (lane == 0 && i + stages - 1 < total) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(i + stages - 1);
+        }
+        const int st = i % stages;
+        ok = mbar_wait(bars + 8 * st, (uint32_t)(i / stages) & 1u, p.status, (4u << 24) | (uint32_t)st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+
+        const int rg = gw + (i / cpr) * GW;
+        const int c = i % cpr;
+        const int row0 = rg * kRows;
+        const int nrow = min(kRows, p.rows - row0);
+        const int blk0 = c * kChunkBlocks + 2 * lane;  // first block of this lane's pair
+        const bool live = blk0 < nblk;                  // nblk is even
+        if (live) {
+            // weights: 17 aligned words per row, quants of block A funnel-shifted by 16 bits
+            uint32_t wq[kRows][16];
+            float wd[kRows][2];
+            const uint8_t *stage = ring + (size_t)st * kStageBytes + lane * (2 * kBlockBytes);
+#pragma unroll
+            for (int r = 0; r < kRows; r++) {
+                if (r < nrow) {
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes);
+                    uint32_t t[17];
+#pragma unroll
+                    for (int j = 0; j < 17; j++) t[j] = src[j];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) wq[r][j] = __funnelshift_r(t[j], t[j + 1], 16);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) wq[r][8 + j] = t[9 + j];
+                    wd[r][0] = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
+                    wd[r][1] = __half2float(__ushort_as_half((unsigned short)(t[8] >> 16)));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) wq[r][j] = 0;
+                    wd[r][0] = wd[r][1] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                uint32_t xq[16];
+                float xd0, xd1;
+                if (ACT_SMEM) {
+                    const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * cols + (size_t)blk0 * 32);
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        const int4 t = a[v];
+                        xq[4 * v] = t.x; xq[4 * v + 1] = t.y; xq[4 * v + 2] = t.z; xq[4 * v + 3] = t.w;
+                    }
+                    const float2 d2 = *reinterpret_cast<const float2 *>(s_d + (size_t)m * nblk + blk0);
+                    xd0 = d2.x;
+                    xd1 = d2.y;
+                } else {
+                    const int4 *a = reinterpret_cast<const int4 *>(p.xq + (size_t)m * cols + (size_t)blk0 * 32);
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        const int4 t = __ldg(a + v);
+                        xq[4 * v] = t.x; xq[4 * v + 1] = t.y; xq[4 * v + 2] = t.z; xq[4 * v + 3] = t.w;
+                    }
+                    const float2 d2 = __ldg(reinterpret_cast<const float2 *>(p.xd + (size_t)m * nblk + blk0));
+                    xd0 = d2.x;
+                    xd1 = d2.y;
+                }
+#pragma unroll
+                for (int r = 0; r < kRows; r++) {
+                    int s0 = 0, s1 = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) s0 = __dp4a((int)wq[r][j], (int)xq[j], s0);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) s1 = __dp4a((int)wq[r][8 + j], (int)xq[8 + j], s1);
+                    acc[r][m] = fmaf(__int2float_rn(s0), wd[r][0] * xd0, acc[r][m]);
+                    acc[r][m] = fmaf(__int2float_rn(s1), wd[r][1] * xd1, acc[r][m]);
+                }
+            }
+        }
+        __syncwarp();
+
+        if (c == cpr - 1) {
+            // row group finished: reduce across the warp, write, reset
+#pragma unroll
+            for (int r = 0; r < kRows; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    float v = acc[r][m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0 && r < nrow) p.y[(size_t)m * p.rows + row0 + r] = v * p.scale;
+                    acc[r][m] = 0.0f;
+                }
+        }
+    }
+}
+
+// Fallback for shapes the bulk-copy path cannot take (row size not a multiple of
+// 16 bytes, i.e. cols % 256 != 0): one warp per weight row, 16-bit global loads.
+template <int M>
+__global__ void __launch_bounds__(256)
+q8_0_gemv_q8n_simple_kernel(const GemvParams p) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= p.rows) return;
+    const uint8_t *wrow = p.w + (size_t)warp * p.nblk * kBlockBytes;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; m++) acc[m] = 0.0f;
+    for (int b = lane; b < p.nblk; b += 32) {
+        const unsigned short *blk = reinterpret_cast<const unsigned short *>(wrow + (size_t)b * kBlockBytes);
+        const float dw = __half2float(__ushort_as_half(blk[0]));
+        uint32_t wq[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) wq[j] = (uint32_t)blk[1 + 2 * j] | ((uint32_t)blk[2 + 2 * j] << 16);
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            const int *xq = reinterpret_cast<const int *>(p.xq + (size_t)m * p.cols + (size_t)b * 32);
+            int s = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) s = __dp4a((int)wq[j], xq[j], s);
+            acc[m] = fmaf(__int2float_rn(s), dw * p.xd[(size_t)m * p.nblk + b], acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+        float v = acc[m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) p.y[(size_t)m * p.rows + warp] = v * p.scale;
+    }
+}
+
+// q8_1 activation quantiser: one warp per 32-element block
+// (src/gpu/cuda/elt.zig:1226-1269).
+__global__ void __launch_bounds__(256)
+q8_1_quantize_kernel(const float *__restrict__ x, float *__restrict__ d, int8_t *__restrict__ qs,
+                     int nblk) {
+    const int blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (blk >= nblk) return;
+    const float xi = x[(size_t)blk * 32 + lane];
+    float amax = fabsf(xi);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(127.0f, amax);
+    qs[(size_t)blk * 32 + lane] = (int8_t)__float2int_rn(__fmul_rn(xi, inv));
+    if (lane == 0) d[blk] = __fdiv_rn(amax, 127.0f);
+}
+
+// M = 1 GEMV in f32 arithmetic on un-quantised activations
+// (src/gpu/cuda/elt.zig:671-727): one warp per row, x staged in shared memory.
+__global__ void __launch_bounds__(256)
+q8_0_gemv_f32_kernel(float *__restrict__ y, const float *__restrict__ x, const uint8_t *__restrict__ w,
+                     float scale, int rows, int cols) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float *sx = reinterpret_cast<float *>(smem);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) sx[i] = x[i];
+    __syncthreads();
+    const int nblk = cols / 32;
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+        const uint8_t *wrow = w + (size_t)row * nblk * kBlockBytes;
+        float acc = 0.0f;
+        for (int b = lane; b < nblk; b += 32) {
+            const unsigned short *blk = reinterpret_cast<const unsigned short *>(wrow + (size_t)b * kBlockBytes);
+            const float dw = __half2float(__ushort_as_half(__ldg(blk)));
+            const float *xb = sx + b * 32;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const unsigned short two = __ldg(blk + 1 + j);
+                const float q0 = (float)(signed char)(two & 0xff);
+                const float q1 = (float)(signed char)(two >> 8);
+                acc = fmaf(q0 * dw, xb[2 * j], acc);
+                acc = fmaf(q1 * dw, xb[2 * j + 1], acc);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) y[row] = acc * scale;
+    }
+}
+
+template <int M>
+int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
+    const size_t row_bytes = (size_t)p.nblk * kBlockBytes;
+    if (row_bytes % 16 != 0) {
+        const int block = 256;
+        const int grid = (p.rows * 32 + block - 1) / block;
+        q8_0_gemv_q8n_simple_kernel<M><<<grid, block, 0, st>>>(p);
+        TPB_CUDA(h, cudaGetLastError());
+        return TPB_OK;
+    }
+    // Fit activations + rings into the opt-in shared memory: prefer 8 warps and
+    // as many stages as fit (at most 4); drop activations to global loads last.
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t act = (size_t)M * p.cols + (size_t)M * p.nblk * 4;
+    int warps = 8, stages = 0;
+    bool act_smem = true;
+    auto fits = [&](int w, int s, bool a) {
+        return (a ? act : 0) + (size_t)w * s * kStageBytes + (size_t)w * s * 8 + 64 <= limit;
+    };
+    const int warp_opts[2] = {8, 4};
+    for (int wi = 0; wi < 2 && stages == 0; wi++)
+        for (int s = 4; s >= 2; s--)
+            if (fits(warp_opts[wi], s, true)) {
+                warps = warp_opts[wi];
+                stages = s;
+                break;
+            }
+    if (stages == 0) {
+        act_smem = false;
+        warps = 8;
+        stages = 3;
+    }
+    const size_t smem = (act_smem ? act : 0) + (size_t)warps * stages * kStageBytes + (size_t)warps * stages * 8 + 64;
+    const int n_rg = (p.rows + kRows - 1) / kRows;
+    int grid = (n_rg + warps - 1) / warps;
+    if (grid > h->sm_count) grid = h->sm_count;
+    if (act_smem) {
+        auto kern = q8_0_gemv_q8n_kernel<M, true>;
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, warps * 32, smem, st>>>(p, stages);
+    } else {
+        auto kern = q8_0_gemv_q8n_kernel<M, false>;
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, warps * 32, smem, st>>>(p, stages);
+    }
+    TPB_CUDA(h, cudaGetLastError());
+    return TPB_OK;
+}
+
+}  // namespace
+
+int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, int64_t n_elems,
+                             void *xq) {
+    const int nblk = (int)(n_elems / 32);
+    float *d = reinterpret_cast<float *>(xq);
+    int8_t *qs = reinterpret_cast<int8_t *>(xq) + (size_t)nblk * 4;
+    const int block = 256;
+    const int grid = (nblk * 32 + block - 1) / block;
+    q8_1_quantize_kernel<<<grid, block, 0, st>>>(x, d, qs, nblk);
+    TPB_CUDA(h, cudaGetLastError());
+    return TPB_OK;
+}
+
+int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
+                             int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
+                             int n_total) {
+    GemvParams p;
+    const int nblk = (int)(cols / 32);
+    p.y = y;
+    p.w = reinterpret_cast<const uint8_t *>(w);
+    // xq: f32 d[n_total * nblk], then int8 qs[n_total * cols]  (the reference's layout)
+    p.xd = reinterpret_cast<const float *>(xq) + (size_t)row_off * nblk;
+    p.xq = reinterpret_cast<const int8_t *>(xq) + (size_t)n_total * nblk * 4 + (size_t)row_off * cols;
+    p.scale = scale;
+    p.rows = (int)rows;
+    p.cols = (int)cols;
+    p.nblk = nblk;
+    p.status = h->d_status;
+    switch (ng) {
+        case 1: return launch_q8n<1>(h, st, p);
+        case 2: return launch_q8n<2>(h, st, p);
+        case 3: return launch_q8n<3>(h, st, p);
+        case 4: return launch_q8n<4>(h, st, p);
+        case 5: return launch_q8n<5>(h, st, p);
+        case 6: return launch_q8n<6>(h, st, p);
+        case 7: return launch_q8n<7>(h, st, p);
+        case 8: return launch_q8n<8>(h, st, p);
+    }
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "q8_0_gemv_q8n: ng out of range");
+}
+
+int tpb_launch_q8_0_gemv_f32(tpb_handle_t h, cudaStream_t st, float *y, const float *x,
+                             const void *w, float scale, int64_t rows, int64_t cols) {
+    const size_t smem = (size_t)cols * 4;
+    if (smem > (size_t)h->smem_optin)
+        return tpb_fail(h, TPB_ERR_INVALID_ARG, "q8_0_gemv_f32: cols too large for shared memory");
+    TPB_CUDA(h, cudaFuncSetAttribute(q8_0_gemv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int grid = (int)((rows + 7) / 8);
+    if (grid > h->sm_count * 4) grid = h->sm_count * 4;
+    q8_0_gemv_f32_kernel<<<grid, 256, smem, st>>>(y, x, reinterpret_cast<const uint8_t *>(w), scale,
+                                                  (int)rows, (int)cols);
+    TPB_CUDA(h, cudaGetLastError());
+    return TPB_OK;
+}

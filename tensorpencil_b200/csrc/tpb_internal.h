@@ -1,0 +1,59 @@
+// Internal declarations shared by the translation units of libtpb200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "tpb200.h"
+
+#define TPB_VERSION 100
+
+struct tpb_handle_s {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    uint32_t *d_status = nullptr;   // device status word written by bounded waits
+    // cuTensorMapEncodeTiled, resolved through the runtime so the library has no
+    // link-time dependency on libcuda (it must load on a host without a driver).
+    void *encode_tiled = nullptr;
+    char err[512] = {0};
+};
+
+int tpb_fail(tpb_handle_t h, int code, const char *fmt, ...);
+
+#define TPB_CHECK_ARG(h, cond, ...)                                   \
+    do {                                                              \
+        if (!(cond)) return tpb_fail((h), TPB_ERR_INVALID_ARG, __VA_ARGS__); \
+    } while (0)
+
+#define TPB_CUDA(h, expr)                                                          \
+    do {                                                                           \
+        cudaError_t e__ = (expr);                                                  \
+        if (e__ != cudaSuccess)                                                    \
+            return tpb_fail((h), e__ == cudaErrorMemoryAllocation ? TPB_ERR_OOM : TPB_ERR_CUDA, \
+                            "%s failed: %s", #expr, cudaGetErrorString(e__));      \
+    } while (0)
+
+static inline bool tpb_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Kernel launchers (one per .cu file).  All return a tpb_status.
+int tpb_launch_prep(tpb_handle_t h, cudaStream_t st, const void *x, int x_dtype, int64_t m,
+                    int64_t k, int bits, int8_t *q, float *act_scale, int32_t *act_sum);
+int tpb_launch_w4_expand(tpb_handle_t h, cudaStream_t st, const void *w4, int64_t n, int64_t k,
+                         int8_t *w8);
+int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
+                    const int8_t *q, const float *act_scale, const int32_t *act_sum,
+                    const void *w, int w_bits, const float *w_scale, int64_t m, int64_t n,
+                    int64_t k);
+int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, int64_t n_elems,
+                             void *xq);
+int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
+                             int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
+                             int n_total);
+int tpb_launch_q8_0_gemv_f32(tpb_handle_t h, cudaStream_t st, float *y, const float *x,
+                             const void *w, float scale, int64_t rows, int64_t cols);
