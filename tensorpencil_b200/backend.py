@@ -238,6 +238,28 @@ class Backend:
             self.opI4Gemm(y, w, w_scale, n)
         return y
 
+    def convrot_linear_host(self, x_host: torch.Tensor, w, w_scale, n: int, bits: int,
+                            y_host: torch.Tensor):
+        """The same linear with HOST activations and a HOST result (pinned
+        tensors): upload x, prep, GEMM, download y, all enqueued on the current
+        stream -- the shape of a call from a host-resident orchestrator
+        (tensorUpload / op / tensorDownload, src/models/dit_cuda.zig:430-433, :527).
+        Weights stay in the device-side weight cache as in the reference."""
+        m, k = x_host.shape
+        key = (m, k, n, x_host.dtype, y_host.dtype)
+        if getattr(self, "_host_io_key", None) != key:
+            self._host_x = torch.empty((m, k), dtype=x_host.dtype, device=self.device)
+            self._host_y = torch.empty((m, n), dtype=y_host.dtype, device=self.device)
+            self._host_io_key = key
+        self._host_x.copy_(x_host, non_blocking=True)
+        if bits == 8:
+            self.opI8Prep(self._host_x, m, k)
+            self.opI8Gemm(self._host_y, w, w_scale, n)
+        else:
+            self.opI4Prep(self._host_x, m, k)
+            self.opI4Gemm(self._host_y, w, w_scale, n)
+        y_host.copy_(self._host_y, non_blocking=True)
+
     def q8_0_linear(self, x: torch.Tensor, w, n: int, k: int, scale: float = 1.0) -> torch.Tensor:
         """Decode linear the way the reference's steppers dispatch it
         (src/models/qwen3_cuda.zig:1497-1517): quantise all rows once, then one

@@ -9,8 +9,12 @@
 //   warp 1      : allocates TMEM and issues tcgen05.mma.kind::i8 (M=128, N=BN,
 //                 K=32) from one thread; int32 accumulators live in TMEM, two
 //                 buffers so the epilogue of tile t overlaps the main loop of t+1;
-//   warps 2..5  : epilogue -- tcgen05.ld the accumulator rows, apply the two
-//                 scales, convert and store.
+//   warps 2..5  : epilogue -- tcgen05.ld the accumulator rows (the load of the
+//                 next 32 columns is in flight while the current ones are
+//                 processed), apply the two scales, convert, stage the 32-row x
+//                 128-byte piece in shared memory in the 128-byte swizzle
+//                 pattern and hand it to a TMA store, so global memory sees
+//                 whole 128-byte lines; two staging buffers per warp.
 // Every wait on an mbarrier is bounded: on expiry the kernel records a status
 // word, every role leaves its loop, TMEM is released and the kernel returns.
 // No TMA load here uses cluster multicast.
@@ -24,7 +28,6 @@ constexpr int BM = 128;            // rows of q per tile (= UMMA M)
 constexpr int BK = 128;            // int8 elements (= bytes) of K per stage: one 128B swizzle row
 constexpr int UMMA_K = 32;         // K of one tcgen05.mma.kind::i8
 constexpr int kThreads = 192;      // 6 warps
-constexpr int kEpiWarp0 = 2;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
 
 enum OutKind { OUT_F32 = 0, OUT_BF16 = 1, OUT_S32 = 2 };
@@ -36,9 +39,11 @@ struct TileCfg {
     static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
     static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
-    // tiles + barriers (full/empty per stage, full/empty per accumulator) + TMEM
-    // base slot + abort flag, plus 1 KB slack to align the tiles to 1024 bytes.
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes)
+    static constexpr int kStagingBytes = 4 * 2 * 4096;
+    // tiles + staging + barriers (full/empty per stage, full/empty per accumulator)
+    // + TMEM base slot + abort flag, plus 1 KB slack to align the tiles to 1024 bytes.
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
 struct GemmParams {
@@ -142,6 +147,27 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, but naming the destination registers of the load as in/out operands
+// so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                   "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                   "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]),
+                   "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
+                   "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// TMA store of one staged box (shared -> global); rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle
 // layout TMA writes: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -176,7 +202,8 @@ __device__ __forceinline__ uint32_t make_idesc_i8(bool b_unsigned) {
 template <int BN, int OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
-                    const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
+                    const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_y, const GemmParams p,
                     const int b_unsigned) {
     using Cfg = TileCfg<BN>;
     constexpr int S = Cfg::kStages;
@@ -184,13 +211,14 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    // layout: [S x (A tile | B tile)] [barriers] [tmem slot] [abort flag]
-    const uint32_t bars = smem_base + S * Cfg::kStageBytes;
+    // layout: [S x (A tile | B tile)] [epilogue staging] [barriers] [tmem slot] [abort flag]
+    const uint32_t stg_base = smem_base + S * Cfg::kStageBytes;
+    const uint32_t bars = stg_base + Cfg::kStagingBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * S + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * S + 2 + a); };
-    uint8_t *tail = smem_gen + S * Cfg::kStageBytes + 8 * (2 * S + 4);
+    uint8_t *tail = smem_gen + S * Cfg::kStageBytes + Cfg::kStagingBytes + 8 * (2 * S + 4);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tail + 8);
 
@@ -283,6 +311,11 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     } else {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+        // two 4 KB staging buffers per warp, each 32 rows x 128 bytes, 1024-byte aligned
+        const uint32_t stg = stg_base + (uint32_t)(warp - 2) * 8192u;
+        const uint32_t my_row_off = (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);  // 128-byte swizzle: 16-byte piece j of row r sits at j ^ (r & 7)
+        uint32_t n_store = 0;                      // stores issued by this warp (selects the staging buffer)
         uint32_t t_it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, t_it++) {
@@ -294,63 +327,82 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
+            const int row0 = m0 + quarter * 32;
+            const int row = row0 + lane;
             const bool row_ok = row < p.m;
             float as = 0.0f;
             int corr = 0;
             if (OUT != OUT_S32 && row_ok) as = __ldg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
+
+            uint32_t ra[32], rb[32];
+            tc_ld_32x32(t_row, ra);
+#pragma unroll
             for (int c = 0; c < BN / 32; c++) {
-                uint32_t r[32];
-                tc_ld_32x32(t_row + (uint32_t)(c * 32), r);
-                tc_wait_ld();
+                uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+                uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+                tc_wait_ld_dep(cur);  // columns 32c.. are in `cur`
+                if (c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), nxt);
                 const int col0 = n0 + c * 32;
-                if (!row_ok || col0 >= p.n) continue;
+                // first piece of a 128-byte staging row: make sure the TMA store that last
+                // read this buffer (two stores ago) is done with it
+                const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
+                const uint32_t buf = stg + (n_store & 1u) * 4096u + my_row_off;
+                if (first_piece) {
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                }
                 if (OUT == OUT_S32) {
-                    int32_t *dst = reinterpret_cast<int32_t *>(p.y) + (size_t)row * p.ldy + col0;
 #pragma unroll
-                    for (int g = 0; g < 8; g++) {
-                        if (col0 + 4 * g < p.n) {
-                            int4 v = make_int4((int)r[4 * g] - corr, (int)r[4 * g + 1] - corr,
-                                               (int)r[4 * g + 2] - corr, (int)r[4 * g + 3] - corr);
-                            *reinterpret_cast<int4 *>(dst + 4 * g) = v;
-                        }
-                    }
+                    for (int g = 0; g < 8; g++)
+                        st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), cur[4 * g] - corr, cur[4 * g + 1] - corr,
+                                     cur[4 * g + 2] - corr, cur[4 * g + 3] - corr);
                 } else if (OUT == OUT_F32) {
-                    float *dst = reinterpret_cast<float *>(p.y) + (size_t)row * p.ldy + col0;
 #pragma unroll
                     for (int g = 0; g < 8; g++) {
-                        if (col0 + 4 * g < p.n) {
-                            const float4 ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
-                            float4 v;
-                            v.x = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g] - corr), as), ws.x);
-                            v.y = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 1] - corr), as), ws.y);
-                            v.z = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 2] - corr), as), ws.z);
-                            v.w = __fmul_rn(__fmul_rn(__int2float_rn((int)r[4 * g + 3] - corr), as), ws.w);
-                            *reinterpret_cast<float4 *>(dst + 4 * g) = v;
-                        }
+                        float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (col0 + 4 * g < p.n) ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                        const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g] - corr), as), ws.x);
+                        const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 1] - corr), as), ws.y);
+                        const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
+                        const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 3] - corr), as), ws.w);
+                        st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), __float_as_uint(v0), __float_as_uint(v1),
+                                     __float_as_uint(v2), __float_as_uint(v3));
                     }
                 } else {
-                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.ldy + col0;
+                    // bf16: 64 columns make one 128-byte row; this chunk fills pieces 4*(c&1) .. +3
 #pragma unroll
                     for (int g = 0; g < 4; g++) {
+                        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
                         if (col0 + 8 * g < p.n) {
-                            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g));
-                            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g + 4));
-                            const float wsv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                            uint32_t pk[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const float lo = __fmul_rn(__fmul_rn(__int2float_rn((int)r[8 * g + 2 * e] - corr), as), wsv[2 * e]);
-                                const float hi = __fmul_rn(__fmul_rn(__int2float_rn((int)r[8 * g + 2 * e + 1] - corr), as), wsv[2 * e + 1]);
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-                                pk[e] = *reinterpret_cast<const uint32_t *>(&b2);
-                            }
-                            *reinterpret_cast<uint4 *>(dst + 8 * g) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            w0 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g));
+                            w1 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g + 4));
                         }
+                        const float wsv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float lo = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[8 * g + 2 * e] - corr), as), wsv[2 * e]);
+                            const float hi = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[8 * g + 2 * e + 1] - corr), as), wsv[2 * e + 1]);
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                            pk[e] = *reinterpret_cast<const uint32_t *>(&b2);
+                        }
+                        const uint32_t piece = (uint32_t)(4 * (c & 1) + g);
+                        st_shared_v4(buf + ((piece ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
                     }
+                }
+                const bool last_piece = OUT != OUT_BF16 || (c & 1) == 1;
+                if (last_piece) {
+                    // generic-proxy writes -> visible to the async proxy, then one lane stores
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    const int scol = OUT == OUT_BF16 ? col0 - 32 : col0;
+                    if (lane == 0 && row0 < p.m && scol < p.n) {
+                        tma_store_2d(&tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    n_store++;
                 }
             }
             // all of this warp's TMEM reads are complete: hand the buffer back
@@ -358,6 +410,9 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+        // staging memory must outlive the stores that read it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
     }
 
     // ---------------- teardown ----------------
@@ -403,25 +458,48 @@ int make_kmajor_map(tpb_handle_t h, CUtensorMap *map, const void *base, int64_t 
     return TPB_OK;
 }
 
+// Output tensor [m][ldy] (row-major), box = 128 bytes x 32 rows, 128B swizzle: the
+// epilogue's staging layout.
+template <int OUT>
+int make_out_map(tpb_handle_t h, CUtensorMap *map, const GemmParams &p) {
+    const int esz = OUT == OUT_BF16 ? 2 : 4;
+    const CUtensorMapDataType dt = OUT == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : OUT == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                    : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    const cuuint64_t gdim[2] = {(cuuint64_t)p.n, (cuuint64_t)p.m};
+    const cuuint64_t gstride[1] = {(cuuint64_t)p.ldy * esz};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+        map, dt, 2, p.y, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) m=%d n=%d ldy=%lld", (int)r,
+                        p.m, p.n, p.ldy);
+    return TPB_OK;
+}
+
 template <int BN, int OUT>
 int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                bool b_unsigned) {
     using Cfg = TileCfg<BN>;
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, my;
     int rc = make_kmajor_map(h, &ma, q, p.m, p.k, BM);
     if (rc != TPB_OK) return rc;
     rc = make_kmajor_map(h, &mb, w8, p.n, p.k, BN);
     if (rc != TPB_OK) return rc;
+    rc = make_out_map<OUT>(h, &my, p);
+    if (rc != TPB_OK) return rc;
     auto kern = convrot_gemm_kernel<BN, OUT>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
+    static bool attr_set[64] = {false};  // per instantiation and device
+    if (!attr_set[h->device & 63]) {
         TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set = true;
+        attr_set[h->device & 63] = true;
     }
     const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
     const int tiles = m_tiles * n_tiles;
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
-    kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(ma, mb, p, b_unsigned ? 1 : 0);
+    kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(ma, mb, my, p, b_unsigned ? 1 : 0);
     TPB_CUDA(h, cudaGetLastError());
     return TPB_OK;
 }
@@ -432,8 +510,7 @@ int launch_out(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
     // Widest tile that still gives every SM work; narrow tiles for small problems.
     const int m_tiles = (p.m + BM - 1) / BM;
     auto tiles = [&](int bn) { return m_tiles * ((p.n + bn - 1) / bn); };
-    if (tiles(256) >= h->sm_count || p.n % 256 == 0 && tiles(128) > 2 * h->sm_count)
-        return launch_cfg<256, OUT>(h, st, p, q, w8, b_unsigned);
+    if (tiles(256) >= h->sm_count) return launch_cfg<256, OUT>(h, st, p, q, w8, b_unsigned);
     if (tiles(128) >= h->sm_count) return launch_cfg<128, OUT>(h, st, p, q, w8, b_unsigned);
     return launch_cfg<64, OUT>(h, st, p, q, w8, b_unsigned);
 }
