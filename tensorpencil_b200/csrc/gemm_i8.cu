@@ -349,6 +349,13 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
                 // read this buffer (two stores ago) is done with it
                 const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
                 const uint32_t buf = stg + (n_store & 1u) * 4096u + my_row_off;
+                // Warp-uniform: does this 128-byte-wide piece reach into the tensor at all?
+                // Skipped pieces touch neither the staging buffers nor the buffer counter,
+                // so "all but the latest store have finished reading" keeps meaning "the
+                // other buffer's store".
+                const int scol = (OUT == OUT_BF16 && (c & 1)) ? col0 - 32 : col0;
+                const bool do_store = row0 < p.m && scol < p.n;
+                if (!do_store) continue;
                 if (first_piece) {
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
@@ -397,8 +404,7 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
                     // generic-proxy writes -> visible to the async proxy, then one lane stores
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
-                    const int scol = OUT == OUT_BF16 ? col0 - 32 : col0;
-                    if (lane == 0 && row0 < p.m && scol < p.n) {
+                    if (lane == 0) {
                         tma_store_2d(&tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }

@@ -137,6 +137,30 @@ def test_gemm_raw_s32_exact(be, m, n, k):
     assert bad == 0, f"{bad} of {got.size} accumulators differ"
 
 
+@pytest.mark.parametrize("out", ["int32", "float32", "bfloat16"])
+def test_gemm_ragged_tail_repeated(be, out):
+    """Tiles that hang over the right and bottom edges skip some of their stores;
+    repeat the launch to shake out any ordering slip between staging buffers."""
+    m, n, k = 1100, 5136, 512
+    rng = np.random.default_rng(99)
+    q = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+    w = rng.integers(-128, 128, size=(n, k), dtype=np.int8)
+    s = rng.uniform(0.5, 1.5, m).astype(np.float32)
+    ws = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    acc = oracle.igemm_s32(q, w)
+    want32 = (acc.astype(np.float32) * s[:, None]) * ws[None, :]
+    want = {"int32": torch.from_numpy(acc), "float32": torch.from_numpy(want32),
+            "bfloat16": torch.from_numpy(want32).to(torch.bfloat16)}[out]
+    be.i8_x, be.i8_scale, be.i8_sum = dev(q.reshape(-1)), dev(s), dev(np.zeros(m, np.int32))
+    be.i8_m, be.i8_cols, be.i8_bits = m, k, 8
+    wd, wsd = dev(w), dev(ws)
+    for _ in range(25):
+        y = torch.zeros((m, n), dtype=getattr(torch, out), device="cuda")
+        be._gemm(y, wd, wsd, n, 8)
+        assert torch.equal(y.cpu(), want)
+    be.status_poll()
+
+
 def test_gemm_extreme_values_no_overflow_surprises(be):
     m, n, k = 128, 128, 8192
     q = np.full((m, k), -127, np.int8)
