@@ -150,6 +150,27 @@ int tpb_q8_0_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, float *y, const void 
 int tpb_q8_0_gemv_f32(tpb_handle_t h, tpb_stream_t stream, float *y, const float *x,
                       const void *w, float scale, int64_t rows, int64_t cols);
 
+/* Decode linear that allocates nothing: quantises x[m][cols] (f32, m <= 8) and runs
+ * the grouped dp4a GEMV, y[i*rows + r] as tpb_q8_0_gemv_q8n, keeping the quantised
+ * activations in a fixed array inside the library instead of a buffer somebody has
+ * to allocate.  It has no counterpart in the reference, whose backend grows its
+ * q8 scratch with ensureDeviceBuffer.  It exists for hosts that cannot let a
+ * plugin call cudaMalloc -- an engine that owns all device memory through its own
+ * budgeted arena, or a decode loop that must not hit cudaMalloc's implicit device
+ * synchronisation.  This call and everything under it makes no cudaMalloc/cudaFree
+ * and calls no allocating library routine.
+ *   - limit: m * cols <= TPB_STATIC_GEMV_MAX_ELEMS (8 rows of 32768 columns); larger
+ *     requests return TPB_ERR_INVALID_ARG.  The array (TPB_STATIC_GEMV_SCRATCH_BYTES,
+ *     288 KiB) is resident on every GPU that loads the library until the process ends.
+ *   - the first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *   - all calls share the one array and it keeps the last call's contents: calls
+ *     that may overlap on the GPU (different streams without ordering) race. */
+#define TPB_STATIC_GEMV_MAX_ELEMS (8 * 32768)
+#define TPB_STATIC_GEMV_SCRATCH_BYTES (TPB_STATIC_GEMV_MAX_ELEMS + TPB_STATIC_GEMV_MAX_ELEMS / 32 * 4)
+int tpb_q8_0_gemv_static(tpb_handle_t h, tpb_stream_t stream, float *y, const float *x, int m,
+                         const void *w, float scale, int64_t rows, int64_t cols);
+
 /* ---- weight streaming ---------------------------------------------------------
  * Replaces the diffusion weight cache's streaming half: Backend.prefetchWeight,
  * cachedWeight's wait on a prefetch, the deferred free behind a compute-stream

@@ -39,6 +39,7 @@ SIGNATURES = {
     "tpb_q8_1_quantize": (_i, [_vp, _vp, _vp, _i64, _vp]),
     "tpb_q8_0_gemv_q8n": (_i, [_vp, _vp, _vp, _vp, _f, _i64, _i64, _vp, _i, _i, _i]),
     "tpb_q8_0_gemv_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i64, _i64]),
+    "tpb_q8_0_gemv_static": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _f, _i64, _i64]),
     "tpb_stream_open": (_i, [_vp, _sz, _sz, _i, C.POINTER(_vp)]),
     "tpb_stream_close": (_i, [_vp]),
     "tpb_stream_register": (_i, [_vp, _i, _vp, _sz]),

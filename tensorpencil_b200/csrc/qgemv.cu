@@ -430,3 +430,61 @@ int tpb_launch_q8_0_gemv_f32(tpb_handle_t h, cudaStream_t st, float *y, const fl
     TPB_CUDA(h, cudaGetLastError());
     return TPB_OK;
 }
+
+// ---- allocation-free decode linear --------------------------------------------------
+//
+// Some hosts cannot let a plugin allocate: an engine that has handed the whole
+// device to its own arena and accounts for every byte against a VRAM budget, or a
+// decode loop that must not meet the implicit device synchronisation of
+// cudaMalloc/cudaFree.  For them the quantised-activation scratch of the GEMV
+// lives in this fixed array instead of a caller- or library-allocated buffer.
+// Every GPU that loads the library carries the array until the process exits.
+// All calls share it and it keeps the previous call's contents: two calls that
+// overlap on the GPU (different streams, no ordering between them) race.
+static __device__ __align__(256) unsigned char g_static_q8_scratch[TPB_STATIC_GEMV_SCRATCH_BYTES];
+
+namespace {
+// Device address of the array per device ordinal.  The array's name in host code
+// is only a handle for the runtime, not a device pointer: the address has to be
+// asked for, with the owning device current.
+void *g_static_q8_ptr[64] = {nullptr};
+
+int static_scratch_setup(tpb_handle_t h, void **out) {
+    const int dev = h->device & 63;
+    if (g_static_q8_ptr[dev] == nullptr) {
+        int prev = 0;
+        TPB_CUDA(h, cudaGetDevice(&prev));
+        TPB_CUDA(h, cudaSetDevice(h->device));
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_q8_scratch);
+        cudaSetDevice(prev);
+        if (e != cudaSuccess || ptr == nullptr)
+            return tpb_fail(h, TPB_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s",
+                            cudaGetErrorString(e));
+        g_static_q8_ptr[dev] = ptr;
+    }
+    *out = g_static_q8_ptr[dev];
+    return TPB_OK;
+}
+}  // namespace
+
+extern "C" int tpb_q8_0_gemv_static(tpb_handle_t h, tpb_stream_t stream, float *y, const float *x,
+                                    int m, const void *w, float scale, int64_t rows, int64_t cols) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, y && x && w, "q8_0_gemv_static: null pointer");
+    TPB_CHECK_ARG(h, m >= 1 && m <= 8, "q8_0_gemv_static: m must be 1..8 (got %d)", m);
+    TPB_CHECK_ARG(h, rows >= 0 && cols > 0 && cols % 32 == 0, "q8_0_gemv_static: cols must be a multiple of 32");
+    TPB_CHECK_ARG(h, (int64_t)m * cols <= (int64_t)TPB_STATIC_GEMV_MAX_ELEMS,
+                  "q8_0_gemv_static: m * cols = %lld exceeds the fixed scratch of %d elements",
+                  (long long)((int64_t)m * cols), TPB_STATIC_GEMV_MAX_ELEMS);
+    TPB_CHECK_ARG(h, tpb_aligned16(w) && tpb_aligned16(x), "q8_0_gemv_static: w and x must be 16-byte aligned");
+    if (rows == 0) return TPB_OK;
+    void *scratch = nullptr;
+    int rc = static_scratch_setup(h, &scratch);
+    if (rc != TPB_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // same two kernels as tpb_q8_1_quantize + tpb_q8_0_gemv_q8n, scratch in the fixed array
+    rc = tpb_launch_q8_1_quantize(h, st, x, (int64_t)m * cols, scratch);
+    if (rc != TPB_OK) return rc;
+    return tpb_launch_q8_0_gemv_q8n(h, st, y, w, scale, rows, cols, scratch, m, 0, m);
+}
