@@ -11,13 +11,17 @@
 //   quantise  : q = round-half-away(v / s)        IEEE division
 //
 // Work split: one CTA per token row; a half-warp owns one 256-group, a lane
-// holds 16 of its elements.  Writing the element index as bits e7..e0, a lane
-// starts with {e0,e1,e6,e7} in registers (four coalesced 16-byte loads) and
-// {e2..e5} in its lane id.  A radix-4 pass over base-4 digit d needs both bits
-// of d in registers, so between passes two register bits are exchanged with two
-// lane bits by __shfl_xor (half of the registers move each time); after the
-// last pass the register bits are {e0,e1,e6,e7} again, so the int8 results
-// leave as 32-bit stores of four consecutive elements.
+// holds 16 of its elements.  Writing the element index as bits e7..e0, a radix-4
+// pass over base-4 digit d needs both bits of d inside one lane's registers:
+//   layout A  registers {e0,e1,e6,e7}, lane {e2..e5}: four coalesced 16-byte
+//             global loads; passes d0 (stride 1) and d3 (stride 64) are local;
+//   layout B  registers {e2,e3,e4,e5}, lane {e0,e1,e6,e7}: passes d1 (stride 4)
+//             and d2 (stride 16) are local.
+// The pass order 1,4,16,64 therefore runs A -> B -> A, and the two layout changes
+// go through a warp-private shared-memory tile (272 words per group: 4 pad words
+// after every 64 so that both layouts are bank-conflict free); only __syncwarp is
+// needed.  Back in layout A the int8 results leave as 32-bit stores of four
+// consecutive elements.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -42,52 +46,43 @@ __device__ __forceinline__ void hadamard4(float &a, float &b, float &c, float &d
     d = o3;
 }
 
-// Exchange one register-index bit with one lane-id bit: of the register pair
-// (r0, r1) that differs in that register bit, a lane whose lane bit is 0 keeps
-// r0 and trades r1 for its partner's r0; a lane whose bit is 1 does the reverse.
-template <int LANE_MASK>
-__device__ __forceinline__ void swap_bit(float &r0, float &r1, bool lane_bit) {
-    const float send = lane_bit ? r0 : r1;
-    const float recv = __shfl_xor_sync(0xffffffffu, send, LANE_MASK);
-    if (lane_bit)
-        r0 = recv;
-    else
-        r1 = recv;
+constexpr int kGroupWords = 272;  // 256 data words + 4 pad words per 64
+
+__device__ __forceinline__ void lds128(float (&v)[4], const float *p) {
+    const float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void sts128(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
-// v[i][j]: i = the two "high" register bits, j = e0,e1.  Exchange both high
-// register bits with lane bits LO (mask) and HI (mask).
-template <int MASK_LO, int MASK_HI>
-__device__ __forceinline__ void swap_high_bits(float (&v)[4][4], int lane) {
-    const bool b_lo = (lane & MASK_LO) != 0;
-    const bool b_hi = (lane & MASK_HI) != 0;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        swap_bit<MASK_LO>(v[0][j], v[1][j], b_lo);
-        swap_bit<MASK_LO>(v[2][j], v[3][j], b_lo);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        swap_bit<MASK_HI>(v[0][j], v[2][j], b_hi);
-        swap_bit<MASK_HI>(v[1][j], v[3][j], b_hi);
-    }
-}
-
-__device__ __forceinline__ void pass_high(float (&v)[4][4]) {
-#pragma unroll
-    for (int j = 0; j < 4; j++) hadamard4(v[0][j], v[1][j], v[2][j], v[3][j]);
-}
-
-// Un-normalised H*v of one 256-group spread over a half-warp.
-__device__ __forceinline__ void rotate_group(float (&v)[4][4], int lane) {
+// Un-normalised H*v of one 256-group spread over a half-warp.  `tile` is this
+// half-warp's 272-word shared tile; element e lives at word e + 4*(e >> 6).
+__device__ __forceinline__ void rotate_group(float (&v)[4][4], float *tile, int l16) {
 #pragma unroll
     for (int i = 0; i < 4; i++) hadamard4(v[i][0], v[i][1], v[i][2], v[i][3]);  // stride 1
-    swap_high_bits<1, 2>(v, lane);  // registers now {e0,e1,e2,e3}
-    pass_high(v);                   // stride 4
-    swap_high_bits<4, 8>(v, lane);  // registers now {e0,e1,e4,e5}
-    pass_high(v);                   // stride 16
-    swap_high_bits<1, 2>(v, lane);  // registers now {e0,e1,e6,e7}
-    pass_high(v);                   // stride 64
+    // layout A -> shared: chunk c = l16 + 16 i (4 elements) at word 4c + 4i
+    float *a_ptr = tile + 4 * l16;
+#pragma unroll
+    for (int i = 0; i < 4; i++) sts128(a_ptr + 68 * i, v[i]);
+    __syncwarp();
+    // layout B: element (l16 & 3) + 4 r + 64 (l16 >> 2), r = 0..15
+    float *b_ptr = tile + (l16 & 3) + 68 * (l16 >> 2);
+    float u[16];
+#pragma unroll
+    for (int r = 0; r < 16; r++) u[r] = b_ptr[4 * r];
+#pragma unroll
+    for (int hi = 0; hi < 4; hi++) hadamard4(u[4 * hi], u[4 * hi + 1], u[4 * hi + 2], u[4 * hi + 3]);  // stride 4
+#pragma unroll
+    for (int lo = 0; lo < 4; lo++) hadamard4(u[lo], u[lo + 4], u[lo + 8], u[lo + 12]);  // stride 16
+#pragma unroll
+    for (int r = 0; r < 16; r++) b_ptr[4 * r] = u[r];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; i++) lds128(v[i], a_ptr + 68 * i);
+    __syncwarp();  // the tile is reused by this half-warp's next group
+#pragma unroll
+    for (int j = 0; j < 4; j++) hadamard4(v[0][j], v[1][j], v[2][j], v[3][j]);  // stride 64
 }
 
 template <typename T>
@@ -114,10 +109,6 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16 *p, flo
     out[3] = __uint_as_float(t.y & 0xffff0000u);
 }
 
-// After the three exchanges the lane-id bits hold (e4,e5,e2,e3): the 16-byte
-// chunk (4 elements) a lane owns inside its group's 64-chunk row.
-__device__ __forceinline__ int out_chunk_of_lane(int l16) { return (l16 >> 2) | ((l16 & 3) << 2); }
-
 constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves rint(x) in the low mantissa bits
 
 // PPW = group pairs per warp (compile time, sizes the register file use).
@@ -127,6 +118,7 @@ convrot_prep_kernel(const T *__restrict__ x, int8_t *__restrict__ q, float *__re
                     int32_t *__restrict__ act_sum, int k, int n_groups, float maxq) {
     __shared__ float s_max[kMaxWarps];
     __shared__ int s_sum[kMaxWarps];
+    __shared__ __align__(16) float s_tile[kMaxWarps][2][kGroupWords];
 
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5;
@@ -153,7 +145,7 @@ convrot_prep_kernel(const T *__restrict__ x, int8_t *__restrict__ q, float *__re
     }
 #pragma unroll
     for (int p = 0; p < PPW; p++) {
-        rotate_group(v[p], lane);
+        rotate_group(v[p], s_tile[warp][hw], l16);
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
@@ -183,26 +175,33 @@ convrot_prep_kernel(const T *__restrict__ x, int8_t *__restrict__ q, float *__re
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             uint32_t yb[4];
+            // Fast path: v*rcp is within 2e-5 of the IEEE quotient for |q| <= 128, so
+            // unless it sits within 1e-4 of a half-integer, rounding it to nearest gives
+            // round-half-away(v / s) exactly.  y = rint(v*rcp) + magic in one FMA; the
+            // distance of v*rcp from that integer in a second one.
+            float y[4];
+            bool near_tie = false;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                // Fast path: v*rcp is within 2e-5 of the IEEE quotient for |q| <= 128,
-                // so unless it sits that close to a half-integer, rounding it to
-                // nearest gives round-half-away(v / s) exactly.
-                const float est = v[p][i][j] * rcp;
-                float y = est + kRoundMagic;
-                const float diff = est - (y - kRoundMagic);
-                if (fabsf(diff) > 0.4999f) {
-                    const float t = __fdiv_rn(v[p][i][j] * 0.0625f, s);
-                    y = roundf(t) + kRoundMagic;  // half away from zero, exact
-                }
-                yb[j] = __float_as_uint(y);
+                y[j] = __fmaf_rn(v[p][i][j], rcp, kRoundMagic);
+                const float diff = __fmaf_rn(v[p][i][j], rcp, -(y[j] - kRoundMagic));
+                near_tie |= fabsf(diff) > 0.4999f;
             }
+            if (near_tie) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float t = __fdiv_rn(v[p][i][j] * 0.0625f, s);
+                    y[j] = roundf(t) + kRoundMagic;  // half away from zero, exact
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) yb[j] = __float_as_uint(y[j]);
             const uint32_t lo = __byte_perm(yb[0], yb[1], 0x0040);
             const uint32_t hi = __byte_perm(yb[2], yb[3], 0x0040);
             const uint32_t word = __byte_perm(lo, hi, 0x5410);
             isum = __dp4a((int)word, 0x01010101, isum);
             if (live) {
-                const int chunk = out_chunk_of_lane(l16) + 16 * i;
+                const int chunk = l16 + 16 * i;
                 *reinterpret_cast<uint32_t *>(q + (size_t)row * k + g * 256 + 4 * chunk) = word;
             }
         }
