@@ -24,11 +24,11 @@
 namespace {
 
 constexpr int kBlockBytes = 34;
-constexpr int kRows = 4;                           // weight rows a warp processes together
 constexpr int kPairsPerChunk = 32;                 // one block pair per lane
 constexpr int kChunkBlocks = 2 * kPairsPerChunk;   // 64 blocks
 constexpr int kChunkBytes = kChunkBlocks * kBlockBytes;  // 2176 per row (multiple of 16)
-constexpr int kStageBytes = kRows * kChunkBytes + 16;    // +16: the last lane over-reads one word
+constexpr int kActPairBytes = 80;  // a block pair's 64 activation bytes + 16 pad: 16-byte reads at lane stride 80 hit distinct banks
+__host__ __device__ constexpr int stage_bytes(int rows_per_group) { return rows_per_group * kChunkBytes; }
 constexpr long long kWaitLimitCycles = 2000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -75,10 +75,14 @@ struct GemvParams {
     uint32_t *status;
 };
 
-// M activation rows (compile time).  ACT_SMEM: activations staged in shared memory.
-template <int M, bool ACT_SMEM>
-__global__ void __launch_bounds__(256, 1)
+// M activation rows, R weight rows a warp processes together (compile time).
+// ACT_SMEM: activations staged in shared memory.  Every warp of the grid owns a
+// contiguous, nearly equal range of weight rows.
+template <int M, int R, bool ACT_SMEM>
+__global__ void __launch_bounds__(R == 2 ? 512 : 256, 1)
 q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
+    constexpr int kRows = R;
+    constexpr int kStageBytes = stage_bytes(R);
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -87,40 +91,40 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
     const int cols = p.cols;
     const size_t row_bytes = (size_t)nblk * kBlockBytes;
 
-    // shared layout: [act q: M*cols][act d: M*nblk f32][per-warp: stages*kStageBytes][barriers]
+    // shared layout: [act q: M rows of (nblk/2) padded pairs][act d: M*nblk f32][per-warp: stages*kStageBytes][barriers]
+    const size_t act_row = (size_t)(nblk / 2) * kActPairBytes;
     int8_t *s_q = reinterpret_cast<int8_t *>(smem);
-    float *s_d = reinterpret_cast<float *>(smem + (ACT_SMEM ? (size_t)M * cols : 0));
-    uint8_t *ring0 = smem + (ACT_SMEM ? (size_t)M * cols + (size_t)M * nblk * 4 : 0);
+    float *s_d = reinterpret_cast<float *>(smem + (ACT_SMEM ? (size_t)M * act_row : 0));
+    uint8_t *ring0 = smem + (ACT_SMEM ? (size_t)M * act_row + (size_t)M * nblk * 4 : 0);
     uint8_t *ring = ring0 + (size_t)warp * stages * kStageBytes;
     const uint32_t bars = smem_u32(ring0 + (size_t)n_warps * stages * kStageBytes) + warp * stages * 8;
 
-    if (ACT_SMEM) {
-        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
-        int4 *sq = reinterpret_cast<int4 *>(s_q);
-        for (int i = threadIdx.x; i < M * cols / 16; i += blockDim.x) sq[i] = __ldg(gq + i);
-        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
-    }
+    // Each warp's barriers are used by that warp alone: initialise them, then start
+    // streaming weights right away.  Weights are constants, so under programmatic
+    // dependent launch this runs while the previous kernel in the stream is still
+    // draining; activations and outputs are only touched after griddepcontrol.wait.
     if (lane == 0) {
         for (int s = 0; s < stages; s++)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * s), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int cpr = (nblk + kChunkBlocks - 1) / kChunkBlocks;  // chunks per row
-    const int n_rg = (p.rows + kRows - 1) / kRows;             // row groups
     const int gw = blockIdx.x * n_warps + warp;
     const int GW = gridDim.x * n_warps;
-    const int my_rg = gw < n_rg ? (n_rg - gw + GW - 1) / GW : 0;
+    const int my_r0 = (int)((long long)p.rows * gw / GW);        // this warp's rows: [my_r0, my_r1)
+    const int my_r1 = (int)((long long)p.rows * (gw + 1) / GW);
+    const int my_rg = (my_r1 - my_r0 + kRows - 1) / kRows;       // groups of up to R rows
     const int total = my_rg * cpr;
 
     auto issue = [&](int i) {
         // lane 0 only: start the copies of iteration i into its stage
-        const int rg = gw + (i / cpr) * GW;
         const int c = i % cpr;
         const int st = i % stages;
-        const int row0 = rg * kRows;
-        const int nrow = min(kRows, p.rows - row0);
+        const int row0 = my_r0 + (i / cpr) * kRows;
+        const int nrow = min(kRows, my_r1 - row0);
         const int blocks = min(kChunkBlocks, nblk - c * kChunkBlocks);
         const uint32_t bytes = (uint32_t)blocks * kBlockBytes;
         const uint32_t bar = bars + 8 * st;
@@ -135,6 +139,19 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
 
     if (lane == 0)
         for (int i = 0; i < stages - 1 && i < total; i++) issue(i);
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (ACT_SMEM) {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        const int per_row = cols / 16;  // 16-byte pieces per activation row, 4 per block pair
+        for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
+            const int m = i / per_row, c16 = i - m * per_row;
+            *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
+                __ldg(gq + i);
+        }
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+    }
+    __syncthreads();
 
     float acc[kRows][M];
 #pragma unroll
@@ -154,10 +171,9 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
 
-        const int rg = gw + (i / cpr) * GW;
         const int c = i % cpr;
-        const int row0 = rg * kRows;
-        const int nrow = min(kRows, p.rows - row0);
+        const int row0 = my_r0 + (i / cpr) * kRows;
+        const int nrow = min(kRows, my_r1 - row0);
         const int blk0 = c * kChunkBlocks + 2 * lane;  // first block of this lane's pair
         const bool live = blk0 < nblk;                  // nblk is even
         if (live) {
@@ -189,7 +205,7 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
                 uint32_t xq[16];
                 float xd0, xd1;
                 if (ACT_SMEM) {
-                    const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * cols + (size_t)blk0 * 32);
+                    const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(blk0 >> 1) * kActPairBytes);
 #pragma unroll
                     for (int v = 0; v < 4; v++) {
                         const int4 t = a[v];
@@ -326,6 +342,67 @@ q8_0_gemv_f32_kernel(float *__restrict__ y, const float *__restrict__ x, const u
     }
 }
 
+// Launch with programmatic stream serialisation: the kernel may begin before the
+// previous kernel in the stream has finished; it orders itself with griddepcontrol.wait.
+template <typename Kern>
+cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t st, const GemvParams &p,
+                       int stages) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, p, stages);
+}
+
+// One (M, R) instantiation: fit activations + per-warp rings into the opt-in shared
+// memory (as many stages as fit, at most 4; fewer warps next; activations left in
+// global memory last) and launch one persistent CTA per SM.
+template <int M, int R>
+int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max_warps) {
+    constexpr int kStage = stage_bytes(R);
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t act = (size_t)M * (p.nblk / 2) * kActPairBytes + (size_t)M * p.nblk * 4;
+    int warps = 0, stages = 0;
+    bool act_smem = true;
+    auto fits = [&](int w, int s, bool a) {
+        return (a ? act : 0) + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit;
+    };
+    for (int w = max_warps; w >= 4 && stages == 0; w /= 2)
+        for (int s = 4; s >= 2; s--)
+            if (fits(w, s, true)) {
+                warps = w;
+                stages = s;
+                break;
+            }
+    if (stages == 0) {
+        if (R == 2) return TPB_ERR_STATE;
+        act_smem = false;
+        warps = max_warps;
+        stages = 3;
+    }
+    const size_t smem = (act_smem ? act : 0) + (size_t)warps * stages * kStage + (size_t)warps * stages * 8 + 64;
+    // at least ~2 row groups per warp before adding CTAs
+    int grid = (int)(((long long)p.rows + (long long)warps * R * 2 - 1) / ((long long)warps * R * 2));
+    if (grid < 1) grid = 1;
+    if (grid > h->sm_count) grid = h->sm_count;
+    if (act_smem) {
+        auto kern = q8_0_gemv_q8n_kernel<M, R, true>;
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TPB_CUDA(h, launch_pdl(kern, grid, warps * 32, smem, st, p, stages));
+    } else {
+        auto kern = q8_0_gemv_q8n_kernel<M, R, false>;
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TPB_CUDA(h, launch_pdl(kern, grid, warps * 32, smem, st, p, stages));
+    }
+    return TPB_OK;
+}
+
 template <int M>
 int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
     const size_t row_bytes = (size_t)p.nblk * kBlockBytes;
@@ -336,43 +413,14 @@ int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
         TPB_CUDA(h, cudaGetLastError());
         return TPB_OK;
     }
-    // Fit activations + rings into the opt-in shared memory: prefer 8 warps and
-    // as many stages as fit (at most 4); drop activations to global loads last.
-    const size_t limit = (size_t)h->smem_optin - 1024;
-    const size_t act = (size_t)M * p.cols + (size_t)M * p.nblk * 4;
-    int warps = 8, stages = 0;
-    bool act_smem = true;
-    auto fits = [&](int w, int s, bool a) {
-        return (a ? act : 0) + (size_t)w * s * kStageBytes + (size_t)w * s * 8 + 64 <= limit;
-    };
-    const int warp_opts[2] = {8, 4};
-    for (int wi = 0; wi < 2 && stages == 0; wi++)
-        for (int s = 4; s >= 2; s--)
-            if (fits(warp_opts[wi], s, true)) {
-                warps = warp_opts[wi];
-                stages = s;
-                break;
-            }
-    if (stages == 0) {
-        act_smem = false;
-        warps = 8;
-        stages = 3;
+    // Few activation rows: arithmetic per byte is light, so run 16 warps with 2 weight
+    // rows each for more loads in flight and more latency hiding; otherwise 8 warps
+    // with 4 rows each (activations are re-read from shared memory once per R rows).
+    if constexpr (M <= 2) {
+        const int rc = launch_q8n_cfg<M, 2>(h, st, p, 16);
+        if (rc != TPB_ERR_STATE) return rc;  // TPB_ERR_STATE: did not fit, try the wider grouping
     }
-    const size_t smem = (act_smem ? act : 0) + (size_t)warps * stages * kStageBytes + (size_t)warps * stages * 8 + 64;
-    const int n_rg = (p.rows + kRows - 1) / kRows;
-    int grid = (n_rg + warps - 1) / warps;
-    if (grid > h->sm_count) grid = h->sm_count;
-    if (act_smem) {
-        auto kern = q8_0_gemv_q8n_kernel<M, true>;
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, warps * 32, smem, st>>>(p, stages);
-    } else {
-        auto kern = q8_0_gemv_q8n_kernel<M, false>;
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, warps * 32, smem, st>>>(p, stages);
-    }
-    TPB_CUDA(h, cudaGetLastError());
-    return TPB_OK;
+    return launch_q8n_cfg<M, 4>(h, st, p, 8);
 }
 
 }  // namespace
