@@ -1,0 +1,300 @@
+// ConvRot int8 GEMM, two-CTA variant for sm_100a: a cluster of two CTAs (two SMs)
+// computes one 256 x 256 output tile with tcgen05.mma.cta_group::2.
+//
+// Why: with one CTA per tile every SM stages a full 256-row weight tile per K
+// block (48 KB written by TMA and read back by the tensor core per 512 MMA
+// cycles), and shared-memory traffic, not the tensor pipe, sets the pace.  In
+// the pair, each CTA stages its own 128 rows of q AND only its half (128 rows)
+// of the weight tile; the hardware feeds both tensor cores from the two halves.
+// Per SM and K block that is 32 KB instead of 48 KB.
+//
+// Roles per CTA (same warp layout in both CTAs of the pair):
+//   warp 0  TMA producer for this CTA's A rows and B half; completion is counted
+//           on the LEADER's (rank 0) "full" barrier.  No load uses multicast.
+//   warp 1  TMEM allocation (collective over the pair); in the leader it also
+//           issues every MMA and the tcgen05.commit arrivals, one to its own
+//           barrier and one to the peer's (plain commits to a cluster address,
+//           no multicast qualifier anywhere in this file).
+//   warps 2..5  epilogue for this CTA's 128 rows, as in the one-CTA kernel.
+// Every mbarrier wait is bounded; both CTAs always run the same collective
+// steps (cluster barriers, TMEM alloc/dealloc) whatever happened in between.
+#include "gemm_common.cuh"
+
+namespace {
+
+using namespace tpb_gemm;
+
+constexpr int BN2 = 256;                       // tile width (UMMA N)
+constexpr int kStageA = BM * BK;               // 16 KB: this CTA's 128 rows of q
+constexpr int kStageB = (BN2 / 2) * BK;        // 16 KB: this CTA's half of the weight tile
+constexpr int kStage2 = kStageA + kStageB;
+constexpr int kStages2 = 6;
+constexpr int kStaging2 = 4 * 2 * 4096;
+constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
+constexpr int kTmemCols2 = 2 * BN2;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// cluster-window address of `addr` (a shared::cta address) in CTA `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion bytes are counted on a barrier that may live in
+// the peer CTA of the pair (cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc2_commit(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+                 : "memory");
+}
+__device__ __forceinline__ void tc2_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// kind::i8, M = 256 across the pair, N = 256, both operands K-major
+__device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
+    uint32_t d = 0;
+    d |= 2u << 4;
+    d |= 1u << 7;
+    d |= (b_unsigned ? 0u : 1u) << 10;
+    d |= (uint32_t)(BN2 >> 3) << 17;
+    d |= (uint32_t)(256 >> 4) << 24;
+    return d;
+}
+
+// The epilogue body is shared with the one-CTA kernel in spirit; it is restated
+// here because it indexes this kernel's staging area and barriers.
+template <int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                     const __grid_constant__ CUtensorMap tma_y, const GemmParams p, const int b_unsigned) {
+    constexpr int S = kStages2;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t stg_base = smem_base + S * kStage2;
+    const uint32_t bars = stg_base + kStaging2;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * S + 2 + a); };
+    uint8_t *tail = smem_gen + S * kStage2 + kStaging2 + 8 * (2 * S + 4);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tail + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const int pair = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
+
+    const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM);  // 256-row tiles
+    const int n_tiles = (p.n + BN2 - 1) / BN2;
+    const int num_tiles = m_tiles * n_tiles;
+    const int k_blocks = p.k / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // collective over the pair: the same warp of both CTAs, same shared offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32((const void *)tmem_slot)),
+                     "r"(kTmemCols2)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
+                const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
+                const int n0 = (tile / m_tiles) * BN2 + (int)rank * (BN2 / 2);
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | (rank << 8) | s);
+                    if (!ok) break;
+                    const uint32_t lead_full = mapa(full_bar(s), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStage2);
+                    const uint32_t a_dst = smem_base + s * kStage2;
+                    tma_load_2d_pair(a_dst, &tma_a, lead_full, kb * BK, m0);
+                    tma_load_2d_pair(a_dst + kStageA, &tma_b, lead_full, kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader only) ----------------
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = make_idesc2_i8(b_unsigned != 0);
+            uint32_t it = 0, t_it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, t_it++) {
+                const int acc = t_it & 1;
+                const uint32_t acc_ph = (t_it >> 1) & 1u;
+                ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, (2u << 24) | 0x100u | acc);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN2);
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, (2u << 24) | s);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * kStage2;
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + kStageA);
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; kk++)
+                        tc2_mma_i8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    // the stage is free in BOTH CTAs once these MMAs have read it
+                    tc2_commit(empty_bar(s));
+                    tc2_commit(mapa(empty_bar(s), 1));
+                }
+                if (ok) {
+                    tc2_commit(tfull_bar(acc));
+                    tc2_commit(mapa(tfull_bar(acc), 1));
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+        const int quarter = warp & 3;
+        const uint32_t stg = stg_base + (uint32_t)(warp - 2) * 8192u;
+        const uint32_t my_row_off = (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);
+        uint32_t n_store = 0;
+        uint32_t t_it = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, t_it++) {
+            const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
+            const int n0 = (tile / m_tiles) * BN2;
+            const int acc = t_it & 1;
+            const uint32_t acc_ph = (t_it >> 1) & 1u;
+            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row0 = m0 + quarter * 32;
+            const int row = row0 + lane;
+            const bool row_ok = row < p.m;
+            float as = 0.0f;
+            int corr = 0;
+            if (OUT != OUT_S32 && row_ok) as = __ldg(p.act_scale + row);
+            if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
+            epilogue_tile<BN2, OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+    }
+
+    // ---------------- teardown (identical in both CTAs) ----------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync();  // nobody frees TMEM or leaves while the peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols2)
+                     : "memory");
+    }
+}
+
+}  // namespace
+
+// ---- host side ------------------------------------------------------------------
+
+namespace {
+
+template <int OUT>
+int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+                bool b_unsigned) {
+    CUtensorMap ma, mb, my;
+    int rc = make_kmajor_map(h, &ma, q, p.m, p.k, BM);            // each CTA loads 128 rows of q
+    if (rc != TPB_OK) return rc;
+    rc = make_kmajor_map(h, &mb, w8, p.n, p.k, BN2 / 2);          // and 128 rows (half a tile) of w
+    if (rc != TPB_OK) return rc;
+    rc = make_out_map<OUT>(h, &my, p);
+    if (rc != TPB_OK) return rc;
+    auto kern = convrot_gemm2_kernel<OUT>;
+    static bool attr_set[64] = {false};
+    if (!attr_set[h->device & 63]) {
+        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
+        attr_set[h->device & 63] = true;
+    }
+    const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
+    const int tiles = m_tiles * n_tiles;
+    const int max_pairs = h->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    kern<<<2 * pairs, kThreads, kSmem2, st>>>(ma, mb, my, p, b_unsigned ? 1 : 0);
+    TPB_CUDA(h, cudaGetLastError());
+    return TPB_OK;
+}
+
+}  // namespace
+
+// True when the two-CTA kernel should take this problem: enough 256 x 256 tiles to
+// occupy every SM pair.
+bool tpb_gemm2_wants(tpb_handle_t h, int64_t m, int64_t n) {
+    const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    return tiles >= h->sm_count / 2;
+}
+
+int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
+                     const int8_t *q, const void *w8, bool b_unsigned) {
+    switch (y_dtype) {
+        case TPB_F32: return launch_pair<OUT_F32>(h, st, p, q, w8, b_unsigned);
+        case TPB_BF16: return launch_pair<OUT_BF16>(h, st, p, q, w8, b_unsigned);
+        case TPB_S32: return launch_pair<OUT_S32>(h, st, p, q, w8, b_unsigned);
+    }
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm: unsupported y_dtype %d", y_dtype);
+}

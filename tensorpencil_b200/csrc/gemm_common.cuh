@@ -1,0 +1,318 @@
+// Device helpers shared by the tcgen05 GEMM kernels: PTX wrappers (mbarrier, TMA,
+// tcgen05), descriptor builders and the tile configuration.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "tpb_internal.h"
+
+namespace tpb_gemm {
+
+constexpr int BM = 128;            // rows of q per tile (= UMMA M)
+constexpr int BK = 128;            // int8 elements (= bytes) of K per stage: one 128B swizzle row
+constexpr int UMMA_K = 32;         // K of one tcgen05.mma.kind::i8
+constexpr int kThreads = 192;      // 6 warps
+constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
+
+enum OutKind { OUT_F32 = 0, OUT_BF16 = 1, OUT_S32 = 2 };
+
+template <int BN>
+struct TileCfg {
+    static constexpr int kStageBytesA = BM * BK;
+    static constexpr int kStageBytesB = BN * BK;
+    static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
+    // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes)
+    static constexpr int kStagingBytes = 4 * 2 * 4096;
+    // tiles + staging + barriers (full/empty per stage, full/empty per accumulator)
+    // + TMEM base slot + abort flag, plus 1 KB slack to align the tiles to 1024 bytes.
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
+struct GemmParams {
+    void *y;
+    long long ldy;
+    const float *act_scale;
+    const float *w_scale;
+    const int32_t *act_sum;  // non-null: subtract 8 * act_sum[row] (unsigned-nibble weights)
+    int m, n, k;
+    uint32_t *status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out or another role already
+// gave up; the caller then leaves its loop.  `code` identifies the waiter.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                            uint32_t *status, uint32_t code) {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicCAS(status, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint32_t *status, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets row (lane
+// base + t), registers 0..31 = columns col..col+31.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, but naming the destination registers of the load as in/out operands
+// so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                   "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                   "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]),
+                   "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
+                   "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// TMA store of one staged box (shared -> global); rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle
+// layout TMA writes: rows of 128 bytes, 8-row groups 1024 bytes apart.
+//   bits  0-13 start address >> 4     bits 16-29 leading byte offset >> 4 (unused here)
+//   bits 32-45 stride byte offset >> 4 (1024)   bits 46-47 descriptor version (1)
+//   bits 61-63 layout (2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::i8: int32 accumulate, A signed int8, B signed or
+// unsigned int8, both K-major, N at bits 17-22 (N/8), M at bits 24-28 (M/16).
+template <int BN>
+__device__ __forceinline__ uint32_t make_idesc_i8(bool b_unsigned) {
+    uint32_t d = 0;
+    d |= 2u << 4;                       // accumulator format S32
+    d |= 1u << 7;                       // A: signed 8-bit
+    d |= (b_unsigned ? 0u : 1u) << 10;  // B: signed / unsigned 8-bit
+    d |= (uint32_t)(BN >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+// Epilogue of one 128 x BN tile for one warp (32 accumulator rows starting at
+// TMEM address t_row): load 32 columns at a time (the next load in flight while
+// the current columns are processed), dequantise, stage 32 rows x 128 bytes in the
+// warp's swizzled staging buffer and hand each full piece to a TMA store.
+template <int BN, int OUT>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
+                                              uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
+                                              int row0, int n0, float as, int corr, int lane) {
+    uint32_t ra[32], rb[32];
+    tc_ld_32x32(t_row, ra);
+#pragma unroll
+    for (int c = 0; c < BN / 32; c++) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        tc_wait_ld_dep(cur);  // columns 32c.. are in `cur`
+        if (c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), nxt);
+        const int col0 = n0 + c * 32;
+        // first piece of a 128-byte staging row: make sure the TMA store that last
+        // read this buffer (two stores ago) is done with it
+        const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
+        const uint32_t buf = stg + (n_store & 1u) * 4096u + my_row_off;
+        // Warp-uniform: does this 128-byte-wide piece reach into the tensor at all?
+        // Skipped pieces touch neither the staging buffers nor the buffer counter,
+        // so "all but the latest store have finished reading" keeps meaning "the
+        // other buffer's store".
+        const int scol = (OUT == OUT_BF16 && (c & 1)) ? col0 - 32 : col0;
+        const bool do_store = row0 < p.m && scol < p.n;
+        if (!do_store) continue;
+        if (first_piece) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+        }
+        if (OUT == OUT_S32) {
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+                st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), cur[4 * g] - corr, cur[4 * g + 1] - corr,
+                             cur[4 * g + 2] - corr, cur[4 * g + 3] - corr);
+        } else if (OUT == OUT_F32) {
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+                float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (col0 + 4 * g < p.n) ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g] - corr), as), ws.x);
+                const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 1] - corr), as), ws.y);
+                const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
+                const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 3] - corr), as), ws.w);
+                st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), __float_as_uint(v0), __float_as_uint(v1),
+                             __float_as_uint(v2), __float_as_uint(v3));
+            }
+        } else {
+            // bf16: 64 columns make one 128-byte row; this chunk fills pieces 4*(c&1) .. +3
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+                if (col0 + 8 * g < p.n) {
+                    w0 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g));
+                    w1 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g + 4));
+                }
+                const float wsv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float lo = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[8 * g + 2 * e] - corr), as), wsv[2 * e]);
+                    const float hi = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[8 * g + 2 * e + 1] - corr), as), wsv[2 * e + 1]);
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                    pk[e] = *reinterpret_cast<const uint32_t *>(&b2);
+                }
+                const uint32_t piece = (uint32_t)(4 * (c & 1) + g);
+                st_shared_v4(buf + ((piece ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+        const bool last_piece = OUT != OUT_BF16 || (c & 1) == 1;
+        if (last_piece) {
+            // generic-proxy writes -> visible to the async proxy, then one lane stores
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            n_store++;
+        }
+    }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D uint8 tensor [rows][k] (k contiguous), box = 128 bytes x box_rows, 128B swizzle,
+// out-of-range rows read as zero.
+inline int make_kmajor_map(tpb_handle_t h, CUtensorMap *map, const void *base, int64_t rows, int64_t k,
+                    int box_rows) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)k};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld", (int)r,
+                        (long long)rows, (long long)k);
+    return TPB_OK;
+}
+
+// Output tensor [m][ldy] (row-major), box = 128 bytes x 32 rows, 128B swizzle: the
+// epilogue's staging layout.
+template <int OUT>
+inline int make_out_map(tpb_handle_t h, CUtensorMap *map, const GemmParams &p) {
+    const int esz = OUT == OUT_BF16 ? 2 : 4;
+    const CUtensorMapDataType dt = OUT == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : OUT == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                    : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    const cuuint64_t gdim[2] = {(cuuint64_t)p.n, (cuuint64_t)p.m};
+    const cuuint64_t gstride[1] = {(cuuint64_t)p.ldy * esz};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+        map, dt, 2, p.y, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) m=%d n=%d ldy=%lld", (int)r,
+                        p.m, p.n, p.ldy);
+    return TPB_OK;
+}
+
+}  // namespace tpb_gemm
