@@ -33,60 +33,6 @@ constexpr int kStaging2 = 4 * 2 * 4096;
 constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
 constexpr int kTmemCols2 = 2 * BN2;
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// cluster-window address of `addr` (a shared::cta address) in CTA `rank`
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// TMA tile load whose completion bytes are counted on a barrier that may live in
-// the peer CTA of the pair (cluster address).  No multicast.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster,
-                                                 int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-        "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tc2_commit(uint32_t bar_cluster) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
-                 : "memory");
-}
-__device__ __forceinline__ void tc2_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// kind::i8, M = 256 across the pair, N = 256, both operands K-major
-__device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
-    uint32_t d = 0;
-    d |= 2u << 4;
-    d |= 1u << 7;
-    d |= (b_unsigned ? 0u : 1u) << 10;
-    d |= (uint32_t)(BN2 >> 3) << 17;
-    d |= (uint32_t)(256 >> 4) << 24;
-    return d;
-}
-
-// The epilogue body is shared with the one-CTA kernel in spirit; it is restated
-// here because it indexes this kernel's staging area and barriers.
 template <int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -153,7 +99,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
-                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | (rank << 8) | s);
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | (rank << 8) | s, true);
                     if (!ok) break;
                     const uint32_t lead_full = mapa(full_bar(s), 0);
                     if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStage2);
@@ -212,7 +158,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             const int n0 = (tile / m_tiles) * BN2;
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
-            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc);
+            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc, true);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();

@@ -72,11 +72,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the limit ran out or another role already
 // gave up; the caller then leaves its loop.  `code` identifies the waiter.
+// `relaxed` waiters (roles with slack: epilogue, TMA producer) sleep between polls so
+// they do not take issue slots from the warps doing the work; latency-critical waiters
+// (MMA issue, unpack) poll flat out.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                            uint32_t *status, uint32_t code) {
+                                            uint32_t *status, uint32_t code, bool relaxed) {
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (relaxed) __nanosleep(it < 8 ? 32 : 128);
         if ((it & 63u) == 63u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
@@ -88,9 +92,9 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          uint32_t *status, uint32_t code) {
+                                          uint32_t *status, uint32_t code, bool relaxed = false) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+    return mbar_wait_slow(bar, parity, abort_flag, status, code, relaxed);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
@@ -181,6 +185,60 @@ __device__ __forceinline__ uint32_t make_idesc_i8(bool b_unsigned) {
     d |= (b_unsigned ? 0u : 1u) << 10;  // B: signed / unsigned 8-bit
     d |= (uint32_t)(BN >> 3) << 17;
     d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+// ---- CTA-pair (cta_group::2) helpers ------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// cluster-window address of `addr` (a shared::cta address) in CTA `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion bytes are counted on a barrier that may live in
+// the peer CTA of the pair (cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc2_commit(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+                 : "memory");
+}
+__device__ __forceinline__ void tc2_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// kind::i8, M = 256 across the pair, N = 256, both operands K-major
+__device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
+    uint32_t d = 0;
+    d |= 2u << 4;
+    d |= 1u << 7;
+    d |= (b_unsigned ? 0u : 1u) << 10;
+    d |= (uint32_t)(256 >> 3) << 17;
+    d |= (uint32_t)(256 >> 4) << 24;
     return d;
 }
 

@@ -25,6 +25,8 @@
 bool tpb_gemm2_wants(tpb_handle_t h, int64_t m, int64_t n);
 int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
                      const int8_t *q, const void *w8, bool b_unsigned);
+int tpb_launch_gemm_w4(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
+                        const int8_t *q, const void *w4);
 
 namespace {
 
@@ -98,7 +100,7 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
-                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | s);
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | s, true);
                     if (!ok) break;
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
@@ -156,7 +158,7 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int n0 = (tile / m_tiles) * BN;
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
-            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | acc);
+            ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | acc, true);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -260,6 +262,15 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     p.k = (int)k;
     p.status = h->d_status;
     const void *w8 = w;
+    const char *one_cta_env = getenv("TPB_GEMM_ONE_CTA");
+    const bool one_cta_only = one_cta_env != nullptr && one_cta_env[0] == '1';
+    const char *fused_env = getenv("TPB_W4_FUSED");
+    if (w_bits == 4 && fused_env != nullptr && fused_env[0] == '1' &&
+        ((m + 127) / 128) * ((n + 255) / 256) >= h->sm_count) {
+        // opt-in: the packed weight is unpacked inside the GEMM (one-CTA kernel)
+        p.act_sum = act_sum;
+        return tpb_launch_gemm_w4(h, st, p, y_dtype, q, w);
+    }
     if (w_bits == 4) {
         W4Scratch &s = g_w4_scratch[h->device & 63];
         const size_t need = (size_t)n * (size_t)k;
@@ -276,8 +287,6 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     }
     // Large problems: two-CTA tiles (256 x 256 per SM pair).  TPB_GEMM_ONE_CTA=1 keeps
     // the one-CTA kernel for comparisons.
-    const char *one_cta_env = getenv("TPB_GEMM_ONE_CTA");
-    const bool one_cta_only = one_cta_env != nullptr && one_cta_env[0] == '1';
     if (!one_cta_only && tpb_gemm2_wants(h, m, n)) return tpb_launch_gemm2(h, st, p, y_dtype, q, w8, false);
     switch (y_dtype) {
         case TPB_F32: return launch_out<OUT_F32>(h, st, p, q, w8, false);

@@ -254,6 +254,31 @@ def test_config1_full_size_sampled(be):
     assert torch.equal(y2, y * 2.0)
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 4864, 1024), (1100, 5136, 512)])
+def test_int4_fused_unpack_kernel(be, monkeypatch, m, n, k):
+    """The opt-in kernel that unpacks the packed weight in shared memory inside the
+    GEMM (TPB_W4_FUSED=1) gives the same accumulators and outputs as the default
+    route (expand to int8, then the int8 kernel) and as the replica."""
+    c = synth.convrot_linear(m, n, k, 4, seed=m + n)
+    x = dev(c["x"])
+    wp, wsc = dev(c["w_packed"]), dev(c["w_scale"])
+    monkeypatch.delenv("TPB_W4_FUSED", raising=False)
+    acc_default = be.convrot_linear(x, wp, wsc, n, 4, torch.int32).clone()
+    y_default = be.convrot_linear(x, wp, wsc, n, 4, torch.float32).clone()
+    monkeypatch.setenv("TPB_W4_FUSED", "1")
+    for _ in range(3):
+        acc_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.int32)
+        y_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.float32)
+        yb_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.bfloat16)
+        be.status_poll()
+        assert torch.equal(acc_fused, acc_default)
+        assert torch.equal(y_fused, y_default)
+        assert torch.equal(yb_fused, y_default.to(torch.bfloat16))
+    rows = np.sort(np.random.default_rng(1).choice(m, 48, replace=False))
+    q_ref, s_ref = oracle.convrot_prep(c["x"][rows], 4)
+    assert np.array_equal(acc_fused.cpu().numpy()[rows], oracle.igemm_s32(q_ref, c["w_i8"]))
+
+
 def test_w4_expand_matches_nibble_decode(be):
     rng = np.random.default_rng(4)
     w = rng.integers(-8, 8, size=(48, 512), dtype=np.int8)
