@@ -87,6 +87,9 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     cluster_sync();  // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up above overlaps the previous kernel's tail; global memory only after this
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -221,8 +224,7 @@ int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    kern<<<2 * pairs, kThreads, kSmem2, st>>>(ma, mb, my, p, b_unsigned ? 1 : 0);
-    TPB_CUDA(h, cudaGetLastError());
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, my, p, b_unsigned ? 1 : 0));
     return TPB_OK;
 }
 

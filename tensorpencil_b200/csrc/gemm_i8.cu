@@ -88,6 +88,9 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up above overlaps the previous kernel's tail; global memory only after this
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -222,8 +225,7 @@ int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
     const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
     const int tiles = m_tiles * n_tiles;
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
-    kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(ma, mb, my, p, b_unsigned ? 1 : 0);
-    TPB_CUDA(h, cudaGetLastError());
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, ma, mb, my, p, b_unsigned ? 1 : 0));
     return TPB_OK;
 }
 

@@ -131,6 +131,9 @@ convrot_gemm_w4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up above overlaps the previous kernel's tail; global memory only after this
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -321,8 +324,7 @@ int launch_w4(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t
     }
     const int tiles = ((p.m + BM - 1) / BM) * ((p.n + 255) / 256);
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
-    kern<<<grid, kThreadsW4, kSmemW4, st>>>(ma, mb, my, p);
-    TPB_CUDA(h, cudaGetLastError());
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(kThreadsW4), kSmemW4, st, ma, mb, my, p));
     return TPB_OK;
 }
 

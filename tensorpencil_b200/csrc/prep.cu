@@ -127,6 +127,8 @@ convrot_prep_kernel(const T *__restrict__ x, int8_t *__restrict__ q, float *__re
     const int hw = lane >> 4;
     const int l16 = lane & 15;
     const T *xrow = x + (size_t)row * k;
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
 
     float v[PPW][4][4];
     float amax = 0.0f;
@@ -222,6 +224,8 @@ convrot_prep_kernel(const T *__restrict__ x, int8_t *__restrict__ q, float *__re
 // int4 -> int8 expansion of a packed weight: 16 packed bytes in, 32 bytes out.
 __global__ void __launch_bounds__(256)
 w4_expand_kernel(const uint4 *__restrict__ w4, uint4 *__restrict__ w8, size_t n_chunks) {
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks;
          c += (size_t)gridDim.x * blockDim.x) {
         const uint4 p = __ldg(w4 + c);
@@ -260,9 +264,10 @@ int launch_prep_t(tpb_handle_t h, cudaStream_t st, const T *x, int64_t m, int64_
     const int warps = (n_pairs + ppw_inst - 1) / ppw_inst;
     const dim3 grid((unsigned)m), block(warps * 32);
     const float maxq = bits == 4 ? 7.0f : 127.0f;
+    cudaError_t err = cudaSuccess;
 #define TPB_PREP_CASE(P)                                                                          \
     case P:                                                                                       \
-        convrot_prep_kernel<T, P><<<grid, block, 0, st>>>(x, q, act_scale, act_sum, (int)k, n_groups, maxq); \
+        err = tpb_launch_pdl(convrot_prep_kernel<T, P>, grid, block, 0, st, x, q, act_scale, act_sum, (int)k, n_groups, maxq); \
         break;
     switch (ppw_inst) {
         TPB_PREP_CASE(1)
@@ -273,7 +278,7 @@ int launch_prep_t(tpb_handle_t h, cudaStream_t st, const T *x, int64_t m, int64_
         TPB_PREP_CASE(8)
     }
 #undef TPB_PREP_CASE
-    TPB_CUDA(h, cudaGetLastError());
+    TPB_CUDA(h, err);
     return TPB_OK;
 }
 
@@ -300,7 +305,6 @@ int tpb_launch_w4_expand(tpb_handle_t h, cudaStream_t st, const void *w4, int64_
     size_t want = (n_chunks + block - 1) / block;
     const size_t cap = (size_t)h->sm_count * 16;
     const unsigned grid = (unsigned)(want < cap ? want : cap);
-    w4_expand_kernel<<<grid, block, 0, st>>>((const uint4 *)w4, (uint4 *)w8, n_chunks);
-    TPB_CUDA(h, cudaGetLastError());
+    TPB_CUDA(h, tpb_launch_pdl(w4_expand_kernel, dim3(grid), dim3(block), 0, st, (const uint4 *)w4, (uint4 *)w8, n_chunks));
     return TPB_OK;
 }

@@ -39,6 +39,31 @@ int tpb_fail(tpb_handle_t h, int code, const char *fmt, ...);
                             "%s failed: %s", #expr, cudaGetErrorString(e__));      \
     } while (0)
 
+// Launch with programmatic stream serialisation: the grid may start while the previous
+// kernel in the stream is still draining.  Every kernel launched this way executes
+// griddepcontrol.wait before it reads or writes global memory, which also keeps the
+// ordering transitive along the stream.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t tpb_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void tpb_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void tpb_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 static inline bool tpb_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Kernel launchers (one per .cu file).  All return a tpb_status.

@@ -1,0 +1,132 @@
+"""Drivers that replay the reference's call sequences over the quantized-linear
+ops: one DiT step's linears (resident or weight-streamed), the N-split GEMM with
+all-gather, and the decode GEMV.  Used by ``bench.py --mode ...`` and the tests.
+
+The DiT driver follows ``dit_cuda.forward`` (src/models/dit_cuda.zig:464-517): per
+block one prep feeds wq/wk/wv/gate, one prep feeds wo, and the MLP runs in
+2048-row tiles (``mlp_tile``, :36-39): prep -> gate, up -> (SiLU * up) -> prep ->
+down.  Only the linears go through this library; attention, norms, RoPE and the
+gated adds belong to the reference's non-quantised ops and are stood in for by
+the cheapest torch expression that keeps shapes and data flow (the step time
+reported is therefore a linears-only figure).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from . import synth
+from .offload import Streamer, packed_size
+
+MLP_TILE = 2048  # src/models/dit_cuda.zig:39
+
+
+class DitWeights:
+    """Random-init quantised weights of the synthetic DiT, on the device
+    (resident) or as per-block pinned host images behind a Streamer."""
+
+    def __init__(self, be, bits: int, blocks: int = synth.DIT_BLOCKS, hidden: int = synth.DIT_HIDDEN,
+                 mlp: int = synth.DIT_MLP, seed: int = 1003, stream_budget: Optional[int] = None,
+                 distinct_blocks: Optional[int] = None):
+        self.be, self.bits, self.blocks, self.hidden, self.mlp = be, bits, blocks, hidden, mlp
+        self.names = [n for n, _, _ in synth.DIT_LINEARS]
+        # Generating 28 distinct blocks of random weights on the host takes a while and
+        # says nothing more about speed than a few: blocks cycle through `distinct` sets.
+        distinct = blocks if distinct_blocks is None else min(blocks, distinct_blocks)
+        host = [synth.dit_block_weights(b, bits, seed, hidden, mlp) for b in range(distinct)]
+        self.shapes = {n: (host[0][n]["n"], host[0][n]["k"]) for n in self.names}
+        self.streamer: Optional[Streamer] = None
+        if stream_budget is None:
+            self.dev: List[Dict[str, tuple]] = []
+            for b in range(blocks):
+                hb = host[b % distinct]
+                self.dev.append({n: (torch.from_numpy(hb[n]["w"]).to(be.device),
+                                     torch.from_numpy(hb[n]["w_scale"]).to(be.device)) for n in self.names})
+        else:
+            arrays0 = [a for n in self.names for a in (host[0][n]["w"], host[0][n]["w_scale"])]
+            slot = packed_size(arrays0)
+            n_slots = max(2, min(4, stream_budget // slot))
+            if n_slots * slot > stream_budget:
+                raise ValueError(f"budget {stream_budget} cannot hold two blocks of {slot} bytes")
+            self.streamer = Streamer(be, stream_budget, slot, n_slots)
+            for b in range(blocks):
+                hb = host[b % distinct]
+                self.streamer.register(b, [a for n in self.names for a in (hb[n]["w"], hb[n]["w_scale"])])
+            self.block_bytes = slot
+
+    def close(self):
+        if self.streamer is not None:
+            self.streamer.close()
+
+
+def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """One step of the block stack's linears on latents x [tokens][hidden] (f32)."""
+    bits, hid, mlp = w.bits, w.hidden, w.mlp
+    prep = be.opI8Prep if bits == 8 else be.opI4Prep
+    gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
+           (lambda y, wt, n: be.opI4Gemm(y, wt[0], wt[1], n))
+    m = x.shape[0]
+    dev = be.device
+    q = torch.empty((m, hid), dtype=out_dtype, device=dev)
+    k = torch.empty_like(q)
+    v = torch.empty_like(q)
+    g = torch.empty_like(q)
+    o = torch.empty_like(q)
+    tile_gate = torch.empty((MLP_TILE, mlp), dtype=out_dtype, device=dev)
+    tile_up = torch.empty_like(tile_gate)
+    tile_down = torch.empty((MLP_TILE, hid), dtype=out_dtype, device=dev)
+    st = w.streamer
+    if st is not None:
+        st.prefetch(0)
+    for b in range(w.blocks):
+        if st is not None:
+            views = st.acquire(b)
+            wb = {n: (views[2 * i], views[2 * i + 1]) for i, n in enumerate(w.names)}
+            if b + 1 < w.blocks:
+                st.prefetch(b + 1)          # prefetchBlock(b+1), dit_cuda.zig:470
+        else:
+            wb = w.dev[b]
+        prep(x, m, hid)                     # one prep, four GEMMs (dit_cuda.zig:474-478)
+        gemm(q, wb["wq"], hid)
+        gemm(k, wb["wk"], hid)
+        gemm(v, wb["wv"], hid)
+        gemm(g, wb["gate"], hid)
+        attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)  # stand-in
+        prep(attn, m, hid)
+        gemm(o, wb["wo"], hid)
+        x = x + o.float() if out_dtype != torch.float32 else x + o
+        for t0 in range(0, m, MLP_TILE):    # dit_cuda.zig:495-516
+            rows = min(MLP_TILE, m - t0)
+            xt = x[t0:t0 + rows]
+            prep(xt, rows, hid)
+            gemm(tile_gate, wb["mlp_gate"], mlp)
+            gemm(tile_up, wb["mlp_up"], mlp)
+            act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float()
+            prep(act, rows, mlp)
+            gemm(tile_down, wb["mlp_down"], hid)
+            x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3
+        if st is not None:
+            st.release(b)
+    return x
+
+
+def dit_linear_ops(tokens: int, blocks: int, hidden: int, mlp: int) -> float:
+    """2*M*N*K summed over the eight linears of every block."""
+    per_block = 5 * 2.0 * tokens * hidden * hidden + 3 * 2.0 * tokens * mlp * hidden
+    return per_block * blocks
+
+
+def rotating_q8_weights(n: int, k: int, copies: int, device) -> List[torch.Tensor]:
+    """`copies` distinct Q8_0 weight buffers with sane f16 scales, generated on the
+    device (the GEMV benchmark cycles through them so every launch streams from HBM)."""
+    nb = k // 32
+    out = []
+    for i in range(copies):
+        g = torch.Generator(device=device).manual_seed(1002 + i)
+        w = torch.randint(0, 256, (n, nb, 34), dtype=torch.uint8, device=device, generator=g)
+        w[:, :, 0] = 0x66
+        w[:, :, 1] = 0x1e  # f16 0x1e66 ~ 6.2e-3
+        out.append(w.reshape(n, nb * 34))
+    return out
