@@ -19,6 +19,8 @@
 // warp, and y = acc * scale.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "tpb_internal.h"
 
 namespace {
@@ -373,13 +375,29 @@ int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max
     auto fits = [&](int w, int s, bool a) {
         return (a ? act : 0) + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit;
     };
-    for (int w = max_warps; w >= 4 && stages == 0; w /= 2)
+    // Warps per CTA: every warp owns a contiguous range of whole rows, so the slowest warp
+    // carries ceil(rows / warps_total) rows.  Among the counts that fit (with >= 2 stages and
+    // the activations in shared memory) take the one with the best balance; ties go to more
+    // warps.  E.g. 5120 rows on 148 SMs: 16 warps -> 2.16 rows per warp (3 vs 2, 72 %),
+    // 12 warps -> 2.88 (96 %).
+    const int min_warps = max_warps / 2;
+    double best_eff = -1.0;
+    for (int w = max_warps; w >= min_warps; w--) {
+        int s_fit = 0;
         for (int s = 4; s >= 2; s--)
             if (fits(w, s, true)) {
-                warps = w;
-                stages = s;
+                s_fit = s;
                 break;
             }
+        if (s_fit == 0) continue;
+        const double per_warp = (double)p.rows / ((double)h->sm_count * w);
+        const double eff = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : per_warp;
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            warps = w;
+            stages = s_fit;
+        }
+    }
     if (stages == 0) {
         if (R == 2) return TPB_ERR_STATE;
         act_smem = false;
@@ -413,10 +431,10 @@ int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
         TPB_CUDA(h, cudaGetLastError());
         return TPB_OK;
     }
-    // Few activation rows: arithmetic per byte is light, so run 16 warps with 2 weight
-    // rows each for more loads in flight and more latency hiding; otherwise 8 warps
-    // with 4 rows each (activations are re-read from shared memory once per R rows).
-    if constexpr (M <= 2) {
+    // Preferred: up to 16 warps with 2 weight rows each (more loads in flight, more latency
+    // hiding).  When the activations leave too little shared memory for that, 8 warps with
+    // 4 rows each (activations are re-read from shared memory once per R rows).
+    {
         const int rc = launch_q8n_cfg<M, 2>(h, st, p, 16);
         if (rc != TPB_ERR_STATE) return rc;  // TPB_ERR_STATE: did not fit, try the wider grouping
     }

@@ -35,16 +35,19 @@ class DitWeights:
         # Generating 28 distinct blocks of random weights on the host takes a while and
         # says nothing more about speed than a few: blocks cycle through `distinct` sets.
         distinct = blocks if distinct_blocks is None else min(blocks, distinct_blocks)
-        host = [synth.dit_block_weights(b, bits, seed, hidden, mlp) for b in range(distinct)]
+        host = [self._random_block(b, seed) for b in range(distinct)]
         self.shapes = {n: (host[0][n]["n"], host[0][n]["k"]) for n in self.names}
         self.streamer: Optional[Streamer] = None
         if stream_budget is None:
             self.dev: List[Dict[str, tuple]] = []
             for b in range(blocks):
                 hb = host[b % distinct]
-                self.dev.append({n: (torch.from_numpy(hb[n]["w"]).to(be.device),
-                                     torch.from_numpy(hb[n]["w_scale"]).to(be.device)) for n in self.names})
+                # every block owns its own device copy, so a step reads 28 blocks' worth of weights
+                self.dev.append({n: (hb[n]["w"].clone() if b >= distinct else hb[n]["w"],
+                                     hb[n]["w_scale"]) for n in self.names})
         else:
+            host = [{n: {"w": hb[n]["w"].cpu().numpy(), "w_scale": hb[n]["w_scale"].cpu().numpy()} for n in self.names}
+                    for hb in host]
             arrays0 = [a for n in self.names for a in (host[0][n]["w"], host[0][n]["w_scale"])]
             slot = packed_size(arrays0)
             n_slots = max(2, min(4, stream_budget // slot))
@@ -55,6 +58,23 @@ class DitWeights:
                 hb = host[b % distinct]
                 self.streamer.register(b, [a for n in self.names for a in (hb[n]["w"], hb[n]["w_scale"])])
             self.block_bytes = slot
+
+    def _random_block(self, b: int, seed: int) -> Dict[str, dict]:
+        """Random-init weights of one block, drawn on the device (same value ranges as
+        synth.dit_block_weights: int8 in [-127,127] or packed int4 nibbles, scales
+        ~U(1e-3,1e-2))."""
+        out = {}
+        g = torch.Generator(device=self.be.device).manual_seed(seed + 1000 * b)
+        for name, n, k in synth.DIT_LINEARS:
+            n = self.mlp if n == synth.DIT_MLP else self.hidden
+            k = self.mlp if k == synth.DIT_MLP else self.hidden
+            if self.bits == 8:
+                wt = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=self.be.device, generator=g)
+            else:
+                wt = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=self.be.device, generator=g)
+            ws = torch.rand(n, device=self.be.device, generator=g) * 9e-3 + 1e-3
+            out[name] = {"w": wt, "w_scale": ws, "n": n, "k": k}
+        return out
 
     def close(self):
         if self.streamer is not None:
