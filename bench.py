@@ -359,9 +359,14 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
     def step(i):
         harness.dit_step_linears(be, w, latents[i % 2].clone())
 
+    def step_kernels_only(i):  # this library's kernels alone, whole batch per MLP pass
+        harness.dit_step_linears(be, w, latents[i % 2], mlp_tile=synth.DIT_TOKENS, glue=False)
+
     for i in range(max(args.warmup, 3)):
         step(i)
+        step_kernels_only(i)
     steps = max(1, min(args.steps, 20))
+    ms_kernels = _events_ms(step_kernels_only, steps, sync)
     copied0 = w.streamer.bytes_copied() if w.streamer else 0
     ms = _events_ms(step, steps, sync)
     be.status_poll()
@@ -375,6 +380,8 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
         line = {"metric": "dit_linears_s_per_step", "value": s_per_step, "unit": "s/step", "n_gpus": world,
                 "steps": steps, "higher_is_better": False, "scaling": "weak", "dtype": "s8", "data": "synthetic",
                 "tops": ops / s_per_step / 1e12,
+                "kernels_only": {"s_per_step": ms_kernels / steps / 1e3, "tops": ops / (ms_kernels / steps / 1e3) / 1e12,
+                                 "note": "prep + GEMM launches only, one MLP pass over all tokens (no 2048-row tiling)"},
                 "config": {"workload": ("config4: INT4 DiT step, weights streamed from pinned host memory, 2 GiB budget"
                                         if streamed else "config3: INT8 DiT step, weights resident"),
                            "blocks": synth.DIT_BLOCKS, "hidden": synth.DIT_HIDDEN, "mlp": synth.DIT_MLP,
@@ -439,21 +446,49 @@ def run_mode_nsplit(args, rank, local, world):
     shard = torch.empty((M, hi - lo), dtype=out_dtype, device="cuda")
     flat = gathered.view(world * M, hi - lo) if chunks == 1 else torch.empty((world * M, hi - lo), dtype=out_dtype, device="cuda")
     ms_gather = _events_ms(lambda i: dist.all_gather_into_tensor(flat, shard), steps, sync)
-    t = torch.tensor([ms_total, ms_compute, ms_gather], device="cuda", dtype=torch.float64)
+    # the same split with the exchange done by the GEMM epilogue itself (peer stores over
+    # NVLink, row-major result on every rank); one device-side barrier per step
+    from tensorpencil_b200.peer import PeerBuffers
+    esz = 4 if args.out_dtype == "f32" else 2
+    pb = PeerBuffers(be, M * N * esz)
+
+    def fused(i):
+        pb.gemm_allgather(w_shard, ws_shard, hi - lo, 8, y_dtype=out_dtype)
+        pb.barrier()
+
+    pb.barrier()
+    for i in range(3):
+        fused(i)
+    sync()
+    same_fused = bool(torch.equal(pb.tensor((M, N), out_dtype), y_full))
+    ms_fused = _events_ms(fused, steps, sync)
+    be.status_poll()
+    t = torch.tensor([ms_total, ms_compute, ms_gather, ms_fused], device="cuda", dtype=torch.float64)
+    flags = torch.tensor([int(same), int(same_fused)], device="cuda")
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    same, same_fused = bool(flags[0]), bool(flags[1])
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
-        esz = 4 if args.out_dtype == "f32" else 2
         recv = (world - 1) / world * M * N * esz
-        line = {"metric": "nsplit_gemm_allgather_tops", "value": OPS_PER_STEP * steps / (float(t[0]) * 1e-3) / 1e12,
+        line = {"metric": "nsplit_gemm_allgather_tops", "value": OPS_PER_STEP * steps / (float(t[3]) * 1e-3) / 1e12,
                 "unit": "TOPS", "n_gpus": world, "steps": steps, "higher_is_better": True, "scaling": "strong",
-                "dtype": "s8", "data": "synthetic", "bit_identical_to_single_gpu": same,
-                "ms_total": float(t[0]) / steps, "ms_compute_only": float(t[1]) / steps,
-                "ms_allgather_only": float(t[2]) / steps,
-                "allgather_recv_gbs_per_gpu": recv / (float(t[2]) / steps * 1e-3) / 1e9,
-                "config": {"workload": "config4: INT8 GEMM 4608x12288x3072 split along N, NCCL all-gather of the output",
-                           "chunks": chunks, "out_dtype": args.out_dtype,
-                           "layout": "gathered[chunk][rank][M][N/world/chunks] (column-blocked)"}}
+                "dtype": "s8", "data": "synthetic", "bit_identical_to_single_gpu": same_fused,
+                "ms_per_step": float(t[3]) / steps,
+                "fused": {"ms": float(t[3]) / steps, "what": "one GEMM launch whose epilogue stores each tile into "
+                          "every rank's row-major y over NVLink, then one device-side barrier",
+                          "nvlink_send_gbs_per_gpu": recv / (float(t[3]) / steps * 1e-3) / 1e9,
+                          "bit_identical_to_single_gpu": same_fused},
+                "nccl": {"ms_total": float(t[0]) / steps, "ms_compute_only": float(t[1]) / steps,
+                         "ms_allgather_only": float(t[2]) / steps, "chunks": chunks,
+                         "tops": OPS_PER_STEP * steps / (float(t[0]) * 1e-3) / 1e12,
+                         "allgather_recv_gbs_per_gpu": recv / (float(t[2]) / steps * 1e-3) / 1e9,
+                         "bit_identical_to_single_gpu": same,
+                         "layout": "gathered[chunk][rank][M][N/world/chunks] (column-blocked)"},
+                "config": {"workload": "config4: INT8 GEMM 4608x12288x3072 split along N across the GPUs, output "
+                                       "all-gathered (fused into the epilogue; NCCL version beside it)",
+                           "out_dtype": args.out_dtype}}
         print(json.dumps(line), flush=True)
+    pb.close()
     dist.barrier()
     dist.destroy_process_group()
     be.close()

@@ -200,6 +200,40 @@ uint64_t tpb_stream_bytes_copied(tpb_streamer_t s);
 int tpb_host_alloc(tpb_handle_t h, size_t bytes, void **out);
 int tpb_host_free(tpb_handle_t h, void *p);
 
+/* ---- One GEMM split along N over the GPUs of a node, all-gather fused in ------------
+ *
+ * No reference counterpart: the reference drives one GPU (src/gpu/cuda/context.zig:111).
+ * One process per GPU.  Rank r holds rows [r*n_shard, (r+1)*n_shard) of the weight and
+ * of w_scale and the whole quantised activations; every rank owns a full row-major
+ * y[m][ldy] in a peer-mapped buffer.  The GEMM's epilogue writes each output tile into
+ * its columns [rank*n_shard, ...) of EVERY rank's y (local copy through TMA, peers with
+ * 16-byte NVLink stores), so the exchange overlaps the tensor-core work tile by tile
+ * and the result lands row-major, bit-identical to the single-GPU GEMM.  A y is complete
+ * on rank r once every rank's launch has finished: run tpb_peer_barrier on the same
+ * stream before reading it, and again before the next launch overwrites it. */
+
+#define TPB_PEER_HANDLE_BYTES 64
+
+/* cudaMalloc + zero fill on the handle's device; ipc_handle receives TPB_PEER_HANDLE_BYTES
+ * opaque bytes to hand to the other processes. */
+int tpb_peer_alloc(tpb_handle_t h, size_t bytes, void **ptr, void *ipc_handle);
+/* Maps another process's buffer (enables peer access on first use). */
+int tpb_peer_open(tpb_handle_t h, const void *ipc_handle, void **ptr);
+int tpb_peer_close(tpb_handle_t h, void *ptr);
+int tpb_peer_free(tpb_handle_t h, void *ptr);
+/* flags[r] = rank r's flag row (>= world uint32, zero at start, inside a peer buffer);
+ * epoch must grow by one per call on every rank.  The wait is bounded by timeout_ms;
+ * on expiry the kernel records it and tpb_status_poll returns TPB_ERR_TIMEOUT. */
+int tpb_peer_barrier(tpb_handle_t h, tpb_stream_t stream, uint32_t *const *flags, int world,
+                     int rank, uint32_t epoch, int timeout_ms);
+/* y_all[r] = base of rank r's y (y_all[rank] is local); other arguments as
+ * tpb_convrot_gemm, with w_shard / w_scale_shard this rank's n_shard rows. */
+int tpb_convrot_gemm_allgather(tpb_handle_t h, tpb_stream_t stream, void *const *y_all, int world,
+                               int rank, int y_dtype, int64_t ldy, const int8_t *q,
+                               const float *act_scale, const int32_t *act_sum,
+                               const void *w_shard, int w_bits, const float *w_scale_shard,
+                               int64_t m, int64_t n_shard, int64_t k);
+
 #ifdef __cplusplus
 }
 #endif

@@ -49,6 +49,13 @@ SIGNATURES = {
     "tpb_stream_bytes_copied": (C.c_uint64, [_vp]),
     "tpb_host_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tpb_host_free": (_i, [_vp, _vp]),
+    "tpb_peer_alloc": (_i, [_vp, _sz, C.POINTER(_vp), _vp]),
+    "tpb_peer_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "tpb_peer_close": (_i, [_vp, _vp]),
+    "tpb_peer_free": (_i, [_vp, _vp]),
+    "tpb_peer_barrier": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, C.c_uint32, _i]),
+    "tpb_convrot_gemm_allgather": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp,
+                                        _i64, _i64, _i64]),
 }
 
 _lib = None

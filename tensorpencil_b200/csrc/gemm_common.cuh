@@ -33,6 +33,8 @@ struct TileCfg {
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
+constexpr int kMaxPeers = 7;  // world size <= 8
+
 struct GemmParams {
     void *y;
     long long ldy;
@@ -41,6 +43,10 @@ struct GemmParams {
     const int32_t *act_sum;  // non-null: subtract 8 * act_sum[row] (unsigned-nibble weights)
     int m, n, k;
     uint32_t *status;
+    // Fused all-gather: every output piece is also written, at the same (row, column)
+    // and with the same ldy, into these peer-mapped buffers (other GPUs' copies of y).
+    int n_peers;
+    void *peer_y[kMaxPeers];
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -148,6 +154,15 @@ __device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&r)[32]) {
                    "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
                    "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void st_global_v4(void *addr, uint4 v) {
+    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -321,6 +336,28 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             if (lane == 0) {
                 tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            if (p.n_peers > 0) {
+                // The staged piece (32 rows x 128 bytes) goes to the peers with plain
+                // 16-byte stores: eight lanes cover one 128-byte row, so every store
+                // instruction writes four whole rows' segments.
+                constexpr int kElemsPerChunk = OUT == OUT_BF16 ? 8 : 4;
+                constexpr int kElemBytes = OUT == OUT_BF16 ? 2 : 4;
+                const uint32_t sbase = stg + (n_store & 1u) * 4096u;
+                const int chunk = lane & 7;
+                const int gcol = scol + chunk * kElemsPerChunk;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = 4 * i + (lane >> 3);
+                    const uint4 v = ld_shared_v4(sbase + (uint32_t)r * 128u + ((uint32_t)(chunk ^ (r & 7)) << 4));
+                    const int grow = row0 + r;
+                    if (grow < p.m && gcol < p.n) {
+                        const size_t off = ((size_t)grow * (size_t)p.ldy + (size_t)gcol) * kElemBytes;
+#pragma unroll
+                        for (int pr = 0; pr < kMaxPeers; pr++)
+                            if (pr < p.n_peers) st_global_v4(static_cast<char *>(p.peer_y[pr]) + off, v);
+                    }
+                }
             }
             n_store++;
         }

@@ -252,8 +252,11 @@ static W4Scratch g_w4_scratch[64];  // per device ordinal
 
 int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
                     const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *w,
-                    int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k) {
+                    int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k,
+                    void *const *peer_y, int n_peers) {
     GemmParams p;
+    p.n_peers = n_peers;
+    for (int i = 0; i < kMaxPeers; i++) p.peer_y[i] = i < n_peers ? peer_y[i] : nullptr;
     p.y = y;
     p.ldy = ldy;
     p.act_scale = act_scale;

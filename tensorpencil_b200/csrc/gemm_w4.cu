@@ -46,11 +46,6 @@ constexpr int kNumBars = 2 * kSA + 2 * kSP + 2 * kU + 4;
 constexpr int kSmemW4 = kSA * kA + kSP * kBp + kU * kBu + kStagingW4 + 1024 + 8 * kNumBars + 64;
 constexpr int kTmemColsW4 = 512;
 
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
 
 __device__ __forceinline__ void unpack16(const uint4 p, uint4 &lo, uint4 &hi) {
     const uint32_t in[4] = {p.x, p.y, p.z, p.w};

@@ -81,8 +81,15 @@ class DitWeights:
             self.streamer.close()
 
 
-def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
-    """One step of the block stack's linears on latents x [tokens][hidden] (f32)."""
+def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
+                     mlp_tile: int = MLP_TILE, glue: bool = True) -> torch.Tensor:
+    """One step of the block stack's linears on latents x [tokens][hidden] (f32).
+
+    mlp_tile: rows per MLP tile.  The reference tiles by 2048 rows to fit a 24 GB card;
+    with 180 GB of HBM the whole 4608-token batch can go through at once (pass
+    ``mlp_tile=tokens``), which also avoids the short last tile.
+    glue=False skips the torch stand-ins for the non-quantised ops (the linears then read
+    whatever their input buffers hold): the time of this library's kernels alone."""
     bits, hid, mlp = w.bits, w.hidden, w.mlp
     prep = be.opI8Prep if bits == 8 else be.opI4Prep
     gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
@@ -94,9 +101,11 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
     v = torch.empty_like(q)
     g = torch.empty_like(q)
     o = torch.empty_like(q)
-    tile_gate = torch.empty((MLP_TILE, mlp), dtype=out_dtype, device=dev)
+    tile_gate = torch.empty((mlp_tile, mlp), dtype=out_dtype, device=dev)
     tile_up = torch.empty_like(tile_gate)
-    tile_down = torch.empty((MLP_TILE, hid), dtype=out_dtype, device=dev)
+    tile_down = torch.empty((mlp_tile, hid), dtype=out_dtype, device=dev)
+    attn_buf = torch.zeros((m, hid), dtype=torch.float32, device=dev) if not glue else None
+    act_buf = torch.zeros((mlp_tile, mlp), dtype=torch.float32, device=dev) if not glue else None
     st = w.streamer
     if st is not None:
         st.prefetch(0)
@@ -113,20 +122,25 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
         gemm(k, wb["wk"], hid)
         gemm(v, wb["wv"], hid)
         gemm(g, wb["gate"], hid)
-        attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)  # stand-in
+        if glue:
+            attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)  # stand-in
+        else:
+            attn = attn_buf
         prep(attn, m, hid)
         gemm(o, wb["wo"], hid)
-        x = x + o.float() if out_dtype != torch.float32 else x + o
-        for t0 in range(0, m, MLP_TILE):    # dit_cuda.zig:495-516
-            rows = min(MLP_TILE, m - t0)
+        if glue:
+            x = x + o.float() if out_dtype != torch.float32 else x + o
+        for t0 in range(0, m, mlp_tile):    # dit_cuda.zig:495-516
+            rows = min(mlp_tile, m - t0)
             xt = x[t0:t0 + rows]
             prep(xt, rows, hid)
             gemm(tile_gate, wb["mlp_gate"], mlp)
             gemm(tile_up, wb["mlp_up"], mlp)
-            act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float()
+            act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float() if glue else act_buf
             prep(act, rows, mlp)
             gemm(tile_down, wb["mlp_down"], hid)
-            x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3
+            if glue:
+                x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3
         if st is not None:
             st.release(b)
     return x
