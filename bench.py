@@ -42,9 +42,9 @@ METRIC = "convrot_qgemm_int8_tops"
 UNIT = "TOPS"
 N_SETS = 4  # distinct input sets rotated through, so each step's inputs come from HBM, not L2
 
-# DRAM bytes of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum)
-# from the ncu capture summarised in profiles/; None until a capture exists.
-GEMM_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes of one full-size GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum)
+# from the ncu capture summarised in profiles/convrot_gemm2_config1.md, per output type.
+GEMM_DRAM_TRAFFIC_BYTES = {"f32": 227.4e6, "bf16": 118.9e6}
 
 
 def measured_peaks():
@@ -304,7 +304,7 @@ def run_ours(args, rank: int, local: int, world: int):
                          "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s", "frac": gemm_tops / int8_peak,
                          "peak_note": f"2 x bf16 cuBLAS burst of {peaks['source']} peaks (the int8 tensor rate is twice bf16)",
                          "frac_of_dense_int8_spec_4500": gemm_tops / 4500.0,
-                         "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC_BYTES},
+                         "gemm_ms": gemm_ms, "traffic": GEMM_DRAM_TRAFFIC_BYTES[args.out_dtype]},
         }
         if world == 1 and not args.no_cpu_baseline:
             tops, cores, sample, _ = cpu_float_path_sample()
