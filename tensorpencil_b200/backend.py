@@ -239,26 +239,60 @@ class Backend:
         return y
 
     def convrot_linear_host(self, x_host: torch.Tensor, w, w_scale, n: int, bits: int,
-                            y_host: torch.Tensor):
+                            y_host: torch.Tensor, chunk_rows: int = 512):
         """The same linear with HOST activations and a HOST result (pinned
-        tensors): upload x, prep, GEMM, download y, all enqueued on the current
-        stream -- the shape of a call from a host-resident orchestrator
+        tensors) -- the shape of a call from a host-resident orchestrator
         (tensorUpload / op / tensorDownload, src/models/dit_cuda.zig:430-433, :527).
-        Weights stay in the device-side weight cache as in the reference."""
+        Weights stay in the device-side weight cache as in the reference.
+
+        The rows are independent, so the call is pipelined in chunks of
+        ``chunk_rows``: chunk i+1 uploads on one side stream while chunk i is
+        prepped and multiplied on the current stream and chunk i-1 downloads on a
+        second side stream (PCIe is full duplex).  An INT4 weight is widened once
+        per call, not once per chunk.  On return everything is enqueued and the
+        current stream waits for the last download."""
         m, k = x_host.shape
         key = (m, k, n, x_host.dtype, y_host.dtype)
         if getattr(self, "_host_io_key", None) != key:
             self._host_x = torch.empty((m, k), dtype=x_host.dtype, device=self.device)
             self._host_y = torch.empty((m, n), dtype=y_host.dtype, device=self.device)
             self._host_io_key = key
-        self._host_x.copy_(x_host, non_blocking=True)
-        if bits == 8:
-            self.opI8Prep(self._host_x, m, k)
-            self.opI8Gemm(self._host_y, w, w_scale, n)
-        else:
-            self.opI4Prep(self._host_x, m, k)
-            self.opI4Gemm(self._host_y, w, w_scale, n)
-        y_host.copy_(self._host_y, non_blocking=True)
+        if getattr(self, "_s_in", None) is None:
+            self._s_in = torch.cuda.Stream(device=self.device)
+            self._s_out = torch.cuda.Stream(device=self.device)
+        cur = torch.cuda.current_stream(self.device)
+        w8 = w
+        if bits == 4:
+            if getattr(self, "_host_w8", None) is None or self._host_w8.numel() < n * k:
+                self._host_w8 = torch.empty(n * k, dtype=torch.int8, device=self.device)
+            self._check(self.lib.tpb_convrot_w4_expand(self.h, self._stream(), w.data_ptr(), n, k,
+                                                       self._host_w8.data_ptr()))
+            self.launches += 1
+            w8 = self._host_w8
+        bounds = [(r0, min(r0 + chunk_rows, m)) for r0 in range(0, m, chunk_rows)]
+        self._s_in.wait_stream(cur)            # earlier work on the staging buffers is done
+        uploaded = []
+        with torch.cuda.stream(self._s_in):
+            for r0, r1 in bounds:
+                self._host_x[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._s_in)
+                uploaded.append(ev)
+        ydt = _TORCH_TO_TPB[y_host.dtype]
+        for (r0, r1), ev in zip(bounds, uploaded):
+            cur.wait_event(ev)
+            self._prep(self._host_x[r0:r1], r1 - r0, k, bits)
+            rc = self.lib.tpb_convrot_gemm(self.h, self._stream(), self._host_y[r0:r1].data_ptr(), ydt, n,
+                                           self.i8_x.data_ptr(), self.i8_scale.data_ptr(), None,
+                                           w8.data_ptr(), 8, _ptr(w_scale), r1 - r0, n, k)
+            self._check(rc)
+            self.launches += 1
+            done = torch.cuda.Event()
+            done.record(cur)
+            self._s_out.wait_event(done)
+            with torch.cuda.stream(self._s_out):
+                y_host[r0:r1].copy_(self._host_y[r0:r1], non_blocking=True)
+        cur.wait_stream(self._s_out)
 
     def q8_0_linear(self, x: torch.Tensor, w, n: int, k: int, scale: float = 1.0) -> torch.Tensor:
         """Decode linear the way the reference's steppers dispatch it

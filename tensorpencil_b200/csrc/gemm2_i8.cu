@@ -33,7 +33,7 @@ constexpr int kStaging2 = 4 * 2 * 4096;
 constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
 constexpr int kTmemCols2 = 2 * BN2;
 
-template <int OUT>
+template <int OUT, bool PEERS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_y, const GemmParams p, const int b_unsigned) {
@@ -173,7 +173,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             if (OUT != OUT_S32 && row_ok) as = __ldg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
-            epilogue_tile<BN2, OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+            epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
@@ -204,8 +204,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 
 namespace {
 
-template <int OUT>
-int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+template <int OUT, bool PEERS>
+int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
     CUtensorMap ma, mb, my;
     int rc = make_kmajor_map(h, &ma, q, p.m, p.k, BM);            // each CTA loads 128 rows of q
@@ -214,7 +214,7 @@ int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8
     if (rc != TPB_OK) return rc;
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
-    auto kern = convrot_gemm2_kernel<OUT>;
+    auto kern = convrot_gemm2_kernel<OUT, PEERS>;
     static bool attr_set[64] = {false};
     if (!attr_set[h->device & 63]) {
         TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
@@ -226,6 +226,13 @@ int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, my, p, b_unsigned ? 1 : 0));
     return TPB_OK;
+}
+
+template <int OUT>
+int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+                bool b_unsigned) {
+    return p.n_peers > 0 ? launch_pair_p<OUT, true>(h, st, p, q, w8, b_unsigned)
+                         : launch_pair_p<OUT, false>(h, st, p, q, w8, b_unsigned);
 }
 
 }  // namespace

@@ -261,7 +261,9 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 // TMEM address t_row): load 32 columns at a time (the next load in flight while
 // the current columns are processed), dequantise, stage 32 rows x 128 bytes in the
 // warp's swizzled staging buffer and hand each full piece to a TMA store.
-template <int BN, int OUT>
+// PEERS: also write every piece to GemmParams::peer_y (the fused all-gather); a template
+// parameter so that the ordinary kernels carry none of that code.
+template <int BN, int OUT, bool PEERS = false>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
                                               uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
                                               int row0, int n0, float as, int corr, int lane) {
@@ -337,7 +339,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            if (p.n_peers > 0) {
+            if (PEERS) {
                 // The staged piece (32 rows x 128 bytes) goes to the peers with plain
                 // 16-byte stores: eight lanes cover one 128-byte row, so every store
                 // instruction writes four whole rows' segments.

@@ -34,7 +34,7 @@ using namespace tpb_gemm;
 
 // ---- the kernel ---------------------------------------------------------------
 
-template <int BN, int OUT>
+template <int BN, int OUT, bool PEERS>
 __global__ void __launch_bounds__(kThreads, 1)
 convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
                     const __grid_constant__ CUtensorMap tma_b,
@@ -174,7 +174,7 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 
-            epilogue_tile<BN, OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+            epilogue_tile<BN, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
             // all of this warp's TMEM reads are complete: hand the buffer back
             tc_fence_before();
             __syncwarp();
@@ -205,8 +205,8 @@ convrot_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
 
 // ---- host side ------------------------------------------------------------------
 
-template <int BN, int OUT>
-int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+template <int BN, int OUT, bool PEERS>
+int launch_cfg_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                bool b_unsigned) {
     using Cfg = TileCfg<BN>;
     CUtensorMap ma, mb, my;
@@ -216,7 +216,7 @@ int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
     if (rc != TPB_OK) return rc;
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
-    auto kern = convrot_gemm_kernel<BN, OUT>;
+    auto kern = convrot_gemm_kernel<BN, OUT, PEERS>;
     static bool attr_set[64] = {false};  // per instantiation and device
     if (!attr_set[h->device & 63]) {
         TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -227,6 +227,13 @@ int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, ma, mb, my, p, b_unsigned ? 1 : 0));
     return TPB_OK;
+}
+
+template <int BN, int OUT>
+int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
+               bool b_unsigned) {
+    return p.n_peers > 0 ? launch_cfg_p<BN, OUT, true>(h, st, p, q, w8, b_unsigned)
+                         : launch_cfg_p<BN, OUT, false>(h, st, p, q, w8, b_unsigned);
 }
 
 template <int OUT>
@@ -270,7 +277,7 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     const char *one_cta_env = getenv("TPB_GEMM_ONE_CTA");
     const bool one_cta_only = one_cta_env != nullptr && one_cta_env[0] == '1';
     const char *fused_env = getenv("TPB_W4_FUSED");
-    if (w_bits == 4 && fused_env != nullptr && fused_env[0] == '1' &&
+    if (w_bits == 4 && n_peers == 0 && fused_env != nullptr && fused_env[0] == '1' &&
         ((m + 127) / 128) * ((n + 255) / 256) >= h->sm_count) {
         // opt-in: the packed weight is unpacked inside the GEMM (one-CTA kernel)
         p.act_sum = act_sum;

@@ -19,7 +19,6 @@
 // warp, and y = acc * scale.
 #include <cuda_fp16.h>
 
-#include <cstdlib>
 
 #include "tpb_internal.h"
 
@@ -405,8 +404,9 @@ int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max
         stages = 3;
     }
     const size_t smem = (act_smem ? act : 0) + (size_t)warps * stages * kStage + (size_t)warps * stages * 8 + 64;
-    // at least ~2 row groups per warp before adding CTAs
-    int grid = (int)(((long long)p.rows + (long long)warps * R * 2 - 1) / ((long long)warps * R * 2));
+    // One persistent CTA per SM as soon as every warp gets at least one row group: leaving SMs
+    // idle costs more bandwidth than an uneven last group.
+    int grid = (int)(((long long)p.rows + (long long)warps * R - 1) / ((long long)warps * R));
     if (grid < 1) grid = 1;
     if (grid > h->sm_count) grid = h->sm_count;
     if (act_smem) {

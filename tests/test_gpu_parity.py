@@ -395,3 +395,28 @@ def test_streamed_forward_bit_identical_to_resident(be):
     assert st.bytes_copied() == layers * (n * k + 4 * n)
     st.close()
     del rng
+
+
+# ---------------------------------------------------------------------------------
+# Host-buffer entry: pinned x in, pinned y out, pipelined in row chunks
+# ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,chunk", [(700, 256), (512, 512), (130, 512), (1100, 300)])
+def test_host_buffer_linear_matches_resident(be, bits, m, chunk):
+    n, k = 1024, 768
+    c = synth.convrot_linear(m, n, k, bits, seed=77 + m + bits)
+    w = dev(c["w_i8"] if bits == 8 else c["w_packed"])
+    ws = dev(c["w_scale"])
+    y_dev = be.convrot_linear(dev(c["x"]), w, ws, n, bits)
+    x_pin = torch.from_numpy(c["x"]).pin_memory()
+    y_pin = torch.full((m, n), float("nan"), dtype=torch.float32).pin_memory()
+    for _ in range(2):                      # second call reuses the staging buffers and streams
+        be.convrot_linear_host(x_pin, w, ws, n, bits, y_pin, chunk_rows=chunk)
+        torch.cuda.current_stream().synchronize()   # the call makes the current stream wait for the last download
+        assert np.array_equal(y_pin.numpy().view(np.uint32), y_dev.cpu().numpy().view(np.uint32))
+        y_pin.fill_(float("nan"))
+    be.status_poll()
+    q, s = oracle.convrot_prep(c["x"], bits)
+    sim = oracle.dequant_sim(oracle.igemm_s32(q, c["w_i8"]), s, c["w_scale"])
+    assert_close_to_sim(y_dev.cpu().numpy(), sim)
