@@ -234,6 +234,46 @@ int tpb_convrot_gemm_allgather(tpb_handle_t h, tpb_stream_t stream, void *const 
                                const void *w_shard, int w_bits, const float *w_scale_shard,
                                int64_t m, int64_t n_shard, int64_t k);
 
+/* ---- Elementwise neighbours of the linears, and the prep with them fused in --------
+ *
+ * The DiT block computes every quantised linear's input with an elementwise op first
+ * (src/models/dit_cuda.zig:473-514).  Stand-alone forms (HBM-bound, f32 results):
+ *
+ *   tpb_silu_mul     out = silu(gate) * up         Backend.siluMul      src/gpu/cuda/backend.zig:3310-3315
+ *   tpb_sigmoid_mul  out = a * sigmoid(gate)       Backend.sigmoidMul   src/gpu/cuda/backend.zig:3294-3299
+ *   tpb_rms_mod      out = x*inv*premul + shift    Backend.rmsMod       src/gpu/cuda/backend.zig:2738-2760
+ *                    inv = 1/sqrt(mean(x^2) + eps) over each row of `dim`
+ *   tpb_gated_add    x  += gate[c] * delta         Backend.gatedAdd     src/gpu/cuda/backend.zig:3342-3347
+ *
+ * out may alias the first input when that input is f32 (the reference's ops are in
+ * place).  Inputs f32 or bf16 (in_dtype); premul/shift/gate are f32 vectors of `dim`
+ * (the reference passes one `mod` buffer plus offsets: pass mod + offset here).
+ * sigmoid uses the fast exponential/reciprocal, like the reference's kernels
+ * (src/gpu/cuda/elt.zig:4-7); results agree with the CPU definitions
+ * (src/ops/act.zig:61-70, :141-149; src/ops/norm.zig:12-23) to ~1e-6.
+ *
+ * tpb_convrot_prep_fused applies the same producer to the values as they are loaded
+ * and goes straight on to rotate + quantise (as tpb_convrot_prep): the f32 activation
+ * is never written.  q / act_scale / act_sum are bit-identical to running the
+ * stand-alone op and then tpb_convrot_prep.  No reference counterpart (it runs the two
+ * steps separately).  op: 1 = silu_mul (a = gate, b = up), 2 = sigmoid_mul (a, b = gate),
+ * 3 = rms_mod (a = x, premul, shift, eps; b unused). */
+#define TPB_OP_SILU_MUL 1
+#define TPB_OP_SIGMOID_MUL 2
+#define TPB_OP_RMS_MOD 3
+int tpb_silu_mul(tpb_handle_t h, tpb_stream_t stream, const void *gate, const void *up, int in_dtype,
+                 float *out, int64_t n);
+int tpb_sigmoid_mul(tpb_handle_t h, tpb_stream_t stream, const void *a, const void *gate, int in_dtype,
+                    float *out, int64_t n);
+int tpb_rms_mod(tpb_handle_t h, tpb_stream_t stream, const void *x, int x_dtype, float *out,
+                const float *premul, const float *shift, float eps, int64_t rows, int64_t dim);
+int tpb_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, const void *delta, int delta_dtype,
+                  const float *gate, int64_t rows, int64_t dim);
+int tpb_convrot_prep_fused(tpb_handle_t h, tpb_stream_t stream, int op, const void *a, const void *b,
+                           const float *premul, const float *shift, float eps, int in_dtype,
+                           int64_t m, int64_t k, int bits, int8_t *q, float *act_scale,
+                           int32_t *act_sum);
+
 #ifdef __cplusplus
 }
 #endif

@@ -233,3 +233,38 @@ def q8_0_block_sumi(w: np.ndarray, n: int, k: int, xq: np.ndarray) -> np.ndarray
     out = np.empty((m, n, k // 32), np.int32)
     lib().tpo_q8_0_block_sumi(_p(w), C.c_size_t(n), C.c_size_t(k), _p(xq), C.c_size_t(m), _p(out))
     return out
+
+
+# -- elementwise neighbours of the linears (producers of the prep input, gated residual) --
+
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    out = np.empty_like(gate)
+    lib().tpo_silu_mul(_p(gate), _p(up), C.c_size_t(gate.size), _p(out))
+    return out
+
+
+def sigmoid_mul(dst: np.ndarray, gate: np.ndarray) -> np.ndarray:
+    dst, gate = _c(dst, np.float32), _c(gate, np.float32)
+    out = np.empty_like(dst)
+    lib().tpo_sigmoid_mul(_p(dst), _p(gate), C.c_size_t(dst.size), _p(out))
+    return out
+
+
+def rms_mod(x: np.ndarray, premul: np.ndarray, shift: np.ndarray, eps: float) -> np.ndarray:
+    x = _c(x, np.float32)
+    rows, dim = x.shape
+    premul, shift = _c(premul, np.float32), _c(shift, np.float32)
+    assert premul.size == dim and shift.size == dim
+    out = np.empty_like(x)
+    lib().tpo_rms_mod(_p(x), C.c_size_t(rows), C.c_size_t(dim), _p(premul), _p(shift), C.c_float(eps), _p(out))
+    return out
+
+
+def gated_add(x: np.ndarray, delta: np.ndarray, gate: np.ndarray) -> np.ndarray:
+    x, delta, gate = _c(x, np.float32), _c(delta, np.float32), _c(gate, np.float32)
+    rows, dim = x.shape
+    assert gate.size == dim
+    out = np.empty_like(x)
+    lib().tpo_gated_add(_p(x), _p(delta), _p(gate), C.c_size_t(rows), C.c_size_t(dim), _p(out))
+    return out

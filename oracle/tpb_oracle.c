@@ -407,3 +407,54 @@ void tpo_q8_0_block_sumi(const uint8_t *w, size_t n, size_t k, const int8_t *xq,
         }
     }
 }
+
+/* ------------------------------------------------------------------------ */
+/* Elementwise neighbours of the quantized linears in the DiT block          */
+/* (the producers that feed the activation prep, and the gated residual).    */
+/* ------------------------------------------------------------------------ */
+
+/* src/ops/vmath.zig:56-59: 1 / (1 + exp(-x)); the reference's own test compares its
+ * vector exp against libm at 2e-7 (vmath.zig:81-88), so libm stands in here. */
+static inline float tpo_sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+/* src/ops/act.zig:61-70: gate[i] = gate[i] * sigmoid(gate[i]) * up[i]. */
+void tpo_silu_mul(const float *gate, const float *up, size_t n, float *out) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)n; i++) out[i] = gate[i] * tpo_sigmoidf(gate[i]) * up[i];
+}
+
+/* src/ops/act.zig:141-149: dst[i] *= sigmoid(gate[i]). */
+void tpo_sigmoid_mul(const float *dst, const float *gate, size_t n, float *out) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)n; i++) out[i] = dst[i] * tpo_sigmoidf(gate[i]);
+}
+
+/* RMS norm + AdaLN modulation as the GPU step applies it: out = (x * inv) * premul[c] +
+ * shift[c], inv = 1/sqrt(mean(x^2) + eps), premul = (1 + scale) * norm_weight prepared by the
+ * host (src/gpu/cuda/backend.zig:2738-2760, src/gpu/cuda/elt.zig:9-66; CPU form
+ * src/ops/norm.zig:12-23, :63-76 followed by modulate, src/models/dit.zig:575-581).
+ * The sum of squares is taken in double: every float summation order the reference uses
+ * (8-lane vectors on the CPU, 256 partials on the GPU) lies within its own 2e-6 gate of it. */
+void tpo_rms_mod(const float *x, size_t rows, size_t dim, const float *premul, const float *shift,
+                 float eps, float *out) {
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < (long long)rows; r++) {
+        const float *xr = x + (size_t)r * dim;
+        double ss = 0.0;
+        for (size_t c = 0; c < dim; c++) ss += (double)xr[c] * (double)xr[c];
+        const float mean = (float)(ss / (double)dim);
+        const float inv = 1.0f / sqrtf(mean + eps);
+        for (size_t c = 0; c < dim; c++) out[(size_t)r * dim + c] = xr[c] * inv * premul[c] + shift[c];
+    }
+}
+
+/* src/models/dit.zig:584-590: x[row][c] += gate[c] * delta[row][c]. */
+void tpo_gated_add(const float *x, const float *delta, const float *gate, size_t rows, size_t dim,
+                   float *out) {
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < (long long)rows; r++)
+        for (size_t c = 0; c < dim; c++) {
+            const size_t i = (size_t)r * dim + c;
+            out[i] = x[i] + gate[c] * delta[i];
+        }
+}

@@ -126,6 +126,15 @@ void tpo_q8_0_gemv_q8(const uint8_t *w, size_t n, size_t k, const float *x,
 void tpo_q8_0_block_sumi(const uint8_t *w, size_t n, size_t k, const int8_t *xq,
                          size_t m, int32_t *sumi);
 
+/* Elementwise neighbours of the quantized linears (producers of the prep input and the
+ * gated residual): src/ops/act.zig:61-70, :141-149; src/ops/norm.zig:12-23 + src/models/dit.zig:575-590. */
+void tpo_silu_mul(const float *gate, const float *up, size_t n, float *out);
+void tpo_sigmoid_mul(const float *dst, const float *gate, size_t n, float *out);
+void tpo_rms_mod(const float *x, size_t rows, size_t dim, const float *premul, const float *shift,
+                 float eps, float *out);
+void tpo_gated_add(const float *x, const float *delta, const float *gate, size_t rows, size_t dim,
+                   float *out);
+
 int tpo_num_threads(void);
 
 #ifdef __cplusplus

@@ -49,6 +49,11 @@ SIGNATURES = {
     "tpb_stream_bytes_copied": (C.c_uint64, [_vp]),
     "tpb_host_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tpb_host_free": (_i, [_vp, _vp]),
+    "tpb_silu_mul": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i64]),
+    "tpb_sigmoid_mul": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i64]),
+    "tpb_rms_mod": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _f, _i64, _i64]),
+    "tpb_gated_add": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i64, _i64]),
+    "tpb_convrot_prep_fused": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _i64, _i, _vp, _vp, _vp]),
     "tpb_peer_alloc": (_i, [_vp, _sz, C.POINTER(_vp), _vp]),
     "tpb_peer_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "tpb_peer_close": (_i, [_vp, _vp]),

@@ -158,6 +158,64 @@ class Backend:
         """int4 (W4A4) analogue of opI8Prep (backend.zig:2532-2553)."""
         self._prep(x, m, cols, 4)
 
+    # -- elementwise neighbours and the prep with them fused in ---------------------------
+    def _prep_fused(self, op: int, a: torch.Tensor, b: Optional[torch.Tensor], premul: Optional[torch.Tensor],
+                    shift: Optional[torch.Tensor], eps: float, m: int, cols: int, bits: int):
+        assert a.is_cuda and a.is_contiguous() and a.dtype in (torch.float32, torch.bfloat16)
+        assert b is None or (b.dtype == a.dtype and b.is_contiguous())
+        if self.i8_x is None or self.i8_x.numel() < m * cols:
+            self.i8_x = torch.empty(max(m * cols, 1), dtype=torch.int8, device=self.device)
+        if self.i8_scale is None or self.i8_scale.numel() < m:
+            self.i8_scale = torch.empty(max(m, 1), dtype=torch.float32, device=self.device)
+            self.i8_sum = torch.empty(max(m, 1), dtype=torch.int32, device=self.device)
+        rc = self.lib.tpb_convrot_prep_fused(self.h, self._stream(), op, a.data_ptr(), _ptr(b), _ptr(premul),
+                                             _ptr(shift), eps, _TORCH_TO_TPB[a.dtype], m, cols, bits,
+                                             self.i8_x.data_ptr(), self.i8_scale.data_ptr(), self.i8_sum.data_ptr())
+        self._check(rc)
+        self.launches += 1
+        self.i8_m, self.i8_cols, self.i8_bits = m, cols, bits
+
+    def prepSiluMul(self, gate: torch.Tensor, up: torch.Tensor, m: int, cols: int, bits: int = 8):
+        """siluMul + op{I8,I4}Prep in one kernel: the prepped activation is
+        rotate+quantise(silu(gate) * up) (dit_cuda.zig:513-514 without the round trip)."""
+        self._prep_fused(1, gate, up, None, None, 0.0, m, cols, bits)
+
+    def prepSigmoidMul(self, a: torch.Tensor, gate: torch.Tensor, m: int, cols: int, bits: int = 8):
+        """sigmoidMul + prep in one kernel (dit_cuda.zig:490-491)."""
+        self._prep_fused(2, a, gate, None, None, 0.0, m, cols, bits)
+
+    def prepRmsMod(self, x: torch.Tensor, mod: torch.Tensor, rows: int, dim: int, premul_off: int, shift_off: int,
+                   eps: float, bits: int = 8):
+        """rmsMod + prep in one kernel (dit_cuda.zig:473-474, :499-500); ``mod`` is
+        the reference's modulation buffer, offsets in elements."""
+        self._prep_fused(3, x, None, mod[premul_off:premul_off + dim], mod[shift_off:shift_off + dim], eps,
+                         rows, dim, bits)
+
+    def siluMul(self, a: torch.Tensor, b: torch.Tensor, total: int):
+        """a = silu(a) * b in place (backend.zig:3310-3315)."""
+        self._check(self.lib.tpb_silu_mul(self.h, self._stream(), a.data_ptr(), b.data_ptr(), _TORCH_TO_TPB[a.dtype],
+                                          a.data_ptr(), total))
+        self.launches += 1
+
+    def sigmoidMul(self, a: torch.Tensor, b: torch.Tensor, total: int):
+        """a = a * sigmoid(b) in place (backend.zig:3294-3299)."""
+        self._check(self.lib.tpb_sigmoid_mul(self.h, self._stream(), a.data_ptr(), b.data_ptr(),
+                                             _TORCH_TO_TPB[a.dtype], a.data_ptr(), total))
+        self.launches += 1
+
+    def rmsMod(self, x: torch.Tensor, out: torch.Tensor, mod: torch.Tensor, rows: int, dim: int, premul_off: int,
+               shift_off: int, eps: float):
+        """out = x * inv_rms(x) * mod[premul_off + c] + mod[shift_off + c] (backend.zig:2738-2760)."""
+        self._check(self.lib.tpb_rms_mod(self.h, self._stream(), x.data_ptr(), _TORCH_TO_TPB[x.dtype], out.data_ptr(),
+                                         mod[premul_off:].data_ptr(), mod[shift_off:].data_ptr(), eps, rows, dim))
+        self.launches += 1
+
+    def gatedAdd(self, a: torch.Tensor, b: torch.Tensor, mod: torch.Tensor, total: int, dim: int, gate_off: int):
+        """a[row][c] += mod[gate_off + c] * b[row][c] (backend.zig:3342-3347)."""
+        self._check(self.lib.tpb_gated_add(self.h, self._stream(), a.data_ptr(), b.data_ptr(), _TORCH_TO_TPB[b.dtype],
+                                           mod[gate_off:].data_ptr(), total // dim, dim))
+        self.launches += 1
+
     def _gemm(self, y: torch.Tensor, w_bytes: np.ndarray, weight_scale: np.ndarray, rows: int,
               w_bits: int, ldy: Optional[int] = None):
         assert self.i8_bits == w_bits, "opI{8,4}Gemm must follow the matching prep"

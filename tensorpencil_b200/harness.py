@@ -81,31 +81,61 @@ class DitWeights:
             self.streamer.close()
 
 
+def dit_modulation(be, blocks: int, hidden: int, seed: int = 7) -> torch.Tensor:
+    """The per-block AdaLN vectors the step reads: for block b, six rows of `hidden` at
+    offset b*6*hidden -- pre-attention premul and shift, attention gate, pre-MLP premul and
+    shift, MLP gate (src/models/dit_cuda.zig:471-516).  premul = 1 + small, the rest small."""
+    g = torch.Generator(device=be.device).manual_seed(seed)
+    mod = (torch.rand(blocks * 6 * hidden, device=be.device, generator=g) - 0.5) * 0.2
+    mod = mod.view(blocks, 6, hidden)
+    mod[:, 0] += 1.0
+    mod[:, 3] += 1.0
+    return mod.reshape(-1).contiguous()
+
+
 def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
-                     mlp_tile: int = MLP_TILE, glue: bool = True) -> torch.Tensor:
-    """One step of the block stack's linears on latents x [tokens][hidden] (f32).
+                     mlp_tile: int = MLP_TILE, glue: bool = True, mode: Optional[str] = None,
+                     mod: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
+    """One step of the block stack on latents x [tokens][hidden] (f32, updated in place).
+
+    mode:
+      "linears"  prep + GEMM only; the linears read whatever their input buffers hold
+                 (the time of the quantized-linear kernels alone);
+      "unfused"  the reference's sequence: rmsMod, prep, GEMMs, sigmoidMul, prep, GEMM,
+                 gatedAdd, and per MLP tile rmsMod, prep, GEMMs, siluMul, prep, GEMM,
+                 gatedAdd -- every elementwise op its own kernel (f32 only);
+      "fused"    the same data flow with rmsMod / sigmoidMul / siluMul folded into the
+                 prep kernels; with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs
+                 stay bf16 end to end;
+      "torch"    legacy: linears through the library, cheap torch stand-ins between them.
+    Attention proper (qk-norm, RoPE, softmax) is not part of this path: v stands in for
+    its output.  ``glue`` is the old switch: True -> "torch", False -> "linears".
 
     mlp_tile: rows per MLP tile.  The reference tiles by 2048 rows to fit a 24 GB card;
-    with 180 GB of HBM the whole 4608-token batch can go through at once (pass
-    ``mlp_tile=tokens``), which also avoids the short last tile.
-    glue=False skips the torch stand-ins for the non-quantised ops (the linears then read
-    whatever their input buffers hold): the time of this library's kernels alone."""
+    with 180 GB of HBM the whole 4608-token batch can go through at once."""
+    if mode is None:
+        mode = "torch" if glue else "linears"
     bits, hid, mlp = w.bits, w.hidden, w.mlp
     prep = be.opI8Prep if bits == 8 else be.opI4Prep
     gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
            (lambda y, wt, n: be.opI4Gemm(y, wt[0], wt[1], n))
     m = x.shape[0]
     dev = be.device
+    if mode == "unfused" and out_dtype != torch.float32:
+        raise ValueError("the unfused sequence is f32 only")
+    if mode in ("unfused", "fused") and mod is None:
+        raise ValueError("mode needs the modulation vectors (dit_modulation)")
     q = torch.empty((m, hid), dtype=out_dtype, device=dev)
     k = torch.empty_like(q)
     v = torch.empty_like(q)
     g = torch.empty_like(q)
     o = torch.empty_like(q)
+    t1 = torch.empty((m, hid), dtype=torch.float32, device=dev) if mode == "unfused" else None
     tile_gate = torch.empty((mlp_tile, mlp), dtype=out_dtype, device=dev)
     tile_up = torch.empty_like(tile_gate)
     tile_down = torch.empty((mlp_tile, hid), dtype=out_dtype, device=dev)
-    attn_buf = torch.zeros((m, hid), dtype=torch.float32, device=dev) if not glue else None
-    act_buf = torch.zeros((mlp_tile, mlp), dtype=torch.float32, device=dev) if not glue else None
+    attn_buf = torch.zeros((m, hid), dtype=torch.float32, device=dev) if mode == "linears" else None
+    act_buf = torch.zeros((mlp_tile, mlp), dtype=torch.float32, device=dev) if mode == "linears" else None
     st = w.streamer
     if st is not None:
         st.prefetch(0)
@@ -117,29 +147,61 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                 st.prefetch(b + 1)          # prefetchBlock(b+1), dit_cuda.zig:470
         else:
             wb = w.dev[b]
-        prep(x, m, hid)                     # one prep, four GEMMs (dit_cuda.zig:474-478)
+        mb = b * 6 * hid
+        # --- attention: one prep, four GEMMs (dit_cuda.zig:473-478) ---
+        if mode == "fused":
+            be.prepRmsMod(x, mod, m, hid, mb, mb + hid, eps, bits)
+        elif mode == "unfused":
+            be.rmsMod(x, t1, mod, m, hid, mb, mb + hid, eps)
+            prep(t1, m, hid)
+        else:
+            prep(x, m, hid)
         gemm(q, wb["wq"], hid)
         gemm(k, wb["wk"], hid)
         gemm(v, wb["wv"], hid)
         gemm(g, wb["gate"], hid)
-        if glue:
-            attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)  # stand-in
+        if mode == "fused":
+            be.prepSigmoidMul(v, g, m, hid, bits)          # v stands in for the attention output
+        elif mode == "unfused":
+            be.sigmoidMul(v, g, m * hid)
+            prep(v, m, hid)
+        elif mode == "torch":
+            attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)
+            prep(attn, m, hid)
         else:
-            attn = attn_buf
-        prep(attn, m, hid)
+            prep(attn_buf, m, hid)
         gemm(o, wb["wo"], hid)
-        if glue:
+        if mode in ("fused", "unfused"):
+            be.gatedAdd(x, o, mod, m * hid, hid, mb + 2 * hid)
+        elif mode == "torch":
             x = x + o.float() if out_dtype != torch.float32 else x + o
-        for t0 in range(0, m, mlp_tile):    # dit_cuda.zig:495-516
+        # --- MLP in row tiles (dit_cuda.zig:495-516) ---
+        for t0 in range(0, m, mlp_tile):
             rows = min(mlp_tile, m - t0)
             xt = x[t0:t0 + rows]
-            prep(xt, rows, hid)
+            if mode == "fused":
+                be.prepRmsMod(xt, mod, rows, hid, mb + 3 * hid, mb + 4 * hid, eps, bits)
+            elif mode == "unfused":
+                be.rmsMod(xt, t1, mod, rows, hid, mb + 3 * hid, mb + 4 * hid, eps)
+                prep(t1, rows, hid)
+            else:
+                prep(xt, rows, hid)
             gemm(tile_gate, wb["mlp_gate"], mlp)
             gemm(tile_up, wb["mlp_up"], mlp)
-            act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float() if glue else act_buf
-            prep(act, rows, mlp)
+            if mode == "fused":
+                be.prepSiluMul(tile_gate, tile_up, rows, mlp, bits)
+            elif mode == "unfused":
+                be.siluMul(tile_gate, tile_up, rows * mlp)
+                prep(tile_gate, rows, mlp)
+            elif mode == "torch":
+                act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float()
+                prep(act, rows, mlp)
+            else:
+                prep(act_buf, rows, mlp)
             gemm(tile_down, wb["mlp_down"], hid)
-            if glue:
+            if mode in ("fused", "unfused"):
+                be.gatedAdd(xt, tile_down, mod, rows * hid, hid, mb + 5 * hid)
+            elif mode == "torch":
                 x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3
         if st is not None:
             st.release(b)

@@ -261,3 +261,54 @@ def test_committed_q8_vectors(golden_dir):
     assert np.array_equal(oracle.q8_0_gemv_q8(g["q8_w"], 16, 512, g["q8_x"]), g["q8_y_q8"])
     d, qs = oracle.q8_1_quantize(g["q8_x"])
     assert np.array_equal(d, g["q8_act_d"]) and np.array_equal(qs, g["q8_act_qs"])
+
+
+# ---------------------------------------------------------------------------------
+# Elementwise neighbours: pinned to the reference's own fixtures
+# (src/ops/act.zig:153-158 and :176-188, src/ops/norm.zig:79-96; tolerances are the
+# reference tests' own, 2e-6 absolute)
+# ---------------------------------------------------------------------------------
+
+ACT_IN = np.array([-3, -1, -0.5, 0, 0.5, 1, 2, 3, 0.100000001, -2.20000005], np.float32)
+SILU_OUT = np.array([-0.142277613, -0.268941432, -0.188770339, 0, 0.311229676, 0.731058598, 1.76159406,
+                     2.85772252, 0.0524979196, -0.21945107], np.float32)
+SIGMOID_OUT = np.array([0.0474258736, 0.268941432, 0.377540678, 0.5, 0.622459352, 0.731058598, 0.880797029,
+                        0.952574134, 0.524979174, 0.0997504815], np.float32)
+
+
+def test_silu_and_sigmoid_match_reference_fixtures():
+    ones = np.ones_like(ACT_IN)
+    assert np.allclose(oracle.silu_mul(ACT_IN, ones), SILU_OUT, rtol=0, atol=2e-6)
+    assert np.allclose(oracle.sigmoid_mul(ones, ACT_IN), SIGMOID_OUT, rtol=0, atol=2e-6)
+    # the "fused gates" cases: silu(1)*2, silu(-0.5)*3; 2*sigmoid(0)... as 1.0, 2*sigmoid(1)
+    got = oracle.silu_mul(np.array([1, -0.5], np.float32), np.array([2, 3], np.float32))
+    assert np.allclose(got, [0.731058598 * 2.0, -0.188770339 * 3.0], rtol=0, atol=1e-6)
+    got = oracle.sigmoid_mul(np.array([2, 2], np.float32), np.array([0, 1], np.float32))
+    assert np.allclose(got, [1.0, 2.0 * 0.731058598], rtol=0, atol=1e-6)
+
+
+def test_rms_mod_matches_reference_rmsnorm_fixture():
+    x = np.array([0.5, -1.5, 2, 0.25, 3, 0, -0.125, 1], np.float32).reshape(2, 4)
+    weight = (1.0 + np.array([0.100000001, -0.200000003, 0, 0.5], np.float32)).astype(np.float32)
+    zero = np.zeros(4, np.float32)
+    want = np.array([0.429394752, -0.936861217, 1.56143546, 0.292769134, 2.08547044, 0, -0.0789950937,
+                     0.947941124], np.float32).reshape(2, 4)
+    assert np.allclose(oracle.rms_mod(x, weight, zero, 1e-5), want, rtol=0, atol=2e-6)
+    want6 = np.array([0.429395914, -0.93686384, 1.56143963, 0.292769939, 2.08547425, 0, -0.0789952353,
+                      0.947942853], np.float32).reshape(2, 4)
+    assert np.allclose(oracle.rms_mod(x, weight, zero, 1e-6), want6, rtol=0, atol=2e-6)
+    # odd dim, eps 0 (norm.zig:98-107), then modulation on top: (1 + scale) * normed + shift
+    x5 = np.array([[1, 2, 3, 4, 5], [-1, -2, -3, -4, -5]], np.float32)
+    rms = np.sqrt(np.float32(11.0))
+    got = oracle.rms_mod(x5, np.ones(5, np.float32), zero[:1].repeat(5), 0.0)
+    assert abs(got[0, 0] - 1.0 / rms) < 1e-6 and abs(got[1, 4] + 5.0 / rms) < 1e-6
+    scale, shift = np.float32(0.25), np.float32(-0.5)
+    got = oracle.rms_mod(x5, np.full(5, 1 + scale, np.float32), np.full(5, shift, np.float32), 0.0)
+    assert np.allclose(got, (1 + scale) * (x5 / rms) + shift, rtol=0, atol=2e-6)
+
+
+def test_gated_add():
+    x = np.arange(6, dtype=np.float32).reshape(2, 3)
+    d = np.ones((2, 3), np.float32) * 2
+    g = np.array([0.5, -1, 0], np.float32)
+    assert np.array_equal(oracle.gated_add(x, d, g), x + g * d)
