@@ -233,6 +233,27 @@ int tpb_convrot_gemm_allgather(tpb_handle_t h, tpb_stream_t stream, void *const 
                                const float *act_scale, const int32_t *act_sum,
                                const void *w_shard, int w_bits, const float *w_scale_shard,
                                int64_t m, int64_t n_shard, int64_t k);
+/* The building block of the above for any destination layout: an ordinary GEMM whose
+ * epilogue writes each output tile to y_local and, at the same (row, column, ldy), to every
+ * y_peers[i] (peer-mapped pointers, 0 <= n_peers <= 7).  With ldy = n and each rank writing
+ * at its own block offset the gathered result is column-blocked [rank][m][n] instead of
+ * row-major, which keeps a sender's writes inside one contiguous region per destination. */
+int tpb_convrot_gemm_multi(tpb_handle_t h, tpb_stream_t stream, void *y_local, void *const *y_peers,
+                           int n_peers, int y_dtype, int64_t ldy, const int8_t *q,
+                           const float *act_scale, const int32_t *act_sum, const void *w,
+                           int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k);
+
+/* The same with ONE store per output element: y_mc is an NVSwitch multicast address that
+ * maps every rank's y (a CUDA multicast object bound to all the ranks' buffers, e.g.
+ * torch's symmetric memory `multicast_ptr`); the epilogue writes each tile with
+ * multimem.st and the switch replicates it into all copies, this rank's included, so a
+ * GPU sends its shard once instead of world-1 times.  y_local is this rank's ordinary
+ * address of the same buffer.  Completion: as above (tpb_peer_barrier). */
+int tpb_convrot_gemm_allgather_mc(tpb_handle_t h, tpb_stream_t stream, void *y_mc, void *y_local,
+                                  int world, int rank, int y_dtype, int64_t ldy, const int8_t *q,
+                                  const float *act_scale, const int32_t *act_sum,
+                                  const void *w_shard, int w_bits, const float *w_scale_shard,
+                                  int64_t m, int64_t n_shard, int64_t k);
 
 /* ---- Elementwise neighbours of the linears, and the prep with them fused in --------
  *

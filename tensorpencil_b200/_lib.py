@@ -59,6 +59,10 @@ SIGNATURES = {
     "tpb_peer_close": (_i, [_vp, _vp]),
     "tpb_peer_free": (_i, [_vp, _vp]),
     "tpb_peer_barrier": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, C.c_uint32, _i]),
+    "tpb_convrot_gemm_multi": (_i, [_vp, _vp, _vp, C.POINTER(_vp), _i, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp,
+                                    _i64, _i64, _i64]),
+    "tpb_convrot_gemm_allgather_mc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp,
+                                           _i64, _i64, _i64]),
     "tpb_convrot_gemm_allgather": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp,
                                         _i64, _i64, _i64]),
 }

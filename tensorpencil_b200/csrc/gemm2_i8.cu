@@ -33,7 +33,7 @@ constexpr int kStaging2 = 4 * 2 * 4096;
 constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
 constexpr int kTmemCols2 = 2 * BN2;
 
-template <int OUT, bool PEERS>
+template <int OUT, int PEERS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_y, const GemmParams p, const int b_unsigned) {
@@ -204,7 +204,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 
 namespace {
 
-template <int OUT, bool PEERS>
+template <int OUT, int PEERS>
 int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
     CUtensorMap ma, mb, my;
@@ -231,8 +231,9 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
 template <int OUT>
 int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
-    return p.n_peers > 0 ? launch_pair_p<OUT, true>(h, st, p, q, w8, b_unsigned)
-                         : launch_pair_p<OUT, false>(h, st, p, q, w8, b_unsigned);
+    if (p.mc_y != nullptr) return launch_pair_p<OUT, 2>(h, st, p, q, w8, b_unsigned);
+    return p.n_peers > 0 ? launch_pair_p<OUT, 1>(h, st, p, q, w8, b_unsigned)
+                         : launch_pair_p<OUT, 0>(h, st, p, q, w8, b_unsigned);
 }
 
 }  // namespace

@@ -47,6 +47,9 @@ struct GemmParams {
     // and with the same ldy, into these peer-mapped buffers (other GPUs' copies of y).
     int n_peers;
     void *peer_y[kMaxPeers];
+    // Or one NVSwitch multicast address of y (same row, column and ldy): a single
+    // multimem store lands in every GPU's copy, this GPU's included.
+    void *mc_y;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -165,6 +168,11 @@ __device__ __forceinline__ void st_global_v4(void *addr, uint4 v) {
     asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
+__device__ __forceinline__ void multimem_st_v4(void *addr, uint4 v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -261,9 +269,10 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 // TMEM address t_row): load 32 columns at a time (the next load in flight while
 // the current columns are processed), dequantise, stage 32 rows x 128 bytes in the
 // warp's swizzled staging buffer and hand each full piece to a TMA store.
-// PEERS: also write every piece to GemmParams::peer_y (the fused all-gather); a template
-// parameter so that the ordinary kernels carry none of that code.
-template <int BN, int OUT, bool PEERS = false>
+// PEERS (the fused all-gather): 1 = also write every piece to GemmParams::peer_y with plain
+// stores; 2 = write every piece once, to the multicast address GemmParams::mc_y, instead of
+// the local TMA store.  A template parameter so that the ordinary kernels carry none of it.
+template <int BN, int OUT, int PEERS = 0>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
                                               uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
                                               int row0, int n0, float as, int corr, int lane) {
@@ -335,11 +344,11 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             // generic-proxy writes -> visible to the async proxy, then one lane stores
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
+            if (PEERS != 2 && lane == 0) {
                 tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            if (PEERS) {
+            if (PEERS != 0) {
                 // The staged piece (32 rows x 128 bytes) goes to the peers with plain
                 // 16-byte stores: eight lanes cover one 128-byte row, so every store
                 // instruction writes four whole rows' segments.
@@ -355,9 +364,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                     const int grow = row0 + r;
                     if (grow < p.m && gcol < p.n) {
                         const size_t off = ((size_t)grow * (size_t)p.ldy + (size_t)gcol) * kElemBytes;
+                        if (PEERS == 2) {
+                            multimem_st_v4(static_cast<char *>(p.mc_y) + off, v);
+                        } else {
 #pragma unroll
-                        for (int pr = 0; pr < kMaxPeers; pr++)
-                            if (pr < p.n_peers) st_global_v4(static_cast<char *>(p.peer_y[pr]) + off, v);
+                            for (int pr = 0; pr < kMaxPeers; pr++)
+                                if (pr < p.n_peers) st_global_v4(static_cast<char *>(p.peer_y[pr]) + off, v);
+                        }
                     }
                 }
             }

@@ -171,4 +171,53 @@ int tpb_convrot_gemm_allgather(tpb_handle_t h, tpb_stream_t stream, void *const 
                            w_scale_shard, m, n_shard, k, peers, n_peers);
 }
 
+int tpb_convrot_gemm_multi(tpb_handle_t h, tpb_stream_t stream, void *y_local, void *const *y_peers, int n_peers,
+                           int y_dtype, int64_t ldy, const int8_t *q, const float *act_scale,
+                           const int32_t *act_sum, const void *w, int w_bits, const float *w_scale, int64_t m,
+                           int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, n_peers >= 0 && n_peers <= 7 && (n_peers == 0 || y_peers), "gemm_multi: need 0 <= n_peers <= 7");
+    for (int i = 0; i < n_peers; i++)
+        TPB_CHECK_ARG(h, y_peers[i] && tpb_aligned16(y_peers[i]), "gemm_multi: y_peers[%d] is null or misaligned", i);
+    // every other check is the plain GEMM's
+    const int rc = tpb_convrot_gemm(h, nullptr, y_local, y_dtype, ldy, q, act_scale, act_sum, w, w_bits, w_scale, 0, n, k);
+    if (rc != TPB_OK) return rc;
+    TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "gemm_multi: bad m");
+    if (m == 0) return TPB_OK;
+    return tpb_launch_gemm(h, (cudaStream_t)stream, y_local, y_dtype, ldy, q, act_scale, act_sum, w, w_bits, w_scale,
+                           m, n, k, y_peers, n_peers);
+}
+
+int tpb_convrot_gemm_allgather_mc(tpb_handle_t h, tpb_stream_t stream, void *y_mc, void *y_local, int world,
+                                  int rank, int y_dtype, int64_t ldy, const int8_t *q, const float *act_scale,
+                                  const int32_t *act_sum, const void *w_shard, int w_bits,
+                                  const float *w_scale_shard, int64_t m, int64_t n_shard, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, y_mc && y_local && tpb_aligned16(y_mc) && tpb_aligned16(y_local),
+                  "gemm_allgather_mc: y_mc / y_local null or misaligned");
+    TPB_CHECK_ARG(h, world >= 1 && world <= 8 && rank >= 0 && rank < world,
+                  "gemm_allgather_mc: need 1 <= world <= 8 and 0 <= rank < world");
+    TPB_CHECK_ARG(h, y_dtype == TPB_F32 || y_dtype == TPB_BF16 || y_dtype == TPB_S32,
+                  "gemm_allgather_mc: y_dtype must be f32, bf16 or s32");
+    TPB_CHECK_ARG(h, n_shard > 0 && ldy >= n_shard * world, "gemm_allgather_mc: ldy must be >= world * n_shard");
+    TPB_CHECK_ARG(h, q && w_shard, "gemm_allgather_mc: null pointer");
+    TPB_CHECK_ARG(h, y_dtype == TPB_S32 || (act_scale && w_scale_shard), "gemm_allgather_mc: scales are required");
+    TPB_CHECK_ARG(h, w_bits == 8 || w_bits == 4, "gemm_allgather_mc: w_bits must be 8 or 4 (got %d)", w_bits);
+    TPB_CHECK_ARG(h, w_bits == 8 || act_sum, "gemm_allgather_mc: act_sum is required when w_bits = 4");
+    TPB_CHECK_ARG(h, m >= 0 && k > 0 && k % 256 == 0 && n_shard % 16 == 0,
+                  "gemm_allgather_mc: need k %% 256 == 0 and n_shard %% 16 == 0");
+    TPB_CHECK_ARG(h, m < (1ll << 31) && n_shard * world < (1ll << 31) && k < (1ll << 31),
+                  "gemm_allgather_mc: dims exceed 2^31");
+    const int64_t ld_mult = y_dtype == TPB_BF16 ? 8 : 4;
+    TPB_CHECK_ARG(h, ldy % ld_mult == 0, "gemm_allgather_mc: ldy must be a multiple of %lld", (long long)ld_mult);
+    TPB_CHECK_ARG(h, tpb_aligned16(q) && tpb_aligned16(w_shard) && tpb_aligned16(w_scale_shard),
+                  "gemm_allgather_mc: q, w and w_scale must be 16-byte aligned");
+    if (m == 0) return TPB_OK;
+    const size_t esz = y_dtype == TPB_BF16 ? 2 : 4;
+    const size_t col_off = (size_t)rank * (size_t)n_shard * esz;
+    return tpb_launch_gemm(h, (cudaStream_t)stream, static_cast<char *>(y_local) + col_off, y_dtype, ldy, q, act_scale,
+                           act_sum, w_shard, w_bits, w_scale_shard, m, n_shard, k, nullptr, 0,
+                           static_cast<char *>(y_mc) + col_off);
+}
+
 }  // extern "C"

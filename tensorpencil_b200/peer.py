@@ -96,6 +96,28 @@ class PeerBuffers:
         be._check(rc)
         be.launches += 2 if w_bits == 4 else 1
 
+    def gemm_allgather_blocked(self, w_shard: torch.Tensor, w_scale_shard: torch.Tensor, n_shard: int, w_bits: int,
+                               y_dtype: torch.dtype = torch.float32):
+        """As gemm_allgather, but every rank's shard lands as one contiguous [m][n_shard]
+        block: the gathered result is column-blocked [rank][m][n_shard] (``nsplit.assemble``
+        turns a [1][world][m][n_shard] view of it into row-major)."""
+        be = self.be
+        assert be.i8_bits == w_bits, "must follow the matching prep"
+        esz = 2 if y_dtype == torch.bfloat16 else 4
+        block = be.i8_m * n_shard * esz
+        if block * self.world > self.payload_bytes:
+            raise ValueError("output does not fit the peer buffer")
+        ydt = {torch.float32: _lib.TPB_F32, torch.bfloat16: _lib.TPB_BF16, torch.int32: _lib.TPB_S32}[y_dtype]
+        off = PAYLOAD_OFFSET + self.rank * block
+        peers = [b + off for r, b in enumerate(self.bases) if r != self.rank]
+        arr = (C.c_void_p * max(1, len(peers)))(*peers)
+        rc = self.lib.tpb_convrot_gemm_multi(
+            be.h, be._stream(), self.local + off, arr, len(peers), ydt, n_shard, be.i8_x.data_ptr(),
+            be.i8_scale.data_ptr(), be.i8_sum.data_ptr() if w_bits == 4 else None, w_shard.data_ptr(), w_bits,
+            w_scale_shard.data_ptr() if w_scale_shard is not None else None, be.i8_m, n_shard, be.i8_cols)
+        be._check(rc)
+        be.launches += 2 if w_bits == 4 else 1
+
     def close(self):
         if self.local is None:
             return
@@ -107,3 +129,63 @@ class PeerBuffers:
         dist.barrier(group=self.group)
         self.lib.tpb_peer_free(self.be.h, self.local)
         self.local = None
+
+
+class MulticastBuffers:
+    """The same role as PeerBuffers, on torch's symmetric memory: one allocation per rank,
+    every rank's copy reachable through the peers' ordinary addresses AND through one
+    NVSwitch multicast address, so the GEMM epilogue can send each output tile once
+    (``tpb_convrot_gemm_allgather_mc``).  ``available`` is False where the platform has no
+    multicast support (no NVSwitch); nothing else is usable then."""
+
+    def __init__(self, be, payload_bytes: int, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.be, self.lib = be, be.lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.payload_bytes = payload_bytes
+        self._buf = symm_mem.empty(PAYLOAD_OFFSET + payload_bytes, dtype=torch.uint8, device=be.device)
+        self._buf.zero_()
+        torch.cuda.synchronize(be.device)
+        self._hdl = symm_mem.rendezvous(self._buf, self.group)
+        self.bases = [int(p) for p in self._hdl.buffer_ptrs]
+        self.mc_base = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+        self.available = self.mc_base != 0
+        self.local = self.bases[self.rank]
+        self.epoch = 0
+        self._flags = (C.c_void_p * self.world)(*self.bases)
+        dist.barrier(group=group)
+
+    tensor = PeerBuffers.tensor
+    barrier = PeerBuffers.barrier
+
+    def gemm_allgather(self, w_shard: torch.Tensor, w_scale_shard: torch.Tensor, n_shard: int, w_bits: int,
+                       y_dtype: torch.dtype = torch.float32, ldy: Optional[int] = None):
+        """As PeerBuffers.gemm_allgather, one multimem store per element instead of world-1
+        peer stores plus a local one."""
+        be = self.be
+        if not self.available:
+            raise RuntimeError("no multicast support on this platform")
+        assert be.i8_bits == w_bits, "must follow the matching prep"
+        ld = ldy if ldy is not None else n_shard * self.world
+        esz = 2 if y_dtype == torch.bfloat16 else 4
+        if be.i8_m * ld * esz > self.payload_bytes:
+            raise ValueError("output does not fit the buffer")
+        ydt = {torch.float32: _lib.TPB_F32, torch.bfloat16: _lib.TPB_BF16, torch.int32: _lib.TPB_S32}[y_dtype]
+        rc = self.lib.tpb_convrot_gemm_allgather_mc(
+            be.h, be._stream(), self.mc_base + PAYLOAD_OFFSET, self.local + PAYLOAD_OFFSET, self.world, self.rank,
+            ydt, ld, be.i8_x.data_ptr(), be.i8_scale.data_ptr(), be.i8_sum.data_ptr() if w_bits == 4 else None,
+            w_shard.data_ptr(), w_bits, w_scale_shard.data_ptr() if w_scale_shard is not None else None,
+            be.i8_m, n_shard, be.i8_cols)
+        be._check(rc)
+        be.launches += 2 if w_bits == 4 else 1
+
+    def close(self):
+        if self._buf is None:
+            return
+        torch.cuda.synchronize(self.be.device)
+        dist.barrier(group=self.group)      # nobody is still writing into a buffer about to go away
+        self._hdl = None
+        self._buf = None
+        dist.barrier(group=self.group)

@@ -65,6 +65,19 @@ def _worker(rank, world, port, ret):
             same_fused = same_fused and bool(torch.equal(pb.tensor((m, n), dt), y_one))
         be.status_poll()
         pb.close()
+        # and with one multicast store per element, where the platform has NVSwitch multicast
+        from tensorpencil_b200.peer import MulticastBuffers
+        mb = MulticastBuffers(be, m * n * 4)
+        if mb.available:
+            for dt in (torch.float32, torch.bfloat16):
+                y_one = torch.empty((m, n), dtype=dt, device="cuda")
+                be.opI8Gemm(y_one, w, ws, n)
+                mb.barrier()
+                mb.gemm_allgather(w[lo:hi], ws[lo:hi], hi - lo, 8, y_dtype=dt)
+                mb.barrier()
+                same_fused = same_fused and bool(torch.equal(mb.tensor((m, n), dt), y_one))
+            be.status_poll()
+        mb.close()
         ret[rank] = (same_split, same_replica, same_fused)
         be.close()
     finally:
