@@ -382,7 +382,7 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
     variants = {
         "unfused_f32": ("reference sequence: rmsMod/sigmoidMul/siluMul/gatedAdd as separate kernels, f32, 2048-row MLP tiles",
                         lambda i: harness.dit_step_linears(be, w, latents[i % 2], mode="unfused", mod=mod)),
-        "fused_f32": ("producers fused into the prep kernels, f32, 2048-row MLP tiles",
+        "fused_f32": ("producers fused into the prep kernels, gated residuals into the GEMM epilogues, f32, 2048-row MLP tiles",
                       lambda i: harness.dit_step_linears(be, w, latents[i % 2], mode="fused", mod=mod)),
         "fused_bf16_whole_batch": ("fused, bf16 activation chain, one MLP pass over all 4608 tokens",
                                    lambda i: harness.dit_step_linears(be, w, latents[i % 2], out_dtype=torch.bfloat16,

@@ -111,6 +111,16 @@ int tpb_convrot_gemm(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, 
                      const void *w, int w_bits, const float *w_scale,
                      int64_t m, int64_t n, int64_t k);
 
+/* GEMM with the gated residual folded into the epilogue: replaces opI{8,4}Gemm followed by
+ * Backend.gatedAdd (src/models/dit_cuda.zig:492-493, :515-516; src/gpu/cuda/backend.zig:3342-3347):
+ *   x[i][j] = fma(gate[j], (float(acc) * act_scale[i]) * w_scale[j], x[i][j])
+ * x is f32 [m][ldx], read and written in place; the result is bit-identical to
+ * tpb_convrot_gemm (f32) followed by tpb_gated_add.  gate is an f32 vector of n. */
+int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, int64_t ldx,
+                               const float *gate, const int8_t *q, const float *act_scale,
+                               const int32_t *act_sum, const void *w, int w_bits,
+                               const float *w_scale, int64_t m, int64_t n, int64_t k);
+
 /* Bytes of the int8 expansion of an [n][k] int4 weight. */
 size_t tpb_convrot_w4_expanded_bytes(int64_t n, int64_t k);
 

@@ -231,6 +231,20 @@ class Backend:
         self._check(rc)
         self.launches += 2 if w_bits == 4 else 1
 
+    def gemmGatedAdd(self, x: torch.Tensor, w_bytes, weight_scale, rows: int, mod: torch.Tensor, gate_off: int,
+                     w_bits: int = 8):
+        """opI{8,4}Gemm + gatedAdd in one kernel: x[m][rows] += mod[gate_off + c] * linear(prepped)
+        (dit_cuda.zig:492-493, :515-516).  x is f32, updated in place."""
+        assert self.i8_bits == w_bits and x.dtype == torch.float32 and x.is_contiguous()
+        w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
+        ws_dev = self.cachedWeight(weight_scale) if isinstance(weight_scale, np.ndarray) else weight_scale
+        rc = self.lib.tpb_convrot_gemm_gated_add(self.h, self._stream(), x.data_ptr(), rows, mod[gate_off:].data_ptr(),
+                                                 self.i8_x.data_ptr(), self.i8_scale.data_ptr(),
+                                                 self.i8_sum.data_ptr() if w_bits == 4 else None, w_dev.data_ptr(),
+                                                 w_bits, _ptr(ws_dev), self.i8_m, rows, self.i8_cols)
+        self._check(rc)
+        self.launches += 2 if w_bits == 4 else 1
+
     def opI8Gemm(self, y: torch.Tensor, w_bytes, weight_scale, rows: int, c_h16: bool = False):
         """y[m][rows] = prepped @ W^T * act_scale[row] * weight_scale[col]
         (backend.zig:2484-2501).  The output type is y.dtype (f32 or bf16; int32

@@ -157,6 +157,20 @@ int tpb_convrot_gemm(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, 
                            w_bits, w_scale, m, n, k);
 }
 
+int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, int64_t ldx, const float *gate,
+                               const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *w,
+                               int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, gate && tpb_aligned16(gate), "gemm_gated_add: gate is null or misaligned");
+    // everything else is checked as for the plain GEMM with an f32 output
+    const int rc = tpb_convrot_gemm(h, nullptr, x, TPB_F32, ldx, q, act_scale, act_sum, w, w_bits, w_scale, 0, n, k);
+    if (rc != TPB_OK) return rc;
+    TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "gemm_gated_add: bad m");
+    if (m == 0) return TPB_OK;
+    return tpb_launch_gemm(h, (cudaStream_t)stream, x, TPB_F32, ldx, q, act_scale, act_sum, w, w_bits, w_scale, m, n,
+                           k, nullptr, 0, nullptr, gate);
+}
+
 int tpb_q8_1_quantize(tpb_handle_t h, tpb_stream_t stream, const float *x, int64_t n_elems,
                       void *xq) {
     if (!h) return TPB_ERR_INVALID_ARG;

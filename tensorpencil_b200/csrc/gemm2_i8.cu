@@ -231,6 +231,7 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
 template <int OUT>
 int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
+    if (p.gate != nullptr) return launch_pair_p<OUT_F32, 3>(h, st, p, q, w8, b_unsigned);
     if (p.mc_y != nullptr) return launch_pair_p<OUT, 2>(h, st, p, q, w8, b_unsigned);
     return p.n_peers > 0 ? launch_pair_p<OUT, 1>(h, st, p, q, w8, b_unsigned)
                          : launch_pair_p<OUT, 0>(h, st, p, q, w8, b_unsigned);

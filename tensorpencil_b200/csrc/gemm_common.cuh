@@ -50,6 +50,9 @@ struct GemmParams {
     // Or one NVSwitch multicast address of y (same row, column and ldy): a single
     // multimem store lands in every GPU's copy, this GPU's included.
     void *mc_y;
+    // Gated residual (epilogue mode 3, f32 only): y is the residual stream x and the
+    // epilogue stores x + gate[col] * (acc * act_scale * w_scale) back into it.
+    const float *gate;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -269,7 +272,9 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 // TMEM address t_row): load 32 columns at a time (the next load in flight while
 // the current columns are processed), dequantise, stage 32 rows x 128 bytes in the
 // warp's swizzled staging buffer and hand each full piece to a TMA store.
-// PEERS (the fused all-gather): 1 = also write every piece to GemmParams::peer_y with plain
+// PEERS is the epilogue mode.  3 = gated residual: read the tile of y, add gate[col] times
+// the dequantised result, store it back (GemmParams::gate).  Modes of the fused all-gather:
+// 1 = also write every piece to GemmParams::peer_y with plain
 // stores; 2 = write every piece once, to the multicast address GemmParams::mc_y, instead of
 // the local TMA store.  A template parameter so that the ordinary kernels carry none of it.
 template <int BN, int OUT, int PEERS = 0>
@@ -310,10 +315,25 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             for (int g = 0; g < 8; g++) {
                 float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (col0 + 4 * g < p.n) ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
-                const float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g] - corr), as), ws.x);
-                const float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 1] - corr), as), ws.y);
-                const float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
-                const float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 3] - corr), as), ws.w);
+                float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g] - corr), as), ws.x);
+                float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 1] - corr), as), ws.y);
+                float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
+                float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 3] - corr), as), ws.w);
+                if (PEERS == 3) {
+                    // this lane's row of the residual stream; the tile is read here and written
+                    // back by this warp's own TMA store below, nobody else touches it
+                    float4 gt = make_float4(0.f, 0.f, 0.f, 0.f), xv = gt;
+                    if (col0 + 4 * g < p.n) {
+                        gt = __ldg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
+                        if (row0 + lane < p.m)
+                            xv = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.y) +
+                                                                   (size_t)(row0 + lane) * (size_t)p.ldy + col0 + 4 * g);
+                    }
+                    v0 = __fmaf_rn(gt.x, v0, xv.x);
+                    v1 = __fmaf_rn(gt.y, v1, xv.y);
+                    v2 = __fmaf_rn(gt.z, v2, xv.z);
+                    v3 = __fmaf_rn(gt.w, v3, xv.w);
+                }
                 st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), __float_as_uint(v0), __float_as_uint(v1),
                              __float_as_uint(v2), __float_as_uint(v3));
             }
@@ -348,7 +368,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            if (PEERS != 0) {
+            if (PEERS == 1 || PEERS == 2) {
                 // The staged piece (32 rows x 128 bytes) goes to the peers with plain
                 // 16-byte stores: eight lanes cover one 128-byte row, so every store
                 // instruction writes four whole rows' segments.

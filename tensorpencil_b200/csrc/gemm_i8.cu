@@ -232,6 +232,7 @@ int launch_cfg_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int
 template <int BN, int OUT>
 int launch_cfg(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                bool b_unsigned) {
+    if (p.gate != nullptr) return launch_cfg_p<BN, OUT_F32, 3>(h, st, p, q, w8, b_unsigned);
     if (p.mc_y != nullptr) return launch_cfg_p<BN, OUT, 2>(h, st, p, q, w8, b_unsigned);
     return p.n_peers > 0 ? launch_cfg_p<BN, OUT, 1>(h, st, p, q, w8, b_unsigned)
                          : launch_cfg_p<BN, OUT, 0>(h, st, p, q, w8, b_unsigned);
@@ -261,9 +262,10 @@ static W4Scratch g_w4_scratch[64];  // per device ordinal
 int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
                     const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *w,
                     int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k,
-                    void *const *peer_y, int n_peers, void *mc_y) {
+                    void *const *peer_y, int n_peers, void *mc_y, const float *gate) {
     GemmParams p;
     p.mc_y = mc_y;
+    p.gate = gate;
     p.n_peers = n_peers;
     for (int i = 0; i < kMaxPeers; i++) p.peer_y[i] = i < n_peers ? peer_y[i] : nullptr;
     p.y = y;
@@ -279,7 +281,7 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     const char *one_cta_env = getenv("TPB_GEMM_ONE_CTA");
     const bool one_cta_only = one_cta_env != nullptr && one_cta_env[0] == '1';
     const char *fused_env = getenv("TPB_W4_FUSED");
-    if (w_bits == 4 && n_peers == 0 && mc_y == nullptr && fused_env != nullptr && fused_env[0] == '1' &&
+    if (w_bits == 4 && n_peers == 0 && mc_y == nullptr && gate == nullptr && fused_env != nullptr && fused_env[0] == '1' &&
         ((m + 127) / 128) * ((n + 255) / 256) >= h->sm_count) {
         // opt-in: the packed weight is unpacked inside the GEMM (one-CTA kernel)
         p.act_sum = act_sum;

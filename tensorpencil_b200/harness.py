@@ -105,8 +105,8 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                  gatedAdd, and per MLP tile rmsMod, prep, GEMMs, siluMul, prep, GEMM,
                  gatedAdd -- every elementwise op its own kernel (f32 only);
       "fused"    the same data flow with rmsMod / sigmoidMul / siluMul folded into the
-                 prep kernels; with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs
-                 stay bf16 end to end;
+                 prep kernels and gatedAdd folded into the wo / mlp.down GEMM epilogues;
+                 with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs stay bf16;
       "torch"    legacy: linears through the library, cheap torch stand-ins between them.
     Attention proper (qk-norm, RoPE, softmax) is not part of this path: v stands in for
     its output.  ``glue`` is the old switch: True -> "torch", False -> "linears".
@@ -170,8 +170,11 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
             prep(attn, m, hid)
         else:
             prep(attn_buf, m, hid)
-        gemm(o, wb["wo"], hid)
-        if mode in ("fused", "unfused"):
+        if mode == "fused":
+            be.gemmGatedAdd(x, wb["wo"][0], wb["wo"][1], hid, mod, mb + 2 * hid, bits)   # GEMM + gated residual
+        else:
+            gemm(o, wb["wo"], hid)
+        if mode == "unfused":
             be.gatedAdd(x, o, mod, m * hid, hid, mb + 2 * hid)
         elif mode == "torch":
             x = x + o.float() if out_dtype != torch.float32 else x + o
@@ -198,8 +201,11 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                 prep(act, rows, mlp)
             else:
                 prep(act_buf, rows, mlp)
-            gemm(tile_down, wb["mlp_down"], hid)
-            if mode in ("fused", "unfused"):
+            if mode == "fused":
+                be.gemmGatedAdd(xt, wb["mlp_down"][0], wb["mlp_down"][1], hid, mod, mb + 5 * hid, bits)
+            else:
+                gemm(tile_down, wb["mlp_down"], hid)
+            if mode == "unfused":
                 be.gatedAdd(xt, tile_down, mod, rows * hid, hid, mb + 5 * hid)
             elif mode == "torch":
                 x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3

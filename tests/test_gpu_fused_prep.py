@@ -163,3 +163,32 @@ def test_fused_prep_rejects_bad_arguments(be):
              s.data_ptr(), None) == _lib.TPB_ERR_INVALID_ARG                                                      # k
     assert f(be.h, None, 1, a.data_ptr(), a.data_ptr(), None, None, 0.0, _lib.TPB_F32, 4, 256, 4, q.data_ptr(),
              s.data_ptr(), None) == _lib.TPB_ERR_INVALID_ARG                                                      # act_sum
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,n,k", [(96, 768, 512), (300, 1040, 256), (4608, 3072, 256), (1100, 3072, 768)])
+def test_gemm_with_gated_residual_is_bit_identical_to_two_steps(be, bits, m, n, k):
+    """x += gate * linear(...) in the GEMM epilogue == f32 GEMM then gated_add, bit for bit
+    (one-CTA kernels for the small shapes, the CTA-pair kernel for the large ones)."""
+    from tensorpencil_b200 import synth
+    c = synth.convrot_linear(m, n, k, bits, seed=41 + m)
+    w = dev(c["w_i8"] if bits == 8 else c["w_packed"])
+    ws = dev(c["w_scale"])
+    x0 = rnd((m, n), 42)
+    mod = dev(rnd((3 * n,), 43, 0.2))
+    be._prep(dev(c["x"]), m, k, bits)
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    be._gemm(y, w, ws, n, bits)
+    two = dev(x0)
+    be.gatedAdd(two, y, mod, m * n, n, n)
+    one = dev(x0)
+    be.gemmGatedAdd(one, w, ws, n, mod, n, bits)
+    be.status_poll()
+    assert torch.equal(one.view(torch.int32), two.view(torch.int32))
+    if m * n * k <= 300 * 1040 * 256:
+        q = be.i8_x[: m * k].cpu().numpy().reshape(m, k)
+        s = be.i8_scale[:m].cpu().numpy()
+        sim = oracle.dequant_sim(oracle.igemm_s32(q, c["w_i8"]), s, c["w_scale"])
+        want = x0.astype(np.float64) + mod.cpu().numpy()[n:2 * n].astype(np.float64) * sim
+        err = np.abs(one.cpu().numpy() - want)
+        assert (err <= 1e-4 + 1e-3 * np.abs(want)).all()
