@@ -587,8 +587,30 @@ def run_mode_gemv(args, rank, local, world):
             steps = max(20, args.steps)
             ms = _events_ms(fn, steps, torch.cuda.synchronize) / steps
             gbs = n * (k // 32) * 34 / (ms * 1e-3) / 1e9
-            rows_out.append({"n": n, "k": k, "m": m, "us": ms * 1e3, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"]})
+            rows_out.append({"fmt": "q8_0", "n": n, "k": k, "m": m, "us": ms * 1e3, "gbs": gbs,
+                             "frac_of_hbm": gbs / peaks["hbm_gbs"]})
         del ws
+    # the other GGUF formats at the up-projection shape; enough rotating copies to exceed L2
+    from tensorpencil_b200 import synth
+    n, k = 17408, 5120
+    for fmt in ("q4_k", "q5_k", "q4_0"):
+        base = torch.from_numpy(synth.gguf_weights(fmt, n, k, seed=11)).cuda()
+        copies = 8
+        ws = [base] + [base.clone() for _ in range(copies - 1)]       # 8 x 50..61 MB > 126 MB of L2
+        wbytes = base.numel()
+        for m in (1, 4, 8):
+            x = torch.randn(m, k, device="cuda")
+            y = torch.empty(m, n, device="cuda")
+            be.opGemvQuantizeX(x, m * k)
+            fn = lambda i: be.opGemvQuantQ8N(fmt, y, ws[i % copies], 1.0, n, k, m, 0, m)
+            for i in range(5):
+                fn(i)
+            steps = max(24, args.steps)
+            ms = _events_ms(fn, steps, torch.cuda.synchronize) / steps
+            gbs = wbytes / (ms * 1e-3) / 1e9
+            rows_out.append({"fmt": fmt, "n": n, "k": k, "m": m, "us": ms * 1e3, "gbs": gbs,
+                             "frac_of_hbm": gbs / peaks["hbm_gbs"]})
+        del ws, base
     be.status_poll()
     head = rows_out[0]
     print(json.dumps({"metric": "qgemv_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1,

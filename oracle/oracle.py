@@ -268,3 +268,31 @@ def gated_add(x: np.ndarray, delta: np.ndarray, gate: np.ndarray) -> np.ndarray:
     out = np.empty_like(x)
     lib().tpo_gated_add(_p(x), _p(delta), _p(gate), C.c_size_t(rows), C.c_size_t(dim), _p(out))
     return out
+
+
+# -- other GGUF block formats ---------------------------------------------------------------
+
+GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3, "q6_k": 4}
+
+
+def gguf_row_bytes(fmt: str, k: int) -> int:
+    lib().tpo_gguf_row_bytes.restype = C.c_size_t
+    return int(lib().tpo_gguf_row_bytes(GGUF_FMT[fmt], C.c_size_t(k)))
+
+
+def gguf_dequant_row(fmt: str, row: np.ndarray, k: int) -> np.ndarray:
+    row = _c(row, np.uint8)
+    out = np.empty(k, np.float32)
+    lib().tpo_gguf_dequant_row(GGUF_FMT[fmt], _p(row), C.c_size_t(k), _p(out))
+    return out
+
+
+def gguf_gemv_q8(fmt: str, w: np.ndarray, n: int, k: int, x: np.ndarray, scale: float = 1.0) -> np.ndarray:
+    """y[m][n]: dequantised weight rows times q8_1-dequantised activations, f64 accumulation."""
+    w = _c(w, np.uint8)
+    x = _c(x, np.float32).reshape(-1, k)
+    m = x.shape[0]
+    y = np.empty((m, n), np.float32)
+    lib().tpo_gguf_gemv_q8(GGUF_FMT[fmt], _p(w), C.c_size_t(n), C.c_size_t(k), _p(x), C.c_size_t(m),
+                           C.c_float(scale), _p(y))
+    return y

@@ -458,3 +458,173 @@ void tpo_gated_add(const float *x, const float *delta, const float *gate, size_t
             out[i] = x[i] + gate[c] * delta[i];
         }
 }
+
+/* ------------------------------------------------------------------------ */
+/* Other GGUF block formats (ggml's published decoders; the reference calls   */
+/* ggml for them, src/core/quants.zig:60-68, and pins them with golden        */
+/* blocks, src/core/quants_fixtures.zig -- which pin these restatements too). */
+/* Layouts: src/core/quants.zig:9-16.                                         */
+/* ------------------------------------------------------------------------ */
+
+/* 6-bit sub-block scale and min number j (0..7) of a q4_k / q5_k super-block. */
+static inline void tpo_scale_min_k4(int j, const uint8_t *q, uint8_t *sc, uint8_t *m) {
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+        *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+/* q4_k: 144 bytes per 256 elements: f16 d, f16 dmin, scales[12], qs[128]. */
+void tpo_q4_k_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t sb = 0; sb < k / 256; sb++) {
+        const uint8_t *b = blocks + sb * 144;
+        uint16_t hd, hm;
+        memcpy(&hd, b, 2);
+        memcpy(&hm, b + 2, 2);
+        const float d = tpo_f16_to_f32(hd), dmin = tpo_f16_to_f32(hm);
+        const uint8_t *sc = b + 4, *q = b + 16;
+        float *y = out + sb * 256;
+        int is = 0;
+        for (int j = 0; j < 256; j += 64) {
+            uint8_t s, m;
+            tpo_scale_min_k4(is + 0, sc, &s, &m);
+            const float d1 = d * s, m1 = dmin * m;
+            tpo_scale_min_k4(is + 1, sc, &s, &m);
+            const float d2 = d * s, m2 = dmin * m;
+            for (int l = 0; l < 32; l++) *y++ = d1 * (q[l] & 0xF) - m1;
+            for (int l = 0; l < 32; l++) *y++ = d2 * (q[l] >> 4) - m2;
+            q += 32;
+            is += 2;
+        }
+    }
+}
+
+/* q5_k: 176 bytes: f16 d, f16 dmin, scales[12], qh[32], qs[128]. */
+void tpo_q5_k_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t sb = 0; sb < k / 256; sb++) {
+        const uint8_t *b = blocks + sb * 176;
+        uint16_t hd, hm;
+        memcpy(&hd, b, 2);
+        memcpy(&hm, b + 2, 2);
+        const float d = tpo_f16_to_f32(hd), dmin = tpo_f16_to_f32(hm);
+        const uint8_t *sc = b + 4, *qh = b + 16, *ql = b + 48;
+        float *y = out + sb * 256;
+        int is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (int j = 0; j < 256; j += 64) {
+            uint8_t s, m;
+            tpo_scale_min_k4(is + 0, sc, &s, &m);
+            const float d1 = d * s, m1 = dmin * m;
+            tpo_scale_min_k4(is + 1, sc, &s, &m);
+            const float d2 = d * s, m2 = dmin * m;
+            for (int l = 0; l < 32; l++) *y++ = d1 * ((ql[l] & 0xF) + (qh[l] & u1 ? 16 : 0)) - m1;
+            for (int l = 0; l < 32; l++) *y++ = d2 * ((ql[l] >> 4) + (qh[l] & u2 ? 16 : 0)) - m2;
+            ql += 32;
+            is += 2;
+            u1 <<= 2;
+            u2 <<= 2;
+        }
+    }
+}
+
+/* q6_k: 210 bytes: ql[128], qh[64], int8 scales[16], f16 d. */
+void tpo_q6_k_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t sb = 0; sb < k / 256; sb++) {
+        const uint8_t *b = blocks + sb * 210;
+        const uint8_t *ql = b, *qh = b + 128;
+        const int8_t *sc = (const int8_t *)(b + 192);
+        uint16_t hd;
+        memcpy(&hd, b + 208, 2);
+        const float d = tpo_f16_to_f32(hd);
+        float *y = out + sb * 256;
+        for (int n = 0; n < 256; n += 128) {
+            for (int l = 0; l < 32; l++) {
+                const int is = l / 16;
+                const int8_t q1 = (int8_t)((ql[l + 0] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+                const int8_t q2 = (int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+                const int8_t q3 = (int8_t)((ql[l + 0] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+                const int8_t q4 = (int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+                y[l + 0] = d * sc[is + 0] * q1;
+                y[l + 32] = d * sc[is + 2] * q2;
+                y[l + 64] = d * sc[is + 4] * q3;
+                y[l + 96] = d * sc[is + 6] * q4;
+            }
+            y += 128;
+            ql += 64;
+            qh += 32;
+            sc += 8;
+        }
+    }
+}
+
+/* q4_0: 18 bytes per 32 elements: f16 d, 16 nibble bytes; element j in the low nibble of
+ * byte j, element j + 16 in the high nibble; v = d * (nibble - 8).  No golden block in the
+ * reference for this one: parity unpinned. */
+void tpo_q4_0_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t blk = 0; blk < k / 32; blk++) {
+        const uint8_t *b = blocks + blk * 18;
+        uint16_t hd;
+        memcpy(&hd, b, 2);
+        const float d = tpo_f16_to_f32(hd);
+        for (int j = 0; j < 16; j++) {
+            out[blk * 32 + j] = ((b[2 + j] & 0xF) - 8) * d;
+            out[blk * 32 + j + 16] = ((b[2 + j] >> 4) - 8) * d;
+        }
+    }
+}
+
+/* GEMV against q8_1-quantised activations for any of the formats above, the way the
+ * reference's device test forms its CPU truth (src/gpu/cuda/backend.zig:3750-3790):
+ * dequantise the weight row, dequantise the activations (d * q per 32-block), f64 dot.
+ * fmt: 0 q8_0, 1 q4_0, 2 q4_k, 3 q5_k, 4 q6_k. */
+size_t tpo_gguf_row_bytes(int fmt, size_t k) {
+    switch (fmt) {
+        case 0: return k / 32 * 34;
+        case 1: return k / 32 * 18;
+        case 2: return k / 256 * 144;
+        case 3: return k / 256 * 176;
+        case 4: return k / 256 * 210;
+    }
+    return 0;
+}
+
+void tpo_gguf_dequant_row(int fmt, const uint8_t *row, size_t k, float *out) {
+    switch (fmt) {
+        case 0: tpo_q8_0_dequant_row(row, k, out); break;
+        case 1: tpo_q4_0_dequant_row(row, k, out); break;
+        case 2: tpo_q4_k_dequant_row(row, k, out); break;
+        case 3: tpo_q5_k_dequant_row(row, k, out); break;
+        case 4: tpo_q6_k_dequant_row(row, k, out); break;
+    }
+}
+
+void tpo_gguf_gemv_q8(int fmt, const uint8_t *w, size_t n, size_t k, const float *x, size_t m, float scale,
+                      float *y) {
+    const size_t rb = tpo_gguf_row_bytes(fmt, k);
+    float *xh = (float *)malloc(m * k * sizeof(float));
+    {
+        float *d = (float *)malloc(m * k / 32 * sizeof(float));
+        int8_t *qs = (int8_t *)malloc(m * k);
+        tpo_q8_1_quantize(x, m * k, 0, d, qs);
+        for (size_t i = 0; i < m * k; i++) xh[i] = d[i / 32] * (float)qs[i];
+        free(d);
+        free(qs);
+    }
+#pragma omp parallel
+    {
+        float *wr = (float *)malloc(k * sizeof(float));
+#pragma omp for schedule(static)
+        for (long long r = 0; r < (long long)n; r++) {
+            tpo_gguf_dequant_row(fmt, w + (size_t)r * rb, k, wr);
+            for (size_t t = 0; t < m; t++) {
+                double acc = 0.0;
+                for (size_t c = 0; c < k; c++) acc += (double)wr[c] * (double)xh[t * k + c];
+                y[t * n + r] = (float)(acc * (double)scale);
+            }
+        }
+        free(wr);
+    }
+}

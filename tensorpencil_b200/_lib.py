@@ -20,6 +20,7 @@ TPB_ERR_STATE = -5
 TPB_ERR_NO_DEVICE = -6
 
 TPB_F32, TPB_BF16, TPB_F16, TPB_S32 = 0, 1, 2, 3
+GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3}
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
@@ -55,6 +56,8 @@ SIGNATURES = {
     "tpb_rms_mod": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _f, _i64, _i64]),
     "tpb_gated_add": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i64, _i64]),
     "tpb_convrot_prep_fused": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _i64, _i, _vp, _vp, _vp]),
+    "tpb_gguf_row_bytes": (_sz, [_i, _i64]),
+    "tpb_gguf_gemv_q8n": (_i, [_vp, _vp, _i, _vp, _vp, _f, _i64, _i64, _vp, _i, _i, _i]),
     "tpb_peer_alloc": (_i, [_vp, _sz, C.POINTER(_vp), _vp]),
     "tpb_peer_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "tpb_peer_close": (_i, [_vp, _vp]),

@@ -275,11 +275,12 @@ class Backend:
         """Grouped dp4a GEMV: y[i][rows] = scale * (W @ x_hat[row_off+i]) for i < ng <= 8
         against the activations staged by ONE opGemvQuantizeX(x, n_total*cols)
         (backend.zig:1719-1735)."""
-        if dt != "q8_0":
-            raise NotImplementedError(f"GEMV weight format {dt!r} is outside this library's scope")
+        from ._lib import GGUF_FMT
+        if dt not in GGUF_FMT:
+            raise NotImplementedError(f"GEMV weight format {dt!r} is not implemented (q8_0, q4_0, q4_k, q5_k are)")
         assert self.q8_act is not None and self._q8_total == n_total * cols
         w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
-        rc = self.lib.tpb_q8_0_gemv_q8n(self.h, self._stream(), y.data_ptr(), w_dev.data_ptr(),
+        rc = self.lib.tpb_gguf_gemv_q8n(self.h, self._stream(), GGUF_FMT[dt], y.data_ptr(), w_dev.data_ptr(),
                                         float(scale), rows, cols, self.q8_act.data_ptr(), ng,
                                         row_off, n_total)
         self._check(rc)

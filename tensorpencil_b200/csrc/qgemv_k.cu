@@ -1,0 +1,425 @@
+// Decode GEMV for the other GGUF block formats a checkpoint mixes with Q8_0 -- q4_0,
+// q4_k and q5_k -- on the same streaming skeleton as the Q8_0 kernel (qgemv.cu): every
+// warp owns a contiguous range of weight rows and streams them, R rows at a time, into a
+// private shared-memory ring with 1-D bulk async copies (mbarrier completion, no
+// multicast); q8_1 activations (int8 + per-32-block scale) stay in shared memory for the
+// kernel's life; dp4a for the integer dots, f32 accumulation, warp butterfly, * scale.
+//
+// The unit of work of a lane is 64 consecutive elements (two q8_1 activation blocks):
+//   q4_0  a pair of 18-byte blocks (f16 d + 16 nibble bytes each; 36 bytes = 9 aligned
+//         words, the first block's nibbles need one funnel shift per word); element j of a
+//         block is the low nibble of byte j, element j+16 the high nibble; w = d*(n - 8);
+//   q4_k  a quarter of a 144-byte super-block (f16 d, f16 dmin, 12 bytes of 6-bit
+//         scales/mins, 128 nibble bytes): 32 bytes whose low nibbles are elements 0..31 of
+//         the quarter and high nibbles elements 32..63; w = d*sc*n - dmin*m per 32;
+//   q5_k  the same with a fifth bit per element from the 32-byte qh field (176 bytes).
+// Block layouts: src/core/quants.zig:9-16 (ggml's).  Reference kernels these stand in for:
+// src/gpu/cuda/elt.zig:2014-2110 (q4_0), :1831-1925 (q4_k), :1526-1713 (q5_k), dispatched
+// from Backend.opGemvQuantQ8N (src/gpu/cuda/backend.zig:1719-1735).
+//
+// With sumi = sum(n * xq) over a 32-block (exact, dp4a) and S = dx * sum(xq) precomputed
+// per activation block, the dequantised dot is
+//   q4_0:  d * (dx * sumi - 8 * S)
+//   q4_k / q5_k:  (d * sc) * (dx * sumi) - (dmin * m) * S
+// which is what the kernels accumulate in f32.
+#include <cuda_fp16.h>
+
+#include "tpb_internal.h"
+
+namespace {
+
+enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3 };
+
+constexpr int kUnitsPerChunk = 32;  // one 64-element unit per lane
+constexpr int kActPairBytes = 80;   // a unit's 64 activation bytes + 16 pad (bank-conflict-free 16-byte reads)
+constexpr long long kWaitLimitCycles = 2000000000ll;
+
+template <int FMT> struct Fmt;
+template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkBytes = 32 * 36; };     // 1152
+template <> struct Fmt<FMT_Q4_K> { static constexpr int kSb = 144, kChunkBytes = 8 * 144; };           // 1152
+template <> struct Fmt<FMT_Q5_K> { static constexpr int kSb = 176, kChunkBytes = 8 * 176; };           // 1408
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the limit ran out (status word written).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && clock64() - t0 > kWaitLimitCycles) {
+            atomicCAS(status, 0u, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+struct KGemvParams {
+    float *y;
+    const uint8_t *w;
+    const float *xd;   // activation block scales [ng][nblk]
+    const int8_t *xq;  // activation quants [ng][cols]
+    float scale;
+    int rows, cols, nblk;  // nblk = cols / 32
+    size_t row_bytes;
+    uint32_t *status;
+};
+
+__device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
+__device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, int a) { return (w >> (8 * a)) & 0xffu; }
+
+// 6-bit scale and min number `is` (0..7) of a q4_k / q5_k super-block; s0, s1, s2 are the
+// three words of the 12-byte scales field (ggml's get_scale_min_k4).
+__device__ __forceinline__ void scale_min_k4(int is, uint32_t s0, uint32_t s1, uint32_t s2, float &sc, float &mn) {
+    const int a = is & 3;
+    uint32_t s, m;
+    if (is < 4) {
+        s = byte_of(s0, a) & 63u;
+        m = byte_of(s1, a) & 63u;
+    } else {
+        s = (byte_of(s2, a) & 0xFu) | ((byte_of(s0, a) >> 6) << 4);
+        m = (byte_of(s2, a) >> 4) | ((byte_of(s1, a) >> 6) << 4);
+    }
+    sc = (float)s;
+    mn = (float)m;
+}
+
+template <int FMT, int M, int R>
+__global__ void __launch_bounds__(512, 1)
+kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
+    constexpr int kChunkBytes = Fmt<FMT>::kChunkBytes;
+    constexpr int kStageBytes = R * kChunkBytes;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5;
+    const int nblk = p.nblk;
+    const int cols = p.cols;
+    const int n_units = cols / 64;
+
+    // shared: [act q: M x n_units x 80][act d: M x nblk f32][act S = d * sum(q): M x nblk f32][rings][barriers]
+    const size_t act_row = (size_t)n_units * kActPairBytes;
+    int8_t *s_q = reinterpret_cast<int8_t *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)M * act_row);
+    float *s_s = s_d + (size_t)M * nblk;
+    uint8_t *ring0 = reinterpret_cast<uint8_t *>(s_s + (size_t)M * nblk);
+    uint8_t *ring = ring0 + (size_t)warp * stages * kStageBytes;
+    const uint32_t bars = smem_u32(ring0 + (size_t)n_warps * stages * kStageBytes) + warp * stages * 8;
+
+    if (lane == 0) {
+        for (int s = 0; s < stages; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * s), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int cpr = (n_units + kUnitsPerChunk - 1) / kUnitsPerChunk;  // chunks per row
+    const int gw = blockIdx.x * n_warps + warp;
+    const int GW = gridDim.x * n_warps;
+    const int my_r0 = (int)((long long)p.rows * gw / GW);
+    const int my_r1 = (int)((long long)p.rows * (gw + 1) / GW);
+    const int my_rg = (my_r1 - my_r0 + R - 1) / R;
+    const int total = my_rg * cpr;
+
+    auto issue = [&](int i) {  // lane 0 only
+        const int c = i % cpr;
+        const int st = i % stages;
+        const int row0 = my_r0 + (i / cpr) * R;
+        const int nrow = min(R, my_r1 - row0);
+        const int units = min(kUnitsPerChunk, n_units - c * kUnitsPerChunk);
+        // q4_0: 36 bytes per unit; k-quants: a super-block per 4 units (cols % 256 == 0)
+        const uint32_t bytes = FMT == FMT_Q4_0 ? (uint32_t)units * 36u : (uint32_t)(units / 4) * (uint32_t)(kChunkBytes / 8);
+        const uint32_t bar = bars + 8 * st;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)nrow)
+                     : "memory");
+        const uint32_t dst = smem_u32(ring + (size_t)st * kStageBytes);
+        for (int r = 0; r < nrow; r++)
+            bulk_g2s(dst + r * kChunkBytes, p.w + (size_t)(row0 + r) * p.row_bytes + (size_t)c * kChunkBytes, bytes, bar);
+    };
+
+    if (lane == 0)
+        for (int i = 0; i < stages - 1 && i < total; i++) issue(i);
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        const int per_row = cols / 16;
+        for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
+            const int m = i / per_row, c16 = i - m * per_row;
+            *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
+                __ldg(gq + i);
+        }
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+    }
+    __syncthreads();
+    // S[m][b] = d[m][b] * sum of the block's 32 quants
+    for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) {
+        const int m = i / nblk, b = i - m * nblk;
+        const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(b >> 1) * kActPairBytes + (b & 1) * 32);
+        const int4 t0 = a[0], t1 = a[1];
+        int s = 0;
+        s = __dp4a(t0.x, 0x01010101, s); s = __dp4a(t0.y, 0x01010101, s);
+        s = __dp4a(t0.z, 0x01010101, s); s = __dp4a(t0.w, 0x01010101, s);
+        s = __dp4a(t1.x, 0x01010101, s); s = __dp4a(t1.y, 0x01010101, s);
+        s = __dp4a(t1.z, 0x01010101, s); s = __dp4a(t1.w, 0x01010101, s);
+        s_s[i] = s_d[i] * (float)s;
+    }
+    __syncthreads();
+
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < total && ok; i++) {
+        if (lane == 0 && i + stages - 1 < total) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(i + stages - 1);
+        }
+        const int st = i % stages;
+        ok = mbar_wait(bars + 8 * st, (uint32_t)(i / stages) & 1u, p.status, (5u << 24) | (uint32_t)st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+
+        const int c = i % cpr;
+        const int row0 = my_r0 + (i / cpr) * R;
+        const int nrow = min(R, my_r1 - row0);
+        const int unit = c * kUnitsPerChunk + lane;
+        if (unit < n_units) {
+            // Decode this lane's 64 weights of each row: lo[8] / hi[8] = the nibbles (plus fifth
+            // bit) of elements 0..31 / 32..63 as bytes, and the two (scale, offset) pairs.
+            uint32_t lo[R][8], hi[R][8];
+            float ws0[R], ws1[R], wo0[R], wo1[R];  // acc += ws * (dx * sumi) - wo * S
+            const uint8_t *stage = ring + (size_t)st * kStageBytes;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (r < nrow) {
+                    if (FMT == FMT_Q4_0) {
+                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + lane * 36);
+                        uint32_t t[9];
+#pragma unroll
+                        for (int j = 0; j < 9; j++) t[j] = src[j];
+                        // block A: d = t[0] low half, nibble bytes 2..17; block B: d = t[4] high half, bytes 20..35
+                        uint32_t na[4], nb[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) na[j] = __funnelshift_r(t[j], t[j + 1], 16);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) nb[j] = t[5 + j];
+                        // unit elements 0..31 = block A (low nibbles 0..15, high 16..31); 32..63 = block B
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            lo[r][j] = na[j] & 0x0f0f0f0fu;
+                            lo[r][4 + j] = (na[j] >> 4) & 0x0f0f0f0fu;
+                            hi[r][j] = nb[j] & 0x0f0f0f0fu;
+                            hi[r][4 + j] = (nb[j] >> 4) & 0x0f0f0f0fu;
+                        }
+                        ws0[r] = f16lo(t[0]);
+                        ws1[r] = f16hi(t[4]);
+                        wo0[r] = 8.0f * ws0[r];
+                        wo1[r] = 8.0f * ws1[r];
+                    } else {
+                        constexpr int kSb = FMT == FMT_Q5_K ? 176 : 144;
+                        constexpr int kQs = FMT == FMT_Q5_K ? 48 : 16;
+                        const int j = lane & 3;  // quarter of the super-block
+                        const uint8_t *sb = stage + r * kChunkBytes + (lane >> 2) * kSb;
+                        const uint4 hdr = *reinterpret_cast<const uint4 *>(sb);
+                        const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j);
+                        const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j + 16);
+                        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                        for (int w = 0; w < 8; w++) {
+                            lo[r][w] = qw[w] & 0x0f0f0f0fu;
+                            hi[r][w] = (qw[w] >> 4) & 0x0f0f0f0fu;
+                        }
+                        if (FMT == FMT_Q5_K) {
+                            const uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16);
+                            const uint4 h1 = *reinterpret_cast<const uint4 *>(sb + 32);
+                            const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                            for (int w = 0; w < 8; w++) {
+                                lo[r][w] |= ((hw[w] >> (2 * j)) & 0x01010101u) << 4;
+                                hi[r][w] |= ((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4;
+                            }
+                        }
+                        const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
+                        float sc, mn;
+                        scale_min_k4(2 * j, hdr.y, hdr.z, hdr.w, sc, mn);
+                        ws0[r] = d * sc;
+                        wo0[r] = dmin * mn;
+                        scale_min_k4(2 * j + 1, hdr.y, hdr.z, hdr.w, sc, mn);
+                        ws1[r] = d * sc;
+                        wo1[r] = dmin * mn;
+                    }
+                } else {
+#pragma unroll
+                    for (int w = 0; w < 8; w++) lo[r][w] = hi[r][w] = 0;
+                    ws0[r] = ws1[r] = wo0[r] = wo1[r] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                uint32_t xq[16];
+                const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)unit * kActPairBytes);
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    const int4 t = a[v];
+                    xq[4 * v] = t.x; xq[4 * v + 1] = t.y; xq[4 * v + 2] = t.z; xq[4 * v + 3] = t.w;
+                }
+                const float2 d2 = *reinterpret_cast<const float2 *>(s_d + (size_t)m * nblk + 2 * unit);
+                const float2 s2 = *reinterpret_cast<const float2 *>(s_s + (size_t)m * nblk + 2 * unit);
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    int i0 = 0, i1 = 0;
+#pragma unroll
+                    for (int w = 0; w < 8; w++) i0 = __dp4a((int)lo[r][w], (int)xq[w], i0);
+#pragma unroll
+                    for (int w = 0; w < 8; w++) i1 = __dp4a((int)hi[r][w], (int)xq[8 + w], i1);
+                    float t = acc[r][m];
+                    t = fmaf(ws0[r], d2.x * __int2float_rn(i0), t);
+                    t = fmaf(-wo0[r], s2.x, t);
+                    t = fmaf(ws1[r], d2.y * __int2float_rn(i1), t);
+                    t = fmaf(-wo1[r], s2.y, t);
+                    acc[r][m] = t;
+                }
+            }
+        }
+        __syncwarp();
+
+        if (c == cpr - 1) {
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    float v = acc[r][m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0 && r < nrow) p.y[(size_t)m * p.rows + row0 + r] = v * p.scale;
+                    acc[r][m] = 0.0f;
+                }
+        }
+    }
+}
+
+template <int FMT, int M>
+int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
+    constexpr int R = 2;
+    constexpr int kStage = R * Fmt<FMT>::kChunkBytes;
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 8;
+    // Warps per CTA: every warp owns a contiguous range of whole rows; among the counts that
+    // fit with >= 2 stages take the one whose ranges divide most evenly (ties: more warps).
+    int warps = 0, stages = 0;
+    double best_eff = -1.0;
+    for (int w = 16; w >= 4; w--) {
+        int s_fit = 0;
+        for (int s = 4; s >= 2; s--)
+            if (act + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit) {
+                s_fit = s;
+                break;
+            }
+        if (s_fit == 0) continue;
+        const double per_warp = (double)p.rows / ((double)h->sm_count * w);
+        const double eff = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : per_warp;
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            warps = w;
+            stages = s_fit;
+        }
+    }
+    if (stages == 0)
+        return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: %d activation rows of %d columns do not fit shared memory",
+                        M, p.cols);
+    const size_t smem = act + (size_t)warps * stages * kStage + (size_t)warps * stages * 8 + 64;
+    int grid = (int)(((long long)p.rows + (long long)warps * R - 1) / ((long long)warps * R));
+    if (grid < 1) grid = 1;
+    if (grid > h->sm_count) grid = h->sm_count;
+    auto kern = kquant_gemv_q8n_kernel<FMT, M, R>;
+    TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, st, p, stages));
+    return TPB_OK;
+}
+
+template <int FMT>
+int launch_fmt(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int ng) {
+    switch (ng) {
+        case 1: return launch_fmt_m<FMT, 1>(h, st, p);
+        case 2: return launch_fmt_m<FMT, 2>(h, st, p);
+        case 3: return launch_fmt_m<FMT, 3>(h, st, p);
+        case 4: return launch_fmt_m<FMT, 4>(h, st, p);
+        case 5: return launch_fmt_m<FMT, 5>(h, st, p);
+        case 6: return launch_fmt_m<FMT, 6>(h, st, p);
+        case 7: return launch_fmt_m<FMT, 7>(h, st, p);
+        case 8: return launch_fmt_m<FMT, 8>(h, st, p);
+    }
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: ng out of range");
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t tpb_gguf_row_bytes(int fmt, int64_t cols) {
+    switch (fmt) {
+        case TPB_GGUF_Q8_0: return (size_t)(cols / 32) * 34;
+        case TPB_GGUF_Q4_0: return (size_t)(cols / 32) * 18;
+        case TPB_GGUF_Q4_K: return (size_t)(cols / 256) * 144;
+        case TPB_GGUF_Q5_K: return (size_t)(cols / 256) * 176;
+    }
+    return 0;
+}
+
+int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, const void *w, float scale,
+                      int64_t rows, int64_t cols, const void *xq, int ng, int row_off, int n_total) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    if (fmt == TPB_GGUF_Q8_0)
+        return tpb_q8_0_gemv_q8n(h, stream, y, w, scale, rows, cols, xq, ng, row_off, n_total);
+    TPB_CHECK_ARG(h, fmt == TPB_GGUF_Q4_0 || fmt == TPB_GGUF_Q4_K || fmt == TPB_GGUF_Q5_K,
+                  "gguf_gemv: unsupported format %d (q8_0, q4_0, q4_k, q5_k)", fmt);
+    TPB_CHECK_ARG(h, y && w && xq, "gguf_gemv: null pointer");
+    TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 31) && cols > 0 && cols % 256 == 0 && cols < (1ll << 24),
+                  "gguf_gemv: cols must be a multiple of 256 (cols=%lld)", (long long)cols);
+    TPB_CHECK_ARG(h, ng >= 1 && ng <= 8 && row_off >= 0 && row_off + ng <= n_total,
+                  "gguf_gemv: need 1 <= ng <= 8 and row_off + ng <= n_total");
+    TPB_CHECK_ARG(h, tpb_aligned16(w) && tpb_aligned16(xq), "gguf_gemv: w and xq must be 16-byte aligned");
+    if (rows == 0) return TPB_OK;
+    KGemvParams p;
+    const int nblk = (int)(cols / 32);
+    p.y = y;
+    p.w = reinterpret_cast<const uint8_t *>(w);
+    p.xd = reinterpret_cast<const float *>(xq) + (size_t)row_off * nblk;
+    p.xq = reinterpret_cast<const int8_t *>(xq) + (size_t)n_total * nblk * 4 + (size_t)row_off * cols;
+    p.scale = scale;
+    p.rows = (int)rows;
+    p.cols = (int)cols;
+    p.nblk = nblk;
+    p.row_bytes = tpb_gguf_row_bytes(fmt, cols);
+    p.status = h->d_status;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (fmt) {
+        case TPB_GGUF_Q4_0: return launch_fmt<FMT_Q4_0>(h, st, p, ng);
+        case TPB_GGUF_Q4_K: return launch_fmt<FMT_Q4_K>(h, st, p, ng);
+        default: return launch_fmt<FMT_Q5_K>(h, st, p, ng);
+    }
+}
+
+}  // extern "C"

@@ -130,3 +130,26 @@ def dit_block_weights(block: int, bits: int, seed: int = 1003, hidden: int = DIT
         out[name] = {"w": w["w_packed"] if bits == 4 else w["w_i8"], "w_scale": w["w_scale"],
                      "n": n, "k": k, "bits": bits}
     return out
+
+
+GGUF_BLOCK = {"q8_0": (32, 34), "q4_0": (32, 18), "q4_k": (256, 144), "q5_k": (256, 176), "q6_k": (256, 210)}
+
+
+def gguf_weights(fmt: str, n: int, k: int, seed: int) -> np.ndarray:
+    """Random block-quantised weight rows [n][row_bytes] with every block's f16 scale
+    fields pinned to small finite values (random bit patterns include NaN/inf), the way the
+    reference's device tests build theirs (src/gpu/cuda/backend.zig:3356-3377): d = 0.05,
+    dmin = 0.02."""
+    elems, nbytes = GGUF_BLOCK[fmt]
+    rng = np.random.default_rng(seed + 7919)
+    w = rng.integers(0, 256, size=(n, k // elems, nbytes), dtype=np.uint8)
+    d16 = np.frombuffer(np.uint16(0x2A66).tobytes(), np.uint8)
+    m16 = np.frombuffer(np.uint16(0x251F).tobytes(), np.uint8)
+    if fmt in ("q8_0", "q4_0"):
+        w[:, :, 0:2] = d16
+    elif fmt in ("q4_k", "q5_k"):
+        w[:, :, 0:2] = d16
+        w[:, :, 2:4] = m16
+    elif fmt == "q6_k":
+        w[:, :, 208:210] = d16
+    return w.reshape(n, -1)

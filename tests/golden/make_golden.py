@@ -6,7 +6,8 @@ Two kinds of fixture live here:
   a TensorPencil checkout (``--reference``, default ``/root/reference``):
   the ComfyUI int4 ConvRot dequant fixture (``testdata/int4_convrot_*``, used by
   the test in ``src/ops/convrot.zig:148-192``) and the ggml Q8_0 dequant block
-  with its expected f32 bit patterns (``src/core/quants_fixtures.zig:6-15``);
+  with its expected f32 bit patterns (``src/core/quants_fixtures.zig:6-15``) and the
+  q4_k / q5_k / q6_k super-blocks of the same file;
 * small seeded input/output vectors produced by the CPU oracle, so a change in
   the oracle's arithmetic shows up as a diff against a committed file.
 
@@ -39,6 +40,11 @@ def copy_reference_fixtures(ref: str) -> None:
         json.dump({"source": "src/core/quants_fixtures.zig:6-15",
                    "block_bytes": table("q8_0_block"),
                    "expected_f32_bits": table("q8_0_expected_bits")}, f, indent=1)
+    # k-quant super-blocks (256 elements) with ggml's expected dequantisation
+    with open(os.path.join(HERE, "kquant_blocks.json"), "w") as f:
+        json.dump({"source": "src/core/quants_fixtures.zig:18-160",
+                   **{fmt: {"block_bytes": table(fmt + "_block"), "expected_f32_bits": table(fmt + "_expected_bits")}
+                      for fmt in ("q4_k", "q5_k", "q6_k")}}, f)
 
 
 def oracle_vectors() -> None:

@@ -312,3 +312,40 @@ def test_gated_add():
     d = np.ones((2, 3), np.float32) * 2
     g = np.array([0.5, -1, 0], np.float32)
     assert np.array_equal(oracle.gated_add(x, d, g), x + g * d)
+
+
+# ---------------------------------------------------------------------------------
+# k-quant decoders pinned to the reference's golden super-blocks
+# (src/core/quants_fixtures.zig, checked bit for bit as src/core/quants.zig:104-140 does)
+# ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "q6_k"])
+def test_kquant_dequant_matches_reference_golden_block(fmt):
+    import json
+    import os
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "kquant_blocks.json")))[fmt]
+    block = np.array(g["block_bytes"], np.uint8)
+    want = np.array(g["expected_f32_bits"], np.uint32)
+    assert block.size == oracle.gguf_row_bytes(fmt, 256)
+    got = oracle.gguf_dequant_row(fmt, block, 256)
+    assert np.array_equal(got.view(np.uint32), want)
+
+
+def test_q4_0_and_generic_gemv_truth():
+    rng = np.random.default_rng(5)
+    # q4_0: d = 0.5, nibbles 0..15 -> (n - 8) * d, low nibbles first
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(0.5).tobytes(), np.uint8)
+    blk[2:18] = np.arange(16, dtype=np.uint8) | ((15 - np.arange(16, dtype=np.uint8)) << 4)
+    got = oracle.gguf_dequant_row("q4_0", blk, 32)
+    assert np.array_equal(got[:16], (np.arange(16) - 8) * 0.5) and np.array_equal(got[16:], (7 - np.arange(16)) * 0.5)
+    # the generic GEMV truth agrees with the Q8_0-specific one
+    g = synth.q8_0_gemv(m=2, n=8, k=512, seed=9)
+    a = oracle.gguf_gemv_q8("q8_0", g["w"], 8, 512, g["x"])
+    b = oracle.q8_0_gemv_f64(g["w"], 8, 512, oracle_q8_1_dequant(g["x"]))
+    assert np.allclose(a, b, rtol=1e-6, atol=1e-6)
+
+
+def oracle_q8_1_dequant(x):
+    d, qs = oracle.q8_1_quantize(x.reshape(-1))
+    return (np.repeat(d, 32) * qs.astype(np.float32)).reshape(x.shape)
