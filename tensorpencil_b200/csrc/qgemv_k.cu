@@ -30,14 +30,16 @@ namespace {
 
 enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3 };
 
-constexpr int kUnitsPerChunk = 32;  // one 64-element unit per lane
+constexpr int kUnitsPerLane = 2;                    // 64-element units a lane takes per pipeline stage
+constexpr int kUnitsPerChunk = 32 * kUnitsPerLane;
 constexpr int kActPairBytes = 80;   // a unit's 64 activation bytes + 16 pad (bank-conflict-free 16-byte reads)
 constexpr long long kWaitLimitCycles = 2000000000ll;
 
 template <int FMT> struct Fmt;
-template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkBytes = 32 * 36; };     // 1152
-template <> struct Fmt<FMT_Q4_K> { static constexpr int kSb = 144, kChunkBytes = 8 * 144; };           // 1152
-template <> struct Fmt<FMT_Q5_K> { static constexpr int kSb = 176, kChunkBytes = 8 * 176; };           // 1408
+// bytes of one 64-element unit (a quarter super-block for the k-quants) and of a chunk of one row
+template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
+template <> struct Fmt<FMT_Q4_K> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };   // 144 / 4
+template <> struct Fmt<FMT_Q5_K> { static constexpr int kUnitBytes = 44, kChunkBytes = kUnitsPerChunk * 44; };   // 176 / 4
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -81,6 +83,12 @@ struct KGemvParams {
     uint32_t *status;
 };
 
+// unsigned bytes of a times signed bytes of b
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
 __device__ __forceinline__ uint32_t byte_of(uint32_t w, int a) { return (w >> (8 * a)) & 0xffu; }
@@ -145,8 +153,8 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         const int row0 = my_r0 + (i / cpr) * R;
         const int nrow = min(R, my_r1 - row0);
         const int units = min(kUnitsPerChunk, n_units - c * kUnitsPerChunk);
-        // q4_0: 36 bytes per unit; k-quants: a super-block per 4 units (cols % 256 == 0)
-        const uint32_t bytes = FMT == FMT_Q4_0 ? (uint32_t)units * 36u : (uint32_t)(units / 4) * (uint32_t)(kChunkBytes / 8);
+        // whole super-blocks for the k-quants: the unit count is a multiple of 4 (cols % 256 == 0)
+        const uint32_t bytes = (uint32_t)units * (uint32_t)Fmt<FMT>::kUnitBytes;
         const uint32_t bar = bars + 8 * st;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)nrow)
                      : "memory");
@@ -204,10 +212,15 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         const int c = i % cpr;
         const int row0 = my_r0 + (i / cpr) * R;
         const int nrow = min(R, my_r1 - row0);
-        const int unit = c * kUnitsPerChunk + lane;
-        if (unit < n_units) {
-            // Decode this lane's 64 weights of each row: lo[8] / hi[8] = the nibbles (plus fifth
-            // bit) of elements 0..31 / 32..63 as bytes, and the two (scale, offset) pairs.
+#pragma unroll
+        for (int t = 0; t < kUnitsPerLane; t++) {
+            const int ul = lane + 32 * t;                 // unit within the chunk
+            const int unit = c * kUnitsPerChunk + ul;
+            if (unit >= n_units) continue;
+            // Decode this lane's 64 weights of each row: lo[8] = elements 0..31 as bytes (nibble,
+            // plus the fifth bit for q5_k), hi[8] = elements 32..63 as bytes times 16 (the high
+            // nibbles left where they are: one AND instead of shift + AND; the dot product is
+            // then an exact multiple of 16), and the two (scale, offset) pairs.
             uint32_t lo[R][8], hi[R][8];
             float ws0[R], ws1[R], wo0[R], wo1[R];  // acc += ws * (dx * sumi) - wo * S
             const uint8_t *stage = ring + (size_t)st * kStageBytes;
@@ -215,33 +228,36 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
             for (int r = 0; r < R; r++) {
                 if (r < nrow) {
                     if (FMT == FMT_Q4_0) {
-                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + lane * 36);
-                        uint32_t t[9];
+                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + ul * 36);
+                        uint32_t tw[9];
 #pragma unroll
-                        for (int j = 0; j < 9; j++) t[j] = src[j];
-                        // block A: d = t[0] low half, nibble bytes 2..17; block B: d = t[4] high half, bytes 20..35
+                        for (int j = 0; j < 9; j++) tw[j] = src[j];
+                        // block A: d = tw[0] low half, nibble bytes 2..17; block B: d = tw[4] high half, bytes 20..35
                         uint32_t na[4], nb[4];
 #pragma unroll
-                        for (int j = 0; j < 4; j++) na[j] = __funnelshift_r(t[j], t[j + 1], 16);
+                        for (int j = 0; j < 4; j++) na[j] = __funnelshift_r(tw[j], tw[j + 1], 16);
 #pragma unroll
-                        for (int j = 0; j < 4; j++) nb[j] = t[5 + j];
-                        // unit elements 0..31 = block A (low nibbles 0..15, high 16..31); 32..63 = block B
+                        for (int j = 0; j < 4; j++) nb[j] = tw[5 + j];
+                        // a block's elements 0..15 are its low nibbles, 16..31 its high nibbles; the
+                        // high-nibble words carry a factor 16 that ws/16 below takes back
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            lo[r][j] = na[j] & 0x0f0f0f0fu;
-                            lo[r][4 + j] = (na[j] >> 4) & 0x0f0f0f0fu;
-                            hi[r][j] = nb[j] & 0x0f0f0f0fu;
-                            hi[r][4 + j] = (nb[j] >> 4) & 0x0f0f0f0fu;
+                            lo[r][j] = (na[j] & 0x0f0f0f0fu) << 4;
+                            lo[r][4 + j] = na[j] & 0xf0f0f0f0u;
+                            hi[r][j] = (nb[j] & 0x0f0f0f0fu) << 4;
+                            hi[r][4 + j] = nb[j] & 0xf0f0f0f0u;
                         }
-                        ws0[r] = f16lo(t[0]);
-                        ws1[r] = f16hi(t[4]);
+                        ws0[r] = f16lo(tw[0]);
+                        ws1[r] = f16hi(tw[4]);
                         wo0[r] = 8.0f * ws0[r];
                         wo1[r] = 8.0f * ws1[r];
+                        ws0[r] *= 0.0625f;
+                        ws1[r] *= 0.0625f;
                     } else {
                         constexpr int kSb = FMT == FMT_Q5_K ? 176 : 144;
                         constexpr int kQs = FMT == FMT_Q5_K ? 48 : 16;
-                        const int j = lane & 3;  // quarter of the super-block
-                        const uint8_t *sb = stage + r * kChunkBytes + (lane >> 2) * kSb;
+                        const int j = lane & 3;  // quarter of the super-block (32 t is a multiple of 4)
+                        const uint8_t *sb = stage + r * kChunkBytes + (ul >> 2) * kSb;
                         const uint4 hdr = *reinterpret_cast<const uint4 *>(sb);
                         const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j);
                         const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j + 16);
@@ -249,16 +265,18 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
 #pragma unroll
                         for (int w = 0; w < 8; w++) {
                             lo[r][w] = qw[w] & 0x0f0f0f0fu;
-                            hi[r][w] = (qw[w] >> 4) & 0x0f0f0f0fu;
+                            hi[r][w] = qw[w] & 0xf0f0f0f0u;
                         }
                         if (FMT == FMT_Q5_K) {
+                            // fifth bits: 16 for the low elements; 16 * 16 = 256 does not fit a byte for
+                            // the (x16) high elements, so those go back to plain values
                             const uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16);
                             const uint4 h1 = *reinterpret_cast<const uint4 *>(sb + 32);
                             const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
                             for (int w = 0; w < 8; w++) {
                                 lo[r][w] |= ((hw[w] >> (2 * j)) & 0x01010101u) << 4;
-                                hi[r][w] |= ((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4;
+                                hi[r][w] = (hi[r][w] >> 4) | (((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4);
                             }
                         }
                         const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
@@ -267,7 +285,7 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                         ws0[r] = d * sc;
                         wo0[r] = dmin * mn;
                         scale_min_k4(2 * j + 1, hdr.y, hdr.z, hdr.w, sc, mn);
-                        ws1[r] = d * sc;
+                        ws1[r] = d * sc * (FMT == FMT_Q5_K ? 1.0f : 0.0625f);
                         wo1[r] = dmin * mn;
                     }
                 } else {
@@ -282,8 +300,8 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                 const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)unit * kActPairBytes);
 #pragma unroll
                 for (int v = 0; v < 4; v++) {
-                    const int4 t = a[v];
-                    xq[4 * v] = t.x; xq[4 * v + 1] = t.y; xq[4 * v + 2] = t.z; xq[4 * v + 3] = t.w;
+                    const int4 tt = a[v];
+                    xq[4 * v] = tt.x; xq[4 * v + 1] = tt.y; xq[4 * v + 2] = tt.z; xq[4 * v + 3] = tt.w;
                 }
                 const float2 d2 = *reinterpret_cast<const float2 *>(s_d + (size_t)m * nblk + 2 * unit);
                 const float2 s2 = *reinterpret_cast<const float2 *>(s_s + (size_t)m * nblk + 2 * unit);
@@ -291,15 +309,15 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                 for (int r = 0; r < R; r++) {
                     int i0 = 0, i1 = 0;
 #pragma unroll
-                    for (int w = 0; w < 8; w++) i0 = __dp4a((int)lo[r][w], (int)xq[w], i0);
+                    for (int w = 0; w < 8; w++) i0 = dp4a_us(lo[r][w], xq[w], i0);
 #pragma unroll
-                    for (int w = 0; w < 8; w++) i1 = __dp4a((int)hi[r][w], (int)xq[8 + w], i1);
-                    float t = acc[r][m];
-                    t = fmaf(ws0[r], d2.x * __int2float_rn(i0), t);
-                    t = fmaf(-wo0[r], s2.x, t);
-                    t = fmaf(ws1[r], d2.y * __int2float_rn(i1), t);
-                    t = fmaf(-wo1[r], s2.y, t);
-                    acc[r][m] = t;
+                    for (int w = 0; w < 8; w++) i1 = dp4a_us(hi[r][w], xq[8 + w], i1);
+                    float tacc = acc[r][m];
+                    tacc = fmaf(ws0[r], d2.x * __int2float_rn(i0), tacc);
+                    tacc = fmaf(-wo0[r], s2.x, tacc);
+                    tacc = fmaf(ws1[r], d2.y * __int2float_rn(i1), tacc);
+                    tacc = fmaf(-wo1[r], s2.y, tacc);
+                    acc[r][m] = tacc;
                 }
             }
         }
