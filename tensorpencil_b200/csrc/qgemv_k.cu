@@ -338,6 +338,254 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
     }
 }
 
+// ---- q6_k -----------------------------------------------------------------------------
+//
+// 210-byte super-blocks (ql[128] low nibbles, qh[64] two high bits, 16 int8 scales, f16 d;
+// w = d * sc * (q - 32)) are only 2-byte aligned and a row of them is in general not a
+// multiple of 16 bytes, while a bulk copy needs 16-byte aligned addresses and sizes.  A
+// chunk is 8 super-blocks (1680 bytes = 105 x 16), so within a row every chunk starts at
+// the same offset `mis` modulo 16: the copy starts `mis` bytes early and is rounded up to
+// 16, and the lanes index from stage + mis.  (The rounding can read up to 14 bytes past a
+// row -- the next row's, or, after the last row, whatever follows the weights in the same
+// allocation; those bytes are never used.)  Fields are fetched as aligned words and funnel-
+// shifted by the (even) byte offset.
+//
+// A lane's unit is 32 elements of one super-block: half n (0/1), eight positions
+// l = 8 lq .. 8 lq + 7 of that half, and the four 32-element strides p -- y[128n + 32p + l].
+// Each of the four 8-element runs lies inside one q8_1 activation block.
+constexpr int kQ6Sb = 210;
+constexpr int kQ6ChunkSb = 8;
+constexpr int kQ6ChunkBytes = kQ6ChunkSb * kQ6Sb;     // 1680
+constexpr int kQ6RowStage = kQ6ChunkBytes + 16 + 16;  // + alignment slack + words read past the last field
+
+// 8 bytes at byte offset `off` (even) from the 4-byte aligned `base`
+__device__ __forceinline__ uint2 ld8_unaligned(const uint8_t *base, int off) {
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(base + (off & ~3));
+    const uint32_t sh = (uint32_t)(off & 3) * 8u;  // 0 or 16
+    const uint32_t a = w[0], b = w[1], c = w[2];
+    return make_uint2(__funnelshift_r(a, b, sh), __funnelshift_r(b, c, sh));
+}
+
+template <int M, int R>
+__global__ void __launch_bounds__(512, 1)
+q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
+    constexpr int kStageBytes = R * kQ6RowStage;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5;
+    const int nblk = p.nblk;
+    const int cols = p.cols;
+    const int n_units = cols / 64;
+    const int n_sb = cols / 256;
+
+    const size_t act_row = (size_t)n_units * kActPairBytes;
+    int8_t *s_q = reinterpret_cast<int8_t *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)M * act_row);
+    uint8_t *ring0 = reinterpret_cast<uint8_t *>(s_d + (size_t)M * nblk);
+    uint8_t *ring = ring0 + (size_t)warp * stages * kStageBytes;
+    const uint32_t bars = smem_u32(ring0 + (size_t)n_warps * stages * kStageBytes) + warp * stages * 8;
+
+    if (lane == 0) {
+        for (int s = 0; s < stages; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * s), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int cpr = (n_sb + kQ6ChunkSb - 1) / kQ6ChunkSb;
+    const int gw = blockIdx.x * n_warps + warp;
+    const int GW = gridDim.x * n_warps;
+    const int my_r0 = (int)((long long)p.rows * gw / GW);
+    const int my_r1 = (int)((long long)p.rows * (gw + 1) / GW);
+    const int my_rg = (my_r1 - my_r0 + R - 1) / R;
+    const int total = my_rg * cpr;
+
+    auto issue = [&](int i) {  // lane 0 only
+        const int c = i % cpr;
+        const int st = i % stages;
+        const int row0 = my_r0 + (i / cpr) * R;
+        const int nrow = min(R, my_r1 - row0);
+        const int sbs = min(kQ6ChunkSb, n_sb - c * kQ6ChunkSb);
+        const uint32_t bar = bars + 8 * st;
+        uint32_t tx = 0;
+        for (int r = 0; r < nrow; r++) {
+            const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
+            tx += (mis + (uint32_t)sbs * kQ6Sb + 15u) & ~15u;
+        }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx) : "memory");
+        const uint32_t dst = smem_u32(ring + (size_t)st * kStageBytes);
+        for (int r = 0; r < nrow; r++) {
+            const size_t goff = (size_t)(row0 + r) * p.row_bytes + (size_t)c * kQ6ChunkBytes;
+            const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
+            const uint32_t bytes = (mis + (uint32_t)sbs * kQ6Sb + 15u) & ~15u;
+            bulk_g2s(dst + r * kQ6RowStage, p.w + goff - mis, bytes, bar);
+        }
+    };
+
+    if (lane == 0)
+        for (int i = 0; i < stages - 1 && i < total; i++) issue(i);
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        const int per_row = cols / 16;
+        for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
+            const int m = i / per_row, c16 = i - m * per_row;
+            *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
+                __ldg(gq + i);
+        }
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+    }
+    __syncthreads();
+
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < total && ok; i++) {
+        if (lane == 0 && i + stages - 1 < total) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(i + stages - 1);
+        }
+        const int st = i % stages;
+        ok = mbar_wait(bars + 8 * st, (uint32_t)(i / stages) & 1u, p.status, (6u << 24) | (uint32_t)st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+
+        const int c = i % cpr;
+        const int row0 = my_r0 + (i / cpr) * R;
+        const int nrow = min(R, my_r1 - row0);
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+            const int ul = lane + 32 * t;              // 64 lane-units per chunk: 8 per super-block
+            const int sb_l = ul >> 3;
+            const int sb = c * kQ6ChunkSb + sb_l;
+            if (sb >= n_sb) continue;
+            const int n = (ul >> 2) & 1, lq = ul & 3;
+            // q values of the four runs as unsigned bytes (0..63) and their scales
+            uint32_t qv[R][4][2];
+            float wsc[R][4];
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (r < nrow) {
+                    const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
+                    const uint8_t *base = ring + (size_t)st * kStageBytes + r * kQ6RowStage;  // 16-byte aligned
+                    const int o = (int)mis + sb_l * kQ6Sb;                                    // super-block offset (even)
+                    const uint2 l0 = ld8_unaligned(base, o + 64 * n + 8 * lq);        // low nibbles: run 0, high: run 2
+                    const uint2 l1 = ld8_unaligned(base, o + 64 * n + 32 + 8 * lq);   // low: run 1, high: run 3
+                    const uint2 hb = ld8_unaligned(base, o + 128 + 32 * n + 8 * lq);  // two high bits of runs 0..3
+                    qv[r][0][0] = (l0.x & 0x0f0f0f0fu) | ((hb.x & 0x03030303u) << 4);
+                    qv[r][0][1] = (l0.y & 0x0f0f0f0fu) | ((hb.y & 0x03030303u) << 4);
+                    qv[r][1][0] = (l1.x & 0x0f0f0f0fu) | (((hb.x >> 2) & 0x03030303u) << 4);
+                    qv[r][1][1] = (l1.y & 0x0f0f0f0fu) | (((hb.y >> 2) & 0x03030303u) << 4);
+                    qv[r][2][0] = ((l0.x >> 4) & 0x0f0f0f0fu) | (((hb.x >> 4) & 0x03030303u) << 4);
+                    qv[r][2][1] = ((l0.y >> 4) & 0x0f0f0f0fu) | (((hb.y >> 4) & 0x03030303u) << 4);
+                    qv[r][3][0] = ((l1.x >> 4) & 0x0f0f0f0fu) | (((hb.x >> 6) & 0x03030303u) << 4);
+                    qv[r][3][1] = ((l1.y >> 4) & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
+                    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(base + o + 208)));
+                    const int8_t *sc = reinterpret_cast<const int8_t *>(base + o + 192 + 8 * n + (lq >> 1));
+#pragma unroll
+                    for (int pp = 0; pp < 4; pp++) wsc[r][pp] = d * (float)sc[2 * pp];
+                } else {
+#pragma unroll
+                    for (int pp = 0; pp < 4; pp++) {
+                        qv[r][pp][0] = qv[r][pp][1] = 0;
+                        wsc[r][pp] = 0.0f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+#pragma unroll
+                for (int pp = 0; pp < 4; pp++) {
+                    // activation elements 256 sb + 128 n + 32 pp + 8 lq .. + 7
+                    const int e = 256 * sb + 128 * n + 32 * pp + 8 * lq;
+                    const int2 xv = *reinterpret_cast<const int2 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
+                    const float dx = s_d[(size_t)m * nblk + (e >> 5)];
+                    int sx = __dp4a(xv.x, 0x01010101, 0);
+                    sx = __dp4a(xv.y, 0x01010101, sx);
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        int sq = dp4a_us(qv[r][pp][0], (uint32_t)xv.x, 0);
+                        sq = dp4a_us(qv[r][pp][1], (uint32_t)xv.y, sq);
+                        acc[r][m] = fmaf(wsc[r][pp], dx * __int2float_rn(sq - 32 * sx), acc[r][m]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+
+        if (c == cpr - 1) {
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    float v = acc[r][m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0 && r < nrow) p.y[(size_t)m * p.rows + row0 + r] = v * p.scale;
+                    acc[r][m] = 0.0f;
+                }
+        }
+    }
+}
+
+template <int M>
+int launch_q6k_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
+    constexpr int R = 2;
+    constexpr int kStage = R * kQ6RowStage;
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 4;
+    int warps = 0, stages = 0;
+    double best_eff = -1.0;
+    for (int w = 16; w >= 4; w--) {
+        int s_fit = 0;
+        for (int s = 4; s >= 2; s--)
+            if (act + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit) {
+                s_fit = s;
+                break;
+            }
+        if (s_fit == 0) continue;
+        const double per_warp = (double)p.rows / ((double)h->sm_count * w);
+        const double eff = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : per_warp;
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            warps = w;
+            stages = s_fit;
+        }
+    }
+    if (stages == 0)
+        return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: %d activation rows of %d columns do not fit shared memory",
+                        M, p.cols);
+    const size_t smem = act + (size_t)warps * stages * kStage + (size_t)warps * stages * 8 + 64;
+    int grid = (int)(((long long)p.rows + (long long)warps * R - 1) / ((long long)warps * R));
+    if (grid < 1) grid = 1;
+    if (grid > h->sm_count) grid = h->sm_count;
+    auto kern = q6k_gemv_q8n_kernel<M, R>;
+    TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, st, p, stages));
+    return TPB_OK;
+}
+
+int launch_q6k(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int ng) {
+    switch (ng) {
+        case 1: return launch_q6k_m<1>(h, st, p);
+        case 2: return launch_q6k_m<2>(h, st, p);
+        case 3: return launch_q6k_m<3>(h, st, p);
+        case 4: return launch_q6k_m<4>(h, st, p);
+        case 5: return launch_q6k_m<5>(h, st, p);
+        case 6: return launch_q6k_m<6>(h, st, p);
+        case 7: return launch_q6k_m<7>(h, st, p);
+        case 8: return launch_q6k_m<8>(h, st, p);
+    }
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: ng out of range");
+}
+
 template <int FMT, int M>
 int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     constexpr int R = 2;
@@ -402,6 +650,7 @@ size_t tpb_gguf_row_bytes(int fmt, int64_t cols) {
         case TPB_GGUF_Q4_0: return (size_t)(cols / 32) * 18;
         case TPB_GGUF_Q4_K: return (size_t)(cols / 256) * 144;
         case TPB_GGUF_Q5_K: return (size_t)(cols / 256) * 176;
+        case TPB_GGUF_Q6_K: return (size_t)(cols / 256) * 210;
     }
     return 0;
 }
@@ -411,8 +660,8 @@ int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, co
     if (!h) return TPB_ERR_INVALID_ARG;
     if (fmt == TPB_GGUF_Q8_0)
         return tpb_q8_0_gemv_q8n(h, stream, y, w, scale, rows, cols, xq, ng, row_off, n_total);
-    TPB_CHECK_ARG(h, fmt == TPB_GGUF_Q4_0 || fmt == TPB_GGUF_Q4_K || fmt == TPB_GGUF_Q5_K,
-                  "gguf_gemv: unsupported format %d (q8_0, q4_0, q4_k, q5_k)", fmt);
+    TPB_CHECK_ARG(h, fmt == TPB_GGUF_Q4_0 || fmt == TPB_GGUF_Q4_K || fmt == TPB_GGUF_Q5_K || fmt == TPB_GGUF_Q6_K,
+                  "gguf_gemv: unsupported format %d (q8_0, q4_0, q4_k, q5_k, q6_k)", fmt);
     TPB_CHECK_ARG(h, y && w && xq, "gguf_gemv: null pointer");
     TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 31) && cols > 0 && cols % 256 == 0 && cols < (1ll << 24),
                   "gguf_gemv: cols must be a multiple of 256 (cols=%lld)", (long long)cols);
@@ -436,6 +685,7 @@ int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, co
     switch (fmt) {
         case TPB_GGUF_Q4_0: return launch_fmt<FMT_Q4_0>(h, st, p, ng);
         case TPB_GGUF_Q4_K: return launch_fmt<FMT_Q4_K>(h, st, p, ng);
+        case TPB_GGUF_Q6_K: return launch_q6k(h, st, p, ng);
         default: return launch_fmt<FMT_Q5_K>(h, st, p, ng);
     }
 }
