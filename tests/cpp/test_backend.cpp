@@ -1,0 +1,146 @@
+// GPU test of the C++ Backend mirror (include/tpb200.hpp), written the way the
+// reference's device tests are (src/gpu/cuda/kernels.zig:2557-2701,
+// src/gpu/cuda/backend.zig:3727-3792): host weights and activations in, one op
+// sequence through the Backend, results compared with the CPU checker.
+// The checker (oracle/) is test infrastructure: it is linked here and nowhere else.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+
+#include "tpb200.hpp"
+extern "C" {
+#include "tpb_oracle.h"
+}
+
+static int failures = 0;
+#define EXPECT(cond, ...)                       \
+    do {                                        \
+        if (!(cond)) {                          \
+            std::printf("FAIL %s:%d: ", __FILE__, __LINE__); \
+            std::printf(__VA_ARGS__);           \
+            std::printf("\n");                  \
+            failures++;                         \
+        }                                       \
+    } while (0)
+
+static void convrot_linear(tpb::Backend &be, int bits, size_t m, size_t n, size_t k, unsigned seed) {
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::uniform_real_distribution<float> us(1e-3f, 1e-2f);
+    std::vector<float> x(m * k), ws(n);
+    for (auto &v : x) v = nd(rng);
+    for (size_t i = 0; i < m; i++) x[i * k + 7] *= 30.f;  // an outlier channel, what the rotation is for
+    for (auto &v : ws) v = us(rng);
+    std::vector<int8_t> w(n * k);
+    const int lo = bits == 4 ? -8 : -127, hi = bits == 4 ? 7 : 127;
+    std::uniform_int_distribution<int> wi(lo, hi);
+    for (auto &v : w) v = (int8_t)wi(rng);
+    std::vector<uint8_t> packed(n * k / 2);
+    if (bits == 4) tpo_pack_i4(w.data(), n * k, packed.data());
+
+    // checker: integer replica (prep -> int32 GEMM -> dequant)
+    std::vector<int8_t> q(m * k);
+    std::vector<float> as(m);
+    tpo_convrot_prep(x.data(), m, k, bits, q.data(), as.data(), nullptr);
+    std::vector<int32_t> acc(m * n);
+    tpo_igemm_s32(q.data(), w.data(), m, n, k, acc.data());
+    std::vector<double> sim(m * n);
+    tpo_dequant_sim(acc.data(), as.data(), ws.data(), m, n, sim.data());
+
+    tpb::DeviceBuffer xd = be.tensorCreate(m * k * 4), yd = be.tensorCreate(m * n * 4);
+    be.tensorUpload(xd, x.data(), m * k * 4);
+    if (bits == 8) {
+        be.opI8Prep(xd, m, k, false);
+        be.opI8Gemm(yd, w.data(), ws.data(), n, false);
+    } else {
+        be.opI4Prep(xd, m, k);
+        be.opI4Gemm(yd, packed.data(), ws.data(), n);
+    }
+    std::vector<float> y(m * n);
+    be.tensorDownload(yd, y.data(), m * n * 4);
+    double worst = 0;
+    for (size_t i = 0; i < m * n; i++) {
+        const double err = std::fabs((double)y[i] - sim[i]);
+        const double tol = 1e-4 + 1e-3 * std::fabs(sim[i]);   // the reference's gate
+        if (err > tol) worst = std::fmax(worst, err);
+    }
+    EXPECT(worst == 0, "int%d linear %zux%zux%zu: worst excess error %g", bits, m, n, k, worst);
+    be.tensorDestroy(xd);
+    be.tensorDestroy(yd);
+    be.dropWeights();  // the cache is keyed by host address, and the weights are about to be freed
+}
+
+static void gguf_gemv(tpb::Backend &be, tpb::DType dt, int fmt, size_t rows, size_t cols, size_t n, unsigned seed) {
+    std::mt19937 rng(seed);
+    std::uniform_real_distribution<float> ux(-1.f, 1.f);
+    std::vector<float> x(n * cols);
+    for (auto &v : x) v = ux(rng);
+    const size_t rb = tpo_gguf_row_bytes(fmt, cols);
+    std::vector<uint8_t> w(rows * rb);
+    for (auto &v : w) v = (uint8_t)(rng() & 0xff);
+    // pin the f16 scale fields to small finite values (src/gpu/cuda/backend.zig:3356-3377)
+    const size_t bb = fmt <= 1 ? (fmt == 0 ? 34 : 18) : (fmt == 2 ? 144 : fmt == 3 ? 176 : 210);
+    for (size_t off = 0; off < w.size(); off += bb) {
+        const size_t dpos = fmt == 4 ? off + 208 : off;
+        w[dpos] = 0x66; w[dpos + 1] = 0x2A;                       // 0.05
+        if (fmt == 2 || fmt == 3) { w[off + 2] = 0x1F; w[off + 3] = 0x25; }  // dmin 0.02
+    }
+    std::vector<float> want(n * rows);
+    tpo_gguf_gemv_q8(fmt, w.data(), rows, cols, x.data(), n, 1.0f, want.data());
+
+    tpb::DeviceBuffer xd = be.tensorCreate(n * cols * 4), yd = be.tensorCreate(n * rows * 4);
+    be.tensorUpload(xd, x.data(), n * cols * 4);
+    be.opGemvQuantizeX(xd, n * cols);
+    be.opGemvQuantQ8N(dt, yd, w.data(), 1.0f, rows, cols, n, 0, n);
+    std::vector<float> y(n * rows);
+    be.tensorDownload(yd, y.data(), n * rows * 4);
+    double worst = 0;
+    for (size_t i = 0; i < y.size(); i++) worst = std::fmax(worst, std::fabs((double)y[i] - (double)want[i]));
+    EXPECT(worst <= 2e-2, "gguf fmt %d gemv: max abs err %g (the reference's gate is 2e-2)", fmt, worst);
+    be.tensorDestroy(xd);
+    be.tensorDestroy(yd);
+    be.dropWeights();  // the cache is keyed by host address, and `w` is about to be freed
+}
+
+int main() {
+    try {
+        tpb::Backend be(0);
+        convrot_linear(be, 8, 256, 384, 512, 1);
+        convrot_linear(be, 4, 130, 272, 768, 2);
+        convrot_linear(be, 8, 300, 3072, 256, 3);
+        // the reference's grouped GEMV test shape: rows 24, cols 512, 5 activation rows
+        gguf_gemv(be, tpb::DType::q8_0, 0, 24, 512, 5, 271);
+        gguf_gemv(be, tpb::DType::q4_0, 1, 24, 512, 5, 272);
+        gguf_gemv(be, tpb::DType::q4_k, 2, 24, 512, 5, 314);
+        gguf_gemv(be, tpb::DType::q5_k, 3, 24, 512, 5, 315);
+        gguf_gemv(be, tpb::DType::q6_k, 4, 24, 512, 5, 316);
+
+        // error behaviour: a GEMM without its prep, a width the rotation cannot take
+        tpb::DeviceBuffer t = be.tensorCreate(1 << 16);
+        std::vector<int8_t> w(256 * 256);
+        std::vector<float> ws(256, 1.f);
+        bool threw = false;
+        try {
+            be.opI4Gemm(t, w.data(), ws.data(), 256);   // last prep was int8
+        } catch (const tpb::Error &e) {
+            threw = e.status == TPB_ERR_STATE;
+        }
+        EXPECT(threw, "opI4Gemm after an int8 prep must fail with TPB_ERR_STATE");
+        threw = false;
+        try {
+            be.opI8Prep(t, 4, 250, false);
+        } catch (const tpb::Error &e) {
+            threw = e.status == TPB_ERR_INVALID_ARG;
+        }
+        EXPECT(threw, "opI8Prep with cols %% 256 != 0 must fail with TPB_ERR_INVALID_ARG");
+        be.sync();
+        be.tensorDestroy(t);
+    } catch (const tpb::Error &e) {
+        std::printf("FAIL: exception %d: %s\n", e.status, e.what());
+        return 1;
+    }
+    if (failures == 0) std::printf("OK\n");
+    return failures ? 1 : 0;
+}
