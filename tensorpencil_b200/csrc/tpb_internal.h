@@ -76,6 +76,8 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
                     const void *w, int w_bits, const float *w_scale, int64_t m, int64_t n,
                     int64_t k, void *const *peer_y = nullptr, int n_peers = 0, void *mc_y = nullptr,
                     const float *gate = nullptr);
+// The int8 expansion scratch of an [n][k] int4 weight on the handle's device (grown on demand).
+int tpb_w4_scratch(tpb_handle_t h, int64_t n, int64_t k, int8_t **out);
 int tpb_launch_peer_barrier(tpb_handle_t h, cudaStream_t st, uint32_t *const *flags, int world,
                             int rank, uint32_t epoch, int timeout_ms);
 int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, int64_t n_elems,

@@ -420,3 +420,25 @@ def test_host_buffer_linear_matches_resident(be, bits, m, chunk):
     q, s = oracle.convrot_prep(c["x"], bits)
     sim = oracle.dequant_sim(oracle.igemm_s32(q, c["w_i8"]), s, c["w_scale"])
     assert_close_to_sim(y_dev.cpu().numpy(), sim)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(96, 768, 512), (4608, 3072, 256), (700, 1040, 768)])
+def test_one_call_linear_matches_prep_then_gemm(be, bits, dtype, m, n, k):
+    """tpb_convrot_linear == tpb_convrot_prep + tpb_convrot_gemm, bit for bit, also when
+    called back to back."""
+    c = synth.convrot_linear(m, n, k, bits, seed=5 + m + bits)
+    x = dev(c["x"])
+    w = dev(c["w_i8"] if bits == 8 else c["w_packed"])
+    ws = dev(c["w_scale"])
+    y_two = torch.empty((m, n), dtype=dtype, device="cuda")
+    be._prep(x, m, k, bits)
+    be._gemm(y_two, w, ws, n, bits)
+    q_two = be.i8_x[: m * k].clone()
+    for _ in range(3):
+        y_one = be.convrot_linear(x, w, ws, n, bits, out_dtype=dtype)
+    be.status_poll()
+    view = torch.int16 if dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(y_one.view(view), y_two.view(view))
+    assert torch.equal(be.i8_x[: m * k], q_two)
