@@ -670,6 +670,37 @@ def run_mode_one_kernel(args, local):
         ws, y = torch.rand(n, device="cuda"), torch.empty(m, n, dtype=dt, device="cuda")
         for _ in range(reps):
             be._gemm(y, w, ws, n, 4 if w4 else 8)
+    elif case in ("gemv1-q4k", "gemv1-q6k", "gemv8-q4k"):
+        from tensorpencil_b200 import synth
+        m = int(case[4])
+        fmt = "q4_k" if case.endswith("q4k") else "q6_k"
+        n, k = 17408, 5120
+        w = torch.from_numpy(synth.gguf_weights(fmt, n, k, seed=11)).cuda()
+        x = torch.randn(m, k, device="cuda")
+        y = torch.empty(m, n, device="cuda")
+        be.opGemvQuantizeX(x, m * k)
+        for _ in range(reps):
+            be.opGemvQuantQ8N(fmt, y, w, 1.0, n, k, m, 0, m)
+    elif case == "copy-sweep":
+        # What a plain device-to-device copy reaches at the byte counts of this path's HBM-bound
+        # kernels (the measured HBM peak is for buffers of gigabytes): rotating buffers, 50
+        # back-to-back copies between two events, traffic = read + write.
+        out = []
+        for mb in (14, 28, 35, 47, 56, 113, 452):
+            nbytes = mb * 1024 * 1024
+            xs = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in range(4)]
+            ys = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in range(4)]
+            ms = _events_ms(lambda i: ys[i % 4].copy_(xs[i % 4]), 50, torch.cuda.synchronize) / 50
+            out.append({"traffic_mb": 2 * nbytes / 1e6, "us": ms * 1e3, "gbs": 2 * nbytes / (ms * 1e-3) / 1e9})
+            del xs, ys
+        print(json.dumps({"mode": "one-kernel", "case": case, "copies": out}), flush=True)
+        be.close()
+        return
+    elif case == "prep-silu":
+        m, k = 2048, N
+        g, u = torch.randn(m, k, device="cuda"), torch.randn(m, k, device="cuda")
+        for _ in range(reps):
+            be.prepSiluMul(g, u, m, k, 8)
     elif case in ("gemv1", "gemv4", "gemv8", "gemv1-down"):
         m = int(case[4]) if case[4].isdigit() else 1
         n, k = (5120, 17408) if case.endswith("down") else (17408, 5120)
@@ -698,7 +729,7 @@ def main():
     ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
-                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down")
+                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
