@@ -611,7 +611,7 @@ def run_mode_gemv(args, rank, local, world):
     # the other GGUF formats at the up-projection shape; enough rotating copies to exceed L2
     from tensorpencil_b200 import synth
     n, k = 17408, 5120
-    for fmt in ("q4_k", "q5_k", "q6_k", "q4_0"):
+    for fmt in ("q4_k", "q5_k", "q6_k", "q4_0", "iq4_nl"):
         base = torch.from_numpy(synth.gguf_weights(fmt, n, k, seed=11)).cuda()
         copies = 8
         ws = [base] + [base.clone() for _ in range(copies - 1)]       # 8 x 50..61 MB > 126 MB of L2

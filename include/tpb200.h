@@ -315,7 +315,7 @@ int tpb_convrot_prep_fused(tpb_handle_t h, tpb_stream_t stream, int op, const vo
                            int32_t *act_sum);
 
 /* ---- Decode GEMV for the other GGUF block formats -----------------------------------
- * Replaces Backend.opGemvQuantQ8N for .q4_0 / .q4_k / .q5_k / .q6_k (src/gpu/cuda/backend.zig:1719-1735;
+ * Replaces Backend.opGemvQuantQ8N for .q4_0 / .q4_k / .q5_k / .q6_k / .iq4_nl (src/gpu/cuda/backend.zig:1719-1735;
  * kernels src/gpu/cuda/elt.zig:2014-2110, :1831-1925, :1526-1713, :1714-1830); TPB_GGUF_Q8_0 forwards to
  * tpb_q8_0_gemv_q8n.  Same arguments and activation buffer (tpb_q8_1_quantize) as
  * tpb_q8_0_gemv_q8n; w holds `rows` rows of tpb_gguf_row_bytes(fmt, cols) bytes in ggml's
@@ -323,13 +323,14 @@ int tpb_convrot_prep_fused(tpb_handle_t h, tpb_stream_t stream, int op, const vo
  *   y[i*rows + r] = scale * sum_k dequant(w[r])[k] * (d_x * q_x)[i][k]
  * q6_k rows are not multiples of 16 bytes: the kernel's bulk copies are rounded out to 16-byte
  * boundaries and may read (and ignore) up to 14 bytes past the last row, inside the same
- * allocation granule.  iq4_nl is not implemented. */
+ * allocation granule.  iq4_nl: q4_0's layout with ggml's 16-entry value table. */
 typedef enum tpb_gguf_format {
     TPB_GGUF_Q8_0 = 0,
     TPB_GGUF_Q4_0 = 1,
     TPB_GGUF_Q4_K = 2,
     TPB_GGUF_Q5_K = 3,
-    TPB_GGUF_Q6_K = 4
+    TPB_GGUF_Q6_K = 4,
+    TPB_GGUF_IQ4_NL = 5
 } tpb_gguf_format;
 size_t tpb_gguf_row_bytes(int fmt, int64_t cols);
 int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, const void *w, float scale,

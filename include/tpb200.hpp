@@ -34,7 +34,7 @@ struct Error : std::runtime_error {
 };
 
 // The reference's DType values this path uses (src/core/dtype.zig).
-enum class DType { f32, f16, bf16, i8, i4, q8_0, q4_0, q4_k, q5_k, q6_k };
+enum class DType { f32, f16, bf16, i8, i4, q8_0, q4_0, q4_k, q5_k, q6_k, iq4_nl };
 
 struct DeviceBuffer {  // src/gpu/cuda/context.zig DeviceBuffer: an address and a size
     void *p = nullptr;
@@ -183,6 +183,7 @@ class Backend {
             case DType::q4_k: return TPB_GGUF_Q4_K;
             case DType::q5_k: return TPB_GGUF_Q5_K;
             case DType::q6_k: return TPB_GGUF_Q6_K;
+            case DType::iq4_nl: return TPB_GGUF_IQ4_NL;
             default: throw Error(TPB_ERR_INVALID_ARG, "unsupported GEMV weight format");
         }
     }

@@ -272,7 +272,7 @@ def gated_add(x: np.ndarray, delta: np.ndarray, gate: np.ndarray) -> np.ndarray:
 
 # -- other GGUF block formats ---------------------------------------------------------------
 
-GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3, "q6_k": 4}
+GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3, "q6_k": 4, "iq4_nl": 5}
 
 
 def gguf_row_bytes(fmt: str, k: int) -> int:

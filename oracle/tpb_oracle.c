@@ -576,10 +576,28 @@ void tpo_q4_0_dequant_row(const uint8_t *blocks, size_t k, float *out) {
     }
 }
 
+/* iq4_nl: 18 bytes per 32 elements like q4_0, but the nibble indexes a non-linear table:
+ * v = d * kvalues[nibble] (ggml's kvalues_iq4nl; layout and table as the reference's test states
+ * them, src/core/quants.zig:133-151). */
+static const int8_t tpo_kvalues_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+void tpo_iq4_nl_dequant_row(const uint8_t *blocks, size_t k, float *out) {
+    for (size_t blk = 0; blk < k / 32; blk++) {
+        const uint8_t *b = blocks + blk * 18;
+        uint16_t hd;
+        memcpy(&hd, b, 2);
+        const float d = tpo_f16_to_f32(hd);
+        for (int j = 0; j < 16; j++) {
+            out[blk * 32 + j] = d * (float)tpo_kvalues_iq4nl[b[2 + j] & 0xF];
+            out[blk * 32 + j + 16] = d * (float)tpo_kvalues_iq4nl[b[2 + j] >> 4];
+        }
+    }
+}
+
 /* GEMV against q8_1-quantised activations for any of the formats above, the way the
  * reference's device test forms its CPU truth (src/gpu/cuda/backend.zig:3750-3790):
  * dequantise the weight row, dequantise the activations (d * q per 32-block), f64 dot.
- * fmt: 0 q8_0, 1 q4_0, 2 q4_k, 3 q5_k, 4 q6_k. */
+ * fmt: 0 q8_0, 1 q4_0, 2 q4_k, 3 q5_k, 4 q6_k, 5 iq4_nl. */
 size_t tpo_gguf_row_bytes(int fmt, size_t k) {
     switch (fmt) {
         case 0: return k / 32 * 34;
@@ -587,6 +605,7 @@ size_t tpo_gguf_row_bytes(int fmt, size_t k) {
         case 2: return k / 256 * 144;
         case 3: return k / 256 * 176;
         case 4: return k / 256 * 210;
+        case 5: return k / 32 * 18;
     }
     return 0;
 }
@@ -598,6 +617,7 @@ void tpo_gguf_dequant_row(int fmt, const uint8_t *row, size_t k, float *out) {
         case 2: tpo_q4_k_dequant_row(row, k, out); break;
         case 3: tpo_q5_k_dequant_row(row, k, out); break;
         case 4: tpo_q6_k_dequant_row(row, k, out); break;
+        case 5: tpo_iq4_nl_dequant_row(row, k, out); break;
     }
 }
 

@@ -137,11 +137,12 @@ void tpo_gated_add(const float *x, const float *delta, const float *gate, size_t
 
 /* Other GGUF block formats (ggml's decoders, pinned by src/core/quants_fixtures.zig) and a
  * format-generic GEMV truth (src/gpu/cuda/backend.zig:3750-3790).  fmt: 0 q8_0, 1 q4_0,
- * 2 q4_k, 3 q5_k, 4 q6_k. */
+ * 2 q4_k, 3 q5_k, 4 q6_k, 5 iq4_nl. */
 void tpo_q4_k_dequant_row(const uint8_t *blocks, size_t k, float *out);
 void tpo_q5_k_dequant_row(const uint8_t *blocks, size_t k, float *out);
 void tpo_q6_k_dequant_row(const uint8_t *blocks, size_t k, float *out);
 void tpo_q4_0_dequant_row(const uint8_t *blocks, size_t k, float *out);
+void tpo_iq4_nl_dequant_row(const uint8_t *blocks, size_t k, float *out);
 size_t tpo_gguf_row_bytes(int fmt, size_t k);
 void tpo_gguf_dequant_row(int fmt, const uint8_t *row, size_t k, float *out);
 void tpo_gguf_gemv_q8(int fmt, const uint8_t *w, size_t n, size_t k, const float *x, size_t m, float scale,

@@ -20,7 +20,7 @@ TPB_ERR_STATE = -5
 TPB_ERR_NO_DEVICE = -6
 
 TPB_F32, TPB_BF16, TPB_F16, TPB_S32 = 0, 1, 2, 3
-GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3, "q6_k": 4}
+GGUF_FMT = {"q8_0": 0, "q4_0": 1, "q4_k": 2, "q5_k": 3, "q6_k": 4, "iq4_nl": 5}
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 

@@ -277,7 +277,7 @@ class Backend:
         (backend.zig:1719-1735)."""
         from ._lib import GGUF_FMT
         if dt not in GGUF_FMT:
-            raise NotImplementedError(f"GEMV weight format {dt!r} is not implemented (q8_0, q4_0, q4_k, q5_k, q6_k are)")
+            raise NotImplementedError(f"GEMV weight format {dt!r} is not implemented (q8_0, q4_0, q4_k, q5_k, q6_k, iq4_nl are)")
         assert self.q8_act is not None and self._q8_total == n_total * cols
         w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
         rc = self.lib.tpb_gguf_gemv_q8n(self.h, self._stream(), GGUF_FMT[dt], y.data_ptr(), w_dev.data_ptr(),

@@ -1,5 +1,5 @@
 // Decode GEMV for the other GGUF block formats a checkpoint mixes with Q8_0 -- q4_0,
-// q4_k and q5_k -- on the same streaming skeleton as the Q8_0 kernel (qgemv.cu): every
+// iq4_nl, q4_k, q5_k (and q6_k further down) -- on the same streaming skeleton as the Q8_0 kernel (qgemv.cu): every
 // warp owns a contiguous range of weight rows and streams them, R rows at a time, into a
 // private shared-memory ring with 1-D bulk async copies (mbarrier completion, no
 // multicast); q8_1 activations (int8 + per-32-block scale) stay in shared memory for the
@@ -28,7 +28,7 @@
 
 namespace {
 
-enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3 };
+enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3, FMT_IQ4_NL = 5 };
 
 constexpr int kUnitsPerLane = 2;                    // 64-element units a lane takes per pipeline stage
 constexpr int kUnitsPerChunk = 32 * kUnitsPerLane;
@@ -38,6 +38,7 @@ constexpr long long kWaitLimitCycles = 2000000000ll;
 template <int FMT> struct Fmt;
 // bytes of one 64-element unit (a quarter super-block for the k-quants) and of a chunk of one row
 template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
+template <> struct Fmt<FMT_IQ4_NL> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
 template <> struct Fmt<FMT_Q4_K> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };   // 144 / 4
 template <> struct Fmt<FMT_Q5_K> { static constexpr int kUnitBytes = 44, kChunkBytes = kUnitsPerChunk * 44; };   // 176 / 4
 
@@ -88,6 +89,21 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
+}
+// Four 4-bit indices (one per byte of idx, 0..15) -> the four signed bytes of ggml's
+// kvalues_iq4nl table: two byte-permutes over the table halves, merged by the index's bit 3.
+__device__ __forceinline__ uint32_t iq4nl_lookup(uint32_t idx) {
+    constexpr uint32_t T0 = 0xBFAD9881u;  // -127 -104 -83 -65
+    constexpr uint32_t T1 = 0xF6EADDCFu;  // -49 -35 -22 -10
+    constexpr uint32_t T2 = 0x26190D01u;  // 1 13 25 38
+    constexpr uint32_t T3 = 0x71594535u;  // 53 69 89 113
+    const uint32_t t = idx & 0x07070707u;
+    const uint32_t u = t | (t >> 4);                     // byte 0: b0 | b1 << 4, byte 2: b2 | b3 << 4
+    const uint32_t sel = __byte_perm(u, 0, 0x4420);      // 16-bit selector b0, b1, b2, b3
+    const uint32_t v_lo = __byte_perm(T0, T1, sel);
+    const uint32_t v_hi = __byte_perm(T2, T3, sel);
+    const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xffu;
+    return (v_lo & ~m) | (v_hi & m);
 }
 __device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
@@ -227,7 +243,25 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
 #pragma unroll
             for (int r = 0; r < R; r++) {
                 if (r < nrow) {
-                    if (FMT == FMT_Q4_0) {
+                    if (FMT == FMT_IQ4_NL) {
+                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + ul * 36);
+                        uint32_t tw[9];
+#pragma unroll
+                        for (int j = 0; j < 9; j++) tw[j] = src[j];
+                        // same 18-byte block pair as q4_0; the nibbles go through the value table and
+                        // come out as signed bytes, so there is no offset term
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t na = __funnelshift_r(tw[j], tw[j + 1], 16), nb = tw[5 + j];
+                            lo[r][j] = iq4nl_lookup(na & 0x0f0f0f0fu);
+                            lo[r][4 + j] = iq4nl_lookup((na >> 4) & 0x0f0f0f0fu);
+                            hi[r][j] = iq4nl_lookup(nb & 0x0f0f0f0fu);
+                            hi[r][4 + j] = iq4nl_lookup((nb >> 4) & 0x0f0f0f0fu);
+                        }
+                        ws0[r] = f16lo(tw[0]);
+                        ws1[r] = f16hi(tw[4]);
+                        wo0[r] = wo1[r] = 0.0f;
+                    } else if (FMT == FMT_Q4_0) {
                         const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + ul * 36);
                         uint32_t tw[9];
 #pragma unroll
@@ -309,9 +343,11 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                 for (int r = 0; r < R; r++) {
                     int i0 = 0, i1 = 0;
 #pragma unroll
-                    for (int w = 0; w < 8; w++) i0 = dp4a_us(lo[r][w], xq[w], i0);
+                    for (int w = 0; w < 8; w++)
+                        i0 = FMT == FMT_IQ4_NL ? __dp4a((int)lo[r][w], (int)xq[w], i0) : dp4a_us(lo[r][w], xq[w], i0);
 #pragma unroll
-                    for (int w = 0; w < 8; w++) i1 = dp4a_us(hi[r][w], xq[8 + w], i1);
+                    for (int w = 0; w < 8; w++)
+                        i1 = FMT == FMT_IQ4_NL ? __dp4a((int)hi[r][w], (int)xq[8 + w], i1) : dp4a_us(hi[r][w], xq[8 + w], i1);
                     float tacc = acc[r][m];
                     tacc = fmaf(ws0[r], d2.x * __int2float_rn(i0), tacc);
                     tacc = fmaf(-wo0[r], s2.x, tacc);
@@ -647,7 +683,8 @@ extern "C" {
 size_t tpb_gguf_row_bytes(int fmt, int64_t cols) {
     switch (fmt) {
         case TPB_GGUF_Q8_0: return (size_t)(cols / 32) * 34;
-        case TPB_GGUF_Q4_0: return (size_t)(cols / 32) * 18;
+        case TPB_GGUF_Q4_0:
+        case TPB_GGUF_IQ4_NL: return (size_t)(cols / 32) * 18;
         case TPB_GGUF_Q4_K: return (size_t)(cols / 256) * 144;
         case TPB_GGUF_Q5_K: return (size_t)(cols / 256) * 176;
         case TPB_GGUF_Q6_K: return (size_t)(cols / 256) * 210;
@@ -660,8 +697,9 @@ int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, co
     if (!h) return TPB_ERR_INVALID_ARG;
     if (fmt == TPB_GGUF_Q8_0)
         return tpb_q8_0_gemv_q8n(h, stream, y, w, scale, rows, cols, xq, ng, row_off, n_total);
-    TPB_CHECK_ARG(h, fmt == TPB_GGUF_Q4_0 || fmt == TPB_GGUF_Q4_K || fmt == TPB_GGUF_Q5_K || fmt == TPB_GGUF_Q6_K,
-                  "gguf_gemv: unsupported format %d (q8_0, q4_0, q4_k, q5_k, q6_k)", fmt);
+    TPB_CHECK_ARG(h, fmt == TPB_GGUF_Q4_0 || fmt == TPB_GGUF_Q4_K || fmt == TPB_GGUF_Q5_K || fmt == TPB_GGUF_Q6_K ||
+                         fmt == TPB_GGUF_IQ4_NL,
+                  "gguf_gemv: unsupported format %d (q8_0, q4_0, q4_k, q5_k, q6_k, iq4_nl)", fmt);
     TPB_CHECK_ARG(h, y && w && xq, "gguf_gemv: null pointer");
     TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 31) && cols > 0 && cols % 256 == 0 && cols < (1ll << 24),
                   "gguf_gemv: cols must be a multiple of 256 (cols=%lld)", (long long)cols);
@@ -686,6 +724,7 @@ int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, co
         case TPB_GGUF_Q4_0: return launch_fmt<FMT_Q4_0>(h, st, p, ng);
         case TPB_GGUF_Q4_K: return launch_fmt<FMT_Q4_K>(h, st, p, ng);
         case TPB_GGUF_Q6_K: return launch_q6k(h, st, p, ng);
+        case TPB_GGUF_IQ4_NL: return launch_fmt<FMT_IQ4_NL>(h, st, p, ng);
         default: return launch_fmt<FMT_Q5_K>(h, st, p, ng);
     }
 }

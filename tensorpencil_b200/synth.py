@@ -132,7 +132,8 @@ def dit_block_weights(block: int, bits: int, seed: int = 1003, hidden: int = DIT
     return out
 
 
-GGUF_BLOCK = {"q8_0": (32, 34), "q4_0": (32, 18), "q4_k": (256, 144), "q5_k": (256, 176), "q6_k": (256, 210)}
+GGUF_BLOCK = {"q8_0": (32, 34), "q4_0": (32, 18), "q4_k": (256, 144), "q5_k": (256, 176), "q6_k": (256, 210),
+              "iq4_nl": (32, 18)}
 
 
 def gguf_weights(fmt: str, n: int, k: int, seed: int) -> np.ndarray:
@@ -145,7 +146,7 @@ def gguf_weights(fmt: str, n: int, k: int, seed: int) -> np.ndarray:
     w = rng.integers(0, 256, size=(n, k // elems, nbytes), dtype=np.uint8)
     d16 = np.frombuffer(np.uint16(0x2A66).tobytes(), np.uint8)
     m16 = np.frombuffer(np.uint16(0x251F).tobytes(), np.uint8)
-    if fmt in ("q8_0", "q4_0"):
+    if fmt in ("q8_0", "q4_0", "iq4_nl"):
         w[:, :, 0:2] = d16
     elif fmt in ("q4_k", "q5_k"):
         w[:, :, 0:2] = d16

@@ -18,7 +18,7 @@ from tensorpencil_b200 import synth  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["q4_0", "q4_k", "q5_k", "q6_k", "q8_0"]
+FORMATS = ["q4_0", "iq4_nl", "q4_k", "q5_k", "q6_k", "q8_0"]
 
 
 @pytest.fixture(scope="module")
@@ -61,7 +61,7 @@ def test_gguf_gemv_matches_truth(be, fmt, m, n, k):
     assert np.abs(got - want).max() <= 2e-2 * max(1.0, k / 512)          # the reference's own gate, scaled with k
 
 
-@pytest.mark.parametrize("fmt", ["q4_0", "q4_k", "q5_k", "q6_k"])
+@pytest.mark.parametrize("fmt", ["q4_0", "iq4_nl", "q4_k", "q5_k", "q6_k"])
 def test_gguf_gemv_reference_test_shape(be, fmt):
     """rows 24, cols 512, 5 activation rows in one partial group: the reference's case."""
     w = synth.gguf_weights(fmt, 24, 512, seed=314)

@@ -349,3 +349,14 @@ def test_q4_0_and_generic_gemv_truth():
 def oracle_q8_1_dequant(x):
     d, qs = oracle.q8_1_quantize(x.reshape(-1))
     return (np.repeat(d, 32) * qs.astype(np.float32)).reshape(x.shape)
+
+
+def test_iq4_nl_dequant_matches_reference_known_answers():
+    """src/core/quants.zig:133-151: d = 2.0, qs[0] = 0x21, the rest 0."""
+    kv = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(2.0).tobytes(), np.uint8)
+    blk[2] = 0x21
+    out = oracle.gguf_dequant_row("iq4_nl", blk, 32)
+    assert out[0] == 2.0 * kv[1] and out[16] == 2.0 * kv[2]
+    assert np.all(out[1:16] == 2.0 * kv[0]) and np.all(out[17:32] == 2.0 * kv[0])
