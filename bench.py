@@ -647,9 +647,11 @@ def run_mode_one_kernel(args, local):
     from tensorpencil_b200 import harness
     from tensorpencil_b200.backend import Backend
     torch.cuda.set_device(local)
+    case = args.case
+    if case == "gemm-w4-fused":
+        os.environ["TPB_W4_FUSED"] = "1"       # read when the handle is created
     be = Backend(local)
     reps = max(1, min(args.steps, 5))
-    case = args.case
     if case in ("prep", "prep-mlp"):
         m, k = (M, K) if case == "prep" else (2048, N)
         x = torch.randn(m, k, device="cuda")
@@ -659,8 +661,6 @@ def run_mode_one_kernel(args, local):
         m, n, k = (2048, 6144, 3072) if case == "gemm-small" else (M, N, K)
         dt = torch.bfloat16 if case == "gemm-bf16" else torch.float32
         w4 = case.startswith("gemm-w4")
-        if case == "gemm-w4-fused":
-            os.environ["TPB_W4_FUSED"] = "1"
         q = torch.randint(-7 if w4 else -127, 8 if w4 else 128, (m, k), dtype=torch.int8, device="cuda")
         w = (torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda") if w4
              else torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda"))

@@ -54,6 +54,9 @@ int tpb_create(tpb_handle_t *out, int device_ordinal) {
     h->device = device_ordinal;
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    const char *e1 = getenv("TPB_W4_FUSED"), *e2 = getenv("TPB_GEMM_ONE_CTA");
+    h->opt_w4_fused = e1 != nullptr && e1[0] == '1';
+    h->opt_gemm_one_cta = e2 != nullptr && e2[0] == '1';
     int prev = 0;
     cudaGetDevice(&prev);
     cudaError_t e = cudaSetDevice(device_ordinal);
@@ -78,6 +81,7 @@ int tpb_create(tpb_handle_t *out, int device_ordinal) {
 
 int tpb_destroy(tpb_handle_t h) {
     if (!h) return TPB_ERR_INVALID_ARG;
+    if (h->w4_scratch) cudaFree(h->w4_scratch);
     if (h->d_status) cudaFree(h->d_status);
     delete h;
     return TPB_OK;
@@ -171,9 +175,7 @@ int tpb_convrot_linear(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype
     if (rc != TPB_OK) return rc;
     TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "linear: bad m");
     if (m == 0) return TPB_OK;
-    const char *fused_env = getenv("TPB_W4_FUSED");
-    const bool fused = fused_env != nullptr && fused_env[0] == '1';
-    if (w_bits != 4 || fused) {
+    if (w_bits != 4 || h->opt_w4_fused) {
         rc = tpb_launch_prep(h, st, x, x_dtype, m, k, w_bits, q, act_scale, act_sum);
         if (rc != TPB_OK) return rc;
         return tpb_launch_gemm(h, st, y, y_dtype, ldy, q, act_scale, act_sum, w, w_bits, w_scale, m, n, k);

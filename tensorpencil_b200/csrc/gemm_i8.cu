@@ -251,25 +251,17 @@ int launch_out(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
 
 }  // namespace
 
-// Scratch for the int8 expansion of an int4 weight (grown on demand, owned by
-// the handle).  Keyed by nothing: the expansion is redone on every call.
-struct W4Scratch {
-    int8_t *buf = nullptr;
-    size_t bytes = 0;
-};
-static W4Scratch g_w4_scratch[64];  // per device ordinal
-
 int tpb_w4_scratch(tpb_handle_t h, int64_t n, int64_t k, int8_t **out) {
-    W4Scratch &s = g_w4_scratch[h->device & 63];
     const size_t need = (size_t)n * (size_t)k;
-    if (s.bytes < need) {
-        if (s.buf) TPB_CUDA(h, cudaFree(s.buf));
-        s.buf = nullptr;
-        s.bytes = 0;
-        TPB_CUDA(h, cudaMalloc(&s.buf, need));
-        s.bytes = need;
+    if (h->w4_scratch_bytes < need) {
+        // cudaFree waits for the work that may still read the old buffer
+        if (h->w4_scratch) TPB_CUDA(h, cudaFree(h->w4_scratch));
+        h->w4_scratch = nullptr;
+        h->w4_scratch_bytes = 0;
+        TPB_CUDA(h, cudaMalloc(&h->w4_scratch, need));
+        h->w4_scratch_bytes = need;
     }
-    *out = s.buf;
+    *out = h->w4_scratch;
     return TPB_OK;
 }
 
@@ -292,10 +284,8 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     p.k = (int)k;
     p.status = h->d_status;
     const void *w8 = w;
-    const char *one_cta_env = getenv("TPB_GEMM_ONE_CTA");
-    const bool one_cta_only = one_cta_env != nullptr && one_cta_env[0] == '1';
-    const char *fused_env = getenv("TPB_W4_FUSED");
-    if (w_bits == 4 && n_peers == 0 && mc_y == nullptr && gate == nullptr && fused_env != nullptr && fused_env[0] == '1' &&
+    const bool one_cta_only = h->opt_gemm_one_cta;
+    if (w_bits == 4 && n_peers == 0 && mc_y == nullptr && gate == nullptr && h->opt_w4_fused &&
         ((m + 127) / 128) * ((n + 255) / 256) >= h->sm_count) {
         // opt-in: the packed weight is unpacked inside the GEMM (one-CTA kernel)
         p.act_sum = act_sum;

@@ -24,7 +24,9 @@
 // which is what the kernels accumulate in f32.
 #include <cuda_fp16.h>
 
-#include "tpb_internal.h"
+#include "qgemv_common.cuh"
+
+using namespace tpb_gemv;
 
 namespace {
 
@@ -33,7 +35,6 @@ enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3, FMT_IQ4_NL = 5 };
 constexpr int kUnitsPerLane = 2;                    // 64-element units a lane takes per pipeline stage
 constexpr int kUnitsPerChunk = 32 * kUnitsPerLane;
 constexpr int kActPairBytes = 80;   // a unit's 64 activation bytes + 16 pad (bank-conflict-free 16-byte reads)
-constexpr long long kWaitLimitCycles = 2000000000ll;
 
 template <int FMT> struct Fmt;
 // bytes of one 64-element unit (a quarter super-block for the k-quants) and of a chunk of one row
@@ -41,37 +42,6 @@ template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkB
 template <> struct Fmt<FMT_IQ4_NL> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
 template <> struct Fmt<FMT_Q4_K> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };   // 144 / 4
 template <> struct Fmt<FMT_Q5_K> { static constexpr int kUnitBytes = 44, kChunkBytes = kUnitsPerChunk * 44; };   // 176 / 4
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait: false when the limit ran out (status word written).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u && clock64() - t0 > kWaitLimitCycles) {
-            atomicCAS(status, 0u, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
 
 struct KGemvParams {
     float *y;

@@ -21,6 +21,14 @@ struct tpb_handle_s {
     // cuTensorMapEncodeTiled, resolved through the runtime so the library has no
     // link-time dependency on libcuda (it must load on a host without a driver).
     void *encode_tiled = nullptr;
+    // int8 expansion of the int4 weight of the call in flight (grown on demand, freed with the
+    // handle).  Calls on one handle are ordered by the caller's stream, so one buffer is enough;
+    // two handles never share it.
+    int8_t *w4_scratch = nullptr;
+    size_t w4_scratch_bytes = 0;
+    // switches read from the environment once, at tpb_create
+    bool opt_w4_fused = false;      // TPB_W4_FUSED=1: unpack int4 weights inside the GEMM
+    bool opt_gemm_one_cta = false;  // TPB_GEMM_ONE_CTA=1: keep large GEMMs on the one-CTA kernel
     char err[512] = {0};
 };
 

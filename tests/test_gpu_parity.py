@@ -265,18 +265,23 @@ def test_int4_fused_unpack_kernel(be, monkeypatch, m, n, k):
     monkeypatch.delenv("TPB_W4_FUSED", raising=False)
     acc_default = be.convrot_linear(x, wp, wsc, n, 4, torch.int32).clone()
     y_default = be.convrot_linear(x, wp, wsc, n, 4, torch.float32).clone()
-    monkeypatch.setenv("TPB_W4_FUSED", "1")
-    for _ in range(3):
-        acc_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.int32)
-        y_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.float32)
-        yb_fused = be.convrot_linear(x, wp, wsc, n, 4, torch.bfloat16)
-        be.status_poll()
-        assert torch.equal(acc_fused, acc_default)
-        assert torch.equal(y_fused, y_default)
-        assert torch.equal(yb_fused, y_default.to(torch.bfloat16))
-    rows = np.sort(np.random.default_rng(1).choice(m, 48, replace=False))
-    q_ref, s_ref = oracle.convrot_prep(c["x"][rows], 4)
-    assert np.array_equal(acc_fused.cpu().numpy()[rows], oracle.igemm_s32(q_ref, c["w_i8"]))
+    monkeypatch.setenv("TPB_W4_FUSED", "1")       # read once, when a handle is created
+    from tensorpencil_b200.backend import Backend
+    bf = Backend(0)
+    try:
+        for _ in range(3):
+            acc_fused = bf.convrot_linear(x, wp, wsc, n, 4, torch.int32)
+            y_fused = bf.convrot_linear(x, wp, wsc, n, 4, torch.float32)
+            yb_fused = bf.convrot_linear(x, wp, wsc, n, 4, torch.bfloat16)
+            bf.status_poll()
+            assert torch.equal(acc_fused, acc_default)
+            assert torch.equal(y_fused, y_default)
+            assert torch.equal(yb_fused, y_default.to(torch.bfloat16))
+        rows = np.sort(np.random.default_rng(1).choice(m, 48, replace=False))
+        q_ref, s_ref = oracle.convrot_prep(c["x"][rows], 4)
+        assert np.array_equal(acc_fused.cpu().numpy()[rows], oracle.igemm_s32(q_ref, c["w_i8"]))
+    finally:
+        bf.close()
 
 
 def test_w4_expand_matches_nibble_decode(be):
