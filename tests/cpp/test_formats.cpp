@@ -1,0 +1,64 @@
+// CPU test of the C++ checkpoint readers (include/tpb200_formats.hpp): parses the files named
+// on the command line and prints one line per tensor -- name, dtype, shape, a checksum of its
+// bytes -- for the Python test to compare with its own reading of the same files; then the
+// ConvRot weight resolution and the error cases.
+#include <cstdio>
+#include <functional>
+#include <string>
+
+#include "tpb200_formats.hpp"
+
+static unsigned long long checksum(const uint8_t *p, size_t n) {
+    unsigned long long h = 1469598103934665603ull;  // FNV-1a
+    for (size_t i = 0; i < n; i++) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
+}
+
+static void dump(const std::map<std::string, tpbfmt::TensorView> &ts) {
+    for (const auto &kv : ts) {
+        const tpbfmt::TensorView &v = kv.second;
+        std::printf("T %s %s [", v.name.c_str(), v.dtype.c_str());
+        for (size_t i = 0; i < v.shape.size(); i++) std::printf(i ? ",%lld" : "%lld", (long long)v.shape[i]);
+        std::printf("] %zu %llu\n", v.bytes, checksum(v.data, v.bytes));
+    }
+}
+
+static std::string errorName(const std::function<void()> &f) {
+    try {
+        f();
+    } catch (const tpbfmt::Error &e) {
+        return e.name;
+    }
+    return "none";
+}
+
+int main(int argc, char **argv) {
+    if (argc < 3) return 2;
+    try {
+        tpbfmt::SafeTensors st(argv[1]);
+        dump(st.tensors());
+        // the two weights the Python test wrote: an int8 one and an int4 one
+        const tpbfmt::ConvRotWeight w8 = tpbfmt::loadConvRotWeight(st, "model.blocks.0.attn.wq.weight", 64, 512);
+        const tpbfmt::ConvRotWeight w4 = tpbfmt::loadConvRotWeight(st, "model.blocks.0.mlp.up.weight", 48, 256);
+        std::printf("W8 %d %zu %llu %.9g\n", w8.bits, w8.w_bytes, checksum(w8.w, w8.w_bytes), (double)w8.row_scale[5]);
+        std::printf("W4 %d %zu %llu %.9g\n", w4.bits, w4.w_bytes, checksum(w4.w, w4.w_bytes), (double)w4.row_scale[5]);
+        std::printf("E %s %s %s\n",
+                    errorName([&] { tpbfmt::loadConvRotWeight(st, "model.blocks.0.attn.wq.weight", 64, 256); }).c_str(),
+                    errorName([&] { tpbfmt::loadConvRotWeight(st, "model.blocks.9.attn.wq.weight", 64, 512); }).c_str(),
+                    errorName([&] { tpbfmt::loadConvRotWeight(st, "model.norm", 1, 4); }).c_str());
+        tpbfmt::Gguf g(argv[2]);
+        std::printf("G %u %zu %s %lld\n", g.version, g.alignment, g.strings["general.architecture"].c_str(),
+                    (long long)g.integers["qwen3.block_count"]);
+        dump(g.tensors());
+        for (int i = 3; i < argc; i++)
+            std::printf("B %s\n", errorName([&] {
+                            const std::string p = argv[i];
+                            if (p.size() > 5 && p.substr(p.size() - 5) == ".gguf") tpbfmt::Gguf x(p);
+                            else tpbfmt::SafeTensors x(p);
+                        }).c_str());
+    } catch (const std::exception &e) {
+        std::printf("FAIL %s\n", e.what());
+        return 1;
+    }
+    return 0;
+}

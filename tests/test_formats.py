@@ -179,3 +179,60 @@ def test_files_to_gpu_results(tmp_path):
         st.close()
     finally:
         be.close()
+
+
+def _fnv1a(b: bytes) -> int:
+    h = 1469598103934665603
+    for x in b:
+        h = ((h ^ x) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def test_cpp_readers_agree_with_python(tmp_path):
+    """include/tpb200_formats.hpp reads the same files the same way (tests/cpp/test_formats.cpp)."""
+    import os
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "test_formats")
+    r = subprocess.run([gxx, "-std=c++17", "-O1", "-Wall", "-I", os.path.join(root, "include"),
+                        os.path.join(root, "tests", "cpp", "test_formats.cpp"), "-o", exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    sp, c8, c4 = _convrot_file(tmp_path)
+    k = 512
+    tensors = {f"blk.0.{fmt}.weight": (fmt.upper(), (24, k), synth.gguf_weights(fmt, 24, k, seed=3))
+               for fmt in ("q4_k", "q6_k", "q8_0", "iq4_nl")}
+    tensors["norm.weight"] = ("F32", (k,), np.linspace(0, 1, k, dtype=np.float32))
+    gp = str(tmp_path / "m.gguf")
+    formats.write_gguf(gp, tensors, metadata={"general.architecture": "qwen3", "qwen3.block_count": 7}, alignment=64)
+    bad_st = str(tmp_path / "bad.safetensors")
+    hj = json.dumps({"t": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}).encode()
+    open(bad_st, "wb").write(struct.pack("<Q", len(hj)) + hj + b"\0" * 16)
+    bad_gg = str(tmp_path / "bad.gguf")
+    raw = bytearray(open(gp, "rb").read())
+    raw[0:4] = b"GGUX"
+    open(bad_gg, "wb").write(raw)
+    out = subprocess.run([exe, sp, gp, bad_st, bad_gg], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    lines = out.stdout.strip().splitlines()
+    got = {ln.split()[1]: ln.split()[2:] for ln in lines if ln.startswith("T ")}
+    st, g = formats.SafeTensors(sp), formats.Gguf(gp)
+    for src in (st, g):
+        for name, v in src.tensors.items():
+            dt, shape, nbytes, cs = got[name]
+            assert dt == v.dtype and shape == "[" + ",".join(str(s) for s in v.shape) + "]"
+            assert int(nbytes) == v.data.size and int(cs) == _fnv1a(v.data.tobytes())
+    w8 = formats.load_convrot_weight(st, "model.blocks.0.attn.wq.weight", 64, 512)
+    w4 = formats.load_convrot_weight(st, "model.blocks.0.mlp.up.weight", 48, 256)
+    l8 = next(ln for ln in lines if ln.startswith("W8 ")).split()
+    l4 = next(ln for ln in lines if ln.startswith("W4 ")).split()
+    assert l8[1] == "8" and int(l8[3]) == _fnv1a(w8.w.tobytes()) and np.float32(float(l8[4])) == w8.row_scale[5]
+    assert l4[1] == "4" and int(l4[3]) == _fnv1a(w4.w.tobytes()) and np.float32(float(l4[4])) == w4.row_scale[5]
+    assert next(ln for ln in lines if ln.startswith("E ")).split()[1:] == ["ShapeMismatch", "MissingTensor", "UnsupportedCheckpoint"]
+    assert next(ln for ln in lines if ln.startswith("G ")).split()[1:] == ["3", "64", "qwen3", "7"]
+    assert [ln.split()[1] for ln in lines if ln.startswith("B ")] == ["InvalidOffsets", "InvalidMagic"]
+    st.close()
+    g.close()
