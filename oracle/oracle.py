@@ -296,3 +296,43 @@ def gguf_gemv_q8(fmt: str, w: np.ndarray, n: int, k: int, x: np.ndarray, scale: 
     lib().tpo_gguf_gemv_q8(GGUF_FMT[fmt], _p(w), C.c_size_t(n), C.c_size_t(k), _p(x), C.c_size_t(m),
                            C.c_float(scale), _p(y))
     return y
+
+
+# -- attention of the DiT block ---------------------------------------------------------------
+
+def qk_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """x [..., hd] normalised per last-dim row, times w[hd]."""
+    x = _c(x, np.float32)
+    hd = x.shape[-1]
+    out = np.empty_like(x)
+    lib().tpo_qk_norm(_p(x), C.c_size_t(x.size // hd), C.c_size_t(hd), _p(_c(w, np.float32)), C.c_float(eps), _p(out))
+    return out
+
+
+def flux_freqs(positions: np.ndarray, axes_dim, theta: float):
+    positions = _c(positions, np.float32).reshape(-1, len(axes_dim))
+    seq = positions.shape[0]
+    half = sum(d // 2 for d in axes_dim)
+    cos, sin = np.empty((seq, half), np.float32), np.empty((seq, half), np.float32)
+    ad = (C.c_int * len(axes_dim))(*axes_dim)
+    lib().tpo_flux_freqs(_p(positions), C.c_size_t(seq), ad, C.c_int(len(axes_dim)), C.c_double(theta), _p(cos), _p(sin))
+    return cos, sin
+
+
+def rope_interleaved(x: np.ndarray, cos: np.ndarray, sin: np.ndarray, heads: int, hd: int) -> np.ndarray:
+    out = _c(x, np.float32).copy()
+    seq = out.size // (heads * hd)
+    lib().tpo_rope_interleaved(_p(out), _p(_c(cos, np.float32)), _p(_c(sin, np.float32)), C.c_size_t(seq),
+                               C.c_size_t(heads), C.c_size_t(hd))
+    return out
+
+
+def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, heads: int, kv_heads: int, hd: int,
+              scale: float = None) -> np.ndarray:
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    seq_q, seq_kv = q.size // (heads * hd), k.size // (kv_heads * hd)
+    out = np.empty((seq_q, heads * hd), np.float32)
+    lib().tpo_attention(_p(q), _p(k), _p(v), C.c_size_t(seq_q), C.c_size_t(seq_kv), C.c_size_t(heads),
+                        C.c_size_t(kv_heads), C.c_size_t(hd), C.c_float(scale if scale is not None else hd ** -0.5),
+                        _p(out))
+    return out

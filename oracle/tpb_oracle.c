@@ -648,3 +648,92 @@ void tpo_gguf_gemv_q8(int fmt, const uint8_t *w, size_t n, size_t k, const float
         free(wr);
     }
 }
+
+/* ------------------------------------------------------------------------ */
+/* Attention of the DiT block: per-head RMS norm of q and k, interleaved-pair */
+/* RoPE, softmax attention with grouped-query heads.                          */
+/* ------------------------------------------------------------------------ */
+
+/* src/ops/norm.zig:12-23 applied per head row of `hd` (dit.zig:623-624): x * inv_rms * w. */
+void tpo_qk_norm(const float *x, size_t rows, size_t hd, const float *w, float eps, float *out) {
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < (long long)rows; r++) {
+        const float *xr = x + (size_t)r * hd;
+        double ss = 0.0;
+        for (size_t c = 0; c < hd; c++) ss += (double)xr[c] * (double)xr[c];
+        const float inv = 1.0f / sqrtf((float)(ss / (double)hd) + eps);
+        for (size_t c = 0; c < hd; c++) out[(size_t)r * hd + c] = xr[c] * inv * w[c];
+    }
+}
+
+/* src/ops/rope.zig:28-66: FLUX multi-axis tables; positions [seq][n_axes], angles in f64. */
+void tpo_flux_freqs(const float *positions, size_t seq, const int *axes_dim, int n_axes, double theta, float *cosv,
+                    float *sinv) {
+    size_t half = 0;
+    for (int a = 0; a < n_axes; a++) half += (size_t)axes_dim[a] / 2;
+    for (size_t p = 0; p < seq; p++) {
+        size_t off = 0;
+        for (int a = 0; a < n_axes; a++) {
+            const double pos = positions[p * (size_t)n_axes + (size_t)a];
+            const int dh = axes_dim[a] / 2;
+            for (int i = 0; i < dh; i++) {
+                const double omega = 1.0 / pow(theta, (double)(2 * i) / (double)axes_dim[a]);
+                cosv[p * half + off + (size_t)i] = (float)cos(pos * omega);
+                sinv[p * half + off + (size_t)i] = (float)sin(pos * omega);
+            }
+            off += (size_t)dh;
+        }
+    }
+}
+
+/* src/ops/rope.zig:68-90: (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) on consecutive pairs; x is [seq][heads*hd]. */
+void tpo_rope_interleaved(float *x, const float *cosv, const float *sinv, size_t seq, size_t heads, size_t hd) {
+    const size_t half = hd / 2;
+    for (size_t p = 0; p < seq; p++)
+        for (size_t h = 0; h < heads; h++) {
+            float *b = x + (p * heads + h) * hd;
+            for (size_t i = 0; i < half; i++) {
+                const float x0 = b[2 * i], x1 = b[2 * i + 1];
+                const float c = cosv[p * half + i], s = sinv[p * half + i];
+                b[2 * i] = x0 * c - x1 * s;
+                b[2 * i + 1] = x0 * s + x1 * c;
+            }
+        }
+}
+
+/* src/ops/attention.zig:46-60, :104-150 (non-causal, no mask): out[seq_q][heads*hd] =
+ * softmax(q k^T * scale) v per head, kv head = h / (heads / kv_heads); f64 accumulation. */
+void tpo_attention(const float *q, const float *k, const float *v, size_t seq_q, size_t seq_kv, size_t heads,
+                   size_t kv_heads, size_t hd, float scale, float *out) {
+    const size_t rep = heads / kv_heads;
+#pragma omp parallel
+    {
+        double *sc = (double *)malloc(seq_kv * sizeof(double));
+#pragma omp for schedule(static) collapse(2)
+        for (long long h = 0; h < (long long)heads; h++)
+            for (long long i = 0; i < (long long)seq_q; i++) {
+                const size_t hk = (size_t)h / rep;
+                const float *qr = q + ((size_t)i * heads + (size_t)h) * hd;
+                double mx = -1e300;
+                for (size_t j = 0; j < seq_kv; j++) {
+                    const float *kr = k + (j * kv_heads + hk) * hd;
+                    double d = 0.0;
+                    for (size_t c = 0; c < hd; c++) d += (double)qr[c] * (double)kr[c];
+                    sc[j] = d * (double)scale;
+                    if (sc[j] > mx) mx = sc[j];
+                }
+                double sum = 0.0;
+                for (size_t j = 0; j < seq_kv; j++) {
+                    sc[j] = exp(sc[j] - mx);
+                    sum += sc[j];
+                }
+                float *o = out + ((size_t)i * heads + (size_t)h) * hd;
+                for (size_t c = 0; c < hd; c++) {
+                    double a = 0.0;
+                    for (size_t j = 0; j < seq_kv; j++) a += sc[j] * (double)v[(j * kv_heads + hk) * hd + c];
+                    o[c] = (float)(a / sum);
+                }
+            }
+        free(sc);
+    }
+}

@@ -148,6 +148,14 @@ void tpo_gguf_dequant_row(int fmt, const uint8_t *row, size_t k, float *out);
 void tpo_gguf_gemv_q8(int fmt, const uint8_t *w, size_t n, size_t k, const float *x, size_t m, float scale,
                       float *y);
 
+/* Attention of the DiT block (src/ops/norm.zig:12-23, src/ops/rope.zig:28-90, src/ops/attention.zig:46-150). */
+void tpo_qk_norm(const float *x, size_t rows, size_t hd, const float *w, float eps, float *out);
+void tpo_flux_freqs(const float *positions, size_t seq, const int *axes_dim, int n_axes, double theta, float *cosv,
+                    float *sinv);
+void tpo_rope_interleaved(float *x, const float *cosv, const float *sinv, size_t seq, size_t heads, size_t hd);
+void tpo_attention(const float *q, const float *k, const float *v, size_t seq_q, size_t seq_kv, size_t heads,
+                   size_t kv_heads, size_t hd, float scale, float *out);
+
 int tpo_num_threads(void);
 
 #ifdef __cplusplus

@@ -360,3 +360,43 @@ def test_iq4_nl_dequant_matches_reference_known_answers():
     out = oracle.gguf_dequant_row("iq4_nl", blk, 32)
     assert out[0] == 2.0 * kv[1] and out[16] == 2.0 * kv[2]
     assert np.all(out[1:16] == 2.0 * kv[0]) and np.all(out[17:32] == 2.0 * kv[0])
+
+
+# ---------------------------------------------------------------------------------
+# Attention pieces pinned to the reference's torch-generated fixtures
+# (src/ops/attention.zig:291-313 at 3e-6, src/ops/rope.zig:353-366 at 2e-6)
+# ---------------------------------------------------------------------------------
+
+def test_attention_matches_reference_sdpa_fixture():
+    q = np.array([-1.12583983, -1.1523602, -0.250578582, -0.433878809, 0.166455343, 0.87438184, -0.143473849,
+                  -0.111609332, 0.848710358, 0.692009151, -0.31601277, -2.11521935, 0.931826591, 1.25900924, 2.00498056,
+                  0.0537369028, 0.468096405, -0.157712445, 1.44366014, 0.266049415, 0.618056655, -0.412802219,
+                  -0.841064811, -2.31604195], np.float32)
+    k = np.array([0.370393544, 1.45650256, 0.939809918, 0.774848819, 0.191869423, 1.26379478, -1.29043508, -0.791102707,
+                  -0.0208794735, -0.718480051, 0.518636763, -1.31252193], np.float32)
+    v = np.array([0.191995069, 0.542771339, -2.21877933, 0.258984536, -1.02970219, -0.50075841, 0.273367733,
+                  -0.918099999, -0.0404210873, 0.288116813, -0.00753730815, -0.914495468], np.float32)
+    want = np.array([-0.233936831, 0.140385717, -0.156303599, -0.80384618, -0.3932935, 0.0334626585, -0.734680712,
+                     -0.463540882, -0.583657682, -0.13896063, -0.0424246602, -0.813088059, 0.0828519836, 0.443475634,
+                     -1.80830443, 0.0511539057, 0.00270056119, 0.361810803, -1.23623109, -0.249404013, -0.469629675,
+                     -0.0521637946, 0.05305776, -0.882563472], np.float32)
+    got = oracle.attention(q, k, v, heads=2, kv_heads=1, hd=4)
+    assert np.allclose(got.reshape(-1), want, rtol=0, atol=3e-6)
+
+
+def test_flux_rope_matches_reference_fixture():
+    q_in = np.array([-1, -0.899999976, -0.800000012, -0.699999988, -0.600000024, -0.5, -0.399999976, -0.300000012,
+                     -0.199999988, -0.100000024, 0, 0.100000024, 0.200000048, 0.299999952, 0.399999976, 0.5, 0.600000024,
+                     0.700000048, 0.799999952, 0.899999976, 1, 1.0999999, 1.20000005, 1.29999995], np.float32)
+    q_out = np.array([-1, -0.899999976, -0.800000012, -0.699999988, -0.600000024, -0.5, -0.399999976, -0.300000012,
+                      -0.0239133313, -0.222324416, -0.0176892225, 0.0984230489, 0.190414816, 0.306173474, 0.397181958,
+                      0.502241433, -0.00754925609, 0.921923578, -0.596392035, 1.04609585, 0.734088182, 1.29271591,
+                      1.14791059, 1.34621739], np.float32)
+    cos, sin = oracle.flux_freqs(np.array([0, 1, 7], np.float32), [8], 1000.0)
+    got = oracle.rope_interleaved(q_in, cos, sin, heads=1, hd=8)
+    assert np.allclose(got, q_out, rtol=0, atol=2e-6)
+    # position zero is the identity (rope.zig:391-398); qk-norm with unit weight has unit RMS
+    assert np.array_equal(got[:8], q_in[:8])
+    x = np.random.default_rng(0).standard_normal((5, 16)).astype(np.float32)
+    n = oracle.qk_norm(x, np.ones(16, np.float32), 0.0)
+    assert np.allclose(np.sqrt((n.astype(np.float64) ** 2).mean(axis=1)), 1.0, atol=1e-6)
