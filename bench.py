@@ -395,6 +395,8 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
 
     mod = harness.dit_modulation(be, synth.DIT_BLOCKS, synth.DIT_HIDDEN)
     T = synth.DIT_TOKENS
+    _, _, _, qn, kn, cos, sin = harness.attention_inputs(T, 1, 1, be.device)
+    attn = {"q_norm": qn, "k_norm": kn, "cos": cos, "sin": sin, "heads": synth.DIT_HIDDEN // 128}
     # name -> (what it runs, call).  "headline" = the reference's op sequence with every
     # elementwise op fused into the prep kernels, f32 activations, reference MLP tiling.
     variants = {
@@ -407,6 +409,10 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
                                                                       mode="fused", mod=mod, mlp_tile=T)),
         "linears_only": ("prep + GEMM launches only, one MLP pass over all tokens",
                          lambda i: harness.dit_step_linears(be, w, latents[i % 2], mode="linears", mlp_tile=T)),
+        "fused_bf16_with_attention": ("fused_bf16_whole_batch plus qk-norm, RoPE and softmax attention (24 heads x 128) in "
+                                      "every block: the whole block stack of a step",
+                                      lambda i: harness.dit_step_linears(be, w, latents[i % 2], out_dtype=torch.bfloat16,
+                                                                         mode="fused", mod=mod, mlp_tile=T, attn=attn)),
     }
     steps = max(1, min(args.steps, 20))
     ms_of = {}
@@ -437,8 +443,9 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
                            "blocks": synth.DIT_BLOCKS, "hidden": synth.DIT_HIDDEN, "mlp": synth.DIT_MLP,
                            "tokens": synth.DIT_TOKENS, "latents_per_gpu": 1,
                            "scope": "the eight quantised linears per block and their elementwise neighbours (RMS norm + "
-                                    "modulation, sigmoid and SiLU gates, gated residual); attention proper is not run "
-                                    "(v stands in for its output); tops counts the linears' 2*M*N*K only"}}
+                                    "modulation, sigmoid and SiLU gates, gated residual); attention proper runs only in the "
+                                    "variant that names it (elsewhere v stands in for its output); tops counts the "
+                                    "linears' 2*M*N*K only"}}
         if w.streamer:
             line["h2d_gbs"] = copied[head] / (ms_of[head] * 1e-3) / 1e9
             line["streamed_bytes_per_step"] = copied[head] / steps
@@ -640,6 +647,63 @@ def run_mode_gemv(args, rank, local, world):
     be.close()
 
 
+def run_mode_attn(args, local):
+    """The attention of one DiT block at config 3's shape (seq 4608, 24 heads x 128, non-causal):
+    the prepare pass (qk-norm + RoPE + per-head bf16 layout) and the tcgen05 softmax(q k^T) v
+    kernel timed separately, with torch's scaled_dot_product_attention on the same operands
+    beside it as the library figure.  FLOPs = 4 * seq^2 * head_dim * heads."""
+    import torch
+    from tensorpencil_b200 import harness
+    from tensorpencil_b200.backend import Backend
+    torch.cuda.set_device(local)
+    be = Backend(local)
+    peaks = measured_peaks()
+    cases = []
+    for (seq, heads, kv_heads) in ((4608, 24, 24), (4608, 24, 8), (1024, 24, 24), (16384, 24, 24)):
+        q, k, v, qn, kn, cos, sin = harness.attention_inputs(seq, heads, kv_heads, be.device, torch.bfloat16)
+        out = torch.empty(seq, heads * 128, dtype=torch.bfloat16, device="cuda")
+        be.attention(q, k, v, qn, kn, cos, sin, heads, kv_heads, out=out)
+        lib = be.lib
+        qb, kb, vt = be._attn_qb, be._attn_kb, be._attn_vt
+        TPB_BF16 = 1
+        prep = lambda i: be._check(lib.tpb_attn_prepare(be.h, be._stream(), q.data_ptr(), k.data_ptr(), v.data_ptr(), TPB_BF16,
+                                                        qn.data_ptr(), kn.data_ptr(), 1e-5, cos.data_ptr(), sin.data_ptr(),
+                                                        seq, heads, kv_heads, 128, qb.data_ptr(), kb.data_ptr(), vt.data_ptr()))
+        att = lambda i: be._check(lib.tpb_attention(be.h, be._stream(), out.data_ptr(), TPB_BF16, qb.data_ptr(), kb.data_ptr(),
+                                                    vt.data_ptr(), seq, seq, heads, kv_heads, 128, 128 ** -0.5))
+        steps = max(10, min(args.steps, 50))
+        for i in range(3):
+            prep(i), att(i)
+        ms_prep = _events_ms(prep, steps, torch.cuda.synchronize) / steps
+        ms_att = _events_ms(att, steps, torch.cuda.synchronize) / steps
+        # library figure: torch SDPA on [1][heads][seq][128] bf16 views of the same prepared operands
+        qt = qb.unsqueeze(0)
+        kt = kb.repeat_interleave(heads // kv_heads, dim=0).unsqueeze(0)
+        vv = v.reshape(seq, kv_heads, 128).permute(1, 0, 2).repeat_interleave(heads // kv_heads, dim=0).unsqueeze(0).contiguous()
+        sd = lambda i: torch.nn.functional.scaled_dot_product_attention(qt, kt, vv)
+        for i in range(3):
+            sd(i)
+        ms_sdpa = _events_ms(sd, steps, torch.cuda.synchronize) / steps
+        ref = sd(0)[0].permute(1, 0, 2).reshape(seq, heads * 128).float()
+        diff = (out.float() - ref).abs().max().item()
+        flops = 4.0 * seq * seq * 128 * heads
+        cases.append({"seq": seq, "heads": heads, "kv_heads": kv_heads, "prepare_us": ms_prep * 1e3,
+                      "attention_us": ms_att * 1e3, "tflops": flops / (ms_att * 1e-3) / 1e12,
+                      "frac_of_bf16_peak": flops / (ms_att * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                      "torch_sdpa_us": ms_sdpa * 1e3, "max_abs_diff_vs_sdpa": diff})
+        del q, k, v, out, qt, kt, vv, ref
+    be.status_poll()
+    head = cases[0]
+    print(json.dumps({"metric": "attention_tflops", "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+                      "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "roofline": {"bound": "tensor", "achieved": head["tflops"], "peak": peaks["bf16_tflops"],
+                                   "unit": "TFLOP/s", "frac": head["frac_of_bf16_peak"],
+                                   "peak_note": f"{peaks['source']} cuBLAS bf16 burst"},
+                      "config": {"workload": "config3's attention: seq 4608, 24 heads x 128, non-causal, bf16 operands"},
+                      "cases": cases}), flush=True)
+    be.close()
+
+
 def run_mode_one_kernel(args, local):
     """Launches one kernel of the path a few times through the C ABI -- the small,
     self-ending command the ncu captures under profiles/ are taken from."""
@@ -696,6 +760,11 @@ def run_mode_one_kernel(args, local):
         print(json.dumps({"mode": "one-kernel", "case": case, "copies": out}), flush=True)
         be.close()
         return
+    elif case == "attn":
+        seq, heads = 4608, 24
+        q, k, v, qn, kn, cos, sin = harness.attention_inputs(seq, heads, heads, be.device, torch.bfloat16)
+        for _ in range(reps):
+            be.attention(q, k, v, qn, kn, cos, sin, heads, heads)
     elif case == "prep-silu":
         m, k = 2048, N
         g, u = torch.randn(m, k, device="cuda"), torch.randn(m, k, device="cuda")
@@ -726,10 +795,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--out-dtype", choices=["f32", "bf16"], default="f32")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "one-kernel"], default="linear",
+    ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "attn", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
-                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu")
+                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -749,6 +818,8 @@ def main():
         return run_mode_nsplit(args, rank, local, world)
     if args.mode == "gemv":
         return run_mode_gemv(args, rank, local, world)
+    if args.mode == "attn":
+        return run_mode_attn(args, local)
     if args.mode == "one-kernel":
         return run_mode_one_kernel(args, local)
     run_ours(args, rank, local, world)

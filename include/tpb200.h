@@ -336,6 +336,28 @@ size_t tpb_gguf_row_bytes(int fmt, int64_t cols);
 int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, const void *w, float scale,
                       int64_t rows, int64_t cols, const void *xq, int ng, int row_off, int n_total);
 
+/* ---- Attention of the DiT block (SURVEY "next" row: the op between the quantised linears) ---
+ * Replaces Backend.qkNorm + rope + attn / opAttnTC for the non-causal, unmasked case
+ * (src/models/dit_cuda.zig:479-489; src/gpu/cuda/backend.zig:2939-3196; CPU definitions
+ * src/ops/norm.zig:12-23, src/ops/rope.zig:68-90, src/ops/attention.zig:46-150).
+ *
+ * tpb_attn_prepare: q [seq][heads*128], k and v [seq][kv_heads*128] (f32 or bf16) ->
+ *   qb [heads][seq][128] and kb [kv_heads][seq][128] = rope(x * inv_rms(x) * norm_weight) in bf16
+ *   (per-head RMS norm over the 128 elements, then the interleaved-pair rotation with the
+ *   per-position tables cos/sin [seq][64]), and vt = v transposed per head,
+ *   [kv_heads][128][seq_pad] bf16 with seq_pad = seq rounded up to 8 (tpb_attn_vt_elems elements).
+ * tpb_attention: out [seq_q][heads*128] (bf16 or f32) = softmax(q k^T * scale) v per head,
+ *   kv head = head / (heads / kv_heads); flash-style on tcgen05, f32 softmax and accumulation,
+ *   probabilities rounded to bf16 for the second product.  head_dim must be 128. */
+size_t tpb_attn_vt_elems(int64_t seq_kv, int kv_heads);
+int tpb_attn_prepare(tpb_handle_t h, tpb_stream_t stream, const void *q, const void *k, const void *v,
+                     int in_dtype, const float *q_norm, const float *k_norm, float eps,
+                     const float *cosv, const float *sinv, int64_t seq, int heads, int kv_heads,
+                     int head_dim, void *qb, void *kb, void *vt);
+int tpb_attention(tpb_handle_t h, tpb_stream_t stream, void *out, int out_dtype, const void *qb,
+                  const void *kb, const void *vt, int64_t seq_q, int64_t seq_kv, int heads,
+                  int kv_heads, int head_dim, float scale);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,9 @@ SIGNATURES = {
     "tpb_convrot_prep_fused": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _i64, _i, _vp, _vp, _vp]),
     "tpb_gguf_row_bytes": (_sz, [_i, _i64]),
     "tpb_gguf_gemv_q8n": (_i, [_vp, _vp, _i, _vp, _vp, _f, _i64, _i64, _vp, _i, _i, _i]),
+    "tpb_attn_vt_elems": (_sz, [_i64, _i]),
+    "tpb_attn_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _f, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp]),
+    "tpb_attention": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i64, _i64, _i, _i, _i, _f]),
     "tpb_peer_alloc": (_i, [_vp, _sz, C.POINTER(_vp), _vp]),
     "tpb_peer_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "tpb_peer_close": (_i, [_vp, _vp]),

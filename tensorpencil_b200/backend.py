@@ -216,6 +216,34 @@ class Backend:
                                            mod[gate_off:].data_ptr(), total // dim, dim))
         self.launches += 1
 
+    # -- attention (qk-norm + RoPE + softmax attention) ------------------------------------
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, heads: int, kv_heads: int, head_dim: int = 128,
+                  eps: float = 1e-5, scale: Optional[float] = None, out_dtype=torch.bfloat16,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """qkNorm + rope on q and k, then attn (dit_cuda.zig:479-489) in two library calls.
+        q [seq][heads*hd], k / v [seq][kv_heads*hd] (f32 or bf16); cos / sin [seq][hd/2]."""
+        seq = q.shape[0]
+        assert q.dtype == k.dtype == v.dtype and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+        key = (seq, heads, kv_heads)
+        if getattr(self, "_attn_key", None) != key:
+            self._attn_qb = torch.empty((heads, seq, head_dim), dtype=torch.bfloat16, device=self.device)
+            self._attn_kb = torch.empty((kv_heads, seq, head_dim), dtype=torch.bfloat16, device=self.device)
+            self._attn_vt = torch.empty(self.lib.tpb_attn_vt_elems(seq, kv_heads), dtype=torch.bfloat16, device=self.device)
+            self._attn_key = key
+        self._check(self.lib.tpb_attn_prepare(self.h, self._stream(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                              _TORCH_TO_TPB[q.dtype], q_norm.data_ptr(), k_norm.data_ptr(), eps,
+                                              cos.data_ptr(), sin.data_ptr(), seq, heads, kv_heads, head_dim,
+                                              self._attn_qb.data_ptr(), self._attn_kb.data_ptr(), self._attn_vt.data_ptr()))
+        if out is None:
+            out = torch.empty((seq, heads * head_dim), dtype=out_dtype, device=self.device)
+        self._check(self.lib.tpb_attention(self.h, self._stream(), out.data_ptr(), _TORCH_TO_TPB[out.dtype],
+                                           self._attn_qb.data_ptr(), self._attn_kb.data_ptr(), self._attn_vt.data_ptr(),
+                                           seq, seq, heads, kv_heads, head_dim,
+                                           float(scale if scale is not None else head_dim ** -0.5)))
+        self.launches += 4
+        return out
+
     def _gemm(self, y: torch.Tensor, w_bytes: np.ndarray, weight_scale: np.ndarray, rows: int,
               w_bits: int, ldy: Optional[int] = None):
         assert self.i8_bits == w_bits, "opI{8,4}Gemm must follow the matching prep"

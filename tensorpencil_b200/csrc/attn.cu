@@ -1,0 +1,533 @@
+// Attention of the DiT block for sm_100a: per-head RMS norm of q and k + interleaved RoPE
+// (one elementwise pass that also lays the operands out per head in bf16), then a
+// flash-style softmax(q k^T * scale) v kernel on tcgen05 (kind::f16, bf16 operands, f32
+// accumulators in TMEM).  Non-causal, no mask, grouped-query heads, head_dim 128: the shape
+// of the Krea 2 transformer (src/models/dit_cuda.zig:479-489; CPU definitions
+// src/ops/attention.zig:46-150, src/ops/rope.zig:68-90, src/ops/norm.zig:12-23).
+//
+// Kernel layout.  One CTA = 128 query rows of one head; it walks the kv sequence in tiles of
+// 128.  Six warps: warp 0 loads tiles with TMA (Q once; K and V^T double-buffered, separate
+// barriers so a K slot is free again as soon as its scores are done), warp 1 issues the MMAs,
+// warps 2-5 are the softmax: thread r owns query row r.
+//   S_j  = Q K_j^T        M 128 x N 128 x K 128 (head_dim), both operands K-major   -> TMEM, 2 buffers
+//   P_j  = exp2(S_j * c - m), running max m and sum l per row (online softmax); P_j goes to
+//          shared memory as bf16 in the K-major 128-byte-swizzled layout of an A operand;
+//          O is multiplied by exp2(m_old - m_new) in TMEM when a row's max moved
+//   O   += P_j V_j        M 128 x N 128 (head_dim) x K 128 (kv); V comes pre-transposed
+//          ([head][d][kv], kv contiguous) so that it is K-major too                 -> TMEM
+// The score MMA of tile j+1 is issued before the softmax of tile j has finished, so the tensor
+// pipe works on S_{j+1} while the softmax warps work on S_j.  Every wait is bounded.
+#include <cuda_bf16.h>
+
+#include "gemm_common.cuh"
+
+using namespace tpb_gemm;
+
+namespace {
+
+constexpr int kHd = 128;          // head_dim
+constexpr int kTile = 128;        // query rows per CTA and kv rows per step
+constexpr int kAtomBytes = 16384; // [128 rows][64 bf16] in the 128-byte swizzle layout
+constexpr int kAttnThreads = 192;
+constexpr int kAttnTmemCols = 512;  // S0, S1, O: 3 x 128 columns (power of two allocation)
+
+// smem: Q (2 atoms) | K stage 0,1 (2 atoms each) | V^T stage 0,1 | P (2 atoms) | barriers
+constexpr int kOffQ = 0;
+constexpr int kOffK = 2 * kAtomBytes;
+constexpr int kOffV = kOffK + 4 * kAtomBytes;
+constexpr int kOffP = kOffV + 4 * kAtomBytes;
+constexpr int kOffBar = kOffP + 2 * kAtomBytes;
+constexpr int kAttnSmem = kOffBar + 256 + 1024;  // + alignment slack
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// kind::f16 instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M 128, N 128.
+__device__ __forceinline__ uint32_t make_idesc_bf16() {
+    uint32_t d = 0;
+    d |= 1u << 4;   // D: f32
+    d |= 1u << 7;   // A: bf16
+    d |= 1u << 10;  // B: bf16
+    d |= (uint32_t)(128 >> 3) << 17;
+    d |= (uint32_t)(128 >> 4) << 24;
+    return d;
+}
+
+struct AttnParams {
+    void *out;            // [seq_q][heads * 128], bf16 or f32
+    int out_f32;
+    int seq_q, seq_kv, heads, kv_heads;
+    float scale_log2;     // scale * log2(e)
+    uint32_t *status;
+};
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                  const __grid_constant__ CUtensorMap tma_vt, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + kOffBar;
+    // barrier slots (8 bytes each)
+    const uint32_t q_full = bars;
+    auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto v_full = [&](int s) { return bars + 8u * (3 + s); };
+    auto k_empty = [&](int s) { return bars + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
+    auto s_full = [&](int b) { return bars + 8u * (9 + b); };
+    auto s_empty = [&](int b) { return bars + 8u * (11 + b); };
+    const uint32_t p_full = bars + 8u * 13, p_empty = bars + 8u * 14;
+    uint8_t *gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + kOffBar + 136);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int q0 = blockIdx.x * kTile;
+    const int head = blockIdx.y;
+    const int hk = head / (p.heads / p.kv_heads);
+    const int n_tiles = (p.seq_kv + kTile - 1) / kTile;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(k_full(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_empty(s), 1);
+            mbar_init(s_full(s), 1);
+            mbar_init(s_empty(s), 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(p_empty, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32((const void *)tmem_slot)),
+                     "r"(kAttnTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;  // S0 at +0, S1 at +128, O at +256
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, 2 * kAtomBytes);
+            tma_load_2d(smem_base + kOffQ, &tma_q, q_full, 0, head * p.seq_q + q0);
+            tma_load_2d(smem_base + kOffQ + kAtomBytes, &tma_q, q_full, 64, head * p.seq_q + q0);
+            bool ok = true;
+            for (int j = 0; ok && j < n_tiles; j++) {
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                ok = mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.status, (9u << 24) | 0x10u | st, true);
+                if (!ok) break;
+                mbar_arrive_expect_tx(k_full(st), 2 * kAtomBytes);
+                const uint32_t kd = smem_base + kOffK + st * 2 * kAtomBytes;
+                tma_load_2d(kd, &tma_k, k_full(st), 0, hk * p.seq_kv + j * kTile);
+                tma_load_2d(kd + kAtomBytes, &tma_k, k_full(st), 64, hk * p.seq_kv + j * kTile);
+                ok = mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.status, (9u << 24) | 0x20u | st, true);
+                if (!ok) break;
+                mbar_arrive_expect_tx(v_full(st), 2 * kAtomBytes);
+                const uint32_t vd = smem_base + kOffV + st * 2 * kAtomBytes;
+                tma_load_2d(vd, &tma_vt, v_full(st), j * kTile, hk * kHd);
+                tma_load_2d(vd + kAtomBytes, &tma_vt, v_full(st), j * kTile + 64, hk * kHd);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_bf16();
+            bool ok = mbar_wait(q_full, 0, abort_flag, p.status, (10u << 24) | 1u);
+            // S_b = Q K_t^T: K dimension = head_dim = 2 atoms x 4 steps of 16 elements (32 bytes)
+            auto issue_qk = [&](int t) {
+                const int st = t & 1, b = t & 1;
+                const uint32_t ka = smem_base + kOffK + st * 2 * kAtomBytes;
+#pragma unroll
+                for (int a = 0; a < 2; a++) {
+                    const uint64_t qd = make_kmajor_sw128_desc(smem_base + kOffQ + a * kAtomBytes);
+                    const uint64_t kd = make_kmajor_sw128_desc(ka + a * kAtomBytes);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++)
+                        tc_mma_bf16(tmem_base + (uint32_t)(b * 128), qd + 2u * kk, kd + 2u * kk, idesc, (a | kk) ? 1u : 0u);
+                }
+                tc_commit(k_empty(st));
+                tc_commit(s_full(b));
+            };
+            if (ok) {
+                ok = mbar_wait(k_full(0), 0, abort_flag, p.status, (10u << 24) | 2u);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(0);
+                }
+            }
+            for (int j = 0; ok && j < n_tiles; j++) {
+                if (j + 1 < n_tiles) {
+                    const int t = j + 1;
+                    ok = mbar_wait(k_full(t & 1), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, (10u << 24) | 3u);
+                    if (!ok) break;
+                    ok = mbar_wait(s_empty(t & 1), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status, (10u << 24) | 4u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(t);
+                }
+                const int st = j & 1;
+                ok = mbar_wait(v_full(st), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, (10u << 24) | 5u);
+                if (!ok) break;
+                ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.status, (10u << 24) | 6u);
+                if (!ok) break;
+                tc_fence_after();
+                // O += P V_j: K dimension = kv = 2 atoms x 4 steps
+                const uint32_t va = smem_base + kOffV + st * 2 * kAtomBytes;
+#pragma unroll
+                for (int a = 0; a < 2; a++) {
+                    const uint64_t pd = make_kmajor_sw128_desc(smem_base + kOffP + a * kAtomBytes);
+                    const uint64_t vd = make_kmajor_sw128_desc(va + a * kAtomBytes);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++)
+                        tc_mma_bf16(tmem_o, pd + 2u * kk, vd + 2u * kk, idesc, (j > 0 || a > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(v_empty(st));
+                tc_commit(p_empty);
+            }
+        }
+    } else {
+        // ---------------- softmax + output: thread = query row ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                 // row within the tile = TMEM lane
+        const uint32_t t_lane = (uint32_t)(quarter * 32) << 16;
+        const uint32_t p_row = smem_base + kOffP + (uint32_t)r * 128u;
+        const uint32_t sw = (uint32_t)(r & 7);
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            const int b = j & 1;
+            ok = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, (11u << 24) | 1u, true);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_s = tmem_base + t_lane + (uint32_t)(b * 128);
+            const int kv_left = p.seq_kv - j * kTile;      // columns >= kv_left are past the sequence
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld_32x32(t_s + (uint32_t)(c * 32), v);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (c * 32 + i < kv_left) mx = fmaxf(mx, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float alpha = ex2(m_run - m_new);         // 0 on the first tile (m_run = -inf)
+            // the P buffer and O are free once the previous P V product is done
+            if (j > 0) {
+                ok = mbar_wait(p_empty, (uint32_t)(j - 1) & 1u, abort_flag, p.status, (11u << 24) | 2u, true);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            // pass 2: P = exp2(S c - m) as bf16 into the A-operand layout, row sum
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld_32x32(t_s + (uint32_t)(c * 32), v);
+                tc_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float e0 = ex2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_new));
+                    float e1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_new));
+                    if (c * 32 + 2 * i >= kv_left) e0 = 0.0f;
+                    if (c * 32 + 2 * i + 1 >= kv_left) e1 = 0.0f;
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    // the sum uses the rounded values, the ones the tensor core multiplies
+                    const float2 f2 = __bfloat1622float2(b2);
+                    sum += f2.x + f2.y;
+                    pk[i] = *reinterpret_cast<const uint32_t *>(&b2);
+                }
+                // 32 columns = 64 bytes = chunks 4 (c & 1) .. + 3 of atom c / 2
+                const uint32_t base = p_row + (uint32_t)(c >> 1) * kAtomBytes;
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint32_t chunk = (uint32_t)(4 * (c & 1) + g);
+                    st_shared_v4(base + ((chunk ^ sw) << 4), pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+                }
+            }
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+            // this S buffer may be overwritten by the scores of tile j + 2
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(b));
+            // rows whose maximum moved: O *= alpha (skipped when no row of the warp moved)
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t v[32];
+                    tc_ld_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tc_st_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
+                }
+                tc_wait_st();
+            }
+            // P (generic-proxy writes) -> visible to the tensor core; O updates ordered before the MMA
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok) {
+            ok = mbar_wait(p_empty, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.status, (11u << 24) | 3u, true);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv_l = 1.0f / l_run;
+            const int q = q0 + r;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tc_ld_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
+                tc_wait_ld();
+                if (q < p.seq_q) {
+                    const size_t off = (size_t)q * p.heads * kHd + (size_t)head * kHd + c * 32;
+                    if (p.out_f32) {
+                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + off);
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            dst[i] = make_float4(__uint_as_float(v[4 * i]) * inv_l, __uint_as_float(v[4 * i + 1]) * inv_l,
+                                                 __uint_as_float(v[4 * i + 2]) * inv_l, __uint_as_float(v[4 * i + 3]) * inv_l);
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + off);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * e]) * inv_l,
+                                                                                __uint_as_float(v[8 * i + 2 * e + 1]) * inv_l);
+                                w[e] = *reinterpret_cast<const uint32_t *>(&b2);
+                            }
+                            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAttnTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- per-head RMS norm + RoPE + per-head bf16 layout ---------------------------------------
+//
+// One warp per (token, head): a lane holds 4 consecutive elements (two rotation pairs).
+// x [seq][heads*128] (f32 or bf16) -> out [heads][seq][128] bf16 = rope(x * inv_rms * w).
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ cosv,
+                    const float *__restrict__ sinv, float eps, int seq, int heads, __nv_bfloat16 *__restrict__ out) {
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
+    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gw >= seq * heads) return;
+    const int p = gw / heads, h = gw - p * heads;
+    const T *src = x + ((size_t)p * heads + h) * kHd + 4 * lane;
+    float v[4];
+    if (sizeof(T) == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+        const uint2 t = __ldg(reinterpret_cast<const uint2 *>(src));
+        v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+        v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+    }
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = __frsqrt_rn(ss * (1.0f / kHd) + eps);
+    const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + lane);
+    const float n0 = v[0] * inv * wv.x, n1 = v[1] * inv * wv.y, n2 = v[2] * inv * wv.z, n3 = v[3] * inv * wv.w;
+    // pairs 2*lane and 2*lane + 1 of this position's table
+    const float2 c2 = __ldg(reinterpret_cast<const float2 *>(cosv + (size_t)p * (kHd / 2)) + lane);
+    const float2 s2 = __ldg(reinterpret_cast<const float2 *>(sinv + (size_t)p * (kHd / 2)) + lane);
+    const float r0 = n0 * c2.x - n1 * s2.x, r1 = n0 * s2.x + n1 * c2.x;
+    const float r2 = n2 * c2.y - n3 * s2.y, r3 = n2 * s2.y + n3 * c2.y;
+    const __nv_bfloat162 a = __floats2bfloat162_rn(r0, r1), b = __floats2bfloat162_rn(r2, r3);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&a);
+    o.y = *reinterpret_cast<const uint32_t *>(&b);
+    *reinterpret_cast<uint2 *>(out + ((size_t)h * seq + p) * kHd + 4 * lane) = o;
+}
+
+// v [seq][kv_heads*128] -> vt [kv_heads][128][seq_pad] bf16 (kv contiguous; columns seq..seq_pad-1 zero).
+// A CTA transposes 64 tokens x 128 dims of one head through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+v_transpose_kernel(const T *__restrict__ v, int seq, int seq_pad, int kv_heads, __nv_bfloat16 *__restrict__ vt) {
+    __shared__ __nv_bfloat16 tile[64][kHd + 2];
+    tpb_grid_dep_launch();
+    tpb_grid_dep_wait();
+    const int p0 = blockIdx.x * 64, h = blockIdx.y;
+    for (int i = threadIdx.x; i < 64 * kHd; i += blockDim.x) {
+        const int pr = i / kHd, d = i - pr * kHd;
+        const int p = p0 + pr;
+        float val = 0.0f;
+        if (p < seq) {
+            const T t = v[((size_t)p * kv_heads + h) * kHd + d];
+            val = sizeof(T) == 4 ? *reinterpret_cast<const float *>(&t) : __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(&t));
+        }
+        tile[pr][d] = __float2bfloat16_rn(val);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * kHd; i += blockDim.x) {
+        const int d = i / 64, pr = i - d * 64;
+        const int p = p0 + pr;
+        if (p < seq_pad) vt[((size_t)h * kHd + d) * seq_pad + p] = tile[pr][d];
+    }
+}
+
+// 2-D bf16 tensor [rows][cols] (cols contiguous), box = 64 columns x 128 rows, 128-byte swizzle,
+// out-of-range elements read as zero.
+int make_bf16_map(tpb_handle_t h, CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int64_t ld) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64u, 128u};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed (%d)", (int)r);
+    return TPB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t tpb_attn_vt_elems(int64_t seq_kv, int kv_heads) {
+    const int64_t seq_pad = (seq_kv + 7) / 8 * 8;
+    return (size_t)kv_heads * kHd * (size_t)seq_pad;
+}
+
+int tpb_attn_prepare(tpb_handle_t h, tpb_stream_t stream, const void *q, const void *k, const void *v, int in_dtype,
+                     const float *q_norm, const float *k_norm, float eps, const float *cosv, const float *sinv,
+                     int64_t seq, int heads, int kv_heads, int head_dim, void *qb, void *kb, void *vt) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, q && k && v && q_norm && k_norm && cosv && sinv && qb && kb && vt, "attn_prepare: null pointer");
+    TPB_CHECK_ARG(h, head_dim == kHd, "attn_prepare: head_dim must be 128 (got %d)", head_dim);
+    TPB_CHECK_ARG(h, in_dtype == TPB_F32 || in_dtype == TPB_BF16, "attn_prepare: inputs must be f32 or bf16");
+    TPB_CHECK_ARG(h, seq > 0 && seq < (1 << 24) && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                  "attn_prepare: bad seq / heads / kv_heads");
+    TPB_CHECK_ARG(h, tpb_aligned16(q) && tpb_aligned16(k) && tpb_aligned16(v) && tpb_aligned16(q_norm) &&
+                         tpb_aligned16(k_norm) && tpb_aligned16(cosv) && tpb_aligned16(sinv) && tpb_aligned16(qb) &&
+                         tpb_aligned16(kb) && tpb_aligned16(vt),
+                  "attn_prepare: pointers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int seq_pad = (int)((seq + 7) / 8 * 8);
+    const dim3 blk(256);
+    const dim3 gq((unsigned)((seq * heads + 7) / 8)), gk((unsigned)((seq * kv_heads + 7) / 8));
+    const dim3 gv((unsigned)((seq_pad + 63) / 64), (unsigned)kv_heads);
+    cudaError_t e;
+    if (in_dtype == TPB_F32) {
+        e = tpb_launch_pdl(qk_norm_rope_kernel<float>, gq, blk, 0, st, (const float *)q, q_norm, cosv, sinv, eps, (int)seq, heads, (__nv_bfloat16 *)qb);
+        if (e == cudaSuccess) e = tpb_launch_pdl(qk_norm_rope_kernel<float>, gk, blk, 0, st, (const float *)k, k_norm, cosv, sinv, eps, (int)seq, kv_heads, (__nv_bfloat16 *)kb);
+        if (e == cudaSuccess) e = tpb_launch_pdl(v_transpose_kernel<float>, gv, blk, 0, st, (const float *)v, (int)seq, seq_pad, kv_heads, (__nv_bfloat16 *)vt);
+    } else {
+        e = tpb_launch_pdl(qk_norm_rope_kernel<__nv_bfloat16>, gq, blk, 0, st, (const __nv_bfloat16 *)q, q_norm, cosv, sinv, eps, (int)seq, heads, (__nv_bfloat16 *)qb);
+        if (e == cudaSuccess) e = tpb_launch_pdl(qk_norm_rope_kernel<__nv_bfloat16>, gk, blk, 0, st, (const __nv_bfloat16 *)k, k_norm, cosv, sinv, eps, (int)seq, kv_heads, (__nv_bfloat16 *)kb);
+        if (e == cudaSuccess) e = tpb_launch_pdl(v_transpose_kernel<__nv_bfloat16>, gv, blk, 0, st, (const __nv_bfloat16 *)v, (int)seq, seq_pad, kv_heads, (__nv_bfloat16 *)vt);
+    }
+    TPB_CUDA(h, e);
+    return TPB_OK;
+}
+
+int tpb_attention(tpb_handle_t h, tpb_stream_t stream, void *out, int out_dtype, const void *qb, const void *kb,
+                  const void *vt, int64_t seq_q, int64_t seq_kv, int heads, int kv_heads, int head_dim, float scale) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, out && qb && kb && vt, "attention: null pointer");
+    TPB_CHECK_ARG(h, head_dim == kHd, "attention: head_dim must be 128 (got %d)", head_dim);
+    TPB_CHECK_ARG(h, out_dtype == TPB_F32 || out_dtype == TPB_BF16, "attention: output must be f32 or bf16");
+    TPB_CHECK_ARG(h, seq_q > 0 && seq_kv > 0 && seq_q < (1 << 24) && seq_kv < (1 << 24) && heads > 0 && kv_heads > 0 &&
+                         heads % kv_heads == 0 && heads <= 65535,
+                  "attention: bad seq / heads / kv_heads");
+    TPB_CHECK_ARG(h, tpb_aligned16(out) && tpb_aligned16(qb) && tpb_aligned16(kb) && tpb_aligned16(vt),
+                  "attention: pointers must be 16-byte aligned");
+    const int64_t seq_pad = (seq_kv + 7) / 8 * 8;
+    CUtensorMap mq, mk, mv;
+    int rc = make_bf16_map(h, &mq, qb, (int64_t)heads * seq_q, kHd, kHd);
+    if (rc != TPB_OK) return rc;
+    rc = make_bf16_map(h, &mk, kb, (int64_t)kv_heads * seq_kv, kHd, kHd);
+    if (rc != TPB_OK) return rc;
+    rc = make_bf16_map(h, &mv, vt, (int64_t)kv_heads * kHd, seq_pad, seq_pad);
+    if (rc != TPB_OK) return rc;
+    AttnParams p;
+    p.out = out;
+    p.out_f32 = out_dtype == TPB_F32;
+    p.seq_q = (int)seq_q;
+    p.seq_kv = (int)seq_kv;
+    p.heads = heads;
+    p.kv_heads = kv_heads;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = h->d_status;
+    static bool attr_set[64] = {false};
+    if (!attr_set[h->device & 63]) {
+        TPB_CUDA(h, cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        attr_set[h->device & 63] = true;
+    }
+    const dim3 grid((unsigned)((seq_q + kTile - 1) / kTile), (unsigned)heads);
+    TPB_CUDA(h, tpb_launch_pdl(flash_attn_kernel, grid, dim3(kAttnThreads), (size_t)kAttnSmem, (cudaStream_t)stream, mq, mk, mv, p));
+    return TPB_OK;
+}
+
+}  // extern "C"

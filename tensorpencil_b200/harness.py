@@ -95,7 +95,8 @@ def dit_modulation(be, blocks: int, hidden: int, seed: int = 7) -> torch.Tensor:
 
 def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
                      mlp_tile: int = MLP_TILE, glue: bool = True, mode: Optional[str] = None,
-                     mod: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
+                     mod: Optional[torch.Tensor] = None, eps: float = 1e-5,
+                     attn: Optional[dict] = None) -> torch.Tensor:
     """One step of the block stack on latents x [tokens][hidden] (f32, updated in place).
 
     mode:
@@ -108,8 +109,10 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                  prep kernels and gatedAdd folded into the wo / mlp.down GEMM epilogues;
                  with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs stay bf16;
       "torch"    legacy: linears through the library, cheap torch stand-ins between them.
-    Attention proper (qk-norm, RoPE, softmax) is not part of this path: v stands in for
-    its output.  ``glue`` is the old switch: True -> "torch", False -> "linears".
+    attn: None -> v stands in for the attention output (the linears and their glue alone);
+    a dict {q_norm, k_norm, cos, sin, heads} -> qk-norm + RoPE + softmax attention run
+    between the projections and the sigmoid gate (dit_cuda.zig:479-489), modes "unfused"
+    and "fused".  ``glue`` is the old switch: True -> "torch", False -> "linears".
 
     mlp_tile: rows per MLP tile.  The reference tiles by 2048 rows to fit a 24 GB card;
     with 180 GB of HBM the whole 4608-token batch can go through at once."""
@@ -160,11 +163,15 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
         gemm(k, wb["wk"], hid)
         gemm(v, wb["wv"], hid)
         gemm(g, wb["gate"], hid)
+        a = v                                              # without attn: v stands in for its output
+        if attn is not None and mode in ("fused", "unfused"):
+            a = be.attention(q, k, v, attn["q_norm"], attn["k_norm"], attn["cos"], attn["sin"],
+                             attn["heads"], attn["heads"], out_dtype=out_dtype, out=o)
         if mode == "fused":
-            be.prepSigmoidMul(v, g, m, hid, bits)          # v stands in for the attention output
+            be.prepSigmoidMul(a, g, m, hid, bits)
         elif mode == "unfused":
-            be.sigmoidMul(v, g, m * hid)
-            prep(v, m, hid)
+            be.sigmoidMul(a, g, m * hid)
+            prep(a, m, hid)
         elif mode == "torch":
             attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)
             prep(attn, m, hid)
@@ -212,6 +219,23 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
         if st is not None:
             st.release(b)
     return x
+
+
+def attention_inputs(seq: int, heads: int, kv_heads: int, device, dtype=torch.bfloat16, seed: int = 5):
+    """Synthetic q, k, v ([seq][heads*128]), unit-ish norm weights and the FLUX cos / sin tables
+    ([seq][64], axes 32/48/48 over a 3-axis position id: src/ops/rope.zig:26-60) on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rnd = lambda *s: torch.randn(*s, device=device, generator=g)
+    q, k, v = rnd(seq, heads * 128).to(dtype), rnd(seq, kv_heads * 128).to(dtype), rnd(seq, kv_heads * 128).to(dtype)
+    qn, kn = 1.0 + 0.1 * rnd(128), 1.0 + 0.1 * rnd(128)
+    idx = torch.arange(seq, device=device, dtype=torch.float32)
+    pos = torch.stack([torch.zeros_like(idx), torch.div(idx, 64, rounding_mode="floor"), idx % 64], dim=1)
+    ang = []
+    for a, d in enumerate((32, 48, 48)):
+        freq = 10000.0 ** (-torch.arange(0, d, 2, device=device, dtype=torch.float32) / d)
+        ang.append(pos[:, a:a + 1] * freq[None, :])
+    ang = torch.cat(ang, dim=1)                            # [seq][64]
+    return q, k, v, qn.contiguous(), kn.contiguous(), torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
 
 
 def dit_linear_ops(tokens: int, blocks: int, hidden: int, mlp: int) -> float:
