@@ -336,7 +336,7 @@ size_t tpb_gguf_row_bytes(int fmt, int64_t cols);
 int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, const void *w, float scale,
                       int64_t rows, int64_t cols, const void *xq, int ng, int row_off, int n_total);
 
-/* ---- Attention of the DiT block (SURVEY "next" row: the op between the quantised linears) ---
+/* ---- Attention of the DiT block (the op between the quantised linears of a block) ---
  * Replaces Backend.qkNorm + rope + attn / opAttnTC for the non-causal, unmasked case
  * (src/models/dit_cuda.zig:479-489; src/gpu/cuda/backend.zig:2939-3196; CPU definitions
  * src/ops/norm.zig:12-23, src/ops/rope.zig:68-90, src/ops/attention.zig:46-150).

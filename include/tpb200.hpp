@@ -56,6 +56,9 @@ class Backend {
         if (stream_) cudaStreamSynchronize(stream_);
         dropWeights();
         release(i8_x_);
+        release(attn_q_);
+        release(attn_k_);
+        release(attn_vt_);
         release(i8_scale_);
         release(i8_sum_);
         release(q8_);
@@ -153,6 +156,24 @@ class Backend {
                             static_cast<const float *>(mod.p) + gate_off, (int64_t)(total / dim), (int64_t)dim));
     }
 
+    // ---- attention of the DiT block (dit_cuda.zig:479-489: qkNorm, rope, attn / opAttnTC) ----
+    // q [seq][heads*hd], k / v [seq][kv_heads*hd] (f32), freqs = cos table [seq][hd/2] then, sin_off floats
+    // later, the sin table; out [seq][heads*hd] f32.  head_dim 128, non-causal.  Unlike the reference's
+    // in-place qkNorm / rope, q and k are left untouched (the rotated bf16 copies live in scratch).
+    void attention(DeviceBuffer q, DeviceBuffer k, DeviceBuffer v, DeviceBuffer out, DeviceBuffer q_norm,
+                   DeviceBuffer k_norm, DeviceBuffer freqs, size_t sin_off, size_t seq, size_t heads, size_t kv_heads,
+                   size_t hd, float eps, float scale) {
+        ensure(attn_q_, heads * seq * hd * 2);
+        ensure(attn_k_, kv_heads * seq * hd * 2);
+        ensure(attn_vt_, tpb_attn_vt_elems((int64_t)seq, (int)kv_heads) * 2);
+        const float *f = static_cast<const float *>(freqs.p);
+        check(tpb_attn_prepare(h_, stream_, q.p, k.p, v.p, TPB_F32, static_cast<const float *>(q_norm.p),
+                               static_cast<const float *>(k_norm.p), eps, f, f + sin_off, (int64_t)seq, (int)heads,
+                               (int)kv_heads, (int)hd, attn_q_.p, attn_k_.p, attn_vt_.p));
+        check(tpb_attention(h_, stream_, out.p, TPB_F32, attn_q_.p, attn_k_.p, attn_vt_.p, (int64_t)seq, (int64_t)seq,
+                            (int)heads, (int)kv_heads, (int)hd, scale));
+    }
+
     // ---- GGUF decode GEMV ----
     // opGemvQuantizeX (backend.zig:1687-1695): cols = total element count, a multiple of 32
     void opGemvQuantizeX(DeviceBuffer x, size_t cols) {
@@ -229,7 +250,7 @@ class Backend {
     tpb_handle_t h_ = nullptr;
     int device_ = 0;
     cudaStream_t stream_ = nullptr;
-    DeviceBuffer i8_x_, i8_scale_, i8_sum_, q8_;
+    DeviceBuffer i8_x_, i8_scale_, i8_sum_, q8_, attn_q_, attn_k_, attn_vt_;
     size_t m_ = 0, cols_ = 0, q8_total_ = 0;
     int bits_ = 0;
     std::unordered_map<const void *, DeviceBuffer> weights_;

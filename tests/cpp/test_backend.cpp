@@ -104,6 +104,55 @@ static void gguf_gemv(tpb::Backend &be, tpb::DType dt, int fmt, size_t rows, siz
     be.dropWeights();  // the cache is keyed by host address, and `w` is about to be freed
 }
 
+// qkNorm + rope + attn against the checker; gate = 2 % of the result's norm (bf16 operands on the
+// tensor cores against the f32 definition)
+static void attention(tpb::Backend &be, size_t seq, size_t heads, size_t kv_heads, unsigned seed) {
+    const size_t hd = 128;
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::vector<float> q(seq * heads * hd), k(seq * kv_heads * hd), v(seq * kv_heads * hd), qn(hd), kn(hd);
+    for (auto &x : q) x = nd(rng);
+    for (auto &x : k) x = nd(rng);
+    for (auto &x : v) x = nd(rng);
+    for (auto &x : qn) x = 1.f + 0.1f * nd(rng);
+    for (auto &x : kn) x = 1.f + 0.1f * nd(rng);
+    std::vector<float> pos(seq * 3), freqs(2 * seq * (hd / 2));
+    for (size_t p = 0; p < seq; p++) {
+        pos[3 * p] = 0.f;
+        pos[3 * p + 1] = (float)(p / 8);
+        pos[3 * p + 2] = (float)(p % 8);
+    }
+    const int axes[3] = {32, 48, 48};
+    const size_t sin_off = seq * (hd / 2);
+    tpo_flux_freqs(pos.data(), seq, axes, 3, 10000.0, freqs.data(), freqs.data() + sin_off);
+    // the checker's result
+    std::vector<float> qr(q.size()), kr(k.size()), want(q.size());
+    tpo_qk_norm(q.data(), seq * heads, hd, qn.data(), 1e-5f, qr.data());
+    tpo_qk_norm(k.data(), seq * kv_heads, hd, kn.data(), 1e-5f, kr.data());
+    tpo_rope_interleaved(qr.data(), freqs.data(), freqs.data() + sin_off, seq, heads, hd);
+    tpo_rope_interleaved(kr.data(), freqs.data(), freqs.data() + sin_off, seq, kv_heads, hd);
+    const float scale = 1.0f / std::sqrt((float)hd);
+    tpo_attention(qr.data(), kr.data(), v.data(), seq, seq, heads, kv_heads, hd, scale, want.data());
+    auto up = [&](const std::vector<float> &a) {
+        tpb::DeviceBuffer d = be.tensorCreate(a.size() * 4);
+        be.tensorUpload(d, a.data(), a.size() * 4);
+        return d;
+    };
+    tpb::DeviceBuffer qd = up(q), kd = up(k), vd = up(v), qnd = up(qn), knd = up(kn), fd = up(freqs);
+    tpb::DeviceBuffer od = be.tensorCreate(q.size() * 4);
+    be.attention(qd, kd, vd, od, qnd, knd, fd, sin_off, seq, heads, kv_heads, hd, 1e-5f, scale);
+    std::vector<float> got(q.size());
+    be.tensorDownload(od, got.data(), got.size() * 4);
+    double num = 0, den = 0;
+    for (size_t i = 0; i < got.size(); i++) {
+        num += ((double)got[i] - want[i]) * ((double)got[i] - want[i]);
+        den += (double)want[i] * want[i];
+    }
+    const double rel = std::sqrt(num / den);
+    EXPECT(rel < 2e-2, "attention seq %zu heads %zu/%zu: relative error %g", seq, heads, kv_heads, rel);
+    for (tpb::DeviceBuffer d : {qd, kd, vd, qnd, knd, fd, od}) be.tensorDestroy(d);
+}
+
 int main() {
     try {
         tpb::Backend be(0);
@@ -116,6 +165,9 @@ int main() {
         gguf_gemv(be, tpb::DType::q4_k, 2, 24, 512, 5, 314);
         gguf_gemv(be, tpb::DType::q5_k, 3, 24, 512, 5, 315);
         gguf_gemv(be, tpb::DType::q6_k, 4, 24, 512, 5, 316);
+
+        attention(be, 200, 4, 2, 401);
+        attention(be, 384, 2, 2, 402);
 
         // error behaviour: a GEMM without its prep, a width the rotation cannot take
         tpb::DeviceBuffer t = be.tensorCreate(1 << 16);

@@ -3,7 +3,7 @@
 Two kinds of fixture live here:
 
 * the reference's own golden vectors for the quantized-linear path, taken from
-  a TensorPencil checkout (``--reference``, default ``/root/reference``):
+  a TensorPencil checkout (``--reference PATH``):
   the ComfyUI int4 ConvRot dequant fixture (``testdata/int4_convrot_*``, used by
   the test in ``src/ops/convrot.zig:148-192``) and the ggml Q8_0 dequant block
   with its expected f32 bit patterns (``src/core/quants_fixtures.zig:6-15``) and the
@@ -79,7 +79,7 @@ def oracle_vectors() -> None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a TensorPencil checkout")
     a = ap.parse_args()
     if os.path.isdir(a.reference):
         copy_reference_fixtures(a.reference)
