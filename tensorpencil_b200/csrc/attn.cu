@@ -417,14 +417,15 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
 //   MMAs of one thread execute in issue order, which is what frees the buffers: S_X(j+1) is
 //   issued after P_X(j) V(j), so it overwrites S_X / P_X only after that product has read them,
 //   and its commit (s_full) also says that O_X holds the products up to tile j.
-// Warps: 0 TMA, 1 MMA issue, 2-5 softmax A, 6-9 softmax B (each SM sub-partition runs one warp
-// of A and one of B).
-constexpr int kAttn2Threads = 320;
+// Warps: 0 TMA, 1 MMA issue, 2-17 softmax: tile A / B x column half 0 / 1 x row quarter (each SM
+// sub-partition runs four softmax warps).
+constexpr int kAttn2Threads = 576;                     // 2 + 16 warps
 constexpr int k2OffQ = 0;                               // Q_A, Q_B: 2 atoms each
 constexpr int k2OffK = 4 * kAtomBytes;                  // K stages 0, 1
 constexpr int k2OffV = k2OffK + 4 * kAtomBytes;         // V^T stages 0, 1
 constexpr int k2OffBar = k2OffV + 4 * kAtomBytes;
-constexpr int kAttn2Smem = k2OffBar + 256 + 1024;
+constexpr int k2OffXch = k2OffBar + 256;               // row-maximum exchange: 2 x 2 x 128 x 2 floats
+constexpr int kAttn2Smem = k2OffXch + 4096 + 1024;
 
 __device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                uint32_t accumulate) {
@@ -442,6 +443,23 @@ __device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t (&r)[
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld_dep16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
 }
 
 __global__ void __launch_bounds__(kAttn2Threads, 1)
@@ -477,7 +495,7 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             mbar_init(k_empty(s), 1);
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
-            mbar_init(p_full(s), 4);
+            mbar_init(p_full(s), 8);
         }
         mbar_init(o_done, 1);
         *abort_flag = 0;
@@ -590,13 +608,21 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             if (ok) tc_commit(o_done);
         }
     } else {
-        // ---------------- softmax + output: thread = query row of tile x ----------------
-        const int x = (warp - 2) >> 2;
+        // ---------------- softmax + output: two threads per query row of tile x ----------------
+        // A thread owns 64 of the row's 128 kv columns (half hf), so each SM sub-partition runs four
+        // softmax warps (tile A / B x half 0 / 1) and has other warps to issue from while one waits on a
+        // dependent instruction.  The two threads of a row share the row maximum through shared memory
+        // (one 64-thread named barrier per tile); their partial sums are added once, at the end.
+        const int idx = (warp - 2) >> 2;                   // 0..3
+        const int x = idx >> 1, hf = idx & 1;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                 // row within the tile = TMEM lane
         const uint32_t t_lane = (uint32_t)(quarter * 32) << 16;
-        const uint32_t t_s = tmem_base + t_lane + (uint32_t)(x * 128);         // S_x; P_x over its first 64 columns
-        const uint32_t t_o = tmem_base + t_lane + 256u + (uint32_t)(x * 128);  // O_x
+        const uint32_t t_s = tmem_base + t_lane + (uint32_t)(x * 128 + hf * 64);        // this half of S_x
+        const uint32_t t_p = tmem_base + t_lane + (uint32_t)(x * 128 + hf * 32);        // this half of P_x (over S_x)
+        const uint32_t t_o = tmem_base + t_lane + 256u + (uint32_t)(x * 128 + hf * 64); // this half of O_x
+        float *xch = reinterpret_cast<float *>(gen + k2OffXch);                         // [2 parity][2 x][128 rows][2 hf]
+        const int bar_id = 1 + x * 4 + quarter;
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
         auto do_tile = [&](auto masked_tag, const int j) -> bool {
@@ -604,22 +630,25 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const bool good = mbar_wait(s_full(x), (uint32_t)j & 1u, abort_flag, p.status, (14u << 24) | 1u, true);
             if (!__all_sync(0xffffffffu, good)) return false;
             tc_fence_after();
-            const int kv_left = p.seq_kv - j * kTile;
-            uint32_t va[32], vb[32];
-            // pass 1: row maximum (loads double-buffered against the compares)
+            const int kv_left = p.seq_kv - j * kTile - hf * 64;     // this half's columns >= kv_left are past the end
+            uint32_t v0[32], v1[32];
+            tc_ld_32x32(t_s, v0);
+            tc_ld_32x32(t_s + 32u, v1);
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            tc_ld_32x32(t_s, va);
+            tc_wait_ld_dep(v0);
+            tc_wait_ld_dep(v1);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t(&cur)[32] = (c & 1) ? vb : va;
-                uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-                tc_wait_ld_dep(cur);
-                if (c + 1 < 4) tc_ld_32x32(t_s + (uint32_t)((c + 1) * 32), nxt);
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                    if (!MASKED || c * 32 + i < kv_left) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(cur[i]));
+            for (int i = 0; i < 32; i++) {
+                if (!MASKED || i < kv_left) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v0[i]));
+                if (!MASKED || 32 + i < kv_left) m4[(i + 2) & 3] = fmaxf(m4[(i + 2) & 3], __uint_as_float(v1[i]));
             }
-            const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            // Row maximum over both halves.  The barrier also orders the other thread's loads of S
+            // before this thread's stores of P over the same columns.
+            float *slot = xch + (((j & 1) * 2 + x) * kTile + r) * 2;
+            slot[hf] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            mx = fmaxf(mx, slot[hf ^ 1]);
             // lazy reference point: moves only when the maximum grew by more than 2^kLazy
             constexpr float kLazy = 8.0f;
             const float m_cand = mx * p.scale_log2;
@@ -629,24 +658,18 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
-                    uint32_t v[32];
-                    tc_ld_32x32(t_o + (uint32_t)(c * 32), v);
-                    tc_wait_ld_dep(v);
+                    uint32_t o[16];
+                    tc_ld_32x16(t_o + (uint32_t)(c * 16), o);
+                    tc_wait_ld_dep16(o);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tc_st_32x32(t_o + (uint32_t)(c * 32), v);
+                    for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tc_st_32x16(t_o + (uint32_t)(c * 16), o);
                 }
             }
-            // pass 2: P = exp2(S c - m) as bf16 pairs over the columns of S already read
+            // P = exp2(S c - m) as bf16 pairs
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const uint64_t c2 = pack_f2(p.scale_log2, p.scale_log2), nm2 = pack_f2(-m_new, -m_new);
-            tc_ld_32x32(t_s, va);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t(&cur)[32] = (c & 1) ? vb : va;
-                uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-                tc_wait_ld_dep(cur);
-                if (c + 1 < 4) tc_ld_32x32(t_s + (uint32_t)((c + 1) * 32), nxt);
+            auto exp_chunk = [&](const uint32_t (&cur)[32], const int c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
@@ -662,9 +685,10 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
                     pk[i] = *reinterpret_cast<const uint32_t *>(&b2);
                 }
-                // columns 16c .. 16c+15 of P lie inside S columns 0 .. 32c+31, all read by now
-                tc_st_32x16(t_s + (uint32_t)(c * 16), pk);
-            }
+                tc_st_32x16(t_p + (uint32_t)(c * 16), pk);
+            };
+            exp_chunk(v0, 0);
+            exp_chunk(v1, 1);
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m_run = m_new;
             tc_wait_st();
@@ -679,17 +703,23 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             ok = mbar_wait(o_done, 0, abort_flag, p.status, (14u << 24) | 3u, true);
             ok = __all_sync(0xffffffffu, ok);
         }
+        // An aborted warp never reaches the named barrier below; its partner then waits in it.  The
+        // partner shares every mbarrier wait with it (same tile, same barriers), so both abort together.
         if (ok) {
             tc_fence_after();
-            const float inv_l = 1.0f / l_run;
+            // the row's sum = this half's + the other half's (both relative to the same reference point)
+            float *slot = xch + ((n_tiles & 1) * 2 + x) * kTile * 2 + r * 2;
+            slot[hf] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            const float inv_l = 1.0f / (l_run + slot[hf ^ 1]);
             const int q = q0 + x * kTile + r;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
                 tc_ld_32x32(t_o + (uint32_t)(c * 32), v);
                 tc_wait_ld_dep(v);
                 if (q < p.seq_q) {
-                    const size_t off = (size_t)q * p.heads * kHd + (size_t)head * kHd + c * 32;
+                    const size_t off = (size_t)q * p.heads * kHd + (size_t)head * kHd + hf * 64 + c * 32;
                     if (p.out_f32) {
                         float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + off);
 #pragma unroll
