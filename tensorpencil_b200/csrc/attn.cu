@@ -5,19 +5,20 @@
 // of the Krea 2 transformer (src/models/dit_cuda.zig:479-489; CPU definitions
 // src/ops/attention.zig:46-150, src/ops/rope.zig:68-90, src/ops/norm.zig:12-23).
 //
-// Kernel layout.  One CTA = 128 query rows of one head; it walks the kv sequence in tiles of
-// 128.  Six warps: warp 0 loads tiles with TMA (Q once; K and V^T double-buffered, separate
-// barriers so a K slot is free again as soon as its scores are done), warp 1 issues the MMAs,
-// warps 2-5 are the softmax: thread r owns query row r.
-//   S_j  = Q K_j^T        M 128 x N 128 x K 128 (head_dim), both operands K-major   -> TMEM, 2 buffers
-//   P_j  = exp2(S_j * c - m), running max m and sum l per row (online softmax); P_j goes to
-//          shared memory as bf16 in the K-major 128-byte-swizzled layout of an A operand;
-//          O is multiplied by exp2(m_old - m_new) in TMEM when a row's reference point m moved
-//          (it moves only when the maximum grew by more than 2^8: until then P stays <= 2^8)
-//   O   += P_j V_j        M 128 x N 128 (head_dim) x K 128 (kv); V comes pre-transposed
-//          ([head][d][kv], kv contiguous) so that it is K-major too                 -> TMEM
-// The score MMA of tile j+1 is issued before the softmax of tile j has finished, so the tensor
-// pipe works on S_{j+1} while the softmax warps work on S_j.  Every wait is bounded.
+// Kernel layout.  One CTA = TWO 128-row query tiles (A, B) of one head; it walks the kv sequence
+// in tiles of 128.  Warp 0 loads tiles with TMA (Q once; K and V^T double-buffered), warp 1 issues
+// the MMAs, warps 2-17 are the softmax (tile A / B x column half x row quarter).  Per tile x:
+//   S_x  = Q_x K_j^T      M 128 x N 128 x K 128 (head_dim), both operands K-major from shared memory
+//   P_x  = exp2(S_x * c - m), running reference point m and sum l per row (online softmax)
+//   O_x += P_x V_j        M 128 x N 128 (head_dim) x K 128 (kv); V comes pre-transposed
+//          ([head][d][kv], kv contiguous) so that it is K-major too
+//   TMEM (512 columns): S_A +0, S_B +128, O_A +256, O_B +384.  P_x (bf16, two per 32-bit column)
+//   is written over the first 64 columns of S_x with tcgen05.st and is the A operand of the second
+//   product straight from tensor memory: no shared-memory round trip, no proxy fence.
+// MMAs of one thread execute in issue order, which is what frees the buffers: S_x(j+1) is issued
+// after P_x(j) V(j), so it overwrites S_x / P_x only after that product has read them, and its
+// commit (s_full) also says that O_x holds the products up to tile j.  While the tensor pipe works
+// for one query tile the other tile's softmax runs.  Every wait is bounded.
 #include <cuda_bf16.h>
 
 #include <type_traits>
@@ -31,16 +32,7 @@ namespace {
 constexpr int kHd = 128;          // head_dim
 constexpr int kTile = 128;        // query rows per CTA and kv rows per step
 constexpr int kAtomBytes = 16384; // [128 rows][64 bf16] in the 128-byte swizzle layout
-constexpr int kAttnThreads = 192;
-constexpr int kAttnTmemCols = 512;  // S0, S1, O: 3 x 128 columns (power of two allocation)
-
-// smem: Q (2 atoms) | K stage 0,1 (2 atoms each) | V^T stage 0,1 | P (2 atoms) | barriers
-constexpr int kOffQ = 0;
-constexpr int kOffK = 2 * kAtomBytes;
-constexpr int kOffV = kOffK + 4 * kAtomBytes;
-constexpr int kOffP = kOffV + 4 * kAtomBytes;
-constexpr int kOffBar = kOffP + 2 * kAtomBytes;
-constexpr int kAttnSmem = kOffBar + 256 + 1024;  // + alignment slack
+constexpr int kAttnTmemCols = 512;  // S_A, S_B, O_A, O_B: 4 x 128 columns
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -69,17 +61,6 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // kind::f16 instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M 128, N 128.
@@ -101,331 +82,14 @@ struct AttnParams {
     uint32_t *status;
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 1)
-flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                  const __grid_constant__ CUtensorMap tma_vt, const AttnParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + kOffBar;
-    // barrier slots (8 bytes each)
-    const uint32_t q_full = bars;
-    auto k_full = [&](int s) { return bars + 8u * (1 + s); };
-    auto v_full = [&](int s) { return bars + 8u * (3 + s); };
-    auto k_empty = [&](int s) { return bars + 8u * (5 + s); };
-    auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
-    auto s_full = [&](int b) { return bars + 8u * (9 + b); };
-    auto s_empty = [&](int b) { return bars + 8u * (11 + b); };
-    const uint32_t p_full = bars + 8u * 13, p_empty = bars + 8u * 14;
-    uint8_t *gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 128);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + kOffBar + 136);
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * kTile;
-    const int head = blockIdx.y;
-    const int hk = head / (p.heads / p.kv_heads);
-    const int n_tiles = (p.seq_kv + kTile - 1) / kTile;
-
-    if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) {
-            mbar_init(k_full(s), 1);
-            mbar_init(v_full(s), 1);
-            mbar_init(k_empty(s), 1);
-            mbar_init(v_empty(s), 1);
-            mbar_init(s_full(s), 1);
-            mbar_init(s_empty(s), 4);
-        }
-        mbar_init(p_full, 4);
-        mbar_init(p_empty, 1);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32((const void *)tmem_slot)),
-                     "r"(kAttnTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;  // S0 at +0, S1 at +128, O at +256
-    tpb_grid_dep_launch();
-    tpb_grid_dep_wait();
-
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, 2 * kAtomBytes);
-            tma_load_2d(smem_base + kOffQ, &tma_q, q_full, 0, head * p.seq_q + q0);
-            tma_load_2d(smem_base + kOffQ + kAtomBytes, &tma_q, q_full, 64, head * p.seq_q + q0);
-            bool ok = true;
-            for (int j = 0; ok && j < n_tiles; j++) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                ok = mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.status, (9u << 24) | 0x10u | st, true);
-                if (!ok) break;
-                mbar_arrive_expect_tx(k_full(st), 2 * kAtomBytes);
-                const uint32_t kd = smem_base + kOffK + st * 2 * kAtomBytes;
-                tma_load_2d(kd, &tma_k, k_full(st), 0, hk * p.seq_kv + j * kTile);
-                tma_load_2d(kd + kAtomBytes, &tma_k, k_full(st), 64, hk * p.seq_kv + j * kTile);
-                ok = mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.status, (9u << 24) | 0x20u | st, true);
-                if (!ok) break;
-                mbar_arrive_expect_tx(v_full(st), 2 * kAtomBytes);
-                const uint32_t vd = smem_base + kOffV + st * 2 * kAtomBytes;
-                tma_load_2d(vd, &tma_vt, v_full(st), j * kTile, hk * kHd);
-                tma_load_2d(vd + kAtomBytes, &tma_vt, v_full(st), j * kTile + 64, hk * kHd);
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16();
-            bool ok = mbar_wait(q_full, 0, abort_flag, p.status, (10u << 24) | 1u);
-            // S_b = Q K_t^T: K dimension = head_dim = 2 atoms x 4 steps of 16 elements (32 bytes)
-            auto issue_qk = [&](int t) {
-                const int st = t & 1, b = t & 1;
-                const uint32_t ka = smem_base + kOffK + st * 2 * kAtomBytes;
-#pragma unroll
-                for (int a = 0; a < 2; a++) {
-                    const uint64_t qd = make_kmajor_sw128_desc(smem_base + kOffQ + a * kAtomBytes);
-                    const uint64_t kd = make_kmajor_sw128_desc(ka + a * kAtomBytes);
-#pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
-                        tc_mma_bf16(tmem_base + (uint32_t)(b * 128), qd + 2u * kk, kd + 2u * kk, idesc, (a | kk) ? 1u : 0u);
-                }
-                tc_commit(k_empty(st));
-                tc_commit(s_full(b));
-            };
-            if (ok) {
-                ok = mbar_wait(k_full(0), 0, abort_flag, p.status, (10u << 24) | 2u);
-                if (ok) {
-                    tc_fence_after();
-                    issue_qk(0);
-                }
-            }
-            for (int j = 0; ok && j < n_tiles; j++) {
-                if (j + 1 < n_tiles) {
-                    const int t = j + 1;
-                    ok = mbar_wait(k_full(t & 1), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, (10u << 24) | 3u);
-                    if (!ok) break;
-                    ok = mbar_wait(s_empty(t & 1), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag, p.status, (10u << 24) | 4u);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(t);
-                }
-                const int st = j & 1;
-                ok = mbar_wait(v_full(st), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, (10u << 24) | 5u);
-                if (!ok) break;
-                ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.status, (10u << 24) | 6u);
-                if (!ok) break;
-                tc_fence_after();
-                // O += P V_j: K dimension = kv = 2 atoms x 4 steps
-                const uint32_t va = smem_base + kOffV + st * 2 * kAtomBytes;
-#pragma unroll
-                for (int a = 0; a < 2; a++) {
-                    const uint64_t pd = make_kmajor_sw128_desc(smem_base + kOffP + a * kAtomBytes);
-                    const uint64_t vd = make_kmajor_sw128_desc(va + a * kAtomBytes);
-#pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
-                        tc_mma_bf16(tmem_o, pd + 2u * kk, vd + 2u * kk, idesc, (j > 0 || a > 0 || kk > 0) ? 1u : 0u);
-                }
-                tc_commit(v_empty(st));
-                tc_commit(p_empty);
-            }
-        }
-    } else {
-        // ---------------- softmax + output: thread = query row ----------------
-        const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;                 // row within the tile = TMEM lane
-        const uint32_t t_lane = (uint32_t)(quarter * 32) << 16;
-        const uint32_t p_row = smem_base + kOffP + (uint32_t)r * 128u;
-        const uint32_t sw = (uint32_t)(r & 7);
-        float m_run = -INFINITY, l_run = 0.0f;
-        bool ok = true;
-        // One kv tile.  MASKED: the sequence ends inside this tile (columns >= kv_left are not scores).
-        auto do_tile = [&](auto masked_tag, const int j) -> bool {
-            constexpr bool MASKED = decltype(masked_tag)::value;
-            const int b = j & 1;
-            bool good = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, (11u << 24) | 1u, true);
-            if (!__all_sync(0xffffffffu, good)) return false;
-            tc_fence_after();
-            const uint32_t t_s = tmem_base + t_lane + (uint32_t)(b * 128);
-            const int kv_left = p.seq_kv - j * kTile;
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tc_ld_32x32(t_s + (uint32_t)(c * 32), v);
-                tc_wait_ld();
-                if (MASKED) {
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (c * 32 + i < kv_left) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
-                    float m4[4] = {mx, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-#pragma unroll
-                        for (int e = 0; e < 4; e++) m4[e] = fmaxf(m4[e], __uint_as_float(v[i + e]));
-                    }
-                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                }
-            }
-            // The reference point of the exponentials moves only when the maximum grew by more than
-            // kLazy (in log2 units): until then P may reach 2^kLazy, which bf16 and the f32 sums take
-            // without loss, and O needs no rescale.  The result is the same softmax: numerator and
-            // denominator share the reference point.
-            constexpr float kLazy = 8.0f;
-            const float m_cand = mx * p.scale_log2;
-            const float m_new = (m_cand > m_run + kLazy) ? m_cand : m_run;   // first tile: m_run = -inf
-            const float alpha = ex2(m_run - m_new);                         // 1 when unmoved, 0 on the first tile
-            // the P buffer and O are free once the previous P V product is done
-            if (j > 0) {
-                good = mbar_wait(p_empty, (uint32_t)(j - 1) & 1u, abort_flag, p.status, (11u << 24) | 2u, true);
-                if (!__all_sync(0xffffffffu, good)) return false;
-                tc_fence_after();
-            }
-            // pass 2: P = exp2(S c - m) as bf16 into the A-operand layout, row sum in f32
-            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const uint64_t c2 = pack_f2(p.scale_log2, p.scale_log2), nm2 = pack_f2(-m_new, -m_new);
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tc_ld_32x32(t_s + (uint32_t)(c * 32), v);
-                tc_wait_ld();
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    float a0, a1;
-                    unpack_f2(fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), c2, nm2), a0, a1);
-                    float e0 = ex2(a0), e1 = ex2(a1);
-                    if (MASKED) {
-                        if (c * 32 + 2 * i >= kv_left) e0 = 0.0f;
-                        if (c * 32 + 2 * i + 1 >= kv_left) e1 = 0.0f;
-                    }
-                    sum4[(2 * i) & 3] += e0;
-                    sum4[(2 * i + 1) & 3] += e1;
-                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    pk[i] = *reinterpret_cast<const uint32_t *>(&b2);
-                }
-                // 32 columns = 64 bytes = chunks 4 (c & 1) .. + 3 of atom c / 2
-                const uint32_t base = p_row + (uint32_t)(c >> 1) * kAtomBytes;
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const uint32_t chunk = (uint32_t)(4 * (c & 1) + g);
-                    st_shared_v4(base + ((chunk ^ sw) << 4), pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-                }
-            }
-            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            m_run = m_new;
-            // this S buffer may be overwritten by the scores of tile j + 2
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(b));
-            // rows whose reference point moved: O *= alpha (skipped when no row of the warp moved)
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    uint32_t v[32];
-                    tc_ld_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tc_st_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
-                }
-                tc_wait_st();
-            }
-            // P (generic-proxy writes) -> visible to the tensor core; O updates ordered before the MMA
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-            return true;
-        };
-        for (int j = 0; ok && j < n_tiles; j++)
-            ok = (p.seq_kv - j * kTile < kTile) ? do_tile(std::true_type{}, j) : do_tile(std::false_type{}, j);
-        if (ok) {
-            ok = mbar_wait(p_empty, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.status, (11u << 24) | 3u, true);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            tc_fence_after();
-            const float inv_l = 1.0f / l_run;
-            const int q = q0 + r;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tc_ld_32x32(tmem_o + t_lane + (uint32_t)(c * 32), v);
-                tc_wait_ld();
-                if (q < p.seq_q) {
-                    const size_t off = (size_t)q * p.heads * kHd + (size_t)head * kHd + c * 32;
-                    if (p.out_f32) {
-                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + off);
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            dst[i] = make_float4(__uint_as_float(v[4 * i]) * inv_l, __uint_as_float(v[4 * i + 1]) * inv_l,
-                                                 __uint_as_float(v[4 * i + 2]) * inv_l, __uint_as_float(v[4 * i + 3]) * inv_l);
-                    } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + off);
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * e]) * inv_l,
-                                                                                __uint_as_float(v[8 * i + 2 * e + 1]) * inv_l);
-                                w[e] = *reinterpret_cast<const uint32_t *>(&b2);
-                            }
-                            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    // ---------------- teardown ----------------
-    __syncwarp();
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag) {
-        for (int i = 0; i < 200; i++) __nanosleep(1000);
-        __syncthreads();
-    }
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAttnTmemCols)
-                     : "memory");
-    }
-}
-
-// ---- two query tiles per CTA ---------------------------------------------------------------
-//
-// The kernel above leaves the tensor pipe idle while the one softmax group works, and the
-// softmax group idle while P V runs.  Here a CTA owns TWO 128-row query tiles (A, B) of one
-// head and has one softmax group per tile, so the tensor pipe works for one tile while the
-// other tile's softmax runs, and every K / V tile fetched from shared memory serves 256 rows.
-//   TMEM (512 columns): S_A +0, S_B +128, O_A +256, O_B +384.  P_X (bf16, two per 32-bit
-//   column) is written over the first 64 columns of S_X with tcgen05.st and is the A operand of
-//   the second product straight from tensor memory: no shared-memory round trip, no proxy fence.
-//   MMAs of one thread execute in issue order, which is what frees the buffers: S_X(j+1) is
-//   issued after P_X(j) V(j), so it overwrites S_X / P_X only after that product has read them,
-//   and its commit (s_full) also says that O_X holds the products up to tile j.
-// Warps: 0 TMA, 1 MMA issue, 2-17 softmax: tile A / B x column half 0 / 1 x row quarter (each SM
-// sub-partition runs four softmax warps).
-constexpr int kAttn2Threads = 576;                     // 2 + 16 warps
-constexpr int k2OffQ = 0;                               // Q_A, Q_B: 2 atoms each
-constexpr int k2OffK = 4 * kAtomBytes;                  // K stages 0, 1
-constexpr int k2OffV = k2OffK + 4 * kAtomBytes;         // V^T stages 0, 1
-constexpr int k2OffBar = k2OffV + 4 * kAtomBytes;
-constexpr int k2OffXch = k2OffBar + 256;               // row-maximum exchange: 2 x 2 x 128 x 2 floats
-constexpr int kAttn2Smem = k2OffXch + 4096 + 1024;
+// ---- the attention kernel -------------------------------------------------------------------
+constexpr int kAttnThreads = 576;                     // 2 + 16 warps
+constexpr int kOffQ = 0;                               // Q_A, Q_B: 2 atoms each
+constexpr int kOffK = 4 * kAtomBytes;                  // K stages 0, 1
+constexpr int kOffV = kOffK + 4 * kAtomBytes;         // V^T stages 0, 1
+constexpr int kOffBar = kOffV + 4 * kAtomBytes;
+constexpr int kOffXch = kOffBar + 256;               // row-maximum exchange: 2 x 2 x 128 x 2 floats
+constexpr int kAttnSmem = kOffXch + 4096 + 1024;
 
 __device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                uint32_t accumulate) {
@@ -462,12 +126,12 @@ __device__ __forceinline__ void tc_wait_ld_dep16(uint32_t (&r)[16]) {
                  : "memory");
 }
 
-__global__ void __launch_bounds__(kAttn2Threads, 1)
-flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+__global__ void __launch_bounds__(kAttnThreads, 1)
+flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_vt, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + k2OffBar;
+    const uint32_t bars = smem_base + kOffBar;
     const uint32_t q_full = bars;
     auto k_full = [&](int s) { return bars + 8u * (1 + s); };
     auto v_full = [&](int s) { return bars + 8u * (3 + s); };
@@ -477,8 +141,8 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     auto p_full = [&](int x) { return bars + 8u * (11 + x); };
     const uint32_t o_done = bars + 8u * 13;
     uint8_t *gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + k2OffBar + 128);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + k2OffBar + 136);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + kOffBar + 136);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -521,7 +185,7 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             mbar_arrive_expect_tx(q_full, 4 * kAtomBytes);
 #pragma unroll
             for (int a = 0; a < 4; a++)
-                tma_load_2d(smem_base + k2OffQ + a * kAtomBytes, &tma_q, q_full, (a & 1) * 64,
+                tma_load_2d(smem_base + kOffQ + a * kAtomBytes, &tma_q, q_full, (a & 1) * 64,
                             head * p.seq_q + q0 + (a >> 1) * kTile);
             bool ok = true;
             for (int j = 0; ok && j < n_tiles; j++) {
@@ -530,13 +194,13 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 ok = mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.status, (12u << 24) | 0x10u | st, true);
                 if (!ok) break;
                 mbar_arrive_expect_tx(k_full(st), 2 * kAtomBytes);
-                const uint32_t kd = smem_base + k2OffK + st * 2 * kAtomBytes;
+                const uint32_t kd = smem_base + kOffK + st * 2 * kAtomBytes;
                 tma_load_2d(kd, &tma_k, k_full(st), 0, hk * p.seq_kv + j * kTile);
                 tma_load_2d(kd + kAtomBytes, &tma_k, k_full(st), 64, hk * p.seq_kv + j * kTile);
                 ok = mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.status, (12u << 24) | 0x20u | st, true);
                 if (!ok) break;
                 mbar_arrive_expect_tx(v_full(st), 2 * kAtomBytes);
-                const uint32_t vd = smem_base + k2OffV + st * 2 * kAtomBytes;
+                const uint32_t vd = smem_base + kOffV + st * 2 * kAtomBytes;
                 tma_load_2d(vd, &tma_vt, v_full(st), j * kTile, hk * kHd);
                 tma_load_2d(vd + kAtomBytes, &tma_vt, v_full(st), j * kTile + 64, hk * kHd);
             }
@@ -547,8 +211,8 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const uint32_t idesc = make_idesc_bf16();
             // S_x = Q_x K_t^T: K dimension = head_dim = 2 atoms x 4 steps of 16 elements (32 bytes)
             auto issue_qk = [&](int x, int t) {
-                const uint32_t ka = smem_base + k2OffK + (t & 1) * 2 * kAtomBytes;
-                const uint32_t qa = smem_base + k2OffQ + x * 2 * kAtomBytes;
+                const uint32_t ka = smem_base + kOffK + (t & 1) * 2 * kAtomBytes;
+                const uint32_t qa = smem_base + kOffQ + x * 2 * kAtomBytes;
 #pragma unroll
                 for (int a = 0; a < 2; a++) {
                     const uint64_t qd = make_kmajor_sw128_desc(qa + a * kAtomBytes);
@@ -561,7 +225,7 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             };
             // O_x += P_x V_t: P from tensor memory (8 columns = 16 bf16 per step), V^T from shared memory
             auto issue_pv = [&](int x, int t) {
-                const uint32_t va = smem_base + k2OffV + (t & 1) * 2 * kAtomBytes;
+                const uint32_t va = smem_base + kOffV + (t & 1) * 2 * kAtomBytes;
 #pragma unroll
                 for (int a = 0; a < 2; a++) {
                     const uint64_t vd = make_kmajor_sw128_desc(va + a * kAtomBytes);
@@ -621,7 +285,7 @@ flash_attn2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const uint32_t t_s = tmem_base + t_lane + (uint32_t)(x * 128 + hf * 64);        // this half of S_x
         const uint32_t t_p = tmem_base + t_lane + (uint32_t)(x * 128 + hf * 32);        // this half of P_x (over S_x)
         const uint32_t t_o = tmem_base + t_lane + 256u + (uint32_t)(x * 128 + hf * 64); // this half of O_x
-        float *xch = reinterpret_cast<float *>(gen + k2OffXch);                         // [2 parity][2 x][128 rows][2 hf]
+        float *xch = reinterpret_cast<float *>(gen + kOffXch);                         // [2 parity][2 x][128 rows][2 hf]
         const int bar_id = 1 + x * 4 + quarter;
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
@@ -916,16 +580,10 @@ int tpb_attention(tpb_handle_t h, tpb_stream_t stream, void *out, int out_dtype,
     static bool attr_set[64] = {false};
     if (!attr_set[h->device & 63]) {
         TPB_CUDA(h, cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        TPB_CUDA(h, cudaFuncSetAttribute(flash_attn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttn2Smem));
         attr_set[h->device & 63] = true;
     }
-    if (h->opt_attn_one_tile || seq_q <= kTile) {
-        const dim3 grid((unsigned)((seq_q + kTile - 1) / kTile), (unsigned)heads);
-        TPB_CUDA(h, tpb_launch_pdl(flash_attn_kernel, grid, dim3(kAttnThreads), (size_t)kAttnSmem, (cudaStream_t)stream, mq, mk, mv, p));
-    } else {
-        const dim3 grid((unsigned)((seq_q + 2 * kTile - 1) / (2 * kTile)), (unsigned)heads);
-        TPB_CUDA(h, tpb_launch_pdl(flash_attn2_kernel, grid, dim3(kAttn2Threads), (size_t)kAttn2Smem, (cudaStream_t)stream, mq, mk, mv, p));
-    }
+    const dim3 grid((unsigned)((seq_q + 2 * kTile - 1) / (2 * kTile)), (unsigned)heads);
+    TPB_CUDA(h, tpb_launch_pdl(flash_attn_kernel, grid, dim3(kAttnThreads), (size_t)kAttnSmem, (cudaStream_t)stream, mq, mk, mv, p));
     return TPB_OK;
 }
 

@@ -28,7 +28,6 @@ struct tpb_handle_s {
     size_t w4_scratch_bytes = 0;
     // switches read from the environment once, at tpb_create
     bool opt_w4_fused = false;      // TPB_W4_FUSED=1: unpack int4 weights inside the GEMM
-    bool opt_attn_one_tile = false; // TPB_ATTN_ONE_TILE=1: attention with one query tile per CTA
     bool opt_gemm_one_cta = false;  // TPB_GEMM_ONE_CTA=1: keep large GEMMs on the one-CTA kernel
     char err[512] = {0};
 };
