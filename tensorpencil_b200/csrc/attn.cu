@@ -426,70 +426,123 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
 
 // ---- per-head RMS norm + RoPE + per-head bf16 layout ---------------------------------------
 //
-// One warp per (token, head): a lane holds 4 consecutive elements (two rotation pairs).
-// x [seq][heads*128] (f32 or bf16) -> out [heads][seq][128] bf16 = rope(x * inv_rms * w).
+// Eight values of a row (f32 or bf16) as floats; the row pointer is 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void load8(const T *src, float (&v)[8]) {
+    if (sizeof(T) == 4) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(src));
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+__device__ __forceinline__ uint32_t bf16_pair(float lo, float hi) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&b);
+}
+
+// q [seq][heads*128] and k [seq][kv_heads*128] in one launch: a half-warp per (token, head) of q or
+// of k, a lane holds 8 consecutive elements (four rotation pairs).
+//   out [heads][seq][128] bf16 = rope(x * inv_rms(x) * w)
 template <typename T>
 __global__ void __launch_bounds__(256)
-qk_norm_rope_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ cosv,
-                    const float *__restrict__ sinv, float eps, int seq, int heads, __nv_bfloat16 *__restrict__ out) {
+qk_norm_rope_kernel(const T *__restrict__ q, const T *__restrict__ k, const float *__restrict__ qw,
+                    const float *__restrict__ kw, const float *__restrict__ cosv, const float *__restrict__ sinv,
+                    float eps, int seq, int heads, int kv_heads, __nv_bfloat16 *__restrict__ qb,
+                    __nv_bfloat16 *__restrict__ kb) {
     tpb_grid_dep_launch();
     tpb_grid_dep_wait();
-    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (gw >= seq * heads) return;
-    const int p = gw / heads, h = gw - p * heads;
-    const T *src = x + ((size_t)p * heads + h) * kHd + 4 * lane;
-    float v[4];
-    if (sizeof(T) == 4) {
-        const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
-        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-    } else {
-        const uint2 t = __ldg(reinterpret_cast<const uint2 *>(src));
-        v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-        v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
-    }
-    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    const int slots = heads + kv_heads;
+    const long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int l = threadIdx.x & 15;
+    // a whole half-warp leaves together: the shuffles below stay inside it
+    const bool live = unit < (long long)seq * slots;
+    const int p = live ? (int)(unit / slots) : 0;
+    const int sl = live ? (int)(unit - (long long)p * slots) : 0;
+    const bool is_q = sl < heads;
+    const int h = is_q ? sl : sl - heads;
+    const int nh = is_q ? heads : kv_heads;
+    const T *src = (is_q ? q : k) + ((size_t)p * nh + h) * kHd + 8 * l;
+    float v[8];
+    load8(src, v);
+    float ss = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    for (int i = 0; i < 8; i++) ss += v[i] * v[i];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!live) return;
     const float inv = __frsqrt_rn(ss * (1.0f / kHd) + eps);
-    const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + lane);
-    const float n0 = v[0] * inv * wv.x, n1 = v[1] * inv * wv.y, n2 = v[2] * inv * wv.z, n3 = v[3] * inv * wv.w;
-    // pairs 2*lane and 2*lane + 1 of this position's table
-    const float2 c2 = __ldg(reinterpret_cast<const float2 *>(cosv + (size_t)p * (kHd / 2)) + lane);
-    const float2 s2 = __ldg(reinterpret_cast<const float2 *>(sinv + (size_t)p * (kHd / 2)) + lane);
-    const float r0 = n0 * c2.x - n1 * s2.x, r1 = n0 * s2.x + n1 * c2.x;
-    const float r2 = n2 * c2.y - n3 * s2.y, r3 = n2 * s2.y + n3 * c2.y;
-    const __nv_bfloat162 a = __floats2bfloat162_rn(r0, r1), b = __floats2bfloat162_rn(r2, r3);
-    uint2 o;
-    o.x = *reinterpret_cast<const uint32_t *>(&a);
-    o.y = *reinterpret_cast<const uint32_t *>(&b);
-    *reinterpret_cast<uint2 *>(out + ((size_t)h * seq + p) * kHd + 4 * lane) = o;
+    const float *w = (is_q ? qw : kw) + 8 * l;
+    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w)), w1 = __ldg(reinterpret_cast<const float4 *>(w) + 1);
+    const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    // rotation pairs 4l .. 4l+3 of this position's table
+    const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cosv + (size_t)p * (kHd / 2)) + l);
+    const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sinv + (size_t)p * (kHd / 2)) + l);
+    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float a = v[2 * i] * inv * wv[2 * i], b = v[2 * i + 1] * inv * wv[2 * i + 1];
+        o[i] = bf16_pair(a * cs[i] - b * sn[i], a * sn[i] + b * cs[i]);
+    }
+    __nv_bfloat16 *dst = (is_q ? qb : kb) + ((size_t)h * seq + p) * kHd + 8 * l;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // v [seq][kv_heads*128] -> vt [kv_heads][128][seq_pad] bf16 (kv contiguous; columns seq..seq_pad-1 zero).
-// A CTA transposes 64 tokens x 128 dims of one head through shared memory.
+// A CTA transposes 64 tokens x 128 dims of one head through shared memory, 16 bytes per thread on
+// both sides.  Shared tile: word [d][c] = tokens (2c', 2c'+1) of dim d, stored at column
+// c = c' ^ (d >> 3): a half-warp (same token pair, 16 dim groups) then hits 16 different banks, and
+// the second half-warp works 16 token pairs further on, in the other 16 banks.
 template <typename T>
 __global__ void __launch_bounds__(256)
 v_transpose_kernel(const T *__restrict__ v, int seq, int seq_pad, int kv_heads, __nv_bfloat16 *__restrict__ vt) {
-    __shared__ __nv_bfloat16 tile[64][kHd + 2];
+    __shared__ uint32_t tile[kHd][32];
     tpb_grid_dep_launch();
     tpb_grid_dep_wait();
     const int p0 = blockIdx.x * 64, h = blockIdx.y;
-    for (int i = threadIdx.x; i < 64 * kHd; i += blockDim.x) {
-        const int pr = i / kHd, d = i - pr * kHd;
-        const int p = p0 + pr;
-        float val = 0.0f;
-        if (p < seq) {
-            const T t = v[((size_t)p * kv_heads + h) * kHd + d];
-            val = sizeof(T) == 4 ? *reinterpret_cast<const float *>(&t) : __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(&t));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = lane & 15;                                   // dim group: dims 8c .. 8c+7
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int pp = warp * 2 + it + 16 * (lane >> 4);        // token pair within the tile
+        float a[8], b[8];
+        const int t0 = p0 + 2 * pp;
+        if (t0 < seq) load8(v + ((size_t)t0 * kv_heads + h) * kHd + 8 * c, a);
+        else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) a[i] = 0.0f;
         }
-        tile[pr][d] = __float2bfloat16_rn(val);
+        if (t0 + 1 < seq) load8(v + ((size_t)(t0 + 1) * kv_heads + h) * kHd + 8 * c, b);
+        else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) b[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) tile[8 * c + i][pp ^ c] = bf16_pair(a[i], b[i]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 64 * kHd; i += blockDim.x) {
-        const int d = i / 64, pr = i - d * 64;
-        const int p = p0 + pr;
-        if (p < seq_pad) vt[((size_t)h * kHd + d) * seq_pad + p] = tile[pr][d];
+    const int s = threadIdx.x & 7;                              // 8 tokens = 4 words = 16 bytes of a row
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int d = (threadIdx.x >> 3) + 32 * i;
+        const int cd = (d >> 3) & 15;
+        // logical words 4s .. 4s+3 sit in the aligned group (4s ^ (cd & 12)), permuted by cd & 3
+        const uint4 w = *reinterpret_cast<const uint4 *>(&tile[d][(4 * s) ^ (cd & 12)]);
+        const uint32_t g[4] = {w.x, w.y, w.z, w.w};
+        const int x = cd & 3;
+        const int t0 = p0 + 8 * s;
+        if (t0 < seq_pad)
+            *reinterpret_cast<uint4 *>(vt + ((size_t)h * kHd + d) * seq_pad + t0) =
+                make_uint4(g[0 ^ x], g[1 ^ x], g[2 ^ x], g[3 ^ x]);
     }
 }
 
@@ -533,16 +586,18 @@ int tpb_attn_prepare(tpb_handle_t h, tpb_stream_t stream, const void *q, const v
     cudaStream_t st = (cudaStream_t)stream;
     const int seq_pad = (int)((seq + 7) / 8 * 8);
     const dim3 blk(256);
-    const dim3 gq((unsigned)((seq * heads + 7) / 8)), gk((unsigned)((seq * kv_heads + 7) / 8));
+    const long long units = (long long)seq * (heads + kv_heads);     // half-warps
+    const dim3 gqk((unsigned)((units + 15) / 16));
     const dim3 gv((unsigned)((seq_pad + 63) / 64), (unsigned)kv_heads);
     cudaError_t e;
     if (in_dtype == TPB_F32) {
-        e = tpb_launch_pdl(qk_norm_rope_kernel<float>, gq, blk, 0, st, (const float *)q, q_norm, cosv, sinv, eps, (int)seq, heads, (__nv_bfloat16 *)qb);
-        if (e == cudaSuccess) e = tpb_launch_pdl(qk_norm_rope_kernel<float>, gk, blk, 0, st, (const float *)k, k_norm, cosv, sinv, eps, (int)seq, kv_heads, (__nv_bfloat16 *)kb);
+        e = tpb_launch_pdl(qk_norm_rope_kernel<float>, gqk, blk, 0, st, (const float *)q, (const float *)k, q_norm, k_norm,
+                           cosv, sinv, eps, (int)seq, heads, kv_heads, (__nv_bfloat16 *)qb, (__nv_bfloat16 *)kb);
         if (e == cudaSuccess) e = tpb_launch_pdl(v_transpose_kernel<float>, gv, blk, 0, st, (const float *)v, (int)seq, seq_pad, kv_heads, (__nv_bfloat16 *)vt);
     } else {
-        e = tpb_launch_pdl(qk_norm_rope_kernel<__nv_bfloat16>, gq, blk, 0, st, (const __nv_bfloat16 *)q, q_norm, cosv, sinv, eps, (int)seq, heads, (__nv_bfloat16 *)qb);
-        if (e == cudaSuccess) e = tpb_launch_pdl(qk_norm_rope_kernel<__nv_bfloat16>, gk, blk, 0, st, (const __nv_bfloat16 *)k, k_norm, cosv, sinv, eps, (int)seq, kv_heads, (__nv_bfloat16 *)kb);
+        e = tpb_launch_pdl(qk_norm_rope_kernel<__nv_bfloat16>, gqk, blk, 0, st, (const __nv_bfloat16 *)q,
+                           (const __nv_bfloat16 *)k, q_norm, k_norm, cosv, sinv, eps, (int)seq, heads, kv_heads,
+                           (__nv_bfloat16 *)qb, (__nv_bfloat16 *)kb);
         if (e == cudaSuccess) e = tpb_launch_pdl(v_transpose_kernel<__nv_bfloat16>, gv, blk, 0, st, (const __nv_bfloat16 *)v, (int)seq, seq_pad, kv_heads, (__nv_bfloat16 *)vt);
     }
     TPB_CUDA(h, e);
