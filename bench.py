@@ -760,6 +760,18 @@ def run_mode_one_kernel(args, local):
         print(json.dumps({"mode": "one-kernel", "case": case, "copies": out}), flush=True)
         be.close()
         return
+    elif case == "dit-blocks":
+        # two blocks of the fused bf16 DiT step with attention, run twice: the launch list of one block
+        from tensorpencil_b200 import synth
+        T = synth.DIT_TOKENS
+        w = harness.DitWeights(be, 8, blocks=2)
+        x = torch.from_numpy(synth.activations(T, synth.DIT_HIDDEN, seed=1003)).cuda()
+        mod = harness.dit_modulation(be, 2, synth.DIT_HIDDEN)
+        _, _, _, qn, kn, cos, sin = harness.attention_inputs(T, 1, 1, be.device)
+        attn = {"q_norm": qn, "k_norm": kn, "cos": cos, "sin": sin, "heads": synth.DIT_HIDDEN // 128}
+        for _ in range(2):
+            harness.dit_step_linears(be, w, x, out_dtype=torch.bfloat16, mode="fused", mod=mod, mlp_tile=T, attn=attn)
+        reps = 2
     elif case == "attn":
         seq, heads = 4608, 24
         q, k, v, qn, kn, cos, sin = harness.attention_inputs(seq, heads, heads, be.device, torch.bfloat16)
@@ -798,7 +810,7 @@ def main():
     ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "attn", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
-                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn")
+                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

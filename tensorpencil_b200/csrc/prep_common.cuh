@@ -83,6 +83,7 @@ __device__ __forceinline__ void w4_expand_chunk(const uint4 *__restrict__ w4, ui
 
 
 constexpr int kMaxWarps = 8;
+constexpr int kMaxWarpsWide = 16;   // rows of the gated preps: one unit per half-warp, more warps per row
 constexpr int kTilePairs = 16 * 18;  // 64-bit slots of one half-warp's tile (2304 bytes)
 
 // Two packed f32 values; every operation rounds each half like the scalar instruction.
@@ -188,9 +189,51 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16 *p, flo
 }
 
 
+// The same four values kept as loaded (8 or 16 bytes), converted later: lets a thread put all the
+// loads of a unit in flight before the first value is used.
+template <typename T>
+struct Raw4 {
+    uint2 r;
+};
+template <>
+struct Raw4<float> {
+    float4 r;
+};
+template <typename T>
+__device__ __forceinline__ Raw4<T> load_raw(const T *p) {
+    Raw4<T> v;
+    v.r = __ldg(reinterpret_cast<const uint2 *>(p));
+    return v;
+}
+template <>
+__device__ __forceinline__ Raw4<float> load_raw<float>(const float *p) {
+    Raw4<float> v;
+    v.r = __ldg(reinterpret_cast<const float4 *>(p));
+    return v;
+}
+__device__ __forceinline__ void raw_to_f4(const Raw4<float> &v, float (&out)[4]) {
+    out[0] = v.r.x; out[1] = v.r.y; out[2] = v.r.z; out[3] = v.r.w;
+}
+__device__ __forceinline__ void raw_to_f4(const Raw4<__half> &v, float (&out)[4]) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.r.y));
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+__device__ __forceinline__ void raw_to_f4(const Raw4<__nv_bfloat16> &v, float (&out)[4]) {
+    out[0] = __uint_as_float(v.r.x << 16);
+    out[1] = __uint_as_float(v.r.x & 0xffff0000u);
+    out[2] = __uint_as_float(v.r.y << 16);
+    out[3] = __uint_as_float(v.r.y & 0xffff0000u);
+}
+
 // sigmoid(x) = 1 / (1 + exp(-x)) with the fast exponential and reciprocal (the reference's
 // GPU kernels use ex2.approx + rcp.approx for it too, src/gpu/cuda/elt.zig:4-7).
-__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_fast(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
 
 constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves rint(x) in the low mantissa bits
 
@@ -198,10 +241,10 @@ constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves rint
 // ONE_WARP: the row fits one warp (k <= 1024): every warp of the CTA takes its own row and
 // no CTA-wide barrier or shared reduction is needed; otherwise one row per CTA.
 template <typename T, int UPW, int OP, bool ACT_ONLY, bool ONE_WARP>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+__global__ void __launch_bounds__((UPW == 1 ? kMaxWarpsWide : kMaxWarps) * 32)
 convrot_prep_kernel(const PrepParams P) {
-    __shared__ float s_max[kMaxWarps];
-    __shared__ int s_sum[kMaxWarps];
+    __shared__ float s_max[kMaxWarpsWide];
+    __shared__ int s_sum[kMaxWarpsWide];
     extern __shared__ __align__(16) unsigned char s_dyn[];
 
     const int cta_warp = threadIdx.x >> 5;
@@ -224,6 +267,40 @@ convrot_prep_kernel(const PrepParams P) {
 #pragma unroll
     for (int p = 0; p < UPW; p++) {
         const int g0 = 2 * ((2 * warp + hw) + p * 2 * n_warps);
+        if (OP == OP_SILU_MUL || OP == OP_SIGMOID_MUL) {
+            // two operands per element and a sigmoid between load and use: all sixteen loads of the
+            // unit go out first, the arithmetic follows (same operations, same order per element)
+            Raw4<T> ra[4][2], rb[4][2];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                    if (g0 + h < n_groups) {
+                        const int off = (g0 + h) * 256 + 4 * (l16 + 16 * i);
+                        ra[i][h] = load_raw<T>(arow + off);
+                        rb[i][h] = load_raw<T>(brow + off);
+                    }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float x[2][4];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    if (g0 + h < n_groups) {
+                        float u[4];
+                        raw_to_f4(ra[i][h], x[h]);
+                        raw_to_f4(rb[i][h], u);
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            x[h][j] = OP == OP_SILU_MUL ? (x[h][j] * sigmoid_fast(x[h][j])) * u[j] : x[h][j] * sigmoid_fast(u[j]);
+                    } else {
+                        x[h][0] = x[h][1] = x[h][2] = x[h][3] = 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) v[p][i][j] = pack2(x[0][j], x[1][j]);
+            }
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             float x[2][4];
@@ -433,7 +510,11 @@ int launch_prep_op(tpb_handle_t h, cudaStream_t st, const PrepParams &P0, int64_
         const size_t smem = ACT_ONLY ? 0 : (size_t)kRowsPerCta * 2 * kTilePairs * sizeof(f2);
         err = tpb_launch_pdl(convrot_prep_kernel<T, 1, OP, ACT_ONLY, true>, grid, block, smem, st, P);
     } else {
-        const int upw = (n_units + 2 * kMaxWarps - 1) / (2 * kMaxWarps);  // 1..4 for k <= 32768
+        // The gated preps do more arithmetic per element and gain from more warps per row (one unit per
+        // half-warp, up to 16 warps) while the row still fits that way; the plain prep does not.
+        const bool wide = (OP == OP_SILU_MUL || OP == OP_SIGMOID_MUL) && n_units <= 2 * kMaxWarpsWide;
+        const int max_warps = wide ? kMaxWarpsWide : kMaxWarps;
+        const int upw = (n_units + 2 * max_warps - 1) / (2 * max_warps);  // 1..4 for k <= 32768
         const int warps = (n_units + 2 * upw - 1) / (2 * upw);
         const dim3 grid((unsigned)m), block(warps * 32);
         const size_t smem = ACT_ONLY ? 0 : (size_t)warps * 2 * kTilePairs * sizeof(f2);
