@@ -153,6 +153,121 @@ static void attention(tpb::Backend &be, size_t seq, size_t heads, size_t kv_head
     for (tpb::DeviceBuffer d : {qd, kd, vd, qnd, knd, fd, od}) be.tensorDestroy(d);
 }
 
+// One block of the DiT step, the reference's op sequence (src/models/dit_cuda.zig:471-516) through the
+// mirror, against the same sequence composed from the checker's functions.  F = 512 (4 heads x 128),
+// MLP 1024, 200 tokens.  Gate: relative Frobenius error of the latents after the block (attention runs
+// with bf16 operands on the tensor cores against the checker's f32: 3e-2).
+struct HostLinear {
+    std::vector<int8_t> w;
+    std::vector<float> ws;
+    size_t n, k;
+};
+static HostLinear make_linear(size_t n, size_t k, std::mt19937 &rng) {
+    HostLinear l{std::vector<int8_t>(n * k), std::vector<float>(n), n, k};
+    std::uniform_int_distribution<int> wi(-127, 127);
+    std::uniform_real_distribution<float> us(1e-3f, 1e-2f);
+    for (auto &v : l.w) v = (int8_t)wi(rng);
+    for (auto &v : l.ws) v = us(rng);
+    return l;
+}
+static std::vector<float> oracle_linear(const std::vector<float> &x, size_t m, const HostLinear &l) {
+    std::vector<int8_t> q(m * l.k);
+    std::vector<float> as(m);
+    tpo_convrot_prep(x.data(), m, l.k, 8, q.data(), as.data(), nullptr);
+    std::vector<int32_t> acc(m * l.n);
+    tpo_igemm_s32(q.data(), l.w.data(), m, l.n, l.k, acc.data());
+    std::vector<double> sim(m * l.n);
+    tpo_dequant_sim(acc.data(), as.data(), l.ws.data(), m, l.n, sim.data());
+    return std::vector<float>(sim.begin(), sim.end());
+}
+static void dit_block(tpb::Backend &be, unsigned seed) {
+    const size_t F = 512, MLPD = 1024, seq = 200, heads = 4, hd = 128;
+    const float eps = 1e-5f, attn_scale = 1.0f / std::sqrt((float)hd);
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    HostLinear wq = make_linear(F, F, rng), wk = make_linear(F, F, rng), wv = make_linear(F, F, rng),
+               gate = make_linear(F, F, rng), wo = make_linear(F, F, rng), mlp_gate = make_linear(MLPD, F, rng),
+               mlp_up = make_linear(MLPD, F, rng), mlp_down = make_linear(F, MLPD, rng);
+    std::vector<float> x(seq * F), mod(6 * F), qn(hd), kn(hd);
+    for (auto &v : x) v = nd(rng);
+    for (size_t i = 0; i < mod.size(); i++) mod[i] = 0.1f * nd(rng) + ((i / F) % 3 == 0 ? 1.0f : 0.0f);  // premul rows ~ 1
+    for (auto &v : qn) v = 1.f + 0.1f * nd(rng);
+    for (auto &v : kn) v = 1.f + 0.1f * nd(rng);
+    std::vector<float> pos(seq * 3), freqs(2 * seq * (hd / 2));
+    for (size_t p = 0; p < seq; p++) {
+        pos[3 * p] = 0.f;
+        pos[3 * p + 1] = (float)(p / 16);
+        pos[3 * p + 2] = (float)(p % 16);
+    }
+    const int axes[3] = {32, 48, 48};
+    const size_t sin_off = seq * (hd / 2);
+    tpo_flux_freqs(pos.data(), seq, axes, 3, 10000.0, freqs.data(), freqs.data() + sin_off);
+
+    // ---- the checker's block ----
+    std::vector<float> want = x, t1(seq * F);
+    tpo_rms_mod(want.data(), seq, F, mod.data(), mod.data() + F, eps, t1.data());
+    std::vector<float> q = oracle_linear(t1, seq, wq), k = oracle_linear(t1, seq, wk), v = oracle_linear(t1, seq, wv),
+                       g = oracle_linear(t1, seq, gate);
+    std::vector<float> qr(q.size()), kr(k.size()), att(q.size());
+    tpo_qk_norm(q.data(), seq * heads, hd, qn.data(), eps, qr.data());
+    tpo_qk_norm(k.data(), seq * heads, hd, kn.data(), eps, kr.data());
+    tpo_rope_interleaved(qr.data(), freqs.data(), freqs.data() + sin_off, seq, heads, hd);
+    tpo_rope_interleaved(kr.data(), freqs.data(), freqs.data() + sin_off, seq, heads, hd);
+    tpo_attention(qr.data(), kr.data(), v.data(), seq, seq, heads, heads, hd, attn_scale, att.data());
+    std::vector<float> ag(att.size());
+    tpo_sigmoid_mul(att.data(), g.data(), att.size(), ag.data());
+    std::vector<float> o = oracle_linear(ag, seq, wo), x1(seq * F);
+    tpo_gated_add(want.data(), o.data(), mod.data() + 2 * F, seq, F, x1.data());
+    tpo_rms_mod(x1.data(), seq, F, mod.data() + 3 * F, mod.data() + 4 * F, eps, t1.data());
+    std::vector<float> mg = oracle_linear(t1, seq, mlp_gate), mu = oracle_linear(t1, seq, mlp_up), act(mg.size());
+    tpo_silu_mul(mg.data(), mu.data(), mg.size(), act.data());
+    std::vector<float> dn = oracle_linear(act, seq, mlp_down);
+    tpo_gated_add(x1.data(), dn.data(), mod.data() + 5 * F, seq, F, want.data());
+
+    // ---- the same calls through the mirror (dit_cuda.zig:471-516) ----
+    auto up = [&](const std::vector<float> &a) {
+        tpb::DeviceBuffer d = be.tensorCreate(a.size() * 4);
+        be.tensorUpload(d, a.data(), a.size() * 4);
+        return d;
+    };
+    tpb::DeviceBuffer x_d = up(x), mv_d = up(mod), qn_d = up(qn), kn_d = up(kn), freqs_d = up(freqs);
+    tpb::DeviceBuffer t1_d = be.tensorCreate(seq * F * 4), q_d = be.tensorCreate(seq * F * 4), k_d = be.tensorCreate(seq * F * 4),
+                      v_d = be.tensorCreate(seq * F * 4), g_d = be.tensorCreate(seq * F * 4), attn_d = be.tensorCreate(seq * F * 4),
+                      mg_d = be.tensorCreate(seq * MLPD * 4), mu_d = be.tensorCreate(seq * MLPD * 4);
+    auto lin = [&](tpb::DeviceBuffer y, const HostLinear &l) { be.opI8Gemm(y, l.w.data(), l.ws.data(), l.n, false); };
+    be.rmsMod(x_d, t1_d, mv_d, seq, F, 0, F, eps);
+    be.opI8Prep(t1_d, seq, F, false);                        // linPrep: one prep, four GEMMs
+    lin(q_d, wq);
+    lin(k_d, wk);
+    lin(v_d, wv);
+    lin(g_d, gate);
+    be.attention(q_d, k_d, v_d, attn_d, qn_d, kn_d, freqs_d, sin_off, seq, heads, heads, hd, eps, attn_scale);
+    be.sigmoidMul(attn_d, g_d, seq * F);
+    be.opI8Prep(attn_d, seq, F, false);
+    lin(t1_d, wo);
+    be.gatedAdd(x_d, t1_d, mv_d, seq * F, F, 2 * F);
+    be.rmsMod(x_d, t1_d, mv_d, seq, F, 3 * F, 4 * F, eps);
+    be.opI8Prep(t1_d, seq, F, false);
+    lin(mg_d, mlp_gate);
+    lin(mu_d, mlp_up);
+    be.siluMul(mg_d, mu_d, seq * MLPD);
+    be.opI8Prep(mg_d, seq, MLPD, false);
+    lin(t1_d, mlp_down);
+    be.gatedAdd(x_d, t1_d, mv_d, seq * F, F, 5 * F);
+    std::vector<float> got(seq * F);
+    be.tensorDownload(x_d, got.data(), got.size() * 4);
+    double num = 0, den = 0, moved = 0;
+    for (size_t i = 0; i < got.size(); i++) {
+        num += ((double)got[i] - want[i]) * ((double)got[i] - want[i]);
+        den += (double)want[i] * want[i];
+        moved += ((double)want[i] - x[i]) * ((double)want[i] - x[i]);
+    }
+    EXPECT(std::sqrt(num / den) < 3e-2, "dit block: relative error %g", std::sqrt(num / den));
+    EXPECT(moved > 0, "dit block: the block did not change the latents");
+    for (tpb::DeviceBuffer d : {x_d, mv_d, qn_d, kn_d, freqs_d, t1_d, q_d, k_d, v_d, g_d, attn_d, mg_d, mu_d}) be.tensorDestroy(d);
+    be.dropWeights();
+}
+
 int main() {
     try {
         tpb::Backend be(0);
@@ -168,6 +283,7 @@ int main() {
 
         attention(be, 200, 4, 2, 401);
         attention(be, 384, 2, 2, 402);
+        dit_block(be, 501);
 
         // error behaviour: a GEMM without its prep, a width the rotation cannot take
         tpb::DeviceBuffer t = be.tensorCreate(1 << 16);
