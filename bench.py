@@ -142,18 +142,27 @@ def physical_gpu_index(local: int) -> int:
 # CPU arms (the only place outside tests/ that runs the CPU checker)
 # ---------------------------------------------------------------------------------------
 
+def host_threads() -> int:
+    """The host threads this process may use.  Asked from the scheduler, not from OpenMP: a launcher
+    such as torch.distributed.run exports OMP_NUM_THREADS=1, which would leave the CPU arm on one core."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_float_path_sample(target_seconds: float = 12.0):
     """Times the CPU restatement of the reference's `--backend cpu` path on a slice
     of the workload's weight rows (all M activation rows, full K), sized for about
     `target_seconds`.  Returns (TOPS, cores, sample description, seconds)."""
     from oracle import oracle
     from tensorpencil_b200 import synth
-    cores = oracle.num_threads()
+    cores = host_threads()
     x = synth.activations(M, K, seed=1001)
     probe_rows = 16 * cores if 16 * cores <= N else N
     w = synth.convrot_weights(probe_rows, K, BITS, seed=1001)
     t0 = time.perf_counter()
-    oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], probe_rows, K)
+    oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], probe_rows, K, nthreads=cores)
     dt = time.perf_counter() - t0
     rate = 2.0 * M * probe_rows * K / dt
     rows = int(min(N, max(probe_rows, (rate * target_seconds) / (2.0 * M * K))))
@@ -162,7 +171,7 @@ def cpu_float_path_sample(target_seconds: float = 12.0):
     reps, dt = 0, 0.0
     t0 = time.perf_counter()
     while dt < target_seconds * 0.8 or reps == 0:
-        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K)
+        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K, nthreads=cores)
         reps += 1
         dt = time.perf_counter() - t0
     tops = 2.0 * M * rows * K * reps / dt / 1e12
@@ -175,21 +184,21 @@ def run_reference_arm(args, rank: int, world: int):
         return
     from oracle import oracle
     from tensorpencil_b200 import synth
-    cores = oracle.num_threads()
+    cores = host_threads()
     x = synth.activations(M, K, seed=1001)
     # size one step at ~2 s of CPU work, bounded so the whole run stays within minutes
     probe_rows = min(N, 16 * cores)
     w = synth.convrot_weights(probe_rows, K, BITS, seed=1001)
     t0 = time.perf_counter()
-    oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], probe_rows, K)
+    oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], probe_rows, K, nthreads=cores)
     rate = 2.0 * M * probe_rows * K / (time.perf_counter() - t0)
     rows = int(min(N, max(16, rate * 2.0 / (2.0 * M * K)))) // 16 * 16 or 16
     w = synth.convrot_weights(rows, K, BITS, seed=1002)
     for _ in range(args.warmup):
-        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K)
+        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K, nthreads=cores)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K)
+        oracle.linear_cpu_backend(x, w["w_packed"], BITS, w["w_scale"], rows, K, nthreads=cores)
     dt = time.perf_counter() - t0
     tops = 2.0 * M * rows * K * args.steps / dt / 1e12
     sample = f"{rows} of {N} weight rows x all {M} tokens per step (float path: dequantise, un-rotate, f32 FMA GEMM)"
