@@ -21,6 +21,8 @@
 // for one query tile the other tile's softmax runs.  Every wait is bounded.
 #include <cuda_bf16.h>
 
+#include <climits>
+#include <cstdint>
 #include <type_traits>
 
 #include "gemm_common.cuh"
@@ -577,7 +579,8 @@ int tpb_attn_prepare(tpb_handle_t h, tpb_stream_t stream, const void *q, const v
     TPB_CHECK_ARG(h, q && k && v && q_norm && k_norm && cosv && sinv && qb && kb && vt, "attn_prepare: null pointer");
     TPB_CHECK_ARG(h, head_dim == kHd, "attn_prepare: head_dim must be 128 (got %d)", head_dim);
     TPB_CHECK_ARG(h, in_dtype == TPB_F32 || in_dtype == TPB_BF16, "attn_prepare: inputs must be f32 or bf16");
-    TPB_CHECK_ARG(h, seq > 0 && seq < (1 << 24) && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+    TPB_CHECK_ARG(h, seq > 0 && seq < (1 << 24) && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && heads <= 65535 &&
+                         (int64_t)(heads + kv_heads) * seq < INT32_MAX,
                   "attn_prepare: bad seq / heads / kv_heads");
     TPB_CHECK_ARG(h, tpb_aligned16(q) && tpb_aligned16(k) && tpb_aligned16(v) && tpb_aligned16(q_norm) &&
                          tpb_aligned16(k_norm) && tpb_aligned16(cosv) && tpb_aligned16(sinv) && tpb_aligned16(qb) &&
@@ -613,6 +616,10 @@ int tpb_attention(tpb_handle_t h, tpb_stream_t stream, void *out, int out_dtype,
     TPB_CHECK_ARG(h, seq_q > 0 && seq_kv > 0 && seq_q < (1 << 24) && seq_kv < (1 << 24) && heads > 0 && kv_heads > 0 &&
                          heads % kv_heads == 0 && heads <= 65535,
                   "attention: bad seq / heads / kv_heads");
+    // row coordinates of the tensor maps are 32-bit: (head, token) pairs must stay below 2^31, with a
+    // tile of slack for the last query tile
+    TPB_CHECK_ARG(h, (int64_t)heads * seq_q + 2 * kTile < INT32_MAX && (int64_t)kv_heads * seq_kv + kTile < INT32_MAX,
+                  "attention: heads * seq exceeds the 32-bit row range");
     TPB_CHECK_ARG(h, tpb_aligned16(out) && tpb_aligned16(qb) && tpb_aligned16(kb) && tpb_aligned16(vt),
                   "attention: pointers must be 16-byte aligned");
     const int64_t seq_pad = (seq_kv + 7) / 8 * 8;

@@ -116,3 +116,5 @@ def test_attention_rejects_bad_arguments(be):
     assert f(be.h, None, t.data_ptr(), _lib.TPB_BF16, t.data_ptr(), t.data_ptr(), t.data_ptr(), 128, 128, 2, 2, 64, 0.1) == _lib.TPB_ERR_INVALID_ARG
     assert f(be.h, None, t.data_ptr(), _lib.TPB_BF16, t.data_ptr(), t.data_ptr(), t.data_ptr(), 128, 128, 3, 2, 128, 0.1) == _lib.TPB_ERR_INVALID_ARG
     assert f(be.h, None, t.data_ptr(), _lib.TPB_S32, t.data_ptr(), t.data_ptr(), t.data_ptr(), 128, 128, 2, 2, 128, 0.1) == _lib.TPB_ERR_INVALID_ARG
+    # heads * seq beyond the 32-bit row coordinates of the tensor maps
+    assert f(be.h, None, t.data_ptr(), _lib.TPB_BF16, t.data_ptr(), t.data_ptr(), t.data_ptr(), (1 << 24) - 1, 128, 256, 256, 128, 0.1) == _lib.TPB_ERR_INVALID_ARG
