@@ -276,6 +276,46 @@ inline const GgmlType *ggmlType(uint32_t id) {
     return it == t.end() ? nullptr : &it->second;
 }
 
+// llama.cpp tensor names -> the HF-style names the model loaders ask for (src/core/gguf.zig:396-480):
+// "blk.<n>.<suffix>" -> "layers.<n>.<HF suffix>" (a suffix without an entry keeps its spelling), the three
+// top-level names, everything else unchanged.  Gemma's "sandwich" norms rename three entries (ffn_norm is
+// the norm before the feed-forward block there); Gemma 4 adds a per-layer output scale.
+inline std::string canonicalName(const std::string &raw, const std::string &arch) {
+    static const std::map<std::string, std::string> top = {
+        {"token_embd.weight", "embed_tokens.weight"}, {"output_norm.weight", "norm.weight"}, {"output.weight", "lm_head.weight"}};
+    static const std::map<std::string, std::string> base = {
+        {"attn_norm.weight", "input_layernorm.weight"},
+        {"post_attention_norm.weight", "post_attention_layernorm.weight"},
+        {"ffn_norm.weight", "post_attention_layernorm.weight"},
+        {"attn_q.weight", "self_attn.q_proj.weight"},
+        {"attn_k.weight", "self_attn.k_proj.weight"},
+        {"attn_v.weight", "self_attn.v_proj.weight"},
+        {"attn_output.weight", "self_attn.o_proj.weight"},
+        {"attn_q_norm.weight", "self_attn.q_norm.weight"},
+        {"attn_k_norm.weight", "self_attn.k_norm.weight"},
+        {"ffn_gate.weight", "mlp.gate_proj.weight"},
+        {"ffn_up.weight", "mlp.up_proj.weight"},
+        {"ffn_down.weight", "mlp.down_proj.weight"}};
+    const auto t = top.find(raw);
+    if (t != top.end()) return t->second;
+    if (raw.compare(0, 4, "blk.") != 0) return raw;
+    const size_t dot = raw.find('.', 4);
+    if (dot == std::string::npos || dot == 4) return raw;
+    const std::string layer = raw.substr(4, dot - 4), suffix = raw.substr(dot + 1);
+    for (char c : layer)
+        if (c < '0' || c > '9') return raw;
+    const bool gemma = arch == "gemma3" || arch == "gemma4";
+    std::string mapped = suffix;
+    if (gemma && suffix == "ffn_norm.weight") mapped = "pre_feedforward_layernorm.weight";
+    else if (gemma && suffix == "post_ffw_norm.weight") mapped = "post_feedforward_layernorm.weight";
+    else if (arch == "gemma4" && suffix == "layer_output_scale.weight") mapped = "out_scale.weight";
+    else {
+        const auto b = base.find(suffix);
+        if (b != base.end()) mapped = b->second;
+    }
+    return "layers." + layer + "." + mapped;
+}
+
 class Gguf {
   public:
     explicit Gguf(const std::string &path) : map_(path) {
@@ -321,9 +361,16 @@ class Gguf {
             tensors_[in.name] = v;
         }
     }
+    // By the name in the file or by the canonical HF-style name (the reference's reader stores the
+    // latter, gguf.zig:256) for the file's general.architecture.
     const TensorView *get(const std::string &name) const {
         auto it = tensors_.find(name);
-        return it == tensors_.end() ? nullptr : &it->second;
+        if (it != tensors_.end()) return &it->second;
+        const auto a = strings.find("general.architecture");
+        const std::string arch = a == strings.end() ? "" : a->second;
+        for (const auto &kv : tensors_)
+            if (canonicalName(kv.first, arch) == name) return &kv.second;
+        return nullptr;
     }
     const std::map<std::string, TensorView> &tensors() const { return tensors_; }
     uint32_t version = 0;

@@ -221,6 +221,41 @@ class _Reader:
         raise FormatError("InvalidHeader", f"kv type {t}")
 
 
+
+# llama.cpp tensor names -> the HF-style names the model loaders ask for (src/core/gguf.zig:396-480).
+# One table for the Qwen / llama family; Gemma's "sandwich" norms rename three entries (there
+# ffn_norm is the norm BEFORE the feed-forward block) and Gemma 4 adds a per-layer output scale.
+_LAYER_SUFFIX = {
+    "attn_norm.weight": "input_layernorm.weight",
+    "post_attention_norm.weight": "post_attention_layernorm.weight",
+    "ffn_norm.weight": "post_attention_layernorm.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight",
+    "ffn_up.weight": "mlp.up_proj.weight",
+    "ffn_down.weight": "mlp.down_proj.weight",
+    "attn_output.weight": "self_attn.o_proj.weight",
+}
+_LAYER_SUFFIX.update({f"attn_{p}.weight": f"self_attn.{p}_proj.weight" for p in "qkv"})
+_LAYER_SUFFIX.update({f"attn_{p}_norm.weight": f"self_attn.{p}_norm.weight" for p in "qk"})
+_GEMMA_SUFFIX = dict(_LAYER_SUFFIX, **{"ffn_norm.weight": "pre_feedforward_layernorm.weight",
+                                       "post_ffw_norm.weight": "post_feedforward_layernorm.weight"})
+_ARCH_SUFFIX = {"gemma3": _GEMMA_SUFFIX, "gemma4": dict(_GEMMA_SUFFIX, **{"layer_output_scale.weight": "out_scale.weight"})}
+_TOP_LEVEL = {"token_embd.weight": "embed_tokens.weight", "output_norm.weight": "norm.weight", "output.weight": "lm_head.weight"}
+
+
+def canonical_name(raw: str, arch: str = "") -> str:
+    """``blk.<n>.<suffix>`` -> ``layers.<n>.<HF suffix>`` (suffixes without an entry keep their
+    llama.cpp spelling under ``layers.<n>.``); the three top-level names; anything else, HF names
+    included, passes through (gguf.zig:454-480)."""
+    if raw in _TOP_LEVEL:
+        return _TOP_LEVEL[raw]
+    if raw.startswith("blk."):
+        layer, dot, suffix = raw[4:].partition(".")
+        if not dot or not layer.isascii() or not layer.isdigit():
+            return raw
+        return f"layers.{layer}.{_ARCH_SUFFIX.get(arch, _LAYER_SUFFIX).get(suffix, suffix)}"
+    return raw
+
+
 class Gguf:
     def __init__(self, path: str):
         self._f = open(path, "rb")
@@ -256,6 +291,7 @@ class Gguf:
         data_start = (r.pos + self.alignment - 1) // self.alignment * self.alignment
         payload = np.frombuffer(self._mm, dtype=np.uint8, offset=min(data_start, len(self._mm)))
         self.tensors: Dict[str, TensorView] = {}
+        self._canonical: Optional[Dict[str, TensorView]] = None
         for name, shape, tid, off in infos:
             tag, be, bb = GGML_TYPES[tid]
             if name in self.tensors:
@@ -271,10 +307,19 @@ class Gguf:
             self.tensors[name] = TensorView(name, tag, shape, payload[off:off + nbytes])
 
     def get(self, name: str) -> Optional[TensorView]:
-        return self.tensors.get(name)
+        """By the name in the file or, as the reference's reader stores them (gguf.zig:256), by the
+        canonical HF-style name for the file's ``general.architecture``."""
+        v = self.tensors.get(name)
+        if v is None:
+            if self._canonical is None:
+                arch = str(self.metadata.get("general.architecture", ""))
+                self._canonical = {canonical_name(n, arch): t for n, t in self.tensors.items()}
+            v = self._canonical.get(name)
+        return v
 
     def close(self):
         self.tensors = {}
+        self._canonical = None
         try:
             self._mm.close()
         except BufferError:

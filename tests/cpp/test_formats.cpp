@@ -50,6 +50,17 @@ int main(int argc, char **argv) {
         std::printf("G %u %zu %s %lld\n", g.version, g.alignment, g.strings["general.architecture"].c_str(),
                     (long long)g.integers["qwen3.block_count"]);
         dump(g.tensors());
+        // name translation: "N raw arch canonical" lines, compared with the Python reader's answers
+        const char *names[][2] = {{"token_embd.weight", "qwen3"}, {"output.weight", "qwen3"}, {"output_norm.weight", "qwen3"},
+                                  {"blk.17.ffn_down.weight", "qwen3"}, {"blk.0.attn_k_norm.weight", "qwen3"},
+                                  {"blk.0.ssm_conv1d.weight", "qwen35"}, {"blk.2.post_attention_norm.weight", "qwen3"},
+                                  {"layers.3.self_attn.q_proj.weight", "qwen3"}, {"blk.0.ffn_norm.weight", "gemma3"},
+                                  {"blk.0.post_ffw_norm.weight", "gemma3"}, {"blk.3.ffn_norm.weight", "qwen3"},
+                                  {"blk.1.layer_output_scale.weight", "gemma4"}, {"blk.1.layer_output_scale.weight", "gemma3"},
+                                  {"blk.x.attn_q.weight", "qwen3"}, {"blk.4", "qwen3"}};
+        for (auto &n : names) std::printf("N %s %s %s\n", n[0], n[1], tpbfmt::canonicalName(n[0], n[1]).c_str());
+        const tpbfmt::TensorView *byhf = g.get("layers.0.q4_k.weight");
+        std::printf("H %d\n", byhf != nullptr && byhf == g.get("blk.0.q4_k.weight"));
         for (int i = 3; i < argc; i++)
             std::printf("B %s\n", errorName([&] {
                             const std::string p = argv[i];

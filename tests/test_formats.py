@@ -234,5 +234,49 @@ def test_cpp_readers_agree_with_python(tmp_path):
     assert next(ln for ln in lines if ln.startswith("E ")).split()[1:] == ["ShapeMismatch", "MissingTensor", "UnsupportedCheckpoint"]
     assert next(ln for ln in lines if ln.startswith("G ")).split()[1:] == ["3", "64", "qwen3", "7"]
     assert [ln.split()[1] for ln in lines if ln.startswith("B ")] == ["InvalidOffsets", "InvalidMagic"]
+    named = [ln.split()[1:] for ln in lines if ln.startswith("N ")]
+    assert len(named) >= 15
+    for raw, arch, canon in named:
+        assert canon == formats.canonical_name(raw, arch), (raw, arch)
+    assert next(ln for ln in lines if ln.startswith("H ")).split()[1] == "1"
     st.close()
+    g.close()
+
+
+# the reference's cases (src/core/gguf.zig:679-727)
+CANONICAL_CASES = [
+    ("token_embd.weight", "qwen3", "embed_tokens.weight"),
+    ("output.weight", "qwen3", "lm_head.weight"),
+    ("output_norm.weight", "qwen3", "norm.weight"),
+    ("blk.17.ffn_down.weight", "qwen3", "layers.17.mlp.down_proj.weight"),
+    ("blk.0.attn_k_norm.weight", "qwen3", "layers.0.self_attn.k_norm.weight"),
+    ("blk.0.ssm_conv1d.weight", "qwen35", "layers.0.ssm_conv1d.weight"),
+    ("blk.5.ssm_dt.bias", "qwen35", "layers.5.ssm_dt.bias"),
+    ("blk.2.post_attention_norm.weight", "qwen3", "layers.2.post_attention_layernorm.weight"),
+    ("layers.3.self_attn.q_proj.weight", "qwen3", "layers.3.self_attn.q_proj.weight"),
+    ("blk.0.ffn_norm.weight", "gemma3", "layers.0.pre_feedforward_layernorm.weight"),
+    ("blk.0.post_attention_norm.weight", "gemma3", "layers.0.post_attention_layernorm.weight"),
+    ("blk.0.post_ffw_norm.weight", "gemma3", "layers.0.post_feedforward_layernorm.weight"),
+    ("blk.7.attn_output.weight", "gemma3", "layers.7.self_attn.o_proj.weight"),
+    # beyond the reference's list: the Qwen reading of ffn_norm, Gemma 4's extra entry, malformed layer ids
+    ("blk.3.ffn_norm.weight", "qwen3", "layers.3.post_attention_layernorm.weight"),
+    ("blk.1.layer_output_scale.weight", "gemma4", "layers.1.out_scale.weight"),
+    ("blk.1.layer_output_scale.weight", "gemma3", "layers.1.layer_output_scale.weight"),
+    ("blk.x.attn_q.weight", "qwen3", "blk.x.attn_q.weight"),
+    ("blk.4", "qwen3", "blk.4"),
+]
+
+
+def test_canonical_tensor_names(tmp_path):
+    for raw, arch, want in CANONICAL_CASES:
+        assert formats.canonical_name(raw, arch) == want, (raw, arch)
+    # a reader answers to both spellings
+    k = 256
+    w = synth.gguf_weights("q8_0", 8, k, seed=5)
+    p = str(tmp_path / "names.gguf")
+    formats.write_gguf(p, {"blk.2.ffn_up.weight": ("Q8_0", (8, k), w), "token_embd.weight": ("Q8_0", (8, k), w)},
+                       metadata={"general.architecture": "gemma3"})
+    g = formats.Gguf(p)
+    assert g.get("layers.2.mlp.up_proj.weight") is g.get("blk.2.ffn_up.weight") is not None
+    assert g.get("embed_tokens.weight") is not None and g.get("layers.2.mlp.down_proj.weight") is None
     g.close()
