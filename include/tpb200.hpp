@@ -25,6 +25,7 @@
 #include <vector>
 
 #include "tpb200.h"
+#include "tpb200_cache.hpp"
 
 namespace tpb {
 
@@ -99,22 +100,23 @@ class Backend {
     // ---- weight cache keyed by host address (backend.zig:1376-1445) ----
     // As in the reference, a cached weight is identified by its host address and size only:
     // keep weight memory alive and unchanged while cached, or call dropWeights() first.
-    const void *cachedWeight(const void *host, size_t bytes) {
-        auto it = weights_.find(host);
-        if (it != weights_.end() && it->second.size == bytes) return it->second.p;
-        if (it != weights_.end()) {
-            release(it->second);
-            weights_.erase(it);
+    const void *cachedWeight(const void *host, size_t bytes, bool pin = false) {
+        try {
+            return weights_.get(host, bytes, pin).p;
+        } catch (const CacheFull &e) {
+            throw Error(TPB_ERR_OOM, e.what());
         }
-        DeviceBuffer db = tensorCreate(bytes);
-        cuda(cudaMemcpyAsync(db.p, host, bytes, cudaMemcpyHostToDevice, stream_), "cachedWeight upload");
-        weights_[host] = db;
-        return db.p;
     }
+    // --vram-budget for the weights (backend.zig:222-252): least-recently-used weights that are not
+    // pinned are freed to make room; 0 = no limit.  Freeing synchronises the device (cudaFree), so a
+    // weight is never released under a kernel that still reads it.
+    void setWeightBudget(size_t bytes) { weights_.setBudget(bytes); }
+    void unpinWeight(const void *host) { weights_.unpin(host); }
+    size_t weightBytes() const { return weights_.bytes(); }
+    size_t weightEvictions() const { return weights_.evictions; }
     void dropWeights() {
         if (stream_) cudaStreamSynchronize(stream_);
-        for (auto &kv : weights_) release(kv.second);
-        weights_.clear();
+        weights_.dropAll();
     }
 
     // ---- ConvRot linears ----
@@ -220,8 +222,17 @@ class Backend {
     }
     void gemm(DeviceBuffer y, const void *w_host, size_t w_bytes, const float *ws_host, size_t rows, int bits, int y_dtype) {
         if (bits_ != bits) throw Error(TPB_ERR_STATE, "op{I8,I4}Gemm must follow the matching prep");
-        const void *w = cachedWeight(w_host, w_bytes);
-        const float *ws = static_cast<const float *>(cachedWeight(ws_host, rows * 4));
+        // the weight stays pinned while its scales are fetched: under a tight budget the second
+        // lookup must not evict the first
+        const void *w = cachedWeight(w_host, w_bytes, true);
+        const float *ws = nullptr;
+        try {
+            ws = static_cast<const float *>(cachedWeight(ws_host, rows * 4));
+        } catch (...) {
+            unpinWeight(w_host);
+            throw;
+        }
+        unpinWeight(w_host);
         check(tpb_convrot_gemm(h_, stream_, y.p, y_dtype, (int64_t)rows, static_cast<const int8_t *>(i8_x_.p),
                                static_cast<const float *>(i8_scale_.p),
                                bits == 4 ? static_cast<const int32_t *>(i8_sum_.p) : nullptr, w, bits, ws, (int64_t)m_,
@@ -253,7 +264,13 @@ class Backend {
     DeviceBuffer i8_x_, i8_scale_, i8_sum_, q8_, attn_q_, attn_k_, attn_vt_;
     size_t m_ = 0, cols_ = 0, q8_total_ = 0;
     int bits_ = 0;
-    std::unordered_map<const void *, DeviceBuffer> weights_;
+    WeightCache<DeviceBuffer> weights_{
+        [this](const void *host, size_t bytes) {
+            DeviceBuffer db = tensorCreate(bytes);
+            cuda(cudaMemcpyAsync(db.p, host, bytes, cudaMemcpyHostToDevice, stream_), "cachedWeight upload");
+            return db;
+        },
+        [](DeviceBuffer &db) { release(db); }};
 };
 
 }  // namespace tpb

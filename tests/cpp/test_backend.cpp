@@ -104,6 +104,42 @@ static void gguf_gemv(tpb::Backend &be, tpb::DType dt, int fmt, size_t rows, siz
     be.dropWeights();  // the cache is keyed by host address, and `w` is about to be freed
 }
 
+// An int8 linear whose host weight outlives the call (the cache is keyed by host address), cache kept.
+static void convrot_linear_keep(tpb::Backend &be, size_t m, size_t n, size_t k, unsigned seed) {
+    static std::vector<std::vector<int8_t>> keep_w;
+    static std::vector<std::vector<float>> keep_ws;
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::uniform_real_distribution<float> us(1e-3f, 1e-2f);
+    std::uniform_int_distribution<int> wi(-127, 127);
+    std::vector<float> x(m * k);
+    for (auto &v : x) v = nd(rng);
+    keep_w.emplace_back(n * k);
+    keep_ws.emplace_back(n);
+    std::vector<int8_t> &w = keep_w.back();
+    std::vector<float> &ws = keep_ws.back();
+    for (auto &v : w) v = (int8_t)wi(rng);
+    for (auto &v : ws) v = us(rng);
+    std::vector<int8_t> q(m * k);
+    std::vector<float> as(m);
+    tpo_convrot_prep(x.data(), m, k, 8, q.data(), as.data(), nullptr);
+    std::vector<int32_t> acc(m * n);
+    tpo_igemm_s32(q.data(), w.data(), m, n, k, acc.data());
+    std::vector<double> sim(m * n);
+    tpo_dequant_sim(acc.data(), as.data(), ws.data(), m, n, sim.data());
+    tpb::DeviceBuffer xd = be.tensorCreate(m * k * 4), yd = be.tensorCreate(m * n * 4);
+    be.tensorUpload(xd, x.data(), m * k * 4);
+    be.opI8Prep(xd, m, k, false);
+    be.opI8Gemm(yd, w.data(), ws.data(), n, false);
+    std::vector<float> y(m * n);
+    be.tensorDownload(yd, y.data(), y.size() * 4);
+    double worst = 0;
+    for (size_t i = 0; i < y.size(); i++) worst = std::fmax(worst, std::fabs((double)y[i] - sim[i]) - 1e-3 * std::fabs(sim[i]));
+    EXPECT(worst <= 1e-4, "linear under a weight budget: error beyond 1e-3 rel + 1e-4 abs by %g", worst);
+    be.tensorDestroy(xd);
+    be.tensorDestroy(yd);
+}
+
 // qkNorm + rope + attn against the checker; gate = 2 % of the result's norm (bf16 operands on the
 // tensor cores against the f32 definition)
 static void attention(tpb::Backend &be, size_t seq, size_t heads, size_t kv_heads, unsigned seed) {
@@ -284,6 +320,25 @@ int main() {
         attention(be, 200, 4, 2, 401);
         attention(be, 384, 2, 2, 402);
         dit_block(be, 501);
+
+        // weights under a budget (--vram-budget): 300 x 3072 int8 = 0.92 MB per weight under 2 MB: the
+        // third linear evicts the first weight and the results stay right
+        be.setWeightBudget(2u << 20);
+        convrot_linear_keep(be, 300, 3072, 256, 31);
+        convrot_linear_keep(be, 300, 3072, 256, 32);
+        convrot_linear_keep(be, 300, 3072, 256, 33);
+        EXPECT(be.weightEvictions() > 0 && be.weightBytes() <= (2u << 20), "budget: %zu evictions, %zu bytes cached",
+               be.weightEvictions(), be.weightBytes());
+        bool full = false;
+        try {
+            std::vector<int8_t> huge(3u << 20);
+            be.cachedWeight(huge.data(), huge.size());
+        } catch (const tpb::Error &e) {
+            full = e.status == TPB_ERR_OOM;
+        }
+        EXPECT(full, "a weight larger than the budget must fail with TPB_ERR_OOM");
+        be.dropWeights();
+        be.setWeightBudget(0);
 
         // error behaviour: a GEMM without its prep, a width the rotation cannot take
         tpb::DeviceBuffer t = be.tensorCreate(1 << 16);

@@ -6,6 +6,7 @@
 #include <functional>
 #include <string>
 
+#include "tpb200_cache.hpp"
 #include "tpb200_formats.hpp"
 
 static unsigned long long checksum(const uint8_t *p, size_t n) {
@@ -61,6 +62,31 @@ int main(int argc, char **argv) {
         for (auto &n : names) std::printf("N %s %s %s\n", n[0], n[1], tpbfmt::canonicalName(n[0], n[1]).c_str());
         const tpbfmt::TensorView *byhf = g.get("layers.0.q4_k.weight");
         std::printf("H %d\n", byhf != nullptr && byhf == g.get("blk.0.q4_k.weight"));
+        // the budgeted weight cache with a fake device: the sequence of tests/test_formats.py
+        {
+            std::vector<size_t> uploads;
+            tpb::WeightCache<size_t> cache([&](const void *, size_t n) { uploads.push_back(n); return n; }, [](size_t &) {}, 1000);
+            static char a[400], b[400], c3[300], d[900], big[2000];
+            bool ok = cache.get(a, 400) == 400 && cache.get(b, 400) == 400 && cache.bytes() == 800;
+            cache.get(a, 400);                       // a becomes the most recent
+            cache.get(c3, 300);                      // evicts b
+            ok = ok && cache.bytes() == 700 && cache.evictions == 1 && cache.hits == 1 && cache.misses == 3;
+            cache.get(b, 400);                       // evicts a
+            ok = ok && cache.misses == 4 && cache.bytes() == 700 && uploads == std::vector<size_t>{400, 400, 300, 400};
+            cache.get(c3, 300, true);
+            bool threw = false;
+            try { cache.get(d, 900); } catch (const tpb::CacheFull &) { threw = true; }
+            ok = ok && threw;
+            cache.unpin(c3);
+            cache.get(d, 900);
+            ok = ok && cache.bytes() == 900;
+            threw = false;
+            try { cache.get(big, 2000); } catch (const tpb::CacheFull &) { threw = true; }
+            ok = ok && threw;
+            cache.get(d, 500);                       // same address, another size: replaced
+            ok = ok && cache.bytes() == 500 && cache.misses == 8;
+            std::printf("C %d\n", ok ? 1 : 0);
+        }
         for (int i = 3; i < argc; i++)
             std::printf("B %s\n", errorName([&] {
                             const std::string p = argv[i];

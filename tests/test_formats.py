@@ -239,6 +239,7 @@ def test_cpp_readers_agree_with_python(tmp_path):
     for raw, arch, canon in named:
         assert canon == formats.canonical_name(raw, arch), (raw, arch)
     assert next(ln for ln in lines if ln.startswith("H ")).split()[1] == "1"
+    assert next(ln for ln in lines if ln.startswith("C ")).split()[1] == "1"      # include/tpb200_cache.hpp
     st.close()
     g.close()
 
