@@ -83,7 +83,11 @@ __device__ __forceinline__ void w4_expand_chunk(const uint4 *__restrict__ w4, ui
 
 
 constexpr int kMaxWarps = 8;
-constexpr int kMaxWarpsWide = 16;   // rows of the gated preps: one unit per half-warp, more warps per row
+constexpr int kMaxWarpsWide = 16;
+#ifndef TPB_F32_LOAD_FIRST
+#define TPB_F32_LOAD_FIRST 1
+#endif
+constexpr bool kF32LoadFirst = TPB_F32_LOAD_FIRST != 0;   // rows of the gated preps: one unit per half-warp, more warps per row
 constexpr int kTilePairs = 16 * 18;  // 64-bit slots of one half-warp's tile (2304 bytes)
 
 // Two packed f32 values; every operation rounds each half like the scalar instruction.
@@ -267,9 +271,11 @@ convrot_prep_kernel(const PrepParams P) {
 #pragma unroll
     for (int p = 0; p < UPW; p++) {
         const int g0 = 2 * ((2 * warp + hw) + p * 2 * n_warps);
-        if (OP == OP_SILU_MUL || OP == OP_SIGMOID_MUL) {
-            // two operands per element and a sigmoid between load and use: all sixteen loads of the
-            // unit go out first, the arithmetic follows (same operations, same order per element)
+        if ((OP == OP_SILU_MUL || OP == OP_SIGMOID_MUL) && sizeof(T) == 2) {
+            // two operands per element and a sigmoid between load and use: with 16-bit inputs all sixteen
+            // loads of the unit go out first, the arithmetic follows (same operations, same order per
+            // element); with f32 inputs the raw values would double the live registers and the
+            // interleaved order below measured faster
             Raw4<T> ra[4][2], rb[4][2];
 #pragma unroll
             for (int i = 0; i < 4; i++)
