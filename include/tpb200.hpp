@@ -158,6 +158,42 @@ class Backend {
                             static_cast<const float *>(mod.p) + gate_off, (int64_t)(total / dim), (int64_t)dim));
     }
 
+    // ---- the same ops folded into the prep and the GEMM epilogue (no reference counterpart: it runs
+    // op, then prep; GEMM, then gatedAdd).  q / scales are bit-identical to the two-call sequences. ----
+    // rmsMod + opI{8,4}Prep (dit_cuda.zig:473-474, :499-500)
+    void prepRmsMod(DeviceBuffer x, DeviceBuffer mod, size_t rows, size_t dim, size_t premul_off, size_t shift_off, float eps,
+                    int bits = 8) {
+        const float *m = static_cast<const float *>(mod.p);
+        prepFused(TPB_OP_RMS_MOD, x.p, nullptr, m + premul_off, m + shift_off, eps, rows, dim, bits);
+    }
+    // siluMul + prep (dit_cuda.zig:513-514) and sigmoidMul + prep (:490-491)
+    void prepSiluMul(DeviceBuffer gate, DeviceBuffer up, size_t m, size_t cols, int bits = 8) {
+        prepFused(TPB_OP_SILU_MUL, gate.p, up.p, nullptr, nullptr, 0.0f, m, cols, bits);
+    }
+    void prepSigmoidMul(DeviceBuffer a, DeviceBuffer gate, size_t m, size_t cols, int bits = 8) {
+        prepFused(TPB_OP_SIGMOID_MUL, a.p, gate.p, nullptr, nullptr, 0.0f, m, cols, bits);
+    }
+    // opI{8,4}Gemm + gatedAdd (dit_cuda.zig:492-493, :515-516): x[m][rows] += mod[gate_off + c] * linear
+    void gemmGatedAdd(DeviceBuffer x, const void *w_bytes, const float *weight_scale, size_t rows, DeviceBuffer mod,
+                      size_t gate_off, int bits = 8) {
+        if (bits_ != bits) throw Error(TPB_ERR_STATE, "gemmGatedAdd must follow the matching prep");
+        const size_t w_size = bits == 4 ? rows * cols_ / 2 : rows * cols_;
+        const void *w = cachedWeight(w_bytes, w_size, true);
+        const float *ws = nullptr;
+        try {
+            ws = static_cast<const float *>(cachedWeight(weight_scale, rows * 4));
+        } catch (...) {
+            unpinWeight(w_bytes);
+            throw;
+        }
+        unpinWeight(w_bytes);
+        check(tpb_convrot_gemm_gated_add(h_, stream_, static_cast<float *>(x.p), (int64_t)rows,
+                                         static_cast<const float *>(mod.p) + gate_off, static_cast<const int8_t *>(i8_x_.p),
+                                         static_cast<const float *>(i8_scale_.p),
+                                         bits == 4 ? static_cast<const int32_t *>(i8_sum_.p) : nullptr, w, bits, ws,
+                                         (int64_t)m_, (int64_t)rows, (int64_t)cols_));
+    }
+
     // ---- attention of the DiT block (dit_cuda.zig:479-489: qkNorm, rope, attn / opAttnTC) ----
     // q [seq][heads*hd], k / v [seq][kv_heads*hd] (f32), freqs = cos table [seq][hd/2] then, sin_off floats
     // later, the sin table; out [seq][heads*hd] f32.  head_dim 128, non-causal.  Unlike the reference's
@@ -216,6 +252,18 @@ class Backend {
         ensure(i8_sum_, m * 4);
         check(tpb_convrot_prep(h_, stream_, x.p, x_dtype, (int64_t)m, (int64_t)cols, bits, static_cast<int8_t *>(i8_x_.p),
                                static_cast<float *>(i8_scale_.p), static_cast<int32_t *>(i8_sum_.p)));
+        m_ = m;
+        cols_ = cols;
+        bits_ = bits;
+    }
+    void prepFused(int op, const void *a, const void *b, const float *premul, const float *shift, float eps, size_t m,
+                   size_t cols, int bits) {
+        ensure(i8_x_, m * cols);
+        ensure(i8_scale_, m * 4);
+        ensure(i8_sum_, m * 4);
+        check(tpb_convrot_prep_fused(h_, stream_, op, a, b, premul, shift, eps, TPB_F32, (int64_t)m, (int64_t)cols, bits,
+                                     static_cast<int8_t *>(i8_x_.p), static_cast<float *>(i8_scale_.p),
+                                     static_cast<int32_t *>(i8_sum_.p)));
         m_ = m;
         cols_ = cols;
         bits_ = bits;

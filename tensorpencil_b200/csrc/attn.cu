@@ -432,12 +432,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
 template <typename T>
 __device__ __forceinline__ void load8(const T *src, float (&v)[8]) {
     if (sizeof(T) == 4) {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(src));
+        const float4 b = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     } else {
-        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(src));
+        const uint4 t = __ldcg(reinterpret_cast<const uint4 *>(src));
         const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) {

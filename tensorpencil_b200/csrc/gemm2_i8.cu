@@ -170,8 +170,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             const bool row_ok = row < p.m;
             float as = 0.0f;
             int corr = 0;
-            if (OUT != OUT_S32 && row_ok) as = __ldg(p.act_scale + row);
-            if (p.act_sum != nullptr && row_ok) corr = 8 * __ldg(p.act_sum + row);
+            if (OUT != OUT_S32 && row_ok) as = __ldcg(p.act_scale + row);
+            if (p.act_sum != nullptr && row_ok) corr = 8 * __ldcg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
             epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
             tc_fence_before();

@@ -324,10 +324,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                     // back by this warp's own TMA store below, nobody else touches it
                     float4 gt = make_float4(0.f, 0.f, 0.f, 0.f), xv = gt;
                     if (col0 + 4 * g < p.n) {
-                        gt = __ldg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
+                        gt = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
+                        // L2-only load: the tile is rewritten below through the TMA (async proxy), which
+                        // does not update a line this load would leave in L1, and a dependent kernel that
+                        // was launched early on this SM could then read the old values from it
                         if (row0 + lane < p.m)
-                            xv = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.y) +
-                                                                   (size_t)(row0 + lane) * (size_t)p.ldy + col0 + 4 * g);
+                            xv = __ldcg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.y) +
+                                                                         (size_t)(row0 + lane) * (size_t)p.ldy + col0 + 4 * g));
                     }
                     v0 = __fmaf_rn(gt.x, v0, xv.x);
                     v1 = __fmaf_rn(gt.y, v1, xv.y);

@@ -63,7 +63,7 @@ struct PrepParams {
 
 // 16 packed int4 bytes -> 32 int8 bytes (element 2j in the low nibble, src/core/dtype.zig:146-149)
 __device__ __forceinline__ void w4_expand_chunk(const uint4 *__restrict__ w4, uint4 *__restrict__ w8, size_t c) {
-    const uint4 p = __ldg(w4 + c);
+    const uint4 p = __ldcg(w4 + c);
     const uint32_t in[4] = {p.x, p.y, p.z, p.w};
     uint32_t out[8];
 #pragma unroll
@@ -173,19 +173,19 @@ __device__ __forceinline__ void load4(const T *p, float (&out)[4]);
 
 template <>
 __device__ __forceinline__ void load4<float>(const float *p, float (&out)[4]) {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+    const float4 t = __ldcg(reinterpret_cast<const float4 *>(p));
     out[0] = t.x; out[1] = t.y; out[2] = t.z; out[3] = t.w;
 }
 template <>
 __device__ __forceinline__ void load4<__half>(const __half *p, float (&out)[4]) {
-    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
+    const uint2 t = __ldcg(reinterpret_cast<const uint2 *>(p));
     const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&t.x));
     const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&t.y));
     out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
 }
 template <>
 __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16 *p, float (&out)[4]) {
-    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
+    const uint2 t = __ldcg(reinterpret_cast<const uint2 *>(p));
     out[0] = __uint_as_float(t.x << 16);
     out[1] = __uint_as_float(t.x & 0xffff0000u);
     out[2] = __uint_as_float(t.y << 16);
@@ -206,13 +206,13 @@ struct Raw4<float> {
 template <typename T>
 __device__ __forceinline__ Raw4<T> load_raw(const T *p) {
     Raw4<T> v;
-    v.r = __ldg(reinterpret_cast<const uint2 *>(p));
+    v.r = __ldcg(reinterpret_cast<const uint2 *>(p));
     return v;
 }
 template <>
 __device__ __forceinline__ Raw4<float> load_raw<float>(const float *p) {
     Raw4<float> v;
-    v.r = __ldg(reinterpret_cast<const float4 *>(p));
+    v.r = __ldcg(reinterpret_cast<const float4 *>(p));
     return v;
 }
 __device__ __forceinline__ void raw_to_f4(const Raw4<float> &v, float (&out)[4]) {
@@ -362,8 +362,8 @@ convrot_prep_kernel(const PrepParams P) {
                 for (int h = 0; h < 2; h++) {
                     if (g0 + h < n_groups) {
                         const int off = (g0 + h) * 256 + 4 * (l16 + 16 * i);
-                        const float4 pm = __ldg(reinterpret_cast<const float4 *>(P.premul + off));
-                        const float4 sh = __ldg(reinterpret_cast<const float4 *>(P.shift + off));
+                        const float4 pm = __ldcg(reinterpret_cast<const float4 *>(P.premul + off));
+                        const float4 sh = __ldcg(reinterpret_cast<const float4 *>(P.shift + off));
                         x[h][0] = __fmaf_rn(x[h][0] * inv, pm.x, sh.x);
                         x[h][1] = __fmaf_rn(x[h][1] * inv, pm.y, sh.y);
                         x[h][2] = __fmaf_rn(x[h][2] * inv, pm.z, sh.z);

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) gated_add_kernel(float *__restrict__ x, c
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n4; c += (size_t)gridDim.x * blockDim.x) {
         float d[4];
         load4<T>(delta + 4 * c, d);
-        const float4 g = __ldg(reinterpret_cast<const float4 *>(gate) + (c % (size_t)dim4));
+        const float4 g = __ldcg(reinterpret_cast<const float4 *>(gate) + (c % (size_t)dim4));
         float4 v = reinterpret_cast<float4 *>(x)[c];
         v.x = __fmaf_rn(g.x, d[0], v.x);
         v.y = __fmaf_rn(g.y, d[1], v.y);

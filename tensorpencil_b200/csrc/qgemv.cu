@@ -115,9 +115,9 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
         for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
             const int m = i / per_row, c16 = i - m * per_row;
             *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
-                __ldg(gq + i);
+                __ldcg(gq + i);
         }
-        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldcg(p.xd + i);
     }
     __syncthreads();
 
@@ -186,10 +186,12 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
                     const int4 *a = reinterpret_cast<const int4 *>(p.xq + (size_t)m * cols + (size_t)blk0 * 32);
 #pragma unroll
                     for (int v = 0; v < 4; v++) {
-                        const int4 t = __ldg(a + v);
+                        // plain (L1-cached, coherent) load: every weight row re-reads these, and unlike a
+                        // read-only-path load it cannot be moved above griddepcontrol.wait
+                        const int4 t = a[v];
                         xq[4 * v] = t.x; xq[4 * v + 1] = t.y; xq[4 * v + 2] = t.z; xq[4 * v + 3] = t.w;
                     }
-                    const float2 d2 = __ldg(reinterpret_cast<const float2 *>(p.xd + (size_t)m * nblk + blk0));
+                    const float2 d2 = *reinterpret_cast<const float2 *>(p.xd + (size_t)m * nblk + blk0);
                     xd0 = d2.x;
                     xd1 = d2.y;
                 }

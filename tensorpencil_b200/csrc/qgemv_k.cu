@@ -159,9 +159,9 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
             const int m = i / per_row, c16 = i - m * per_row;
             *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
-                __ldg(gq + i);
+                __ldcg(gq + i);
         }
-        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldcg(p.xd + i);
     }
     __syncthreads();
     // S[m][b] = d[m][b] * sum of the block's 32 quants
@@ -440,9 +440,9 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
             const int m = i / per_row, c16 = i - m * per_row;
             *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
-                __ldg(gq + i);
+                __ldcg(gq + i);
         }
-        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldg(p.xd + i);
+        for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldcg(p.xd + i);
     }
     __syncthreads();
 

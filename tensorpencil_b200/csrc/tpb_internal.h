@@ -6,6 +6,7 @@
 
 #include <cstdarg>
 #include <cstdint>
+#include <cstdlib>
 #include <cstdio>
 #include <string>
 
@@ -50,7 +51,11 @@ int tpb_fail(tpb_handle_t h, int code, const char *fmt, ...);
 // Launch with programmatic stream serialisation: the grid may start while the previous
 // kernel in the stream is still draining.  Every kernel launched this way executes
 // griddepcontrol.wait before it reads or writes global memory, which also keeps the
-// ordering transitive along the stream.
+// ordering transitive along the stream.  Data that another kernel of the stream may have written
+// (activations, scales, modulation vectors, residuals) is loaded with __ldcg, never __ldg: a load
+// through the read-only path counts as invariant for the compiler, which may move it above
+// griddepcontrol.wait, where it reads what the previous kernel has not written yet.  __ldg is for
+// weights and tables that no kernel writes.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t tpb_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                          cudaStream_t st, Args... args) {
@@ -61,7 +66,8 @@ static inline cudaError_t tpb_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool no_pdl = getenv("TPB_NO_PDL") != nullptr;
+    attr[0].val.programmaticStreamSerializationAllowed = no_pdl ? 0 : 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);

@@ -292,6 +292,35 @@ static void dit_block(tpb::Backend &be, unsigned seed) {
     be.gatedAdd(x_d, t1_d, mv_d, seq * F, F, 5 * F);
     std::vector<float> got(seq * F);
     be.tensorDownload(x_d, got.data(), got.size() * 4);
+
+    // ---- the block again with the producers folded into the preps and the gated residuals into the
+    // GEMM epilogues: same arithmetic, one FMA contraction in the residual ----
+    // No host synchronisation anywhere in this sequence: every kernel is launched while its predecessor
+    // still runs (programmatic dependent launch), so a kernel that read its input ahead of
+    // griddepcontrol.wait would show up here as a wrong residual.
+    be.tensorUpload(x_d, x.data(), x.size() * 4);
+    be.prepRmsMod(x_d, mv_d, seq, F, 0, F, eps);
+    lin(q_d, wq);
+    lin(k_d, wk);
+    lin(v_d, wv);
+    lin(g_d, gate);
+    be.attention(q_d, k_d, v_d, attn_d, qn_d, kn_d, freqs_d, sin_off, seq, heads, heads, hd, eps, attn_scale);
+    be.prepSigmoidMul(attn_d, g_d, seq, F);
+    be.gemmGatedAdd(x_d, wo.w.data(), wo.ws.data(), F, mv_d, 2 * F);
+    be.prepRmsMod(x_d, mv_d, seq, F, 3 * F, 4 * F, eps);
+    lin(mg_d, mlp_gate);
+    lin(mu_d, mlp_up);
+    be.prepSiluMul(mg_d, mu_d, seq, MLPD);
+    be.gemmGatedAdd(x_d, mlp_down.w.data(), mlp_down.ws.data(), F, mv_d, 5 * F);
+    std::vector<float> fused(seq * F);
+    be.tensorDownload(x_d, fused.data(), fused.size() * 4);
+    double fnum = 0, fden = 0;
+    for (size_t i = 0; i < got.size(); i++) {
+        fnum += ((double)fused[i] - got[i]) * ((double)fused[i] - got[i]);
+        fden += (double)got[i] * got[i];
+    }
+    EXPECT(std::sqrt(fnum / fden) < 1e-4, "dit block, fused against the reference sequence: relative error %g", std::sqrt(fnum / fden));
+
     double num = 0, den = 0, moved = 0;
     for (size_t i = 0; i < got.size(); i++) {
         num += ((double)got[i] - want[i]) * ((double)got[i] - want[i]);
