@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <random>
 #include <vector>
 
@@ -333,6 +334,47 @@ static void dit_block(tpb::Backend &be, unsigned seed) {
     be.dropWeights();
 }
 
+// Forty prep + GEMM pairs issued as fast as the host can, alternating between two activations, no
+// synchronisation until the end: each output must be bit-identical to the one obtained with a
+// synchronisation after every call (a GEMM that picked up the scales or the quantised rows of the
+// previous iteration, or read them before its dependency wait, differs).
+static void launch_order(tpb::Backend &be, unsigned seed) {
+    const size_t m = 300, k = 1024, n = 512, iters = 40;
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    static HostLinear lin = make_linear(n, k, rng);          // outlives the call: the cache is keyed by address
+    std::vector<float> x0(m * k), x1(m * k);
+    for (auto &v : x0) v = nd(rng);
+    for (auto &v : x1) v = 7.f * nd(rng);
+    tpb::DeviceBuffer xd[2] = {be.tensorCreate(m * k * 4), be.tensorCreate(m * k * 4)};
+    be.tensorUpload(xd[0], x0.data(), m * k * 4);
+    be.tensorUpload(xd[1], x1.data(), m * k * 4);
+    std::vector<float> ref[2] = {std::vector<float>(m * n), std::vector<float>(m * n)};
+    tpb::DeviceBuffer yd = be.tensorCreate(iters * m * n * 4);
+    for (int s = 0; s < 2; s++) {
+        be.opI8Prep(xd[s], m, k, false);
+        be.opI8Gemm(yd, lin.w.data(), lin.ws.data(), n, false);
+        be.tensorDownload(yd, ref[s].data(), m * n * 4);     // synchronises
+    }
+    for (size_t i = 0; i < iters; i++) {
+        tpb::DeviceBuffer yi;
+        yi.p = static_cast<char *>(yd.p) + i * m * n * 4;
+        yi.size = m * n * 4;
+        be.opI8Prep(xd[i & 1], m, k, false);
+        be.opI8Gemm(yi, lin.w.data(), lin.ws.data(), n, false);
+    }
+    std::vector<float> all(iters * m * n);
+    be.tensorDownload(yd, all.data(), all.size() * 4);
+    size_t bad = 0;
+    for (size_t i = 0; i < iters; i++)
+        if (std::memcmp(all.data() + i * m * n, ref[i & 1].data(), m * n * 4) != 0) bad++;
+    EXPECT(bad == 0, "launch order: %zu of %zu back-to-back linears differ from the synchronised result", bad, iters);
+    be.tensorDestroy(xd[0]);
+    be.tensorDestroy(xd[1]);
+    be.tensorDestroy(yd);
+    be.dropWeights();
+}
+
 int main() {
     try {
         tpb::Backend be(0);
@@ -349,6 +391,7 @@ int main() {
         attention(be, 200, 4, 2, 401);
         attention(be, 384, 2, 2, 402);
         dit_block(be, 501);
+        launch_order(be, 601);
 
         // weights under a budget (--vram-budget): 300 x 3072 int8 = 0.92 MB per weight under 2 MB: the
         // third linear evicts the first weight and the results stay right
