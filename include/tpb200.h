@@ -130,6 +130,17 @@ int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, in
                                const int32_t *act_sum, const void *w, int w_bits,
                                const float *w_scale, int64_t m, int64_t n, int64_t k);
 
+/* INT4 weights run on the int8 tensor-core path: unless TPB_W4_FUSED=1 selects the kernel that
+ * unpacks nibbles in shared memory, every int4 GEMM first widens its weight into a scratch
+ * buffer the handle owns.  tpb_convrot_w4_reserve sizes that buffer for weights of up to n x k
+ * elements (cudaMalloc; it may cudaFree a smaller one, which waits for the device).  Call it
+ * once per handle, at set-up, outside any stream capture: the stream-ordered entry points
+ * (tpb_convrot_gemm, tpb_convrot_linear, tpb_convrot_gemm_gated_add, the all-gather forms)
+ * never allocate, and return TPB_ERR_STATE for an int4 weight larger than the reservation.
+ * Replaces the reference's ensureDeviceBuffer growth of its backend scratch
+ * (src/gpu/cuda/backend.zig:2457-2470), made explicit. */
+int tpb_convrot_w4_reserve(tpb_handle_t h, int64_t n, int64_t k);
+
 /* Bytes of the int8 expansion of an [n][k] int4 weight. */
 size_t tpb_convrot_w4_expanded_bytes(int64_t n, int64_t k);
 

@@ -187,6 +187,7 @@ class Backend {
             throw;
         }
         unpinWeight(w_bytes);
+        if (bits == 4) reserveW4(rows, cols_);
         check(tpb_convrot_gemm_gated_add(h_, stream_, static_cast<float *>(x.p), (int64_t)rows,
                                          static_cast<const float *>(mod.p) + gate_off, static_cast<const int8_t *>(i8_x_.p),
                                          static_cast<const float *>(i8_scale_.p),
@@ -281,10 +282,18 @@ class Backend {
             throw;
         }
         unpinWeight(w_host);
+        if (bits == 4) reserveW4(rows, cols_);
         check(tpb_convrot_gemm(h_, stream_, y.p, y_dtype, (int64_t)rows, static_cast<const int8_t *>(i8_x_.p),
                                static_cast<const float *>(i8_scale_.p),
                                bits == 4 ? static_cast<const int32_t *>(i8_sum_.p) : nullptr, w, bits, ws, (int64_t)m_,
                                (int64_t)rows, (int64_t)cols_));
+    }
+    // int4 weights are widened into a scratch the library owns; it is sized here, on the set-up
+    // side, so that the GEMM entry points never allocate (tpb_convrot_w4_reserve)
+    void reserveW4(size_t rows, size_t cols) {
+        if (rows * cols <= w4_reserved_) return;
+        check(tpb_convrot_w4_reserve(h_, (int64_t)rows, (int64_t)cols));
+        w4_reserved_ = rows * cols;
     }
     void ensure(DeviceBuffer &db, size_t bytes) {
         if (db.size >= bytes && db.p) return;
@@ -312,6 +321,7 @@ class Backend {
     DeviceBuffer i8_x_, i8_scale_, i8_sum_, q8_, attn_q_, attn_k_, attn_vt_;
     size_t m_ = 0, cols_ = 0, q8_total_ = 0;
     int bits_ = 0;
+    size_t w4_reserved_ = 0;
     WeightCache<DeviceBuffer> weights_{
         [this](const void *host, size_t bytes) {
             DeviceBuffer db = tensorCreate(bytes);

@@ -66,6 +66,7 @@ class Backend:
         # host-pointer-keyed weight cache (backend.zig:1376-1378)
         self._wcache: Dict[Tuple[int, int], Tuple[torch.Tensor, np.ndarray]] = {}
         self.launches = 0  # kernels launched through this backend (bench accounting)
+        self._w4_reserved = 0  # elements of int4-expansion scratch reserved in the library
 
     # -- plumbing -----------------------------------------------------------------
     def close(self):
@@ -131,6 +132,15 @@ class Backend:
     def dropWeights(self):
         self._wcache.clear()
 
+    def reserveW4(self, n: int, k: int):
+        """Sizes the library's int4-expansion scratch for weights of up to n x k elements
+        (tpb_convrot_w4_reserve: the one place that allocates; the GEMM entries never do).
+        The mirror calls it on first sight of a larger int4 weight, as the reference grows
+        its scratch (backend.zig:2457-2470); a host that captures graphs calls it up front."""
+        if n * k > self._w4_reserved:
+            self._check(self.lib.tpb_convrot_w4_reserve(self.h, n, k))
+            self._w4_reserved = n * k
+
     # -- ConvRot linear ---------------------------------------------------------------
     def _prep(self, x: torch.Tensor, m: int, cols: int, bits: int):
         assert x.is_cuda and x.is_contiguous()
@@ -191,27 +201,61 @@ class Backend:
         self._prep_fused(3, x, None, mod[premul_off:premul_off + dim], mod[shift_off:shift_off + dim], eps,
                          rows, dim, bits)
 
-    def siluMul(self, a: torch.Tensor, b: torch.Tensor, total: int):
-        """a = silu(a) * b in place (backend.zig:3310-3315)."""
+    @staticmethod
+    def _check_f32_out(name: str, t: torch.Tensor, total: int):
+        """The stand-alone elementwise ops write f32: a narrower or shorter tensor behind
+        the output pointer would be overrun on the device, so refuse it here."""
+        if t.dtype != torch.float32:
+            raise TypeError(f"{name}: the output tensor must be float32 (got {t.dtype}); "
+                            "pass a separate f32 output for bf16 inputs")
+        if not t.is_contiguous() or t.numel() < total:
+            raise ValueError(f"{name}: the output tensor must be contiguous and hold {total} elements")
+
+    @staticmethod
+    def _check_in(name: str, t: torch.Tensor, total: int):
+        if t.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError(f"{name}: inputs must be float32 or bfloat16 (got {t.dtype})")
+        if not t.is_contiguous() or t.numel() < total:
+            raise ValueError(f"{name}: input tensors must be contiguous and hold {total} elements")
+
+    def siluMul(self, a: torch.Tensor, b: torch.Tensor, total: int, out: Optional[torch.Tensor] = None):
+        """out = silu(a) * b; in place on ``a`` (backend.zig:3310-3315) unless ``out`` is given.
+        The result is f32, so the in-place form needs f32 inputs."""
+        out = a if out is None else out
+        self._check_f32_out("siluMul", out, total)
+        self._check_in("siluMul", a, total)
+        self._check_in("siluMul", b, total)
+        if a.dtype != b.dtype:
+            raise TypeError("siluMul: both inputs must have the same dtype")
         self._check(self.lib.tpb_silu_mul(self.h, self._stream(), a.data_ptr(), b.data_ptr(), _TORCH_TO_TPB[a.dtype],
-                                          a.data_ptr(), total))
+                                          out.data_ptr(), total))
         self.launches += 1
 
-    def sigmoidMul(self, a: torch.Tensor, b: torch.Tensor, total: int):
-        """a = a * sigmoid(b) in place (backend.zig:3294-3299)."""
+    def sigmoidMul(self, a: torch.Tensor, b: torch.Tensor, total: int, out: Optional[torch.Tensor] = None):
+        """out = a * sigmoid(b); in place on ``a`` (backend.zig:3294-3299) unless ``out`` is given."""
+        out = a if out is None else out
+        self._check_f32_out("sigmoidMul", out, total)
+        self._check_in("sigmoidMul", a, total)
+        self._check_in("sigmoidMul", b, total)
+        if a.dtype != b.dtype:
+            raise TypeError("sigmoidMul: both inputs must have the same dtype")
         self._check(self.lib.tpb_sigmoid_mul(self.h, self._stream(), a.data_ptr(), b.data_ptr(),
-                                             _TORCH_TO_TPB[a.dtype], a.data_ptr(), total))
+                                             _TORCH_TO_TPB[a.dtype], out.data_ptr(), total))
         self.launches += 1
 
     def rmsMod(self, x: torch.Tensor, out: torch.Tensor, mod: torch.Tensor, rows: int, dim: int, premul_off: int,
                shift_off: int, eps: float):
         """out = x * inv_rms(x) * mod[premul_off + c] + mod[shift_off + c] (backend.zig:2738-2760)."""
+        self._check_f32_out("rmsMod", out, rows * dim)
+        self._check_in("rmsMod", x, rows * dim)
         self._check(self.lib.tpb_rms_mod(self.h, self._stream(), x.data_ptr(), _TORCH_TO_TPB[x.dtype], out.data_ptr(),
                                          mod[premul_off:].data_ptr(), mod[shift_off:].data_ptr(), eps, rows, dim))
         self.launches += 1
 
     def gatedAdd(self, a: torch.Tensor, b: torch.Tensor, mod: torch.Tensor, total: int, dim: int, gate_off: int):
-        """a[row][c] += mod[gate_off + c] * b[row][c] (backend.zig:3342-3347)."""
+        """a[row][c] += mod[gate_off + c] * b[row][c] (backend.zig:3342-3347); a is f32."""
+        self._check_f32_out("gatedAdd", a, total)
+        self._check_in("gatedAdd", b, total)
         self._check(self.lib.tpb_gated_add(self.h, self._stream(), a.data_ptr(), b.data_ptr(), _TORCH_TO_TPB[b.dtype],
                                            mod[gate_off:].data_ptr(), total // dim, dim))
         self.launches += 1
@@ -250,6 +294,8 @@ class Backend:
         w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
         ws_dev = self.cachedWeight(weight_scale) if isinstance(weight_scale, np.ndarray) else weight_scale
         ydt = _TORCH_TO_TPB[y.dtype]
+        if w_bits == 4:
+            self.reserveW4(rows, self.i8_cols)
         rc = self.lib.tpb_convrot_gemm(self.h, self._stream(), y.data_ptr(), ydt,
                                        ldy if ldy is not None else rows,
                                        self.i8_x.data_ptr(), self.i8_scale.data_ptr(),
@@ -266,6 +312,8 @@ class Backend:
         assert self.i8_bits == w_bits and x.dtype == torch.float32 and x.is_contiguous()
         w_dev = self.cachedWeight(w_bytes) if isinstance(w_bytes, np.ndarray) else w_bytes
         ws_dev = self.cachedWeight(weight_scale) if isinstance(weight_scale, np.ndarray) else weight_scale
+        if w_bits == 4:
+            self.reserveW4(rows, self.i8_cols)
         rc = self.lib.tpb_convrot_gemm_gated_add(self.h, self._stream(), x.data_ptr(), rows, mod[gate_off:].data_ptr(),
                                                  self.i8_x.data_ptr(), self.i8_scale.data_ptr(),
                                                  self.i8_sum.data_ptr() if w_bits == 4 else None, w_dev.data_ptr(),
@@ -343,6 +391,8 @@ class Backend:
         if self.i8_scale is None or self.i8_scale.numel() < m:
             self.i8_scale = torch.empty(max(m, 1), dtype=torch.float32, device=self.device)
             self.i8_sum = torch.empty(max(m, 1), dtype=torch.int32, device=self.device)
+        if bits == 4:
+            self.reserveW4(n, k)
         rc = self.lib.tpb_convrot_linear(self.h, self._stream(), y.data_ptr(), _TORCH_TO_TPB[y.dtype], n,
                                          x.data_ptr(), _TORCH_TO_TPB[x.dtype], self.i8_x.data_ptr(),
                                          self.i8_scale.data_ptr(), self.i8_sum.data_ptr(), w.data_ptr(), bits,
@@ -353,7 +403,7 @@ class Backend:
         return y
 
     def convrot_linear_host(self, x_host: torch.Tensor, w, w_scale, n: int, bits: int,
-                            y_host: torch.Tensor, chunk_rows: int = 512):
+                            y_host: torch.Tensor, chunk_rows: int = 512, copy_only: bool = False):
         """The same linear with HOST activations and a HOST result (pinned
         tensors) -- the shape of a call from a host-resident orchestrator
         (tensorUpload / op / tensorDownload, src/models/dit_cuda.zig:430-433, :527).
@@ -364,7 +414,10 @@ class Backend:
         prepped and multiplied on the current stream and chunk i-1 downloads on a
         second side stream (PCIe is full duplex).  An INT4 weight is widened once
         per call, not once per chunk.  On return everything is enqueued and the
-        current stream waits for the last download."""
+        current stream waits for the last download.
+
+        ``copy_only`` runs the same uploads and downloads over the same buffers, streams and
+        events with no kernel between them: the floor the host link sets for this call."""
         m, k = x_host.shape
         key = (m, k, n, x_host.dtype, y_host.dtype)
         if getattr(self, "_host_io_key", None) != key:
@@ -376,7 +429,7 @@ class Backend:
             self._s_out = torch.cuda.Stream(device=self.device)
         cur = torch.cuda.current_stream(self.device)
         w8 = w
-        if bits == 4:
+        if bits == 4 and not copy_only:
             if getattr(self, "_host_w8", None) is None or self._host_w8.numel() < n * k:
                 self._host_w8 = torch.empty(n * k, dtype=torch.int8, device=self.device)
             self._check(self.lib.tpb_convrot_w4_expand(self.h, self._stream(), w.data_ptr(), n, k,
@@ -395,12 +448,13 @@ class Backend:
         ydt = _TORCH_TO_TPB[y_host.dtype]
         for (r0, r1), ev in zip(bounds, uploaded):
             cur.wait_event(ev)
-            self._prep(self._host_x[r0:r1], r1 - r0, k, bits)
-            rc = self.lib.tpb_convrot_gemm(self.h, self._stream(), self._host_y[r0:r1].data_ptr(), ydt, n,
-                                           self.i8_x.data_ptr(), self.i8_scale.data_ptr(), None,
-                                           w8.data_ptr(), 8, _ptr(w_scale), r1 - r0, n, k)
-            self._check(rc)
-            self.launches += 1
+            if not copy_only:
+                self._prep(self._host_x[r0:r1], r1 - r0, k, bits)
+                rc = self.lib.tpb_convrot_gemm(self.h, self._stream(), self._host_y[r0:r1].data_ptr(), ydt, n,
+                                               self.i8_x.data_ptr(), self.i8_scale.data_ptr(), None,
+                                               w8.data_ptr(), 8, _ptr(w_scale), r1 - r0, n, k)
+                self._check(rc)
+                self.launches += 1
             done = torch.cuda.Event()
             done.record(cur)
             self._s_out.wait_event(done)

@@ -43,7 +43,7 @@ int tpb_create(tpb_handle_t *out, int device_ordinal) {
         cudaGetLastError();
         return TPB_ERR_NO_DEVICE;
     }
-    if (device_ordinal < 0 || device_ordinal >= n_dev) return TPB_ERR_INVALID_ARG;
+    if (device_ordinal < 0 || device_ordinal >= n_dev || device_ordinal >= TPB_MAX_DEVICES) return TPB_ERR_INVALID_ARG;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return TPB_ERR_CUDA;
     // The kernels are built for sm_100a only: refuse anything else instead of
@@ -121,6 +121,22 @@ int tpb_convrot_prep(tpb_handle_t h, tpb_stream_t stream, const void *x, int x_d
     TPB_CHECK_ARG(h, tpb_aligned16(x) && tpb_aligned16(q), "prep: x and q must be 16-byte aligned");
     if (m == 0) return TPB_OK;
     return tpb_launch_prep(h, (cudaStream_t)stream, x, x_dtype, m, k, bits, q, act_scale, act_sum);
+}
+
+int tpb_convrot_w4_reserve(tpb_handle_t h, int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, n > 0 && k > 0 && n < (1ll << 31) && k < (1ll << 31), "w4_reserve: bad shape");
+    const size_t need = (size_t)n * (size_t)k;
+    if (h->w4_scratch_bytes >= need) return TPB_OK;
+    tpb_device_guard guard(h->device);
+    TPB_CUDA(h, guard.err);
+    // cudaFree waits for the work that may still read the old buffer
+    if (h->w4_scratch) TPB_CUDA(h, cudaFree(h->w4_scratch));
+    h->w4_scratch = nullptr;
+    h->w4_scratch_bytes = 0;
+    TPB_CUDA(h, cudaMalloc(&h->w4_scratch, need));
+    h->w4_scratch_bytes = need;
+    return TPB_OK;
 }
 
 size_t tpb_convrot_w4_expanded_bytes(int64_t n, int64_t k) {
@@ -222,7 +238,8 @@ int tpb_q8_0_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, float *y, const void 
                       int n_total) {
     if (!h) return TPB_ERR_INVALID_ARG;
     TPB_CHECK_ARG(h, y && w && xq, "q8_0_gemv_q8n: null pointer");
-    TPB_CHECK_ARG(h, rows >= 0 && cols > 0 && cols % 32 == 0, "q8_0_gemv_q8n: cols must be a multiple of 32");
+    TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 26) && cols > 0 && cols % 32 == 0 && cols < (1ll << 24),
+                  "q8_0_gemv_q8n: cols must be a multiple of 32 (below 2^24) and rows below 2^26");
     TPB_CHECK_ARG(h, ng >= 1 && ng <= 8 && row_off >= 0 && row_off + ng <= n_total,
                   "q8_0_gemv_q8n: need 1 <= ng <= 8 and row_off + ng <= n_total");
     TPB_CHECK_ARG(h, tpb_aligned16(w) && tpb_aligned16(xq), "q8_0_gemv_q8n: w and xq must be 16-byte aligned");
@@ -235,7 +252,8 @@ int tpb_q8_0_gemv_f32(tpb_handle_t h, tpb_stream_t stream, float *y, const float
                       float scale, int64_t rows, int64_t cols) {
     if (!h) return TPB_ERR_INVALID_ARG;
     TPB_CHECK_ARG(h, y && x && w, "q8_0_gemv_f32: null pointer");
-    TPB_CHECK_ARG(h, rows >= 0 && cols > 0 && cols % 32 == 0, "q8_0_gemv_f32: cols must be a multiple of 32");
+    TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 31) && cols > 0 && cols % 32 == 0,
+                  "q8_0_gemv_f32: cols must be a multiple of 32 and rows below 2^31");
     TPB_CHECK_ARG(h, tpb_aligned16(w) && tpb_aligned16(x), "q8_0_gemv_f32: w and x must be 16-byte aligned");
     if (rows == 0) return TPB_OK;
     return tpb_launch_q8_0_gemv_f32(h, (cudaStream_t)stream, y, x, w, scale, rows, cols);

@@ -639,11 +639,8 @@ int tpb_attention(tpb_handle_t h, tpb_stream_t stream, void *out, int out_dtype,
     p.kv_heads = kv_heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = h->d_status;
-    static bool attr_set[64] = {false};
-    if (!attr_set[h->device & 63]) {
-        TPB_CUDA(h, cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        attr_set[h->device & 63] = true;
-    }
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, flash_attn_kernel, kAttnSmem, smem_set));
     const dim3 grid((unsigned)((seq_q + 2 * kTile - 1) / (2 * kTile)), (unsigned)heads);
     TPB_CUDA(h, tpb_launch_pdl(flash_attn_kernel, grid, dim3(kAttnThreads), (size_t)kAttnSmem, (cudaStream_t)stream, mq, mk, mv, p));
     return TPB_OK;

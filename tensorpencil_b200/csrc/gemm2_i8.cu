@@ -215,11 +215,8 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
     auto kern = convrot_gemm2_kernel<OUT, PEERS>;
-    static bool attr_set[64] = {false};
-    if (!attr_set[h->device & 63]) {
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
-        attr_set[h->device & 63] = true;
-    }
+    static tpb_per_device_once smem_set;   // per instantiation
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;

@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdint>
+#include <cstring>
 
 #include "tpb_internal.h"
 
@@ -409,43 +410,72 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Looks the map up in the handle's cache, or encodes it and remembers it.  `key` names everything
+// the encoding depends on.
+template <typename Encode>
+inline int tpb_tensor_map_cached(tpb_handle_t h, CUtensorMap *map, const uint64_t (&key)[5], Encode encode) {
+    static_assert(sizeof(CUtensorMap) <= sizeof(tpb_map_slot::map), "tensor map larger than a cache slot");
+    uint64_t hsh = 0x9E3779B97F4A7C15ull;
+    for (int i = 0; i < 5; i++) hsh = (hsh ^ key[i]) * 0xFF51AFD7ED558CCDull, hsh ^= hsh >> 29;
+    tpb_map_slot &slot = h->map_cache[hsh % TPB_MAP_CACHE_SLOTS];
+    if (slot.valid && slot.key[0] == key[0] && slot.key[1] == key[1] && slot.key[2] == key[2] &&
+        slot.key[3] == key[3] && slot.key[4] == key[4]) {
+        memcpy(map, slot.map, sizeof(CUtensorMap));
+        return TPB_OK;
+    }
+    const int rc = encode(map);
+    if (rc != TPB_OK) return rc;
+    for (int i = 0; i < 5; i++) slot.key[i] = key[i];
+    memcpy(slot.map, map, sizeof(CUtensorMap));
+    slot.valid = true;
+    return TPB_OK;
+}
+
 // 2-D uint8 tensor [rows][k] (k contiguous), box = 128 bytes x box_rows, 128B swizzle,
 // out-of-range rows read as zero.
 inline int make_kmajor_map(tpb_handle_t h, CUtensorMap *map, const void *base, int64_t rows, int64_t k,
                     int box_rows) {
-    const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)k};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t estride[2] = {1, 1};
-    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
-        map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estride,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld", (int)r,
-                        (long long)rows, (long long)k);
-    return TPB_OK;
+    const uint64_t key[5] = {(uint64_t)reinterpret_cast<uintptr_t>(base), (uint64_t)rows, (uint64_t)k,
+                             (uint64_t)box_rows, 0x100u};
+    return tpb_tensor_map_cached(h, map, key, [&](CUtensorMap *out) {
+        const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)k};
+        const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+        const cuuint32_t estride[2] = {1, 1};
+        const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+            out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld k=%lld", (int)r,
+                            (long long)rows, (long long)k);
+        return (int)TPB_OK;
+    });
 }
 
 // Output tensor [m][ldy] (row-major), box = 128 bytes x 32 rows, 128B swizzle: the
 // epilogue's staging layout.
 template <int OUT>
 inline int make_out_map(tpb_handle_t h, CUtensorMap *map, const GemmParams &p) {
-    const int esz = OUT == OUT_BF16 ? 2 : 4;
-    const CUtensorMapDataType dt = OUT == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                   : OUT == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                    : CU_TENSOR_MAP_DATA_TYPE_INT32;
-    const cuuint64_t gdim[2] = {(cuuint64_t)p.n, (cuuint64_t)p.m};
-    const cuuint64_t gstride[1] = {(cuuint64_t)p.ldy * esz};
-    const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
-    const cuuint32_t estride[2] = {1, 1};
-    const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
-        map, dt, 2, p.y, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) m=%d n=%d ldy=%lld", (int)r,
-                        p.m, p.n, p.ldy);
-    return TPB_OK;
+    const uint64_t key[5] = {(uint64_t)reinterpret_cast<uintptr_t>(p.y), (uint64_t)p.m, (uint64_t)p.n,
+                             (uint64_t)p.ldy, 0x200u + (uint64_t)OUT};
+    return tpb_tensor_map_cached(h, map, key, [&](CUtensorMap *out) {
+        const int esz = OUT == OUT_BF16 ? 2 : 4;
+        const CUtensorMapDataType dt = OUT == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : OUT == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                        : CU_TENSOR_MAP_DATA_TYPE_INT32;
+        const cuuint64_t gdim[2] = {(cuuint64_t)p.n, (cuuint64_t)p.m};
+        const cuuint64_t gstride[1] = {(cuuint64_t)p.ldy * esz};
+        const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+        const cuuint32_t estride[2] = {1, 1};
+        const CUresult r = reinterpret_cast<EncodeTiledFn>(h->encode_tiled)(
+            out, dt, 2, p.y, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return tpb_fail(h, TPB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) m=%d n=%d ldy=%lld", (int)r,
+                            p.m, p.n, p.ldy);
+        return (int)TPB_OK;
+    });
 }
 
 }  // namespace tpb_gemm

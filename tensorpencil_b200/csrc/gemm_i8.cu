@@ -217,11 +217,8 @@ int launch_cfg_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
     auto kern = convrot_gemm_kernel<BN, OUT, PEERS>;
-    static bool attr_set[64] = {false};  // per instantiation and device
-    if (!attr_set[h->device & 63]) {
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[h->device & 63] = true;
-    }
+    static tpb_per_device_once smem_set;   // per instantiation
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, Cfg::kSmemBytes, smem_set));
     const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
     const int tiles = m_tiles * n_tiles;
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
@@ -253,14 +250,11 @@ int launch_out(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_
 
 int tpb_w4_scratch(tpb_handle_t h, int64_t n, int64_t k, int8_t **out) {
     const size_t need = (size_t)n * (size_t)k;
-    if (h->w4_scratch_bytes < need) {
-        // cudaFree waits for the work that may still read the old buffer
-        if (h->w4_scratch) TPB_CUDA(h, cudaFree(h->w4_scratch));
-        h->w4_scratch = nullptr;
-        h->w4_scratch_bytes = 0;
-        TPB_CUDA(h, cudaMalloc(&h->w4_scratch, need));
-        h->w4_scratch_bytes = need;
-    }
+    if (h->w4_scratch_bytes < need)
+        return tpb_fail(h, TPB_ERR_STATE,
+                        "int4 weight of %lld x %lld needs %zu bytes of expansion scratch, %zu reserved: call "
+                        "tpb_convrot_w4_reserve(h, n, k) once, outside the stream-ordered path",
+                        (long long)n, (long long)k, need, h->w4_scratch_bytes);
     *out = h->w4_scratch;
     return TPB_OK;
 }

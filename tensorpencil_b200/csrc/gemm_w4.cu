@@ -312,11 +312,8 @@ int launch_w4(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
     auto kern = convrot_gemm_w4_kernel<OUT>;
-    static bool attr_set[64] = {false};
-    if (!attr_set[h->device & 63]) {
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemW4));
-        attr_set[h->device & 63] = true;
-    }
+    static tpb_per_device_once smem_set;   // per instantiation
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmemW4, smem_set));
     const int tiles = ((p.m + BM - 1) / BM) * ((p.n + 255) / 256);
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(kThreadsW4), kSmemW4, st, ma, mb, my, p));

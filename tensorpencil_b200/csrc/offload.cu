@@ -92,7 +92,9 @@ int tpb_stream_open(tpb_handle_t h, size_t budget_bytes, size_t slot_bytes, int 
     if (!s) return tpb_fail(h, TPB_ERR_OOM, "stream_open: host allocation failed");
     s->h = h;
     s->slot_bytes = slot_bytes;
-    cudaError_t e = cudaStreamCreateWithFlags(&s->xfer, cudaStreamNonBlocking);
+    tpb_device_guard guard(h->device);   // the stream, the slots and the events belong to the handle's device
+    cudaError_t e = guard.err;
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->xfer, cudaStreamNonBlocking);
     s->slots.resize(n_slots);
     for (int i = 0; i < n_slots && e == cudaSuccess; i++) {
         Slot &c = s->slots[i];

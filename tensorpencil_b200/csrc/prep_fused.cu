@@ -18,8 +18,7 @@ using namespace tpb_prep;
 namespace {
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(256) gate_mul_kernel(const T *__restrict__ a, const T *__restrict__ b,
-                                                        float *__restrict__ out, size_t n4) {
+__global__ void __launch_bounds__(256) gate_mul_kernel(const T *a, const T *b, float *out, size_t n4) {
     tpb_grid_dep_launch();
     tpb_grid_dep_wait();
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n4; c += (size_t)gridDim.x * blockDim.x) {
@@ -43,8 +42,8 @@ __global__ void __launch_bounds__(256) gate_mul_kernel(const T *__restrict__ a, 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) gated_add_kernel(float *__restrict__ x, const T *__restrict__ delta,
-                                                         const float *__restrict__ gate, size_t n4, int dim4) {
+__global__ void __launch_bounds__(256) gated_add_kernel(float *x, const T *delta, const float *gate, size_t n4,
+                                                         int dim4) {
     tpb_grid_dep_launch();
     tpb_grid_dep_wait();
     for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n4; c += (size_t)gridDim.x * blockDim.x) {

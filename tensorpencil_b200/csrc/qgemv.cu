@@ -197,13 +197,15 @@ q8_0_gemv_q8n_kernel(const GemvParams p, const int stages) {
                 }
 #pragma unroll
                 for (int r = 0; r < kRows; r++) {
-                    int s0 = 0, s1 = 0;
+                    // the sums start at the bit pattern of 1.5 * 2^23, so that they ARE their own float
+                    // conversion plus that constant (|sum| <= 32 * 127 * 128 < 2^22): see i2f_small
+                    int s0 = kI2FMagicBits, s1 = kI2FMagicBits;
 #pragma unroll
                     for (int j = 0; j < 8; j++) s0 = __dp4a((int)wq[r][j], (int)xq[j], s0);
 #pragma unroll
                     for (int j = 0; j < 8; j++) s1 = __dp4a((int)wq[r][8 + j], (int)xq[8 + j], s1);
-                    acc[r][m] = fmaf(__int2float_rn(s0), wd[r][0] * xd0, acc[r][m]);
-                    acc[r][m] = fmaf(__int2float_rn(s1), wd[r][1] * xd1, acc[r][m]);
+                    acc[r][m] = fmaf(__int_as_float(s0) - kI2FMagic, wd[r][0] * xd0, acc[r][m]);
+                    acc[r][m] = fmaf(__int_as_float(s1) - kI2FMagic, wd[r][1] * xd1, acc[r][m]);
                 }
             }
         }
@@ -249,7 +251,7 @@ q8_0_gemv_q8n_simple_kernel(const GemvParams p) {
             int s = 0;
 #pragma unroll
             for (int j = 0; j < 8; j++) s = __dp4a((int)wq[j], xq[j], s);
-            acc[m] = fmaf(__int2float_rn(s), dw * p.xd[(size_t)m * p.nblk + b], acc[m]);
+            acc[m] = fmaf(i2f_small(s), dw * p.xd[(size_t)m * p.nblk + b], acc[m]);
         }
     }
 #pragma unroll
@@ -378,13 +380,16 @@ int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max
     int grid = (int)(((long long)p.rows + (long long)warps * R - 1) / ((long long)warps * R));
     if (grid < 1) grid = 1;
     if (grid > h->sm_count) grid = h->sm_count;
+    // the dynamic size varies per call: each instantiation opts in to the device maximum, once
     if (act_smem) {
         auto kern = q8_0_gemv_q8n_kernel<M, R, true>;
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static tpb_per_device_once smem_set;
+        TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
         TPB_CUDA(h, launch_pdl(kern, grid, warps * 32, smem, st, p, stages));
     } else {
         auto kern = q8_0_gemv_q8n_kernel<M, R, false>;
-        TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static tpb_per_device_once smem_set;
+        TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
         TPB_CUDA(h, launch_pdl(kern, grid, warps * 32, smem, st, p, stages));
     }
     return TPB_OK;
@@ -395,7 +400,7 @@ int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
     const size_t row_bytes = (size_t)p.nblk * kBlockBytes;
     if (row_bytes % 16 != 0) {
         const int block = 256;
-        const int grid = (p.rows * 32 + block - 1) / block;
+        const int grid = (int)(((long long)p.rows * 32 + block - 1) / block);   // rows < 2^26 (checked at the entry)
         q8_0_gemv_q8n_simple_kernel<M><<<grid, block, 0, st>>>(p);
         TPB_CUDA(h, cudaGetLastError());
         return TPB_OK;
@@ -457,7 +462,8 @@ int tpb_launch_q8_0_gemv_f32(tpb_handle_t h, cudaStream_t st, float *y, const fl
     const size_t smem = (size_t)cols * 4;
     if (smem > (size_t)h->smem_optin)
         return tpb_fail(h, TPB_ERR_INVALID_ARG, "q8_0_gemv_f32: cols too large for shared memory");
-    TPB_CUDA(h, cudaFuncSetAttribute(q8_0_gemv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, q8_0_gemv_f32_kernel, h->smem_optin, smem_set));
     int grid = (int)((rows + 7) / 8);
     if (grid > h->sm_count * 4) grid = h->sm_count * 4;
     q8_0_gemv_f32_kernel<<<grid, 256, smem, st>>>(y, x, reinterpret_cast<const uint8_t *>(w), scale,
@@ -482,23 +488,23 @@ namespace {
 // Device address of the array per device ordinal.  The array's name in host code
 // is only a handle for the runtime, not a device pointer: the address has to be
 // asked for, with the owning device current.
-void *g_static_q8_ptr[64] = {nullptr};
+// Handles on different devices, or on different host threads, may get here at the same time:
+// the table is atomic, and two racing look-ups store the same address.  tpb_create admits
+// ordinals below TPB_MAX_DEVICES only, so the index never aliases.
+std::atomic<void *> g_static_q8_ptr[TPB_MAX_DEVICES];
 
 int static_scratch_setup(tpb_handle_t h, void **out) {
-    const int dev = h->device & 63;
-    if (g_static_q8_ptr[dev] == nullptr) {
-        int prev = 0;
-        TPB_CUDA(h, cudaGetDevice(&prev));
-        TPB_CUDA(h, cudaSetDevice(h->device));
-        void *ptr = nullptr;
+    void *ptr = g_static_q8_ptr[h->device].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        tpb_device_guard guard(h->device);
+        TPB_CUDA(h, guard.err);
         const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_q8_scratch);
-        cudaSetDevice(prev);
         if (e != cudaSuccess || ptr == nullptr)
             return tpb_fail(h, TPB_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s",
                             cudaGetErrorString(e));
-        g_static_q8_ptr[dev] = ptr;
+        g_static_q8_ptr[h->device].store(ptr, std::memory_order_release);
     }
-    *out = g_static_q8_ptr[dev];
+    *out = ptr;
     return TPB_OK;
 }
 }  // namespace
@@ -508,7 +514,8 @@ extern "C" int tpb_q8_0_gemv_static(tpb_handle_t h, tpb_stream_t stream, float *
     if (!h) return TPB_ERR_INVALID_ARG;
     TPB_CHECK_ARG(h, y && x && w, "q8_0_gemv_static: null pointer");
     TPB_CHECK_ARG(h, m >= 1 && m <= 8, "q8_0_gemv_static: m must be 1..8 (got %d)", m);
-    TPB_CHECK_ARG(h, rows >= 0 && cols > 0 && cols % 32 == 0, "q8_0_gemv_static: cols must be a multiple of 32");
+    TPB_CHECK_ARG(h, rows >= 0 && rows < (1ll << 26) && cols > 0 && cols % 32 == 0,
+                  "q8_0_gemv_static: cols must be a multiple of 32 and rows below 2^26");
     TPB_CHECK_ARG(h, (int64_t)m * cols <= (int64_t)TPB_STATIC_GEMV_MAX_ELEMS,
                   "q8_0_gemv_static: m * cols = %lld exceeds the fixed scratch of %d elements",
                   (long long)((int64_t)m * cols), TPB_STATIC_GEMV_MAX_ELEMS);

@@ -35,6 +35,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
         }
     }
 }
+// Exact int -> float for |v| < 2^22 on the ALU/FMA pipes: 0x4B400000 is 1.5 * 2^23 as a float, where
+// one unit in the last place is 1, so adding v to the bit pattern adds v to the value.  The
+// cvt instruction gives the same bits but issues at a quarter of the rate, which made it the
+// limiter of the GEMVs with several activation rows (one conversion per block, row and column).
+constexpr int kI2FMagicBits = 0x4B400000;
+constexpr float kI2FMagic = 12582912.0f;
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(v + kI2FMagicBits) - kI2FMagic; }
+
 // Untiled bulk copy global -> shared; both addresses and the size are multiples of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile(

@@ -319,9 +319,9 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                     for (int w = 0; w < 8; w++)
                         i1 = FMT == FMT_IQ4_NL ? __dp4a((int)hi[r][w], (int)xq[8 + w], i1) : dp4a_us(hi[r][w], xq[8 + w], i1);
                     float tacc = acc[r][m];
-                    tacc = fmaf(ws0[r], d2.x * __int2float_rn(i0), tacc);
+                    tacc = fmaf(ws0[r], d2.x * i2f_small(i0), tacc);
                     tacc = fmaf(-wo0[r], s2.x, tacc);
-                    tacc = fmaf(ws1[r], d2.y * __int2float_rn(i1), tacc);
+                    tacc = fmaf(ws1[r], d2.y * i2f_small(i1), tacc);
                     tacc = fmaf(-wo1[r], s2.y, tacc);
                     acc[r][m] = tacc;
                 }
@@ -519,7 +519,7 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                     for (int r = 0; r < R; r++) {
                         int sq = dp4a_us(qv[r][pp][0], (uint32_t)xv.x, 0);
                         sq = dp4a_us(qv[r][pp][1], (uint32_t)xv.y, sq);
-                        acc[r][m] = fmaf(wsc[r][pp], dx * __int2float_rn(sq - 32 * sx), acc[r][m]);
+                        acc[r][m] = fmaf(wsc[r][pp], dx * i2f_small(sq - 32 * sx), acc[r][m]);
                     }
                 }
             }
@@ -573,7 +573,8 @@ int launch_q6k_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     if (grid < 1) grid = 1;
     if (grid > h->sm_count) grid = h->sm_count;
     auto kern = q6k_gemv_q8n_kernel<M, R>;
-    TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static tpb_per_device_once smem_set;   // the size varies per call: opt in to the device maximum, once
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, st, p, stages));
     return TPB_OK;
 }
@@ -626,7 +627,8 @@ int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     if (grid < 1) grid = 1;
     if (grid > h->sm_count) grid = h->sm_count;
     auto kern = kquant_gemv_q8n_kernel<FMT, M, R>;
-    TPB_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static tpb_per_device_once smem_set;   // the size varies per call: opt in to the device maximum, once
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, st, p, stages));
     return TPB_OK;
 }

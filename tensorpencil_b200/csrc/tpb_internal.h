@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdlib>
@@ -12,9 +13,21 @@
 
 #include "tpb200.h"
 
-#define TPB_VERSION 100
+#define TPB_VERSION 101
+#define TPB_MAX_DEVICES 64   // per-device tables below are indexed by the device ordinal; tpb_create refuses more
+
+// One slot of the per-handle tensor-map cache (see tpb_tensor_map_cached in gemm_common.cuh): a
+// tensor map depends only on (base, dims, stride, box, type), and a model calls the same linears with
+// the same buffers step after step, so the driver's encode call is made once per distinct operand.
+struct tpb_map_slot {
+    uint64_t key[5] = {0, 0, 0, 0, 0};
+    bool valid = false;
+    alignas(64) unsigned char map[128];
+};
+constexpr int TPB_MAP_CACHE_SLOTS = 128;
 
 struct tpb_handle_s {
+    tpb_map_slot map_cache[TPB_MAP_CACHE_SLOTS];
     int device = 0;
     int sm_count = 0;
     int smem_optin = 0;
@@ -22,9 +35,9 @@ struct tpb_handle_s {
     // cuTensorMapEncodeTiled, resolved through the runtime so the library has no
     // link-time dependency on libcuda (it must load on a host without a driver).
     void *encode_tiled = nullptr;
-    // int8 expansion of the int4 weight of the call in flight (grown on demand, freed with the
-    // handle).  Calls on one handle are ordered by the caller's stream, so one buffer is enough;
-    // two handles never share it.
+    // int8 expansion of the int4 weight of the call in flight (sized by tpb_convrot_w4_reserve, freed
+    // with the handle).  Calls on one handle are ordered by the caller's stream, so one buffer is
+    // enough; two handles never share it.
     int8_t *w4_scratch = nullptr;
     size_t w4_scratch_bytes = 0;
     // switches read from the environment once, at tpb_create
@@ -55,7 +68,10 @@ int tpb_fail(tpb_handle_t h, int code, const char *fmt, ...);
 // (activations, scales, modulation vectors, residuals) is loaded with __ldcg, never __ldg: a load
 // through the read-only path counts as invariant for the compiler, which may move it above
 // griddepcontrol.wait, where it reads what the previous kernel has not written yet.  __ldg is for
-// weights and tables that no kernel writes.
+// weights and tables that no kernel writes.  For the same reason a kernel parameter that may alias
+// another (the in-place elementwise ops: out == first input) or that another kernel of the stream
+// writes is never declared `const __restrict__`: that qualifier lets the compiler pick the
+// read-only path by itself.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t tpb_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                          cudaStream_t st, Args... args) {
@@ -78,6 +94,40 @@ __device__ __forceinline__ void tpb_grid_dep_wait() { asm volatile("griddepcontr
 __device__ __forceinline__ void tpb_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 
+// Makes `device` current for the lifetime of the object (allocations and symbol look-ups go to the
+// current device, which need not be the handle's when a host drives several handles).
+struct tpb_device_guard {
+    int prev = -1;
+    bool switched = false;
+    cudaError_t err = cudaSuccess;
+    explicit tpb_device_guard(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) {
+            err = cudaSetDevice(device);
+            switched = err == cudaSuccess;
+        }
+    }
+    ~tpb_device_guard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+// "Done once per device" flags for settings that belong to a kernel, not to a handle
+// (cudaFuncSetAttribute).  Racing threads at worst both apply the same setting.
+struct tpb_per_device_once {
+    std::atomic<unsigned char> done[TPB_MAX_DEVICES];
+    bool test(int device) const { return done[device & (TPB_MAX_DEVICES - 1)].load(std::memory_order_acquire) != 0; }
+    void set(int device) { done[device & (TPB_MAX_DEVICES - 1)].store(1, std::memory_order_release); }
+};
+// Opts `kern` in to `bytes` of dynamic shared memory, once per device.
+template <typename Kern>
+static inline cudaError_t tpb_set_max_smem_once(tpb_handle_t h, Kern kern, int bytes, tpb_per_device_once &once) {
+    if (once.test(h->device)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) once.set(h->device);
+    return e;
+}
+
 static inline bool tpb_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Kernel launchers (one per .cu file).  All return a tpb_status.
@@ -90,7 +140,8 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
                     const void *w, int w_bits, const float *w_scale, int64_t m, int64_t n,
                     int64_t k, void *const *peer_y = nullptr, int n_peers = 0, void *mc_y = nullptr,
                     const float *gate = nullptr);
-// The int8 expansion scratch of an [n][k] int4 weight on the handle's device (grown on demand).
+// The int8 expansion scratch of an [n][k] int4 weight (tpb_convrot_w4_reserve sized it; TPB_ERR_STATE
+// when it is too small: no compute entry allocates).
 int tpb_w4_scratch(tpb_handle_t h, int64_t n, int64_t k, int8_t **out);
 int tpb_launch_peer_barrier(tpb_handle_t h, cudaStream_t st, uint32_t *const *flags, int world,
                             int rank, uint32_t epoch, int timeout_ms);

@@ -1,14 +1,17 @@
 """Drivers that replay the reference's call sequences over the quantized-linear
-ops: one DiT step's linears (resident or weight-streamed), the N-split GEMM with
-all-gather, and the decode GEMV.  Used by ``bench.py --mode ...`` and the tests.
+ops: one DiT step's block stack (resident or weight-streamed, one latent or a batch
+of independent latents), and helpers for the decode GEMV benchmark.  Used by
+``bench.py`` and the tests.
 
 The DiT driver follows ``dit_cuda.forward`` (src/models/dit_cuda.zig:464-517): per
-block one prep feeds wq/wk/wv/gate, one prep feeds wo, and the MLP runs in
-2048-row tiles (``mlp_tile``, :36-39): prep -> gate, up -> (SiLU * up) -> prep ->
-down.  Only the linears go through this library; attention, norms, RoPE and the
-gated adds belong to the reference's non-quantised ops and are stood in for by
-the cheapest torch expression that keeps shapes and data flow (the step time
-reported is therefore a linears-only figure).
+block one prep feeds wq/wk/wv/gate, one prep feeds wo, and the MLP runs in row
+tiles (``mlp_tile``, :36-39): prep -> gate, up -> (SiLU * up) -> prep -> down.
+Everything between the linears runs through this library too: RMS norm +
+modulation, the sigmoid and SiLU gates and the gated residuals as the reference's
+stand-alone ops (mode "unfused") or folded into the prep kernels and GEMM
+epilogues (mode "fused"); qk-norm, RoPE and softmax attention when ``attn`` is
+given.  Without ``attn`` the value projection stands in for the attention output,
+which leaves every row independent (what the full-size parity tests rely on).
 """
 from __future__ import annotations
 
@@ -94,10 +97,10 @@ def dit_modulation(be, blocks: int, hidden: int, seed: int = 7) -> torch.Tensor:
 
 
 def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
-                     mlp_tile: int = MLP_TILE, glue: bool = True, mode: Optional[str] = None,
+                     mlp_tile: int = MLP_TILE, mode: str = "linears",
                      mod: Optional[torch.Tensor] = None, eps: float = 1e-5,
-                     attn: Optional[dict] = None) -> torch.Tensor:
-    """One step of the block stack on latents x [tokens][hidden] (f32, updated in place).
+                     attn: Optional[dict] = None, latents: int = 1) -> torch.Tensor:
+    """One step of the block stack on x [latents * tokens][hidden] (f32, updated in place).
 
     mode:
       "linears"  prep + GEMM only; the linears read whatever their input buffers hold
@@ -107,27 +110,35 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                  gatedAdd -- every elementwise op its own kernel (f32 only);
       "fused"    the same data flow with rmsMod / sigmoidMul / siluMul folded into the
                  prep kernels and gatedAdd folded into the wo / mlp.down GEMM epilogues;
-                 with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs stay bf16;
-      "torch"    legacy: linears through the library, cheap torch stand-ins between them.
-    attn: None -> v stands in for the attention output (the linears and their glue alone);
-    a dict {q_norm, k_norm, cos, sin, heads} -> qk-norm + RoPE + softmax attention run
-    between the projections and the sigmoid gate (dit_cuda.zig:479-489), modes "unfused"
-    and "fused".  ``glue`` is the old switch: True -> "torch", False -> "linears".
+                 with out_dtype=bf16 the q/k/v/gate and MLP gate/up outputs stay bf16.
+    attn: None -> v stands in for the attention output (the linears and their elementwise
+    neighbours alone); a dict {q_norm, k_norm, cos, sin, heads} -> qk-norm + RoPE + softmax
+    attention run between the projections and the sigmoid gate (dit_cuda.zig:479-489),
+    modes "unfused" and "fused".
+
+    latents: x stacks this many independent latents of equal token count along the rows.
+    Every op but attention is row-wise, so a block's linears run ONCE over all rows -- with
+    streamed weights each block's image crosses PCIe once per step for the whole batch
+    (the block is acquired, used by every latent, then released); attention runs per latent.
 
     mlp_tile: rows per MLP tile.  The reference tiles by 2048 rows to fit a 24 GB card;
-    with 180 GB of HBM the whole 4608-token batch can go through at once."""
-    if mode is None:
-        mode = "torch" if glue else "linears"
+    with 180 GB of HBM the whole batch can go through at once."""
     bits, hid, mlp = w.bits, w.hidden, w.mlp
     prep = be.opI8Prep if bits == 8 else be.opI4Prep
     gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
            (lambda y, wt, n: be.opI4Gemm(y, wt[0], wt[1], n))
     m = x.shape[0]
     dev = be.device
+    if mode not in ("linears", "unfused", "fused"):
+        raise ValueError(f"unknown mode {mode!r}")
     if mode == "unfused" and out_dtype != torch.float32:
         raise ValueError("the unfused sequence is f32 only")
     if mode in ("unfused", "fused") and mod is None:
         raise ValueError("mode needs the modulation vectors (dit_modulation)")
+    if latents < 1 or m % latents:
+        raise ValueError("x must stack `latents` latents of equal token count")
+    tokens = m // latents
+    mlp_tile = min(mlp_tile, m)
     q = torch.empty((m, hid), dtype=out_dtype, device=dev)
     k = torch.empty_like(q)
     v = torch.empty_like(q)
@@ -136,7 +147,7 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
     t1 = torch.empty((m, hid), dtype=torch.float32, device=dev) if mode == "unfused" else None
     tile_gate = torch.empty((mlp_tile, mlp), dtype=out_dtype, device=dev)
     tile_up = torch.empty_like(tile_gate)
-    tile_down = torch.empty((mlp_tile, hid), dtype=out_dtype, device=dev)
+    tile_down = torch.empty((mlp_tile, hid), dtype=out_dtype, device=dev) if mode != "fused" else None
     attn_buf = torch.zeros((m, hid), dtype=torch.float32, device=dev) if mode == "linears" else None
     act_buf = torch.zeros((mlp_tile, mlp), dtype=torch.float32, device=dev) if mode == "linears" else None
     st = w.streamer
@@ -164,17 +175,17 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
         gemm(v, wb["wv"], hid)
         gemm(g, wb["gate"], hid)
         a = v                                              # without attn: v stands in for its output
-        if attn is not None and mode in ("fused", "unfused"):
-            a = be.attention(q, k, v, attn["q_norm"], attn["k_norm"], attn["cos"], attn["sin"],
-                             attn["heads"], attn["heads"], out_dtype=out_dtype, out=o)
+        if attn is not None and mode != "linears":
+            for l in range(latents):
+                r = slice(l * tokens, (l + 1) * tokens)
+                be.attention(q[r], k[r], v[r], attn["q_norm"], attn["k_norm"], attn["cos"], attn["sin"],
+                             attn["heads"], attn["heads"], out_dtype=out_dtype, out=o[r])
+            a = o
         if mode == "fused":
             be.prepSigmoidMul(a, g, m, hid, bits)
         elif mode == "unfused":
             be.sigmoidMul(a, g, m * hid)
             prep(a, m, hid)
-        elif mode == "torch":
-            attn = (v * torch.sigmoid(g)).float() if out_dtype != torch.float32 else v * torch.sigmoid(g)
-            prep(attn, m, hid)
         else:
             prep(attn_buf, m, hid)
         if mode == "fused":
@@ -183,8 +194,6 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
             gemm(o, wb["wo"], hid)
         if mode == "unfused":
             be.gatedAdd(x, o, mod, m * hid, hid, mb + 2 * hid)
-        elif mode == "torch":
-            x = x + o.float() if out_dtype != torch.float32 else x + o
         # --- MLP in row tiles (dit_cuda.zig:495-516) ---
         for t0 in range(0, m, mlp_tile):
             rows = min(mlp_tile, m - t0)
@@ -203,9 +212,6 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
             elif mode == "unfused":
                 be.siluMul(tile_gate, tile_up, rows * mlp)
                 prep(tile_gate, rows, mlp)
-            elif mode == "torch":
-                act = (torch.nn.functional.silu(tile_gate[:rows]) * tile_up[:rows]).float()
-                prep(act, rows, mlp)
             else:
                 prep(act_buf, rows, mlp)
             if mode == "fused":
@@ -214,8 +220,6 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                 gemm(tile_down, wb["mlp_down"], hid)
             if mode == "unfused":
                 be.gatedAdd(xt, tile_down, mod, rows * hid, hid, mb + 5 * hid)
-            elif mode == "torch":
-                x[t0:t0 + rows] += tile_down[:rows].float() * 1e-3
         if st is not None:
             st.release(b)
     return x

@@ -84,6 +84,8 @@ class PeerBuffers:
         Call ``barrier()`` before reading y and before the next overwrite."""
         be = self.be
         assert be.i8_bits == w_bits, "must follow the matching prep"
+        if w_bits == 4:
+            be.reserveW4(n_shard, be.i8_cols)
         ld = ldy if ldy is not None else n_shard * self.world
         esz = 2 if y_dtype == torch.bfloat16 else 4
         if be.i8_m * ld * esz > self.payload_bytes:
@@ -103,6 +105,8 @@ class PeerBuffers:
         turns a [1][world][m][n_shard] view of it into row-major)."""
         be = self.be
         assert be.i8_bits == w_bits, "must follow the matching prep"
+        if w_bits == 4:
+            be.reserveW4(n_shard, be.i8_cols)
         esz = 2 if y_dtype == torch.bfloat16 else 4
         block = be.i8_m * n_shard * esz
         if block * self.world > self.payload_bytes:
@@ -168,6 +172,8 @@ class MulticastBuffers:
         if not self.available:
             raise RuntimeError("no multicast support on this platform")
         assert be.i8_bits == w_bits, "must follow the matching prep"
+        if w_bits == 4:
+            be.reserveW4(n_shard, be.i8_cols)
         ld = ldy if ldy is not None else n_shard * self.world
         esz = 2 if y_dtype == torch.bfloat16 else 4
         if be.i8_m * ld * esz > self.payload_bytes:

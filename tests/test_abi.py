@@ -62,6 +62,30 @@ def test_backend_refuses_to_run_without_cuda():
         Backend(0)
 
 
+def test_elementwise_wrappers_refuse_outputs_they_would_overrun():
+    """The stand-alone elementwise ops write f32.  A bf16 tensor passed as the in-place operand
+    would be overrun on the device, so the mirror refuses it before anything is launched (the
+    checks need no device: they run on CPU tensors here, on an object without a handle)."""
+    import torch
+    from tensorpencil_b200.backend import Backend
+    be = Backend.__new__(Backend)              # no device, no library: the checks come first
+    a16 = torch.zeros(8, 256, dtype=torch.bfloat16)
+    b16 = torch.zeros(8, 256, dtype=torch.bfloat16)
+    a32 = torch.zeros(8, 256, dtype=torch.float32)
+    mod = torch.zeros(3 * 256)
+    for call in (lambda: be.siluMul(a16, b16, 8 * 256), lambda: be.sigmoidMul(a16, b16, 8 * 256),
+                 lambda: be.rmsMod(a32, a16, mod, 8, 256, 0, 256, 1e-5),
+                 lambda: be.gatedAdd(a16, b16, mod, 8 * 256, 256, 0)):
+        with pytest.raises(TypeError, match="float32"):
+            call()
+    with pytest.raises(ValueError, match="hold"):
+        be.siluMul(a32[:4], a32, 8 * 256)          # output shorter than the element count
+    with pytest.raises(ValueError, match="contiguous"):
+        be.sigmoidMul(a32.t(), a32.t(), 8 * 256)
+    with pytest.raises(TypeError, match="same dtype"):
+        be.siluMul(a32, b16, 8 * 256)
+
+
 def test_product_never_imports_the_oracle():
     """The oracle is test infrastructure: nothing in the package may import it."""
     pkg = os.path.join(ROOT, "tensorpencil_b200")

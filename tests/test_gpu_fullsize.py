@@ -1,0 +1,141 @@
+"""Full-size checks of BASELINE configs 1, 3 and 4: the real shapes (hidden 3072, MLP 12288,
+4608 tokens) through the block sequence of src/models/dit_cuda.zig:466-520, where the other
+tests use a toy model.
+
+Without attention every op of the stack is row-wise, so the library runs all 4608 rows and the
+CPU oracle replays the same sequence on a sample of rows.  Tolerances are those of
+tests/test_gpu_dit_step.py (relative Frobenius error of the latents after the stack): the
+reference's op sequence in f32 against the oracle 2e-3, fused f32 against unfused 1e-4, the bf16
+chain 3e-2.  The reference's own full-model gates are far looser (rel-RMSE <= 0.08 for int8,
+0.25 for int4: src/main.zig:1389-1410).  Weight streaming must not change a bit
+(src/main.zig:1288-1304): the INT4 stack streamed through two 80 MB slots equals the resident
+run exactly, for one latent and for a stacked batch of latents."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from oracle import oracle  # noqa: E402
+from tensorpencil_b200 import synth  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+HID, MLP, TOKENS = synth.DIT_HIDDEN, synth.DIT_MLP, synth.DIT_TOKENS
+BLOCKS = 2
+N_SAMPLE = 32
+
+
+@pytest.fixture(scope="module")
+def be():
+    from tensorpencil_b200.backend import Backend
+    b = Backend(0)
+    yield b
+    b.close()
+
+
+def sample_rows(m, n=N_SAMPLE, seed=9):
+    rows = np.random.default_rng(seed).choice(m, size=n, replace=False)
+    rows[:3] = (0, m - 1, m // 2)
+    return np.sort(np.unique(rows))
+
+
+def oracle_stack(dev_blocks, bits, mod, x, eps=1e-5):
+    """The reference's sequence composed from the oracle's functions (f32 activations, exact
+    int32 GEMM, f64 dequant), on the rows of x."""
+    mod = mod.cpu().numpy()
+    x = x.copy()
+
+    def lin(inp, wt):
+        wq, ws = wt[0].cpu().numpy(), wt[1].cpu().numpy()
+        if bits == 4:
+            wq = synth.unpack_i4(wq)
+        return oracle.convrot_linear_sim(inp, wq, ws, bits)[3].astype(np.float32)
+
+    for b, wb in enumerate(dev_blocks):
+        mb = b * 6 * HID
+        row = lambda i: mod[mb + i * HID: mb + (i + 1) * HID]
+        t = oracle.rms_mod(x, row(0), row(1), eps)
+        v, g = lin(t, wb["wv"]), lin(t, wb["gate"])
+        o = lin(oracle.sigmoid_mul(v, g), wb["wo"])
+        x = oracle.gated_add(x, o, row(2))
+        t = oracle.rms_mod(x, row(3), row(4), eps)
+        act = oracle.silu_mul(lin(t, wb["mlp_gate"]), lin(t, wb["mlp_up"]))
+        x = oracle.gated_add(x, lin(act, wb["mlp_down"]), row(5))
+    return x
+
+
+def rel(a, b):
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_full_size_block_stack_matches_oracle_on_sampled_rows(be, bits):
+    from tensorpencil_b200 import harness
+    w = harness.DitWeights(be, bits, blocks=BLOCKS, seed=41)
+    mod = harness.dit_modulation(be, BLOCKS, HID, seed=6)
+    x0 = synth.activations(TOKENS, HID, seed=1003)
+    rows = sample_rows(TOKENS)
+    want = oracle_stack(w.dev, bits, mod, x0[rows])
+
+    def run(mode, dtype, tile):
+        x = torch.from_numpy(x0.copy()).cuda()
+        out = harness.dit_step_linears(be, w, x, out_dtype=dtype, mode=mode, mod=mod, mlp_tile=tile)
+        be.status_poll()
+        return out[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+
+    unfused = run("unfused", torch.float32, harness.MLP_TILE)       # the reference's tiling: 2048, 2048, 512 rows
+    assert rel(unfused, want) < 2e-3
+    assert np.abs(unfused - x0[rows]).max() > 1e-3                   # the stack did change the latents
+    assert rel(run("fused", torch.float32, harness.MLP_TILE), unfused) < 1e-4
+    assert rel(run("fused", torch.float32, TOKENS), unfused) < 1e-4
+    assert rel(run("fused", torch.bfloat16, TOKENS), unfused) < 3e-2
+    w.close()
+
+
+def test_int4_streamed_equals_resident_at_real_block_size(be):
+    """Three blocks of the full-size INT4 model through two 80 MB slots (so a slot is reused
+    while the step runs) against the same weights resident: identical bits, for one latent and
+    for two latents stacked into one batch."""
+    from tensorpencil_b200 import harness
+    blocks = 3
+    res = harness.DitWeights(be, 4, blocks=blocks, seed=43)
+    probe = harness.DitWeights(be, 4, blocks=1, seed=43, stream_budget=1 << 30)
+    slot = probe.block_bytes
+    probe.close()
+    assert slot > 75 * 1024 * 1024                                   # the real block: 80 MB of packed weights
+    st = harness.DitWeights(be, 4, blocks=blocks, seed=43, stream_budget=2 * slot)
+    mod = harness.dit_modulation(be, blocks, HID, seed=6)
+    for latents in (1, 2):
+        x0 = np.concatenate([synth.activations(TOKENS, HID, seed=1003 + i) for i in range(latents)])
+        outs = []
+        for w in (res, st):
+            x = torch.from_numpy(x0.copy()).cuda()
+            outs.append(harness.dit_step_linears(be, w, x, out_dtype=torch.bfloat16, mode="fused", mod=mod,
+                                                 mlp_tile=x.shape[0], latents=latents).clone())
+            be.status_poll()
+        assert torch.equal(outs[0], outs[1])
+        if latents == 2:
+            # stacking changes nothing for a latent: the first 4608 rows equal the one-latent run
+            assert torch.equal(outs[0][:TOKENS], first)
+        first = outs[0][:TOKENS].clone()
+    assert st.streamer.bytes_copied() >= 2 * blocks * slot * 0.9
+    st.close()
+    res.close()
+
+
+def test_config1_bf16_output_is_the_rounded_f32_output(be):
+    """Config 1 at full size, bf16 output: every element equals the f32 result rounded to
+    nearest even, and the f32 result of 96 sampled rows is within 1e-3 / 1e-4 of the replica."""
+    c = synth.config1()
+    x = torch.from_numpy(c["x"]).cuda()
+    w = torch.from_numpy(c["w_packed"]).cuda()
+    ws = torch.from_numpy(c["w_scale"]).cuda()
+    y32 = be.convrot_linear(x, w, ws, c["n"], 4, torch.float32)
+    y16 = be.convrot_linear(x, w, ws, c["n"], 4, torch.bfloat16)
+    be.status_poll()
+    assert torch.equal(y16, y32.to(torch.bfloat16))
+    rows = sample_rows(c["m"], 96, seed=4)
+    sim = oracle.convrot_linear_sim(c["x"][rows], c["w_i8"], c["w_scale"], 4)[3]
+    got = y32[torch.from_numpy(rows).cuda()].cpu().numpy().astype(np.float64)
+    assert (np.abs(got - sim) <= 1e-4 + 1e-3 * np.abs(sim)).all()
+    got16 = y16[torch.from_numpy(rows).cuda()].float().cpu().numpy().astype(np.float64)
+    assert (np.abs(got16 - sim) <= 1e-4 + (1e-3 + 2.0 ** -8) * np.abs(sim)).all()   # plus half a bf16 ulp
