@@ -155,16 +155,19 @@ def convrot_linear_sim(x: np.ndarray, w_i8: np.ndarray, w_scale: np.ndarray, bit
 # -- `--backend cpu` float path ----------------------------------------------
 
 def linear_cpu_backend(x: np.ndarray, w: np.ndarray, w_bits: int, row_scale: np.ndarray,
-                       n: int, k: int, convrot: int = 256, bias=None, nthreads: int = 0) -> np.ndarray:
+                       n: int, k: int, convrot: int = 256, bias=None, nthreads: int = 0,
+                       path: str = "auto") -> np.ndarray:
+    """The reference's `--backend cpu` linear.  path: "auto" dispatches on the row count as
+    matmul.zig:152 does (m < 16: small-m path, else packed); "small" / "packed" force one."""
     x = _c(x, np.float32)
     m = x.shape[0]
     w = _c(w, np.int8 if w_bits == 8 else np.uint8)
     y = np.empty((m, n), np.float32)
     b = _c(bias, np.float32) if bias is not None else None
-    lib().tpo_linear_cpu_backend(_p(x), C.c_size_t(m), _p(w), C.c_int(w_bits),
-                                 _p(_c(row_scale, np.float32)), C.c_size_t(n), C.c_size_t(k),
-                                 C.c_int(convrot), _p(b) if b is not None else None, _p(y),
-                                 C.c_int(nthreads))
+    fn = {"auto": lib().tpo_linear_cpu_backend, "small": lib().tpo_linear_cpu_small_m,
+          "packed": lib().tpo_linear_cpu_packed}[path]
+    fn(_p(x), C.c_size_t(m), _p(w), C.c_int(w_bits), _p(_c(row_scale, np.float32)), C.c_size_t(n),
+       C.c_size_t(k), C.c_int(convrot), _p(b) if b is not None else None, _p(y), C.c_int(nthreads))
     return y
 
 

@@ -266,10 +266,83 @@ static void packed_task(float *y, const float *x, size_t m, const void *w,
     }
 }
 
+/* matmul.zig:669-717 (runRangeTyped, .i8) and :722-767 (runRangeI4): the path for fewer than
+ * small_m_max = 16 activation rows.  Panels of 8 weight rows are dequantised (q * row_scale)
+ * and un-rotated whole; every output is a vlen-lane vector accumulator over k (a multiply and
+ * an add per step, as the Zig source writes `acc += xv * wv` in strict float mode: no fused
+ * multiply-add), reduced lane 0..7 in order, plus the scalar tail, plus the bias.  vlen = 8 is
+ * what std.simd.suggestVectorLength(f32) gives on the AVX2 targets the reference is built for
+ * (matmul.zig:63).  A row's sum does not depend on how rows are grouped into panels or tasks. */
+enum { PANEL_ROWS = 8, VLEN = 8, SMALL_M_MAX = 16 }; /* matmul.zig:61-72 */
+
+void tpo_linear_cpu_small_m(const float *x, size_t m, const void *w, int w_bits,
+                            const float *row_scale, size_t n, size_t k,
+                            int convrot, const float *bias, float *y,
+                            int nthreads) {
+    if (m == 0 || n == 0) return;
+    const int nt = nthreads > 0 ? nthreads : tpo_num_threads();
+#pragma omp parallel num_threads(nt)
+    {
+        float *row = (float *)aligned_alloc(64, ((k * sizeof(float) + 63) / 64) * 64);
+#pragma omp for schedule(dynamic, PANEL_ROWS)
+        for (long long r = 0; r < (long long)n; r++) {
+            const float rs = row_scale[r];
+            if (w_bits == 8) {
+                const int8_t *src = (const int8_t *)w + (size_t)r * k;
+                for (size_t c = 0; c < k; c++) row[c] = (float)src[c] * rs;
+            } else {
+                const uint8_t *src = (const uint8_t *)w + ((size_t)r * k) / 2;
+                for (size_t c = 0; c < k; c++)
+                    row[c] = (float)tpo_nibble_i4(src[c / 2], (int)(c & 1)) * rs;
+            }
+            if (convrot) tpo_convrot_rotate(row, k);
+            for (size_t t = 0; t < m; t++) {
+                const float *xr = x + t * k;
+                float acc[VLEN];
+                for (int l = 0; l < VLEN; l++) acc[l] = 0.0f;
+                float tail = 0.0f;
+                size_t c = 0;
+                for (; c + VLEN <= k; c += VLEN)
+                    for (int l = 0; l < VLEN; l++) {
+                        volatile float prod = xr[c + l] * row[c + l]; /* rounded product, then the add */
+                        acc[l] += prod;
+                    }
+                for (; c < k; c++) {
+                    volatile float prod = xr[c] * row[c];
+                    tail += prod;
+                }
+                float sum = acc[0];
+                for (int l = 1; l < VLEN; l++) sum += acc[l];
+                sum += tail;
+                if (bias) sum += bias[r];
+                y[t * n + (size_t)r] = sum;
+            }
+        }
+        free(row);
+    }
+}
+
+void tpo_linear_cpu_packed(const float *x, size_t m, const void *w, int w_bits,
+                           const float *row_scale, size_t n, size_t k,
+                           int convrot, const float *bias, float *y,
+                           int nthreads);
+
+/* matmul.zig:105-194: fewer than 16 activation rows take the small-m path, the rest the
+ * packed outer-product path. */
 void tpo_linear_cpu_backend(const float *x, size_t m, const void *w, int w_bits,
                             const float *row_scale, size_t n, size_t k,
                             int convrot, const float *bias, float *y,
                             int nthreads) {
+    if (m < SMALL_M_MAX)
+        tpo_linear_cpu_small_m(x, m, w, w_bits, row_scale, n, k, convrot, bias, y, nthreads);
+    else
+        tpo_linear_cpu_packed(x, m, w, w_bits, row_scale, n, k, convrot, bias, y, nthreads);
+}
+
+void tpo_linear_cpu_packed(const float *x, size_t m, const void *w, int w_bits,
+                           const float *row_scale, size_t n, size_t k,
+                           int convrot, const float *bias, float *y,
+                           int nthreads) {
     if (m == 0 || n == 0) return;
     int nt = nthreads > 0 ? nthreads : tpo_num_threads();
     /* matmul.zig:206-211: 4 x ncpu row chunks, rounded up to whole NR panels. */

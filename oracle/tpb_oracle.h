@@ -92,6 +92,16 @@ void tpo_linear_cpu_backend(const float *x, size_t m, const void *w, int w_bits,
                             const float *row_scale, size_t n, size_t k,
                             int convrot, const float *bias, float *y,
                             int nthreads);
+/* The two halves of the above, callable on their own: the path for m < 16 activation rows
+ * (src/ops/matmul.zig:669-767) and the packed outer-product path (:196-234, :408-639). */
+void tpo_linear_cpu_small_m(const float *x, size_t m, const void *w, int w_bits,
+                            const float *row_scale, size_t n, size_t k,
+                            int convrot, const float *bias, float *y,
+                            int nthreads);
+void tpo_linear_cpu_packed(const float *x, size_t m, const void *w, int w_bits,
+                           const float *row_scale, size_t n, size_t k,
+                           int convrot, const float *bias, float *y,
+                           int nthreads);
 
 /* -- GGUF Q8_0 -------------------------------------------------------------- */
 

@@ -21,7 +21,7 @@ OUT_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(OUT_DIR, "libtpb200.so")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
 
-SOURCES = ["api.cu", "prep.cu", "prep_fused.cu", "gemm_i8.cu", "gemm2_i8.cu", "gemm_w4.cu", "qgemv.cu", "qgemv_k.cu", "offload.cu", "peer.cu", "attn.cu"]
+SOURCES = ["api.cu", "prep.cu", "prep_fused.cu", "gemm_i8.cu", "gemm2_i8.cu", "gemm_w4.cu", "qgemv.cu", "qgemv_mma.cu", "qgemv_k.cu", "offload.cu", "peer.cu", "attn.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

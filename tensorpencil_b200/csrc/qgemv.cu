@@ -335,6 +335,15 @@ cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t
 // One (M, R) instantiation: fit activations + per-warp rings into the opt-in shared
 // memory (as many stages as fit, at most 4; fewer warps next; activations left in
 // global memory last) and launch one persistent CTA per SM.
+// Diagnostic override of the launch shape: TPB_GEMV_CFG="R,warps,stages" (read at every launch,
+// so one process can sweep shapes).
+struct GemvOverride { int r = 0, warps = 0, stages = 0; };
+static GemvOverride gemv_override() {
+    GemvOverride v;
+    if (const char *e = getenv("TPB_GEMV_CFG")) sscanf(e, "%d,%d,%d", &v.r, &v.warps, &v.stages);
+    return v;
+}
+
 template <int M, int R>
 int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max_warps) {
     constexpr int kStage = stage_bytes(R);
@@ -342,6 +351,18 @@ int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max
     const size_t act = (size_t)M * (p.nblk / 2) * kActPairBytes + (size_t)M * p.nblk * 4;
     int warps = 0, stages = 0;
     bool act_smem = true;
+    const GemvOverride ov = gemv_override();
+    if (ov.r == R && ov.warps > 0 && ov.warps <= max_warps && ov.stages >= 2) {
+        const size_t need = act + (size_t)ov.warps * ov.stages * kStage + (size_t)ov.warps * ov.stages * 8 + 64;
+        if (need > limit) return tpb_fail(h, TPB_ERR_INVALID_ARG, "TPB_GEMV_CFG does not fit shared memory (%zu bytes)", need);
+        int grid = (int)(((long long)p.rows + (long long)ov.warps * R - 1) / ((long long)ov.warps * R));
+        if (grid > h->sm_count) grid = h->sm_count;
+        auto kern = q8_0_gemv_q8n_kernel<M, R, true>;
+        static tpb_per_device_once smem_set_ov;
+        TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set_ov));
+        TPB_CUDA(h, launch_pdl(kern, grid, ov.warps * 32, need, st, p, ov.stages));
+        return TPB_OK;
+    }
     auto fits = [&](int w, int s, bool a) {
         return (a ? act : 0) + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit;
     };
@@ -408,7 +429,7 @@ int launch_q8n(tpb_handle_t h, cudaStream_t st, const GemvParams &p) {
     // Preferred: up to 16 warps with 2 weight rows each (more loads in flight, more latency
     // hiding).  When the activations leave too little shared memory for that, 8 warps with
     // 4 rows each (activations are re-read from shared memory once per R rows).
-    {
+    if (gemv_override().r != 4) {
         const int rc = launch_q8n_cfg<M, 2>(h, st, p, 16);
         if (rc != TPB_ERR_STATE) return rc;  // TPB_ERR_STATE: did not fit, try the wider grouping
     }
@@ -432,6 +453,15 @@ int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, in
 int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total) {
+    // Default: the kernel that keeps the activations in registers (qgemv_mma.cu).  The dp4a
+    // streaming kernel below takes the shapes that one cannot (row length not a multiple of
+    // 256, or too long for the register file) and TPB_GEMV_KERNEL=dp4a (diagnosis, A/B runs).
+    {
+        const char *e = getenv("TPB_GEMV_KERNEL");
+        const bool force_dp4a = e != nullptr && e[0] == 'd';
+        if (!force_dp4a && tpb_q8_0_gemv_mma_fits(h, rows, cols))
+            return tpb_launch_q8_0_gemv_mma(h, st, y, w, scale, rows, cols, xq, ng, row_off, n_total);
+    }
     GemvParams p;
     const int nblk = (int)(cols / 32);
     p.y = y;

@@ -178,8 +178,8 @@ def test_cpu_backend_is_a_sequential_fma_chain():
     """The packed path accumulates one FMA per k, k ascending, per output
     (matmul.zig:611-619), whatever the k-blocking or thread split."""
     c = synth.convrot_linear(3, 16, 1024, 8, seed=77)
-    y = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024)
-    y1 = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024, nthreads=1)
+    y = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024, path="packed")
+    y1 = oracle.linear_cpu_backend(c["x"], c["w_i8"], 8, c["w_scale"], 16, 1024, nthreads=1, path="packed")
     assert np.array_equal(y, y1)
     wd = oracle.rotate((c["w_i8"].astype(np.float32) * c["w_scale"][:, None]).astype(np.float32))
     import math
@@ -191,6 +191,44 @@ def test_cpu_backend_is_a_sequential_fma_chain():
                 acc = np.float32(math.fma(float(c["x"][i, kk]), float(wd[j, kk]), float(acc))) \
                     if hasattr(math, "fma") else np.float32(np.float64(c["x"][i, kk]) * np.float64(wd[j, kk]) + np.float64(acc))
             assert abs(float(acc) - float(y[i, j])) <= 2e-6 * max(1.0, abs(float(acc)))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_cpu_backend_small_m_path(bits):
+    """Fewer than 16 activation rows take the reference's small-m path (matmul.zig:152, :669-767):
+    eight lane-wise partial sums over k, multiply and add rounded separately, reduced lane 0..7,
+    then the scalar tail and the bias.  Checked against that recipe spelled out in numpy, against
+    the packed path (another summation order of the same products: close, not equal), and for
+    independence from the thread split; 16 rows and more dispatch to the packed path."""
+    m, n, k = 5, 24, 1024 + 256       # ConvRot needs k % 256 == 0, so the scalar tail is empty here
+    c = synth.convrot_linear(m, n, k, bits, seed=90 + bits)
+    w = c["w_packed"] if bits == 4 else c["w_i8"]
+    bias = np.random.default_rng(4).standard_normal(n).astype(np.float32)
+    y = oracle.linear_cpu_backend(c["x"], w, bits, c["w_scale"], n, k, bias=bias)
+    assert np.array_equal(y, oracle.linear_cpu_backend(c["x"], w, bits, c["w_scale"], n, k, bias=bias, path="small"))
+    assert np.array_equal(y, oracle.linear_cpu_backend(c["x"], w, bits, c["w_scale"], n, k, bias=bias, nthreads=1))
+    wd = oracle.rotate((c["w_i8"].astype(np.float32) * c["w_scale"][:, None]).astype(np.float32))
+    for t in (0, m - 1):
+        for r in (0, 7, n - 1):
+            prod = (c["x"][t] * wd[r]).astype(np.float32).reshape(-1, 8)      # rounded products, 8 lanes
+            acc = np.zeros(8, np.float32)
+            for row in prod:
+                acc = (acc + row).astype(np.float32)
+            s = acc[0]
+            for lane in range(1, 8):
+                s = np.float32(s + acc[lane])
+            s = np.float32(np.float32(s + np.float32(0)) + bias[r])
+            assert y[t, r] == s, (t, r, y[t, r], s)
+    yp = oracle.linear_cpu_backend(c["x"], w, bits, c["w_scale"], n, k, bias=bias, path="packed")
+    assert not np.array_equal(y, yp)
+    assert np.allclose(y, yp, rtol=2e-5, atol=2e-4 * np.sqrt(k))
+    # the dispatch threshold: 15 rows small-m, 16 rows packed
+    c16 = synth.convrot_linear(16, n, 512, bits, seed=95)
+    w16 = c16["w_packed"] if bits == 4 else c16["w_i8"]
+    assert np.array_equal(oracle.linear_cpu_backend(c16["x"], w16, bits, c16["w_scale"], n, 512),
+                          oracle.linear_cpu_backend(c16["x"], w16, bits, c16["w_scale"], n, 512, path="packed"))
+    assert np.array_equal(oracle.linear_cpu_backend(c16["x"][:15], w16, bits, c16["w_scale"], n, 512),
+                          oracle.linear_cpu_backend(c16["x"][:15], w16, bits, c16["w_scale"], n, 512, path="small"))
 
 
 def test_cpu_backend_bias_and_no_convrot():
