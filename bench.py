@@ -1021,6 +1021,55 @@ def run_mode_one_kernel(args, local):
     case = args.case
     if case == "gemm-w4-fused":
         os.environ["TPB_W4_FUSED"] = "1"       # read when the handle is created
+    if case == "gemm-ablation":
+        # What each part of the two-CTA GEMM's pipeline costs the tensor pipe: the same launch with
+        # loads of q, loads of w and / or the epilogue switched off (TPB_GEMM_ABLATE, read when a
+        # handle is created; results are meaningless, timings are not).  Variants are interleaved
+        # and repeated so that clock drift under the power cap hits them alike; time x sampled SM
+        # MHz is printed beside the time for the same reason.
+        variants = (("full", 0), ("no q loads", 1), ("no w loads", 2), ("no loads", 3), ("no epilogue", 4),
+                    ("no loads, no epilogue", 7), ("epilogue reads tensor memory only", 8),
+                    ("epilogue without its stores", 16), ("no loads, epilogue reads tensor memory only", 11),
+                    ("no loads, epilogue without its stores", 19))
+        dt = torch.bfloat16 if args.out_dtype == "bf16" else torch.float32
+        rows = {name: [] for name, _ in variants}
+        q = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda")
+        ws_ = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda") for _ in range(N_SETS)]
+        sc, y = torch.rand(N, device="cuda"), torch.empty(M, N, dtype=dt, device="cuda")
+        asc = torch.rand(M, device="cuda")
+        for rep in range(3):
+            for name, bits in variants:
+                os.environ["TPB_GEMM_ABLATE"] = str(bits)
+                be = Backend(local)
+                be.i8_x, be.i8_scale = q.reshape(-1), asc
+                be.i8_m, be.i8_cols, be.i8_bits = M, K, 8
+                fn = lambda i: be._gemm(y, ws_[i % N_SETS], sc, N, 8)
+                for i in range(3):
+                    fn(i)
+                sampler = ClockSampler(physical_gpu_index(local))
+                torch.cuda.synchronize()
+                sampler.start()
+                ms = _events_ms(fn, 100, torch.cuda.synchronize) / 100
+                clk = sampler.stop()
+                try:
+                    be.status_poll()
+                except Exception as e:
+                    print(json.dumps({"variant": name, "error": str(e)}), flush=True)
+                rows[name].append((ms, clk.get("sm_mhz")))
+                be.close()
+        os.environ.pop("TPB_GEMM_ABLATE", None)
+        out = []
+        for name, _ in variants:
+            ms = float(np.median([r[0] for r in rows[name]]))
+            mhz = [r[1] for r in rows[name] if r[1]]
+            mhz = float(np.median(mhz)) if mhz else None
+            tops = OPS_PER_STEP / (ms * 1e-3) / 1e12
+            out.append({"variant": name, "us": ms * 1e3, "tops": tops, "sm_mhz": mhz,
+                        "us_x_ghz": ms * 1e3 * mhz / 1e3 if mhz else None,
+                        "tensor_util_at_sampled_clock": (tops / (148 * 8192 * 2 * mhz * 1e6 / 1e12)) if mhz else None})
+        print(json.dumps({"mode": "one-kernel", "case": case, "out_dtype": args.out_dtype, "m": M, "n": N, "k": K,
+                          "variants": out}), flush=True)
+        return
     be = Backend(local)
     reps = max(1, min(args.steps, 5))
     if case in ("prep", "prep-mlp"):
@@ -1122,7 +1171,7 @@ def main():
     ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "attn", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
-                    "gemm-small, gemm-w4, gemm-w4-fused, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
+                    "gemm-small, gemm-w4, gemm-w4-fused, gemm-ablation, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -57,6 +57,7 @@ int tpb_create(tpb_handle_t *out, int device_ordinal) {
     const char *e1 = getenv("TPB_W4_FUSED"), *e2 = getenv("TPB_GEMM_ONE_CTA");
     h->opt_w4_fused = e1 != nullptr && e1[0] == '1';
     h->opt_gemm_one_cta = e2 != nullptr && e2[0] == '1';
+    if (const char *e3 = getenv("TPB_GEMM_ABLATE")) h->opt_gemm_ablate = atoi(e3) & 31;
     int prev = 0;
     cudaGetDevice(&prev);
     cudaError_t e = cudaSetDevice(device_ordinal);

@@ -105,10 +105,12 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (1u << 24) | (rank << 8) | s, true);
                     if (!ok) break;
                     const uint32_t lead_full = mapa(full_bar(s), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStage2);
+                    const bool load_a = !(p.ablate & 1), load_b = !(p.ablate & 2);
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(full_bar(s), 2u * ((load_a ? kStageA : 0) + (load_b ? kStageB : 0)));
                     const uint32_t a_dst = smem_base + s * kStage2;
-                    tma_load_2d_pair(a_dst, &tma_a, lead_full, kb * BK, m0);
-                    tma_load_2d_pair(a_dst + kStageA, &tma_b, lead_full, kb * BK, n0);
+                    if (load_a) tma_load_2d_pair(a_dst, &tma_a, lead_full, kb * BK, m0);
+                    if (load_b) tma_load_2d_pair(a_dst + kStageA, &tma_b, lead_full, kb * BK, n0);
                 }
             }
         }
@@ -173,7 +175,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             if (OUT != OUT_S32 && row_ok) as = __ldcg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldcg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
-            epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+            if (!(p.ablate & 4))
+                epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));

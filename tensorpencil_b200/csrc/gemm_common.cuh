@@ -54,6 +54,12 @@ struct GemmParams {
     // Gated residual (epilogue mode 3, f32 only): y is the residual stream x and the
     // epilogue stores x + gate[col] * (acc * act_scale * w_scale) back into it.
     const float *gate;
+    // Diagnosis only (TPB_GEMM_ABLATE, two-CTA kernel): bit 0 = issue no loads of q, bit 1 = no loads
+    // of w, bit 2 = no epilogue (accumulators are handed back unread), bit 3 = the epilogue only
+    // reads the accumulators out of tensor memory, bit 4 = it also converts and stages them in
+    // shared memory but issues no stores.  Results are meaningless; the timings show what each
+    // part of the pipeline costs the tensor pipe.
+    int ablate;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -300,7 +306,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
         // so "all but the latest store have finished reading" keeps meaning "the
         // other buffer's store".
         const int scol = (OUT == OUT_BF16 && (c & 1)) ? col0 - 32 : col0;
-        const bool do_store = row0 < p.m && scol < p.n;
+        const bool do_store = row0 < p.m && scol < p.n && !(p.ablate & 8);
         if (!do_store) continue;
         if (first_piece) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -368,7 +374,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             // generic-proxy writes -> visible to the async proxy, then one lane stores
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (PEERS != 2 && lane == 0) {
+            if (PEERS != 2 && lane == 0 && !(p.ablate & 16)) {
                 tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }

@@ -266,6 +266,7 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
     GemmParams p;
     p.mc_y = mc_y;
     p.gate = gate;
+    p.ablate = h->opt_gemm_ablate;
     p.n_peers = n_peers;
     for (int i = 0; i < kMaxPeers; i++) p.peer_y[i] = i < n_peers ? peer_y[i] : nullptr;
     p.y = y;

@@ -453,13 +453,12 @@ int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, in
 int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total) {
-    // Default: the kernel that keeps the activations in registers (qgemv_mma.cu).  The dp4a
-    // streaming kernel below takes the shapes that one cannot (row length not a multiple of
-    // 256, or too long for the register file) and TPB_GEMV_KERNEL=dp4a (diagnosis, A/B runs).
+    // TPB_GEMV_KERNEL=mma selects the kernel that keeps the activations in registers and takes the
+    // block sums from mma.sync (qgemv_mma.cu); the dp4a streaming kernel below is the default.
     {
         const char *e = getenv("TPB_GEMV_KERNEL");
-        const bool force_dp4a = e != nullptr && e[0] == 'd';
-        if (!force_dp4a && tpb_q8_0_gemv_mma_fits(h, rows, cols))
+        const bool want_mma = e != nullptr && e[0] == 'm';
+        if (want_mma && tpb_q8_0_gemv_mma_fits(h, rows, cols))
             return tpb_launch_q8_0_gemv_mma(h, st, y, w, scale, rows, cols, xq, ng, row_off, n_total);
     }
     GemvParams p;

@@ -15,15 +15,21 @@
 // and activation row for.  The per-block scaling stays the reference's
 // (src/gpu/cuda/elt.zig:1984-2005):
 //   acc += float(sumi) * (d_w * d_x)   in f32, block after block.
+// Rows too long for the registers (more than 12 block pairs per warp) are taken in several
+// passes over K: a pass streams one K range of all the CTA's rows, and the passes after the
+// first add to the y the first one wrote.
 //
-// Data path.  One CTA per SM owns a contiguous range of weight rows.  A producer warp streams
+// Data path.  One CTA per SM owns a contiguous range of weight rows.  Four producer warps stream
 // them in stages of 16 rows x one K segment with one 1-D bulk copy per row (cp.async.bulk,
 // completion on the stage's "full" mbarrier, no multicast) into a ring that fills most of
-// shared memory; it starts before griddepcontrol.wait, so under programmatic dependent launch
-// the ring fills while the previous kernel drains.  The warps whose K slice lies in a stage's
+// shared memory; they start before griddepcontrol.wait, so under programmatic dependent launch
+// the ring fills while the previous kernel drains.  (Four warps, four rows each, because a warp
+// gets a bulk copy under way only every ~225 cycles: measured, one warp issuing all sixteen
+// copies of every stage capped the kernel at 3.4 TB/s.  The register file hands out registers
+// to warps in fours, so warps 17..19 cost nothing.)  The warps whose K slice lies in a stage's
 // segment wait for it, multiply, write their 16 x 8 partial sums to a small buffer and arrive
 // on the stage's "empty" mbarrier.  When the last segment of a row group has been released,
-// the producer warp -- which has to wait for that anyway before it may refill the slot -- adds
+// the first producer warp -- which has to wait for that anyway before it may refill the slot -- adds
 // the partials in warp order (a fixed order: results do not depend on timing), applies
 // `scale`, and stores y.  No warp ever waits for another consumer warp.
 //
@@ -45,8 +51,9 @@ namespace {
 
 constexpr int kBlockBytes = 34;
 constexpr int kPairBytes = 68;
-constexpr int kConsumers = 16;                 // consumer warps; warp 16 is the producer
-constexpr int kThreadsMma = (kConsumers + 1) * 32;
+constexpr int kConsumers = 16;                 // consumer warps 0..15
+constexpr int kProducers = 4;                  // producer warps 16..19, four rows of every stage each
+constexpr int kThreadsMma = (kConsumers + kProducers) * 32;
 constexpr int kStageRows = 16;                 // weight rows per stage = m of the MMA
 constexpr int kActRows = 8;                    // activation rows = n of the MMA
 constexpr int kPartFloats = kStageRows * kActRows;   // partial sums of one warp for one stage
@@ -58,16 +65,21 @@ struct MmaGemvParams {
     const int8_t *xq;  // activation quants [m][cols]
     float scale;
     int rows, cols, nblk, m;
-    int nseg;          // K segments per row group (divides kConsumers)
+    int npass;         // passes over K (each covers a contiguous range of whole 8-block units)
+    int nseg;          // K segments per pass and row group (divides kConsumers)
     int pitch;         // bytes between rows of a stage
     int stages;        // ring depth
     int rgbuf;         // row groups of partial sums kept
+    int debug;         // TPB_GEMV_MMA_DEBUG (diagnosis): bit 0 = consumers skip the arithmetic
     uint32_t *status;
 };
 
-// K segment s of a row: blocks [seg_blk0(s), seg_blk0(s + 1)), always whole units of 8 blocks
-// (272 bytes, a multiple of 16).
-__host__ __device__ inline int seg_blk0(int nblk, int nseg, int s) { return (int)((long long)(nblk / 8) * s / nseg) * 8; }
+// Pass p of a row covers blocks [pass_blk0(p), pass_blk0(p + 1)); K segment s of a pass covers
+// [seg_blk0(s), seg_blk0(s + 1)) of those.  Both are whole units of 8 blocks (272 bytes, a multiple of 16).
+__host__ __device__ inline int pass_blk0(int nblk, int npass, int p) { return (int)((long long)(nblk / 8) * p / npass) * 8; }
+__host__ __device__ inline int seg_blk0(int pb0, int pb1, int nseg, int s) {
+    return pb0 + (int)((long long)((pb1 - pb0) / 8) * s / nseg) * 8;
+}
 // pairs [lo, hi) of consumer `wi` (0 .. wps-1) inside a segment of `pairs` block pairs
 __host__ __device__ inline int warp_pair0(int pairs, int wps, int wi) { return (int)((long long)pairs * wi / wps); }
 
@@ -95,10 +107,9 @@ __device__ __forceinline__ float2 lds_f2(uint32_t addr) {
 __device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
 
-// 17 warps x 32 lanes x 120 registers = 65280 of the SM's 65536: the register budget is stated
-// directly (a launch bound of 544 threads makes the compiler settle for 96).
+// 20 warps: 65536 / 640 = 102 registers per thread, 96 after rounding to the allocation unit.
 template <int NP>
-__global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
+__global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -117,7 +128,7 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
     const int wps = kConsumers / p.nseg;  // consumer warps per K segment
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(kProducers));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(wps));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -125,31 +136,40 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // this CTA's rows and its stages: (row group, segment), row groups of 16 rows
+    // this CTA's rows and its stages: (pass, row group, segment), row groups of 16 rows
     const int r_begin = (int)((long long)p.rows * blockIdx.x / gridDim.x);
     const int r_end = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
     const int n_rg = (r_end - r_begin + kStageRows - 1) / kStageRows;
-    const int total = n_rg * p.nseg;
+    const int total = p.npass * n_rg * p.nseg;
 
-    if (warp == kConsumers) {
-        // ---------------- producer + reducer ----------------
-        auto issue = [&](int i) {  // lane 0: copies of stage i
-            const int rg = i / p.nseg, seg = i - rg * p.nseg;
+    if (warp >= kConsumers) {
+        // ---------------- producers (the first one also reduces) ----------------
+        const int pw = warp - kConsumers;
+        constexpr int kRowsPerProducer = kStageRows / kProducers;
+        auto issue = [&](int i) {  // whole warp: lane r starts the copy of this warp's r-th row of stage i
+            const int v = i / p.nseg, seg = i - v * p.nseg;      // v = row-group visit: pass * n_rg + rg
+            const int pass = v / n_rg, rg = v - pass * n_rg;
             const int row0 = r_begin + rg * kStageRows;
             const int nrow = min(kStageRows, r_end - row0);
-            const int b0 = seg_blk0(nblk, p.nseg, seg), b1 = seg_blk0(nblk, p.nseg, seg + 1);
+            const int pb0 = pass_blk0(nblk, p.npass, pass), pb1 = pass_blk0(nblk, p.npass, pass + 1);
+            const int b0 = seg_blk0(pb0, pb1, p.nseg, seg), b1 = seg_blk0(pb0, pb1, p.nseg, seg + 1);
             const uint32_t bytes = (uint32_t)(b1 - b0) * kBlockBytes;
             const int slot = i % S;
             const uint32_t bar = full_bar(slot);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)nrow)
-                         : "memory");
+            const int my_rows = max(0, min(kRowsPerProducer, nrow - pw * kRowsPerProducer));
+            if (lane == 0)   // every producer warp arrives, also with nothing to copy (the barrier counts four)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)my_rows)
+                             : "memory");
+            __syncwarp();
+            const int r = pw * kRowsPerProducer + lane;
             const uint32_t dst = smem_u32(ring + (size_t)slot * stage_bytes);
             const uint8_t *src = p.w + (size_t)row0 * row_bytes + (size_t)b0 * kBlockBytes;
-            for (int r = 0; r < nrow; r++) bulk_g2s(dst + (uint32_t)(r * p.pitch), src + (size_t)r * row_bytes, bytes, bar);
+            if (lane < my_rows) bulk_g2s(dst + (uint32_t)(r * p.pitch), src + (size_t)r * row_bytes, bytes, bar);
         };
-        auto reduce = [&](int rg) {  // all lanes: y for row group rg from the consumers' partial sums
+        auto reduce = [&](int v) {  // all lanes: y of one row-group visit from the consumers' partial sums
             // a warp's partials: [16 weight rows][8 activation rows]; this lane: row lane / 2, activation rows 4 (lane % 2) ..
-            const float *part = s_part + (size_t)(rg % p.rgbuf) * kConsumers * kPartFloats + 4 * lane;
+            const int pass = v / n_rg, rg = v - pass * n_rg;
+            const float *part = s_part + (size_t)(v % p.rgbuf) * kConsumers * kPartFloats + 4 * lane;
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < kConsumers; w++) {
@@ -162,15 +182,18 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
             const int row = r_begin + rg * kStageRows + (lane >> 1);
             const int m0 = 4 * (lane & 1);
             if (row < r_end) {
-                if (m0 + 0 < p.m) p.y[(size_t)(m0 + 0) * p.rows + row] = sum.x * p.scale;
-                if (m0 + 1 < p.m) p.y[(size_t)(m0 + 1) * p.rows + row] = sum.y * p.scale;
-                if (m0 + 2 < p.m) p.y[(size_t)(m0 + 2) * p.rows + row] = sum.z * p.scale;
-                if (m0 + 3 < p.m) p.y[(size_t)(m0 + 3) * p.rows + row] = sum.w * p.scale;
+                // later passes add to what this same lane stored in the pass before
+                const float v4[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (m0 + e < p.m) {
+                        float *dst = p.y + (size_t)(m0 + e) * p.rows + row;
+                        *dst = pass == 0 ? v4[e] * p.scale : fmaf(v4[e], p.scale, *dst);
+                    }
             }
         };
         // weights are constants: the ring starts filling before the previous kernel has finished
-        if (lane == 0)
-            for (int i = 0; i < S && i < total; i++) issue(i);
+        for (int i = 0; i < S && i < total; i++) issue(i);
         asm volatile("griddepcontrol.wait;" ::: "memory");
         bool ok = true;
         for (int j = 0; j < total && ok; j++) {
@@ -178,9 +201,11 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
             ok = mbar_wait(empty_bar(j % S), (uint32_t)(j / S) & 1u, p.status, (7u << 24) | (uint32_t)(j % S));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (j % p.nseg == p.nseg - 1) reduce(j / p.nseg);
+            // Partial sums are added before this warp's part of the refill goes out, and the refilled
+            // stage is not "full" without it: no consumer can overwrite a partial that is still needed.
+            if (pw == 0 && j % p.nseg == p.nseg - 1) reduce(j / p.nseg);
             __syncwarp();
-            if (j + S < total && lane == 0) {
+            if (j + S < total) {
                 // order the consumers' generic-proxy reads of the slot before the async-proxy refill
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue(j + S);
@@ -192,18 +217,41 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
     const int seg = warp / wps, wi = warp - seg * wps;
-    const int sb0 = seg_blk0(nblk, p.nseg, seg), sb1 = seg_blk0(nblk, p.nseg, seg + 1);
-    const int seg_pairs = (sb1 - sb0) / 2;
-    const int pp0 = warp_pair0(seg_pairs, wps, wi), pp1 = warp_pair0(seg_pairs, wps, wi + 1);
-    const int np = pp1 - pp0;  // <= NP (checked by the host)
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // activation scales of all 8 (padded) rows -> shared memory; consumers only
-    for (int i = threadIdx.x; i < kActRows * nblk; i += kConsumers * 32) {
-        const int m = i / nblk;
-        s_dx[i] = m < p.m ? __ldcg(p.xd + (size_t)m * nblk + (i - m * nblk)) : 0.0f;
+    // (the loads of four rounds go out together: a round trip to L2 each would cost a microsecond)
+    for (int i0 = threadIdx.x; i0 < kActRows * nblk; i0 += 4 * kConsumers * 32) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * kConsumers * 32;
+            const int m = i / nblk;
+            v[u] = (i < kActRows * nblk && m < p.m) ? __ldcg(p.xd + (size_t)m * nblk + (i - m * nblk)) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * kConsumers * 32;
+            if (i < kActRows * nblk) s_dx[i] = v[u];
+        }
     }
-    // this lane's part of the B operand: activation row g, K positions of its pairs
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+
+    const uint32_t hi_rows = 8u * (uint32_t)p.pitch;   // weight row g + 8
+    const uint32_t dx_next = 4u * (uint32_t)nblk;      // next activation row's scales
+    bool ok = true;
+  for (int pass = 0; pass < p.npass && ok; pass++) {
+    const int pb0 = pass_blk0(nblk, p.npass, pass), pb1 = pass_blk0(nblk, p.npass, pass + 1);
+    const int sb0 = seg_blk0(pb0, pb1, p.nseg, seg), sb1 = seg_blk0(pb0, pb1, p.nseg, seg + 1);
+    const int seg_pairs = (sb1 - sb0) / 2;
+    const int pp0 = warp_pair0(seg_pairs, wps, wi), pp1 = warp_pair0(seg_pairs, wps, wi + 1);
+    const int np = pp1 - pp0;  // <= NP (checked by the host)
+    // this lane's part of the B operand: activation row g, K positions of its pairs in this pass
+    // Lane (g, t) loads words t and 4+t of both blocks of each pair (all loads independent, so they
+    // go out together), then the first block is put into the order "aligned words 1..7 of the
+    // weight block, then its two end halves": slot j holds activation bytes 4j-2 .. 4j+1, i.e. the
+    // high half of word j-1 and the low half of word j; slot 0 holds bytes 0, 1, 30, 31.  The
+    // neighbouring words come from the neighbouring lanes of the same activation row.
     uint32_t b[NP][4];
 #pragma unroll
     for (int q = 0; q < NP; q++) {
@@ -211,27 +259,34 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
         if (q < np && g < p.m) {
             const int blk = sb0 + 2 * (pp0 + q);
             const uint32_t *x0 = reinterpret_cast<const uint32_t *>(p.xq + (size_t)g * p.cols + (size_t)blk * 32);
-            // first block of the pair, in the order "aligned words 1..7, then the two end halves"
-            const uint32_t lo_a = __ldcg(x0 + (t == 0 ? 0 : t - 1)), lo_b = __ldcg(x0 + (t == 0 ? 7 : t));
-            b[q][0] = t == 0 ? ((lo_a & 0x0000ffffu) | (lo_b & 0xffff0000u)) : __funnelshift_r(lo_a, lo_b, 16);
-            b[q][1] = __funnelshift_r(__ldcg(x0 + 3 + t), __ldcg(x0 + 4 + t), 16);
-            // second block: word-aligned in the weight row, natural order
-            b[q][2] = __ldcg(x0 + 8 + t);
+            b[q][0] = __ldcg(x0 + t);
+            b[q][1] = __ldcg(x0 + 4 + t);
+            b[q][2] = __ldcg(x0 + 8 + t);    // second block: word-aligned in the weight row, natural order
             b[q][3] = __ldcg(x0 + 12 + t);
         }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-
+#pragma unroll
+    for (int q = 0; q < NP; q++) {
+        // all 32 lanes take part in the shuffles (q < np is warp-uniform)
+        if (q < np) {
+            const uint32_t w_lo = b[q][0], w_hi = b[q][1];
+            const int prev = (lane & ~3) | ((t + 3) & 3);                 // lane (g, t-1), wrapping to t = 3
+            const uint32_t p_lo = __shfl_sync(0xffffffffu, w_lo, prev);   // word t-1      (t = 0: word 3)
+            const uint32_t p_hi = __shfl_sync(0xffffffffu, w_hi, prev);   // word 3+t      (t = 0: word 7)
+            // slot t: t >= 1 -> words (t-1, t); t = 0 -> low half of word 0, high half of word 7
+            b[q][0] = t == 0 ? ((w_lo & 0x0000ffffu) | (p_hi & 0xffff0000u)) : __funnelshift_r(p_lo, w_lo, 16);
+            // slot 4+t: words (3+t, 4+t); word 3+t is lane t-1's second word, for t = 0 lane 3's first
+            b[q][1] = __funnelshift_r(t == 0 ? p_lo : p_hi, w_hi, 16);
+        }
+    }
     // shared addresses relative to a stage: this warp's first pair in weight row g, word t
     const uint32_t ring_u32 = smem_u32(ring) + (uint32_t)(pp0 * kPairBytes) + (uint32_t)(g * p.pitch) + 4u * (uint32_t)t;
-    const uint32_t hi_rows = 8u * (uint32_t)p.pitch;   // weight row g + 8
     // activation scales of activation rows 2t and 2t+1, this warp's first block
     const uint32_t dx_u32 = smem_u32(s_dx + (size_t)(2 * t) * nblk + sb0 + 2 * pp0);
-    const uint32_t dx_next = 4u * (uint32_t)nblk;
 
-    bool ok = true;
     for (int rg = 0; rg < n_rg && ok; rg++) {
-        const int i = rg * p.nseg + seg;
+        const int v = pass * n_rg + rg;
+        const int i = v * p.nseg + seg;
         const int slot = i % S;
         ok = mbar_wait(full_bar(slot), (uint32_t)(i / S) & 1u, p.status, (8u << 24) | (uint32_t)slot);
         ok = __all_sync(0xffffffffu, ok);
@@ -240,7 +295,7 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int q = 0; q < NP; q++) {
-            if (q < np) {
+            if (q < np && !(p.debug & 1)) {
                 const uint32_t o = (uint32_t)(q * kPairBytes);
                 // words t, 4+t, 8 (and 0 for the scale) of the first block, 9+t and 13+t of the second
                 const uint32_t l0 = lds32(wl + o - 4u * t), l_lo = lds32(wl + o), l_hi = lds32(wl + o + 16);
@@ -265,59 +320,74 @@ __global__ void __maxnreg__(120) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
             }
         }
         // this warp's K slice of C[weight row][activation row]: rows g and g + 8, activation rows 2t, 2t+1
-        float *part = s_part + ((size_t)(rg % p.rgbuf) * kConsumers + warp) * kPartFloats;
+        float *part = s_part + ((size_t)(v % p.rgbuf) * kConsumers + warp) * kPartFloats;
         *reinterpret_cast<float2 *>(part + g * kActRows + 2 * t) = make_float2(acc[0], acc[1]);
         *reinterpret_cast<float2 *>(part + (g + 8) * kActRows + 2 * t) = make_float2(acc[2], acc[3]);
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot)) : "memory");
     }
+  }
 }
 
 struct MmaPlan {
-    int nseg = 0, pitch = 0, stages = 0, rgbuf = 0, max_pairs = 0;
+    int npass = 0, nseg = 0, pitch = 0, stages = 0, rgbuf = 0, max_pairs = 0;
     size_t smem = 0;
 };
 
-// Ring geometry for `nblk` blocks per row, or nseg = 0 when the shape does not fit this kernel.
+constexpr int kMaxPairs = 12;   // block pairs a consumer warp can keep in registers (largest instantiation)
+
+// Ring geometry for `nblk` blocks per row: the fewest passes over K whose K slices fit the
+// registers, then the fewest segments that still give a ring of at least 4 stages (else the
+// deepest ring).  npass = 0 when nothing fits.
 MmaPlan plan_mma(tpb_handle_t h, int nblk) {
-    MmaPlan best;
     const size_t limit = (size_t)h->smem_optin - 1024;
-    for (int nseg = 1; nseg <= kConsumers; nseg *= 2) {
-        if (nblk / 8 < nseg) break;
-        int seg_blocks = 0, max_pairs = 0;
-        const int wps = kConsumers / nseg;
-        for (int s = 0; s < nseg; s++) {
-            const int b = seg_blk0(nblk, nseg, s + 1) - seg_blk0(nblk, nseg, s);
-            seg_blocks = b > seg_blocks ? b : seg_blocks;
-            for (int wi = 0; wi < wps; wi++) {
-                const int n = warp_pair0(b / 2, wps, wi + 1) - warp_pair0(b / 2, wps, wi);
-                max_pairs = n > max_pairs ? n : max_pairs;
+    for (int npass = 1; npass <= 8; npass++) {
+        if (nblk / 8 < npass) break;
+        MmaPlan best;
+        for (int nseg = 1; nseg <= kConsumers; nseg *= 2) {
+            int seg_blocks = 0, max_pairs = 0;
+            bool ok = true;
+            const int wps = kConsumers / nseg;
+            for (int ps = 0; ps < npass && ok; ps++) {
+                const int pb0 = pass_blk0(nblk, npass, ps), pb1 = pass_blk0(nblk, npass, ps + 1);
+                if ((pb1 - pb0) / 8 < nseg) ok = false;
+                for (int sg = 0; sg < nseg && ok; sg++) {
+                    const int nb = seg_blk0(pb0, pb1, nseg, sg + 1) - seg_blk0(pb0, pb1, nseg, sg);
+                    seg_blocks = nb > seg_blocks ? nb : seg_blocks;
+                    for (int wi = 0; wi < wps; wi++) {
+                        const int n = warp_pair0(nb / 2, wps, wi + 1) - warp_pair0(nb / 2, wps, wi);
+                        max_pairs = n > max_pairs ? n : max_pairs;
+                    }
+                }
             }
-        }
-        // rows at 4 words modulo 32 banks, 16-byte aligned
-        int pitch_w = seg_blocks * kBlockBytes / 4;
-        pitch_w += ((4 - pitch_w % 32) + 32) % 32;
-        const int pitch = pitch_w * 4;
-        const size_t stage = (size_t)kStageRows * pitch;
-        const size_t fixed = (size_t)kActRows * nblk * 4 + 64 + 2 * 8 * 16;
-        for (int stages = 8; stages >= 3; stages--) {
-            const int rgbuf = (stages - 1 + nseg - 1) / nseg + 1;
-            const size_t smem = stages * stage + fixed + (size_t)rgbuf * kConsumers * kPartFloats * 4;
-            if (smem > limit) continue;
-            // prefer the fewest segments that still give >= 4 stages, else the deepest ring
-            if (best.nseg == 0 || (best.stages < 4 && stages > best.stages)) {
-                best.nseg = nseg;
-                best.pitch = pitch;
-                best.stages = stages;
-                best.rgbuf = rgbuf;
-                best.max_pairs = max_pairs;
-                best.smem = smem;
+            if (!ok) break;
+            if (max_pairs > kMaxPairs) continue;
+            // rows at 4 words modulo 32 banks, 16-byte aligned
+            int pitch_w = seg_blocks * kBlockBytes / 4;
+            pitch_w += ((4 - pitch_w % 32) + 32) % 32;
+            const int pitch = pitch_w * 4;
+            const size_t stage = (size_t)kStageRows * pitch;
+            const size_t fixed = (size_t)kActRows * nblk * 4 + 64 + 2 * 8 * 16;
+            for (int stages = 8; stages >= 3; stages--) {
+                const int rgbuf = (stages - 1 + nseg - 1) / nseg + 1;
+                const size_t smem = stages * stage + fixed + (size_t)rgbuf * kConsumers * kPartFloats * 4;
+                if (smem > limit) continue;
+                if (best.npass == 0 || (best.stages < 4 && stages > best.stages)) {
+                    best.npass = npass;
+                    best.nseg = nseg;
+                    best.pitch = pitch;
+                    best.stages = stages;
+                    best.rgbuf = rgbuf;
+                    best.max_pairs = max_pairs;
+                    best.smem = smem;
+                }
+                break;
             }
-            break;
+            if (best.npass != 0 && best.stages >= 4) break;
         }
-        if (best.nseg != 0 && best.stages >= 4) break;
+        if (best.npass != 0) return best;
     }
-    return best;
+    return MmaPlan();
 }
 
 template <int NP>
@@ -337,14 +407,14 @@ int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, size_t sm
 bool tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols) {
     if (cols % 256 != 0 || rows < 1) return false;
     const MmaPlan pl = plan_mma(h, (int)(cols / 32));
-    return pl.nseg != 0 && pl.max_pairs <= 18;
+    return pl.npass != 0;
 }
 
 int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale, int64_t rows,
                              int64_t cols, const void *xq, int ng, int row_off, int n_total) {
     const int nblk = (int)(cols / 32);
     const MmaPlan pl = plan_mma(h, nblk);
-    if (pl.nseg == 0 || pl.max_pairs > 18)
+    if (pl.npass == 0)
         return tpb_fail(h, TPB_ERR_INVALID_ARG, "q8_0 gemv: %lld columns do not fit the register-resident kernel",
                         (long long)cols);
     MmaGemvParams p;
@@ -357,12 +427,25 @@ int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const vo
     p.cols = (int)cols;
     p.nblk = nblk;
     p.m = ng;
+    p.npass = pl.npass;
     p.nseg = pl.nseg;
     p.pitch = pl.pitch;
     p.stages = pl.stages;
     p.rgbuf = pl.rgbuf;
     p.status = h->d_status;
+    {
+        const char *e = getenv("TPB_GEMV_MMA_DEBUG");
+        p.debug = e ? atoi(e) : 0;
+        if (p.debug & 2) {   // experiment: rows of a stage 128-byte aligned (bank conflicts, aligned copies)
+            const int pitch128 = (pl.pitch + 127) / 128 * 128;
+            if ((size_t)pl.stages * kStageRows * (pitch128 - pl.pitch) + pl.smem <= (size_t)h->smem_optin - 1024) {
+                p.pitch = pitch128;
+                const_cast<MmaPlan &>(pl).smem += (size_t)pl.stages * kStageRows * (pitch128 - pl.pitch);
+            } else {
+                p.debug &= ~2;
+            }
+        }
+    }
     if (pl.max_pairs <= 6) return launch_np<6>(h, st, p, pl.smem);
-    if (pl.max_pairs <= 12) return launch_np<12>(h, st, p, pl.smem);
-    return launch_np<18>(h, st, p, pl.smem);
+    return launch_np<kMaxPairs>(h, st, p, pl.smem);
 }

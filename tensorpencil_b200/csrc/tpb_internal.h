@@ -43,6 +43,7 @@ struct tpb_handle_s {
     // switches read from the environment once, at tpb_create
     bool opt_w4_fused = false;      // TPB_W4_FUSED=1: unpack int4 weights inside the GEMM
     bool opt_gemm_one_cta = false;  // TPB_GEMM_ONE_CTA=1: keep large GEMMs on the one-CTA kernel
+    int opt_gemm_ablate = 0;        // TPB_GEMM_ABLATE=<bits>: timing diagnosis of the two-CTA GEMM (see GemmParams)
     char err[512] = {0};
 };
 
