@@ -333,8 +333,11 @@ int tpb_convrot_prep_fused(tpb_handle_t h, tpb_stream_t stream, int op, const vo
  * block layout (src/core/quants.zig:9-16).  cols % 256 == 0.
  *   y[i*rows + r] = scale * sum_k dequant(w[r])[k] * (d_x * q_x)[i][k]
  * q6_k rows are not multiples of 16 bytes: the kernel's bulk copies are rounded out to 16-byte
- * boundaries and may read (and ignore) up to 14 bytes past the last row, inside the same
- * allocation granule.  iq4_nl: q4_0's layout with ggml's 16-entry value table. */
+ * boundaries, so the copy of the last row may read (and ignore) up to 14 bytes beyond the
+ * weights -- never beyond the 16-byte word their last byte lies in.  With w 16-byte aligned, as
+ * required, that word cannot straddle a page or an allocation boundary, so the read cannot
+ * fault; when rows * row_bytes is a multiple of 16 nothing outside the weights is read at all.
+ * iq4_nl: q4_0's layout with ggml's 16-entry value table. */
 typedef enum tpb_gguf_format {
     TPB_GGUF_Q8_0 = 0,
     TPB_GGUF_Q4_0 = 1,

@@ -10,9 +10,12 @@
 // swapped.  Every consumer warp owns a fixed slice of K; a lane keeps its part of the
 // activations of that slice in registers from start to end, laid out as the B operand of
 // mma.sync.m16n8k32 (8 activation rows on the n side: two registers per Q8_0 block), and
-// each Q8_0 block of 16 weight rows is one A operand: four shared-memory words per lane and
-// one MMA give the 16 x 8 exact int32 block sums that the dp4a kernel needs 8 dp4a per row
-// and activation row for.  The per-block scaling stays the reference's
+// each Q8_0 block of 8 weight rows is the upper half of an A operand (the lower half is zero):
+// two shared-memory words per lane and one MMA give the 8 x 8 exact int32 block sums that the
+// dp4a kernel needs 8 dp4a per row and activation row for.  (Eight rows, not the sixteen the
+// instruction could take: a stage of the ring is then half as large, there are twice as many
+// of them, and a stage is consumed in half the time -- with sixteen-row stages the round trip
+// "consumed, refill requested, data back" was longer than four stages could cover.)  The per-block scaling stays the reference's
 // (src/gpu/cuda/elt.zig:1984-2005):
 //   acc += float(sumi) * (d_w * d_x)   in f32, block after block.
 // Rows too long for the registers (more than 12 block pairs per warp) are taken in several
@@ -20,14 +23,14 @@
 // first add to the y the first one wrote.
 //
 // Data path.  One CTA per SM owns a contiguous range of weight rows.  Four producer warps stream
-// them in stages of 16 rows x one K segment with one 1-D bulk copy per row (cp.async.bulk,
+// them in stages of 8 rows x one K segment with one 1-D bulk copy per row (cp.async.bulk,
 // completion on the stage's "full" mbarrier, no multicast) into a ring that fills most of
 // shared memory; they start before griddepcontrol.wait, so under programmatic dependent launch
-// the ring fills while the previous kernel drains.  (Four warps, four rows each, because a warp
+// the ring fills while the previous kernel drains.  (Four warps, two rows each, because a warp
 // gets a bulk copy under way only every ~225 cycles: measured, one warp issuing all sixteen
 // copies of every stage capped the kernel at 3.4 TB/s.  The register file hands out registers
 // to warps in fours, so warps 17..19 cost nothing.)  The warps whose K slice lies in a stage's
-// segment wait for it, multiply, write their 16 x 8 partial sums to a small buffer and arrive
+// segment wait for it, multiply, write their 8 x 8 partial sums to a small buffer and arrive
 // on the stage's "empty" mbarrier.  When the last segment of a row group has been released,
 // the first producer warp -- which has to wait for that anyway before it may refill the slot -- adds
 // the partials in warp order (a fixed order: results do not depend on timing), applies
@@ -52,11 +55,12 @@ namespace {
 constexpr int kBlockBytes = 34;
 constexpr int kPairBytes = 68;
 constexpr int kConsumers = 16;                 // consumer warps 0..15
-constexpr int kProducers = 4;                  // producer warps 16..19, four rows of every stage each
+constexpr int kProducers = 4;                  // producer warps 16..19, two rows of every stage each
 constexpr int kThreadsMma = (kConsumers + kProducers) * 32;
-constexpr int kStageRows = 16;                 // weight rows per stage = m of the MMA
+constexpr int kStageRows = 8;                  // weight rows per stage (rows 0..7 of the MMA's m side)
 constexpr int kActRows = 8;                    // activation rows = n of the MMA
-constexpr int kPartFloats = kStageRows * kActRows;   // partial sums of one warp for one stage
+constexpr int kPartFloats = kStageRows * kActRows;
+constexpr int kGroup = 3;                      // pairs whose loads and MMAs are issued before any of their results is used   // partial sums of one warp for one stage
 
 struct MmaGemvParams {
     float *y;
@@ -70,27 +74,28 @@ struct MmaGemvParams {
     int pitch;         // bytes between rows of a stage
     int stages;        // ring depth
     int rgbuf;         // row groups of partial sums kept
-    int debug;         // TPB_GEMV_MMA_DEBUG (diagnosis): bit 0 = consumers skip the arithmetic
     uint32_t *status;
 };
 
 // Pass p of a row covers blocks [pass_blk0(p), pass_blk0(p + 1)); K segment s of a pass covers
 // [seg_blk0(s), seg_blk0(s + 1)) of those.  Both are whole units of 8 blocks (272 bytes, a multiple of 16).
-__host__ __device__ inline int pass_blk0(int nblk, int npass, int p) { return (int)((long long)(nblk / 8) * p / npass) * 8; }
-__host__ __device__ inline int seg_blk0(int pb0, int pb1, int nseg, int s) {
-    return pb0 + (int)((long long)((pb1 - pb0) / 8) * s / nseg) * 8;
-}
+// (32-bit arithmetic on purpose: nblk <= 2^19, p, s <= 16, and a 64-bit division costs hundreds of
+// cycles on the GPU -- four of them per stage made the producer warps the bottleneck of the kernel.)
+__host__ __device__ inline int pass_blk0(int nblk, int npass, int p) { return (nblk / 8) * p / npass * 8; }
+__host__ __device__ inline int seg_blk0(int pb0, int pb1, int nseg, int s) { return pb0 + ((pb1 - pb0) / 8) * s / nseg * 8; }
 // pairs [lo, hi) of consumer `wi` (0 .. wps-1) inside a segment of `pairs` block pairs
-__host__ __device__ inline int warp_pair0(int pairs, int wps, int wi) { return (int)((long long)pairs * wi / wps); }
+__host__ __device__ inline int warp_pair0(int pairs, int wps, int wi) { return pairs * wi / wps; }
 
-// C[16 weight rows][8 activation rows] = A[16][32] * B[32][8], int8 -> int32, C starts at zero.
-// Lane (g = lane / 4, t = lane % 4): a0/a2 = weight row g, k = 4t.. and 16+4t..; a1/a3 = weight row
-// g + 8; b0/b1 = activation row g, same k; c0,c1 = row g x activation rows 2t, 2t+1; c2,c3 = row g + 8.
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+// C[8 weight rows][8 activation rows] = A[8 (of 16)][32] * B[32][8], int8 -> int32, C starts at zero.
+// Lane (g = lane / 4, t = lane % 4): a0/a2 = weight row g, k = 4t.. and 16+4t..; a1/a3 (rows 8..15)
+// are zero; b0/b1 = activation row g, same k; c0, c1 = weight row g x activation rows 2t, 2t+1.
+__device__ __forceinline__ void mma_s8(int &c0, int &c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    int c2, c3;
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%8,%5,%8}, {%6,%7}, {%8,%8,%8,%8};"
+        : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+        : "r"(a0), "r"(a2), "r"(b0), "r"(b1), "r"(0));
+    (void)c2;
+    (void)c3;
 }
 
 // Shared-memory loads by 32-bit shared address: one address register instead of a generic pointer pair.
@@ -119,11 +124,18 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     const size_t row_bytes = (size_t)nblk * kBlockBytes;
 
     uint8_t *ring = smem;
-    float *s_dx = reinterpret_cast<float *>(smem + (size_t)S * stage_bytes);       // [8][nblk]
+    float *s_dx = reinterpret_cast<float *>(smem + (size_t)S * stage_bytes);       // [nblk][8 activation rows]
     float *s_part = s_dx + (size_t)kActRows * nblk;                                 // [rgbuf][kConsumers][128]
     const uint32_t bars = smem_u32(s_part + (size_t)p.rgbuf * kConsumers * kPartFloats);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    // first block of every (pass, segment), plus one entry that closes the last segment of each pass:
+    // s_seg[pass * (nseg + 1) + seg]; looked up instead of recomputed (integer divisions) per stage
+    int *s_seg = reinterpret_cast<int *>(s_part + (size_t)p.rgbuf * kConsumers * kPartFloats) + 2 * 2 * 16;
+    for (int e = threadIdx.x; e < p.npass * (p.nseg + 1); e += blockDim.x) {
+        const int ps = e / (p.nseg + 1), sg = e - ps * (p.nseg + 1);
+        s_seg[e] = seg_blk0(pass_blk0(nblk, p.npass, ps), pass_blk0(nblk, p.npass, ps + 1), p.nseg, sg);
+    }
 
     const int wps = kConsumers / p.nseg;  // consumer warps per K segment
     if (threadIdx.x == 0) {
@@ -137,8 +149,9 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // this CTA's rows and its stages: (pass, row group, segment), row groups of 16 rows
-    const int r_begin = (int)((long long)p.rows * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int r_base = p.rows / (int)gridDim.x, r_rem = p.rows % (int)gridDim.x;   // the first r_rem CTAs take one row more
+    const int r_begin = (int)blockIdx.x * r_base + min((int)blockIdx.x, r_rem);
+    const int r_end = r_begin + r_base + ((int)blockIdx.x < r_rem ? 1 : 0);
     const int n_rg = (r_end - r_begin + kStageRows - 1) / kStageRows;
     const int total = p.npass * n_rg * p.nseg;
 
@@ -146,69 +159,87 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
         // ---------------- producers (the first one also reduces) ----------------
         const int pw = warp - kConsumers;
         constexpr int kRowsPerProducer = kStageRows / kProducers;
-        auto issue = [&](int i) {  // whole warp: lane r starts the copy of this warp's r-th row of stage i
-            const int v = i / p.nseg, seg = i - v * p.nseg;      // v = row-group visit: pass * n_rg + rg
-            const int pass = v / n_rg, rg = v - pass * n_rg;
-            const int row0 = r_begin + rg * kStageRows;
+        // the stage the next issue() fills: (pass, row group, segment), ring slot, all advanced by one per call
+        int is_pass = 0, is_rg = 0, is_seg = 0, is_slot = 0;
+        auto issue = [&]() {  // whole warp: lane r starts the copy of this warp's r-th row of the next stage
+            const int row0 = r_begin + is_rg * kStageRows;
             const int nrow = min(kStageRows, r_end - row0);
-            const int pb0 = pass_blk0(nblk, p.npass, pass), pb1 = pass_blk0(nblk, p.npass, pass + 1);
-            const int b0 = seg_blk0(pb0, pb1, p.nseg, seg), b1 = seg_blk0(pb0, pb1, p.nseg, seg + 1);
+            const int b0 = s_seg[is_pass * (p.nseg + 1) + is_seg], b1 = s_seg[is_pass * (p.nseg + 1) + is_seg + 1];
             const uint32_t bytes = (uint32_t)(b1 - b0) * kBlockBytes;
-            const int slot = i % S;
-            const uint32_t bar = full_bar(slot);
+            const uint32_t bar = full_bar(is_slot);
             const int my_rows = max(0, min(kRowsPerProducer, nrow - pw * kRowsPerProducer));
             if (lane == 0)   // every producer warp arrives, also with nothing to copy (the barrier counts four)
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)my_rows)
                              : "memory");
             __syncwarp();
             const int r = pw * kRowsPerProducer + lane;
-            const uint32_t dst = smem_u32(ring + (size_t)slot * stage_bytes);
+            const uint32_t dst = smem_u32(ring) + (uint32_t)(is_slot * stage_bytes);
             const uint8_t *src = p.w + (size_t)row0 * row_bytes + (size_t)b0 * kBlockBytes;
             if (lane < my_rows) bulk_g2s(dst + (uint32_t)(r * p.pitch), src + (size_t)r * row_bytes, bytes, bar);
+            if (++is_slot == S) is_slot = 0;
+            if (++is_seg == p.nseg) {
+                is_seg = 0;
+                if (++is_rg == n_rg) {
+                    is_rg = 0;
+                    is_pass++;
+                }
+            }
         };
-        auto reduce = [&](int v) {  // all lanes: y of one row-group visit from the consumers' partial sums
-            // a warp's partials: [16 weight rows][8 activation rows]; this lane: row lane / 2, activation rows 4 (lane % 2) ..
-            const int pass = v / n_rg, rg = v - pass * n_rg;
-            const float *part = s_part + (size_t)(v % p.rgbuf) * kConsumers * kPartFloats + 4 * lane;
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto reduce = [&](int pass, int rg, int pbuf) {  // all lanes: y of one row-group visit from the consumers' partial sums
+            // a warp's partials: [8 weight rows][8 activation rows]; this lane: row lane / 4, activation rows 2 (lane % 4) ..
+            const float *part = s_part + (size_t)pbuf * kConsumers * kPartFloats + 2 * lane;
+            float2 sum = make_float2(0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < kConsumers; w++) {
-                const float4 v = *reinterpret_cast<const float4 *>(part + w * kPartFloats);
-                sum.x += v.x;
-                sum.y += v.y;
-                sum.z += v.z;
-                sum.w += v.w;
+                const float2 pv = *reinterpret_cast<const float2 *>(part + w * kPartFloats);
+                sum.x += pv.x;
+                sum.y += pv.y;
             }
-            const int row = r_begin + rg * kStageRows + (lane >> 1);
-            const int m0 = 4 * (lane & 1);
+            const int row = r_begin + rg * kStageRows + (lane >> 2);
+            const int m0 = 2 * (lane & 3);
             if (row < r_end) {
                 // later passes add to what this same lane stored in the pass before
-                const float v4[4] = {sum.x, sum.y, sum.z, sum.w};
+                const float v2[2] = {sum.x, sum.y};
 #pragma unroll
-                for (int e = 0; e < 4; e++)
+                for (int e = 0; e < 2; e++)
                     if (m0 + e < p.m) {
                         float *dst = p.y + (size_t)(m0 + e) * p.rows + row;
-                        *dst = pass == 0 ? v4[e] * p.scale : fmaf(v4[e], p.scale, *dst);
+                        *dst = pass == 0 ? v2[e] * p.scale : fmaf(v2[e], p.scale, *dst);
                     }
             }
         };
         // weights are constants: the ring starts filling before the previous kernel has finished
-        for (int i = 0; i < S && i < total; i++) issue(i);
+        for (int i = 0; i < S && i < total; i++) issue();
         asm volatile("griddepcontrol.wait;" ::: "memory");
         bool ok = true;
+        // the stage whose release is awaited next: ring slot and phase, segment, row group, pass, partial buffer
+        int w_slot = 0, w_seg = 0, w_rg = 0, w_pass = 0, w_pbuf = 0;
+        uint32_t w_par = 0;
         for (int j = 0; j < total && ok; j++) {
             // stage j has been consumed by its warps
-            ok = mbar_wait(empty_bar(j % S), (uint32_t)(j / S) & 1u, p.status, (7u << 24) | (uint32_t)(j % S));
+            ok = mbar_wait(empty_bar(w_slot), w_par, p.status, (7u << 24) | (uint32_t)w_slot);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             // Partial sums are added before this warp's part of the refill goes out, and the refilled
             // stage is not "full" without it: no consumer can overwrite a partial that is still needed.
-            if (pw == 0 && j % p.nseg == p.nseg - 1) reduce(j / p.nseg);
+            if (pw == 0 && w_seg == p.nseg - 1) reduce(w_pass, w_rg, w_pbuf);
             __syncwarp();
             if (j + S < total) {
                 // order the consumers' generic-proxy reads of the slot before the async-proxy refill
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue(j + S);
+                issue();
+            }
+            if (++w_slot == S) {
+                w_slot = 0;
+                w_par ^= 1u;
+            }
+            if (++w_seg == p.nseg) {
+                w_seg = 0;
+                if (++w_pbuf == p.rgbuf) w_pbuf = 0;
+                if (++w_rg == n_rg) {
+                    w_rg = 0;
+                    w_pass++;
+                }
             }
         }
         return;
@@ -219,30 +250,12 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     const int seg = warp / wps, wi = warp - seg * wps;
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // activation scales of all 8 (padded) rows -> shared memory; consumers only
-    // (the loads of four rounds go out together: a round trip to L2 each would cost a microsecond)
-    for (int i0 = threadIdx.x; i0 < kActRows * nblk; i0 += 4 * kConsumers * 32) {
-        float v[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * kConsumers * 32;
-            const int m = i / nblk;
-            v[u] = (i < kActRows * nblk && m < p.m) ? __ldcg(p.xd + (size_t)m * nblk + (i - m * nblk)) : 0.0f;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * kConsumers * 32;
-            if (i < kActRows * nblk) s_dx[i] = v[u];
-        }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-
-    const uint32_t hi_rows = 8u * (uint32_t)p.pitch;   // weight row g + 8
-    const uint32_t dx_next = 4u * (uint32_t)nblk;      // next activation row's scales
     bool ok = true;
+    // this warp's next stage: ring slot and phase (it takes every nseg-th stage), partial buffer
+    int c_slot = seg % S, c_pbuf = 0;
+    uint32_t c_par = (uint32_t)(seg / S) & 1u;
   for (int pass = 0; pass < p.npass && ok; pass++) {
-    const int pb0 = pass_blk0(nblk, p.npass, pass), pb1 = pass_blk0(nblk, p.npass, pass + 1);
-    const int sb0 = seg_blk0(pb0, pb1, p.nseg, seg), sb1 = seg_blk0(pb0, pb1, p.nseg, seg + 1);
+    const int sb0 = s_seg[pass * (p.nseg + 1) + seg], sb1 = s_seg[pass * (p.nseg + 1) + seg + 1];
     const int seg_pairs = (sb1 - sb0) / 2;
     const int pp0 = warp_pair0(seg_pairs, wps, wi), pp1 = warp_pair0(seg_pairs, wps, wi + 1);
     const int np = pp1 - pp0;  // <= NP (checked by the host)
@@ -265,6 +278,30 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
             b[q][3] = __ldcg(x0 + 12 + t);
         }
     }
+    if (pass == 0) {
+        // (after the activation loads above have gone out, so that the two round trips overlap)
+        // activation scales of all 8 (padded) rows -> shared memory; consumers only
+        // (the loads of four rounds go out together: a round trip to L2 each would cost a microsecond)
+        for (int i0 = threadIdx.x; i0 < kActRows * nblk; i0 += 4 * kConsumers * 32) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * kConsumers * 32;
+                const int m = i / nblk;
+                v[u] = (i < kActRows * nblk && m < p.m) ? __ldcg(p.xd + (size_t)m * nblk + (i - m * nblk)) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                // shared layout [block][activation row]: the four lanes t of a quad then read 32 contiguous
+                // bytes per block (row-major [m][nblk] put all four in one bank: measured, those loads
+                // alone made the consumers the bottleneck)
+                const int i = i0 + u * kConsumers * 32;
+                const int m = i / nblk;
+                if (i < kActRows * nblk) s_dx[(i - m * nblk) * kActRows + m] = v[u];
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+    }
 #pragma unroll
     for (int q = 0; q < NP; q++) {
         // all 32 lanes take part in the shuffles (q < np is warp-uniform)
@@ -282,49 +319,60 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     // shared addresses relative to a stage: this warp's first pair in weight row g, word t
     const uint32_t ring_u32 = smem_u32(ring) + (uint32_t)(pp0 * kPairBytes) + (uint32_t)(g * p.pitch) + 4u * (uint32_t)t;
     // activation scales of activation rows 2t and 2t+1, this warp's first block
-    const uint32_t dx_u32 = smem_u32(s_dx + (size_t)(2 * t) * nblk + sb0 + 2 * pp0);
+    const uint32_t dx_u32 = smem_u32(s_dx + (size_t)(sb0 + 2 * pp0) * kActRows + 2 * t);
 
     for (int rg = 0; rg < n_rg && ok; rg++) {
-        const int v = pass * n_rg + rg;
-        const int i = v * p.nseg + seg;
-        const int slot = i % S;
-        ok = mbar_wait(full_bar(slot), (uint32_t)(i / S) & 1u, p.status, (8u << 24) | (uint32_t)slot);
+        ok = mbar_wait(full_bar(c_slot), c_par, p.status, (8u << 24) | (uint32_t)c_slot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint32_t wl = ring_u32 + (uint32_t)(slot * stage_bytes), wh = wl + hi_rows;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t wl = ring_u32 + (uint32_t)(c_slot * stage_bytes);
+        float acc0 = 0.0f, acc1 = 0.0f;
+        // kGroup pairs at a time: first every load and both MMAs of each pair (independent of one
+        // another, so the loads and the tensor-core latencies overlap), then the scaling.
 #pragma unroll
-        for (int q = 0; q < NP; q++) {
-            if (q < np && !(p.debug & 1)) {
-                const uint32_t o = (uint32_t)(q * kPairBytes);
-                // words t, 4+t, 8 (and 0 for the scale) of the first block, 9+t and 13+t of the second
-                const uint32_t l0 = lds32(wl + o - 4u * t), l_lo = lds32(wl + o), l_hi = lds32(wl + o + 16);
-                const uint32_t l8 = lds32(wl + o + 32 - 4u * t), l_v0 = lds32(wl + o + 36), l_v1 = lds32(wl + o + 52);
-                const uint32_t h0 = lds32(wh + o - 4u * t), h_lo = lds32(wh + o), h_hi = lds32(wh + o + 16);
-                const uint32_t h8 = lds32(wh + o + 32 - 4u * t), h_v0 = lds32(wh + o + 36), h_v1 = lds32(wh + o + 52);
-                const float2 dxa = lds_f2(dx_u32 + 8u * q), dxb = lds_f2(dx_u32 + dx_next + 8u * q);
-                int c0[4], c1[4];
-                mma_s8(c0, t == 0 ? __funnelshift_r(l_lo, l8, 16) : l_lo, t == 0 ? __funnelshift_r(h_lo, h8, 16) : h_lo,
-                       l_hi, h_hi, b[q][0], b[q][1]);
-                mma_s8(c1, l_v0, h_v0, l_v1, h_v1, b[q][2], b[q][3]);
-                // weight scales: f16 in the low half of word 0 (first block) and the high half of word 8 (second)
-                const float dl0 = f16lo(l0), dl1 = f16hi(l8), dh0 = f16lo(h0), dh1 = f16hi(h8);
-                acc[0] = fmaf(i2f_small(c0[0]), dl0 * dxa.x, acc[0]);
-                acc[1] = fmaf(i2f_small(c0[1]), dl0 * dxb.x, acc[1]);
-                acc[2] = fmaf(i2f_small(c0[2]), dh0 * dxa.x, acc[2]);
-                acc[3] = fmaf(i2f_small(c0[3]), dh0 * dxb.x, acc[3]);
-                acc[0] = fmaf(i2f_small(c1[0]), dl1 * dxa.y, acc[0]);
-                acc[1] = fmaf(i2f_small(c1[1]), dl1 * dxb.y, acc[1]);
-                acc[2] = fmaf(i2f_small(c1[2]), dh1 * dxa.y, acc[2]);
-                acc[3] = fmaf(i2f_small(c1[3]), dh1 * dxb.y, acc[3]);
+        for (int q0 = 0; q0 < NP; q0 += kGroup) {
+            int c[kGroup][4];
+            uint32_t sc[kGroup][2];
+#pragma unroll
+            for (int u = 0; u < kGroup; u++) {
+                const int q = q0 + u;
+                if (q < NP && q < np) {
+                    const uint32_t o = (uint32_t)(q * kPairBytes);
+                    // words t, 4+t, 8 (and 0 for the scale) of the first block, 9+t and 13+t of the second
+                    const uint32_t l0 = lds32(wl + o - 4u * t), l_lo = lds32(wl + o), l_hi = lds32(wl + o + 16);
+                    const uint32_t l8 = lds32(wl + o + 32 - 4u * t), l_v0 = lds32(wl + o + 36), l_v1 = lds32(wl + o + 52);
+                    mma_s8(c[u][0], c[u][1], t == 0 ? __funnelshift_r(l_lo, l8, 16) : l_lo, l_hi, b[q][0], b[q][1]);
+                    mma_s8(c[u][2], c[u][3], l_v0, l_v1, b[q][2], b[q][3]);
+                    sc[u][0] = l0;
+                    sc[u][1] = l8;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kGroup; u++) {
+                const int q = q0 + u;
+                if (q < NP && q < np) {
+                    // scales of activation rows (2t, 2t+1) for the pair's first and second block
+                    const float2 dx0 = lds_f2(dx_u32 + 64u * q), dx1 = lds_f2(dx_u32 + 64u * q + 32u);
+                    // weight scales: f16 in the low half of word 0 (first block) and the high half of word 8 (second)
+                    const float d0 = f16lo(sc[u][0]), d1 = f16hi(sc[u][1]);
+                    acc0 = fmaf(i2f_small(c[u][0]), d0 * dx0.x, acc0);
+                    acc1 = fmaf(i2f_small(c[u][1]), d0 * dx0.y, acc1);
+                    acc0 = fmaf(i2f_small(c[u][2]), d1 * dx1.x, acc0);
+                    acc1 = fmaf(i2f_small(c[u][3]), d1 * dx1.y, acc1);
+                }
             }
         }
-        // this warp's K slice of C[weight row][activation row]: rows g and g + 8, activation rows 2t, 2t+1
-        float *part = s_part + ((size_t)(v % p.rgbuf) * kConsumers + warp) * kPartFloats;
-        *reinterpret_cast<float2 *>(part + g * kActRows + 2 * t) = make_float2(acc[0], acc[1]);
-        *reinterpret_cast<float2 *>(part + (g + 8) * kActRows + 2 * t) = make_float2(acc[2], acc[3]);
+        // this warp's K slice of C[weight row g][activation rows 2t, 2t+1]
+        float *part = s_part + ((size_t)c_pbuf * kConsumers + warp) * kPartFloats;
+        *reinterpret_cast<float2 *>(part + g * kActRows + 2 * t) = make_float2(acc0, acc1);
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot)) : "memory");
+        if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty_bar(c_slot)) : "memory");
+        c_slot += p.nseg;
+        while (c_slot >= S) {
+            c_slot -= S;
+            c_par ^= 1u;
+        }
+        if (++c_pbuf == p.rgbuf) c_pbuf = 0;
     }
   }
 }
@@ -337,7 +385,7 @@ struct MmaPlan {
 constexpr int kMaxPairs = 12;   // block pairs a consumer warp can keep in registers (largest instantiation)
 
 // Ring geometry for `nblk` blocks per row: the fewest passes over K whose K slices fit the
-// registers, then the fewest segments that still give a ring of at least 4 stages (else the
+// registers, then the fewest segments that still give a ring of at least 6 stages (else the
 // deepest ring).  npass = 0 when nothing fits.
 MmaPlan plan_mma(tpb_handle_t h, int nblk) {
     const size_t limit = (size_t)h->smem_optin - 1024;
@@ -367,12 +415,12 @@ MmaPlan plan_mma(tpb_handle_t h, int nblk) {
             pitch_w += ((4 - pitch_w % 32) + 32) % 32;
             const int pitch = pitch_w * 4;
             const size_t stage = (size_t)kStageRows * pitch;
-            const size_t fixed = (size_t)kActRows * nblk * 4 + 64 + 2 * 8 * 16;
-            for (int stages = 8; stages >= 3; stages--) {
+            const size_t fixed = (size_t)kActRows * nblk * 4 + 64 + 2 * 8 * 16 + 4 * 8 * 17;   // + the segment table
+            for (int stages = 12; stages >= 3; stages--) {
                 const int rgbuf = (stages - 1 + nseg - 1) / nseg + 1;
                 const size_t smem = stages * stage + fixed + (size_t)rgbuf * kConsumers * kPartFloats * 4;
                 if (smem > limit) continue;
-                if (best.npass == 0 || (best.stages < 4 && stages > best.stages)) {
+                if (best.npass == 0 || (best.stages < 6 && stages > best.stages)) {
                     best.npass = npass;
                     best.nseg = nseg;
                     best.pitch = pitch;
@@ -383,7 +431,7 @@ MmaPlan plan_mma(tpb_handle_t h, int nblk) {
                 }
                 break;
             }
-            if (best.npass != 0 && best.stages >= 4) break;
+            if (best.npass != 0 && best.stages >= 6) break;
         }
         if (best.npass != 0) return best;
     }
@@ -433,19 +481,6 @@ int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const vo
     p.stages = pl.stages;
     p.rgbuf = pl.rgbuf;
     p.status = h->d_status;
-    {
-        const char *e = getenv("TPB_GEMV_MMA_DEBUG");
-        p.debug = e ? atoi(e) : 0;
-        if (p.debug & 2) {   // experiment: rows of a stage 128-byte aligned (bank conflicts, aligned copies)
-            const int pitch128 = (pl.pitch + 127) / 128 * 128;
-            if ((size_t)pl.stages * kStageRows * (pitch128 - pl.pitch) + pl.smem <= (size_t)h->smem_optin - 1024) {
-                p.pitch = pitch128;
-                const_cast<MmaPlan &>(pl).smem += (size_t)pl.stages * kStageRows * (pitch128 - pl.pitch);
-            } else {
-                p.debug &= ~2;
-            }
-        }
-    }
     if (pl.max_pairs <= 6) return launch_np<6>(h, st, p, pl.smem);
     return launch_np<kMaxPairs>(h, st, p, pl.smem);
 }

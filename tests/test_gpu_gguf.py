@@ -96,3 +96,27 @@ def test_gguf_gemv_rejects_bad_arguments(be):
     assert f(be.h, None, 2, y.data_ptr(), w.data_ptr(), 1.0, 8, 288, xq.data_ptr(), 1, 0, 1) == _lib.TPB_ERR_INVALID_ARG
     assert f(be.h, None, 2, y.data_ptr(), w.data_ptr(), 1.0, 8, 256, xq.data_ptr(), 9, 0, 9) == _lib.TPB_ERR_INVALID_ARG
     assert be.lib.tpb_gguf_row_bytes(2, 5120) == 20 * 144 and be.lib.tpb_gguf_row_bytes(3, 5120) == 20 * 176
+
+
+def test_q6k_weight_at_the_very_end_of_its_allocation(be):
+    """q6_k rows (210 bytes per 256 columns) are not multiples of 16 bytes, and the kernel's bulk
+    copies round the last row's copy out to the next 16-byte boundary.  The weight is placed so
+    that its last byte is the last byte but two of a torch allocation (7 rows of 2 super-blocks =
+    2940 bytes, 12 short of a multiple of 16): the rounded copy ends exactly at the allocation's
+    end, never beyond it, and the results are those of the same weight elsewhere in memory."""
+    n, k = 7, 512
+    w = synth.gguf_weights("q6_k", n, k, seed=3)
+    nbytes = w.size
+    assert nbytes % 16 == 12
+    x = (np.random.default_rng(8).random((3, k), dtype=np.float32) * 2 - 1).astype(np.float32)
+    want = run(be, "q6_k", w, n, k, x)
+    total = 1 << 20                                   # a whole allocator block of its own
+    store = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    off = total - (nbytes + 4)                        # 16-byte aligned start, 4 spare bytes at the end
+    assert off % 16 == 0 and store.data_ptr() % 512 == 0
+    store[off:off + nbytes] = torch.from_numpy(w.reshape(-1)).cuda()
+    y = torch.empty((3, n), dtype=torch.float32, device="cuda")
+    be.opGemvQuantizeX(torch.from_numpy(x).cuda(), 3 * k)
+    be.opGemvQuantQ8N("q6_k", y, store[off:off + nbytes], 1.0, n, k, 3, 0, 3)
+    be.status_poll()
+    assert np.array_equal(y.cpu().numpy(), want)
