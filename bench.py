@@ -399,6 +399,21 @@ def run_ours(args, rank: int, local: int, world: int):
                                "frac_of_dense_int8_spec_4500": tops / 4500.0,
                                "frac_of_2x_measured_bf16": tops / (2.0 * peaks["bf16_tflops"])})
                 del yy
+            # context only: the library's int8 GEMM (cuBLASLt through torch._int_mm) on the same operands,
+            # raw int32 output (4 bytes per element like the f32 case), no dequantisation
+            try:
+                fn = lambda i: torch._int_mm(qq, wsets[i % N_SETS].t())
+                for i in range(3):
+                    fn(i)
+                torch.cuda.synchronize()
+                e = timed_regions(fn, 20, stream, min_total_ms=60.0)
+                torch.cuda.synchronize()
+                ms = region_stats(e)["median_ms"] / 20
+                tops = 2.0 * M * n_ * k_ / (ms * 1e-3) / 1e12
+                shapes.append({"m": M, "n": n_, "k": k_, "out": "s32, library torch._int_mm (comparison only, not a product path)",
+                               "us": ms * 1e3, "tops": tops, "frac_of_dense_int8_spec_4500": tops / 4500.0})
+            except Exception as ex:      # the library has no int8 GEMM for this device / shape
+                shapes.append({"m": M, "n": n_, "k": k_, "out": "s32, library torch._int_mm", "unavailable": f"{type(ex).__name__}: {ex}"[:200]})
             be.i8_x, be.i8_scale, be.i8_m, be.i8_cols = saved
             del qq, wsets
         be.status_poll()
@@ -438,7 +453,13 @@ def run_ours(args, rank: int, local: int, world: int):
         value = OPS_PER_STEP * args.steps * world / (ms_total * 1e-3) / 1e12
         e2e_value = OPS_PER_STEP * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
         gemm_tops = OPS_PER_STEP / (gemm_ms * 1e-3) / 1e12
-        int8_peak = 2.0 * peaks["bf16_tflops"]
+        # The GEMM loop above runs for a fifth of a second and more without a pause, i.e. at the power-capped
+        # clock: its median region is compared with the SUSTAINED library figure; the first (fastest) region
+        # ran at the full clock and is compared with the burst figure.
+        long_loop = greg["total_ms"] >= 100.0 and bool(peaks.get("bf16_tflops_sustained"))
+        int8_peak = 2.0 * (peaks["bf16_tflops_sustained"] if long_loop else peaks["bf16_tflops"])
+        burst_ms = greg["min_ms"] / args.steps
+        burst_tops = OPS_PER_STEP / (burst_ms * 1e-3) / 1e12
         ob2 = 2 if out_bytes == 4 else 4
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -469,9 +490,15 @@ def run_ours(args, rank: int, local: int, world: int):
             "gpu_launches": gpu_launches,
             "roofline": {"bound": "tensor", "kernel": "convrot_gemm2_kernel (tcgen05 kind::i8, cta_group::2), timed alone over the same operands",
                          "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s", "frac": gemm_tops / int8_peak,
-                         "peak_note": f"2 x bf16 cuBLAS burst of {peaks['source']} peaks (the int8 tensor rate is twice bf16)",
+                         "peak_note": f"2 x the {'sustained' if long_loop else 'burst'} cuBLAS bf16 figure of {peaks['source']} peaks "
+                                      f"(the int8 tensor rate is twice bf16); achieved is the median of "
+                                      f"{greg['total_ms']:.0f} ms of back-to-back launches",
                          "frac_of_dense_int8_spec_4500": gemm_tops / 4500.0,
                          "gemm_ms": gemm_ms,
+                         "burst": {"gemm_ms": burst_ms, "tops": burst_tops,
+                                   "frac_of_2x_measured_bf16_burst": burst_tops / (2.0 * peaks["bf16_tflops"]),
+                                   "frac_of_dense_int8_spec_4500": burst_tops / 4500.0,
+                                   "what": "fastest region of the same loop (full clock, before the power cap engages)"},
                          "regions": {"count": greg["count"], "launches_each": args.steps,
                                      "ms_min": greg["min_ms"] / args.steps, "ms_max": greg["max_ms"] / args.steps},
                          "traffic": GEMM_DRAM_TRAFFIC_BYTES[args.out_dtype],
@@ -1139,7 +1166,7 @@ def run_mode_one_kernel(args, local):
         g, u = torch.randn(m, k, device="cuda"), torch.randn(m, k, device="cuda")
         for _ in range(reps):
             be.prepSiluMul(g, u, m, k, 8)
-    elif case in ("gemv1", "gemv4", "gemv8", "gemv1-down"):
+    elif case in ("gemv1", "gemv4", "gemv8", "gemv1-down", "gemv4-down", "gemv8-down"):
         m = int(case[4]) if case[4].isdigit() else 1
         n, k = (5120, 17408) if case.endswith("down") else (17408, 5120)
         w = harness.rotating_q8_weights(n, k, 1, be.device)[0]
@@ -1172,7 +1199,7 @@ def main():
     ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "attn", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
-                    "gemm-small, gemm-w4, gemm-w4-fused, gemm-w4-small, gemm-w4-fused-small, gemm-ablation, gemv1, gemv4, gemv8, gemv1-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
+                    "gemm-small, gemm-w4, gemm-w4-fused, gemm-w4-small, gemm-w4-fused-small, gemm-ablation, gemv1, gemv4, gemv8, gemv1-down, gemv4-down, gemv8-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -20,7 +20,10 @@
 //   acc += float(sumi) * (d_w * d_x)   in f32, block after block.
 // Rows too long for the registers (more than 12 block pairs per warp) are taken in several
 // passes over K: a pass streams one K range of all the CTA's rows, and the passes after the
-// first add to the y the first one wrote.
+// first add to the y the first one wrote.  Where that halves the number of passes, K is split
+// across a cluster of two CTAs instead: both stream the same rows (twice as many as a lone CTA
+// would own, so the 8-row stages divide them better), each its own half of K in one pass, and
+// at the end the first CTA adds the second one's sums, read from its shared memory, to its own.
 //
 // Data path.  One CTA per SM owns a contiguous range of weight rows.  Four producer warps stream
 // them in stages of 8 rows x one K segment with one 1-D bulk copy per row (cp.async.bulk,
@@ -74,6 +77,7 @@ struct MmaGemvParams {
     int pitch;         // bytes between rows of a stage
     int stages;        // ring depth
     int rgbuf;         // row groups of partial sums kept
+    int out_rg;        // K split: row groups of unscaled sums a CTA keeps for the final addition
     uint32_t *status;
 };
 
@@ -112,9 +116,27 @@ __device__ __forceinline__ float2 lds_f2(uint32_t addr) {
 __device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+
 // 20 warps: 65536 / 640 = 102 registers per thread, 96 after rounding to the allocation unit.
-template <int NP>
-__global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
+// KS = CTAs per cluster = parts K is split into (1 or 2).
+template <int NP, int KS>
+__global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -132,10 +154,15 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     // first block of every (pass, segment), plus one entry that closes the last segment of each pass:
     // s_seg[pass * (nseg + 1) + seg]; looked up instead of recomputed (integer divisions) per stage
     int *s_seg = reinterpret_cast<int *>(s_part + (size_t)p.rgbuf * kConsumers * kPartFloats) + 2 * 2 * 16;
+    // K split: this CTA's passes are passes crank * npass .. of npass * KS over the whole row
+    const int crank = KS > 1 ? (int)cluster_rank() : 0;
+    const int npt = p.npass * KS;
     for (int e = threadIdx.x; e < p.npass * (p.nseg + 1); e += blockDim.x) {
         const int ps = e / (p.nseg + 1), sg = e - ps * (p.nseg + 1);
-        s_seg[e] = seg_blk0(pass_blk0(nblk, p.npass, ps), pass_blk0(nblk, p.npass, ps + 1), p.nseg, sg);
+        const int gp = crank * p.npass + ps;
+        s_seg[e] = seg_blk0(pass_blk0(nblk, npt, gp), pass_blk0(nblk, npt, gp + 1), p.nseg, sg);
     }
+    float *s_out = reinterpret_cast<float *>(s_seg + 8 * 17);   // [out_rg][8 weight rows][8 activation rows], KS > 1 only
 
     const int wps = kConsumers / p.nseg;  // consumer warps per K segment
     if (threadIdx.x == 0) {
@@ -149,9 +176,11 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // this CTA's rows and its stages: (pass, row group, segment), row groups of 16 rows
-    const int r_base = p.rows / (int)gridDim.x, r_rem = p.rows % (int)gridDim.x;   // the first r_rem CTAs take one row more
-    const int r_begin = (int)blockIdx.x * r_base + min((int)blockIdx.x, r_rem);
-    const int r_end = r_begin + r_base + ((int)blockIdx.x < r_rem ? 1 : 0);
+    // (the CTAs of a cluster share their rows)
+    const int n_own = (int)gridDim.x / KS, own = (int)blockIdx.x / KS;
+    const int r_base = p.rows / n_own, r_rem = p.rows % n_own;   // the first r_rem owners take one row more
+    const int r_begin = own * r_base + min(own, r_rem);
+    const int r_end = r_begin + r_base + (own < r_rem ? 1 : 0);
     const int n_rg = (r_end - r_begin + kStageRows - 1) / kStageRows;
     const int total = p.npass * n_rg * p.nseg;
 
@@ -197,7 +226,16 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
             }
             const int row = r_begin + rg * kStageRows + (lane >> 2);
             const int m0 = 2 * (lane & 3);
-            if (row < r_end) {
+            if (KS > 1) {
+                // unscaled sums of this CTA's part of K; the cluster's first CTA adds the parts at the end
+                float2 *o = reinterpret_cast<float2 *>(s_out + (size_t)rg * kPartFloats + 2 * lane);
+                if (pass != 0) {
+                    const float2 prev = *o;
+                    sum.x += prev.x;
+                    sum.y += prev.y;
+                }
+                *o = sum;
+            } else if (row < r_end) {
                 // later passes add to what this same lane stored in the pass before
                 const float v2[2] = {sum.x, sum.y};
 #pragma unroll
@@ -242,9 +280,7 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
                 }
             }
         }
-        return;
-    }
-
+    } else {
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
     const int seg = warp / wps, wi = warp - seg * wps;
@@ -259,53 +295,56 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
     const int seg_pairs = (sb1 - sb0) / 2;
     const int pp0 = warp_pair0(seg_pairs, wps, wi), pp1 = warp_pair0(seg_pairs, wps, wi + 1);
     const int np = pp1 - pp0;  // <= NP (checked by the host)
-    // this lane's part of the B operand: activation row g, K positions of its pairs in this pass
-    // Lane (g, t) loads words t and 4+t of both blocks of each pair (all loads independent, so they
-    // go out together), then the first block is put into the order "aligned words 1..7 of the
-    // weight block, then its two end halves": slot j holds activation bytes 4j-2 .. 4j+1, i.e. the
-    // high half of word j-1 and the low half of word j; slot 0 holds bytes 0, 1, 30, 31.  The
-    // neighbouring words come from the neighbouring lanes of the same activation row.
+    // this lane's part of the B operand: activation row g, K positions of its pairs in this pass.
+    // A pair's 64 activation bytes are 16 words; lane (g, t) needs words t, 4+t (first block) and
+    // 8+t, 12+t (second block).  It loads words 4t .. 4t+3 with one 16-byte load -- the quad then covers
+    // the pair's 64 contiguous bytes, where four 4-byte loads per lane took four times as many
+    // instructions with eight rows (eight cache lines) each, and with many activation rows that
+    // address traffic alone cost microseconds before the first weight byte was used -- and the
+    // quad transposes its 4 x 4 words with two exchange steps.
     uint32_t b[NP][4];
 #pragma unroll
     for (int q = 0; q < NP; q++) {
         b[q][0] = b[q][1] = b[q][2] = b[q][3] = 0u;
         if (q < np && g < p.m) {
             const int blk = sb0 + 2 * (pp0 + q);
-            const uint32_t *x0 = reinterpret_cast<const uint32_t *>(p.xq + (size_t)g * p.cols + (size_t)blk * 32);
-            b[q][0] = __ldcg(x0 + t);
-            b[q][1] = __ldcg(x0 + 4 + t);
-            b[q][2] = __ldcg(x0 + 8 + t);    // second block: word-aligned in the weight row, natural order
-            b[q][3] = __ldcg(x0 + 12 + t);
+            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(p.xq + (size_t)g * p.cols + (size_t)blk * 32) + t);
+            b[q][0] = v.x; b[q][1] = v.y; b[q][2] = v.z; b[q][3] = v.w;
         }
     }
-    if (pass == 0) {
-        // (after the activation loads above have gone out, so that the two round trips overlap)
-        // activation scales of all 8 (padded) rows -> shared memory; consumers only
-        // (the loads of four rounds go out together: a round trip to L2 each would cost a microsecond)
-        for (int i0 = threadIdx.x; i0 < kActRows * nblk; i0 += 4 * kConsumers * 32) {
-            float v[4];
+    {
+        // Activation scales of this warp's blocks in this pass, all 8 (padded) activation rows, into the
+        // warp's own part of s_dx ([block][activation row]: the four lanes t of a quad then read 32
+        // contiguous bytes per block; row-major [m][nblk] put all four in one bank).  Issued after the
+        // loads above so that the round trips overlap; nobody else reads this part, so a warp
+        // barrier is all it takes.
+        const int blk0 = sb0 + 2 * pp0;
+        float v[kActRows];     // lane = block of the warp's slice (at most 2 NP <= 24 of them)
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = i0 + u * kConsumers * 32;
-                const int m = i / nblk;
-                v[u] = (i < kActRows * nblk && m < p.m) ? __ldcg(p.xd + (size_t)m * nblk + (i - m * nblk)) : 0.0f;
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                // shared layout [block][activation row]: the four lanes t of a quad then read 32 contiguous
-                // bytes per block (row-major [m][nblk] put all four in one bank: measured, those loads
-                // alone made the consumers the bottleneck)
-                const int i = i0 + u * kConsumers * 32;
-                const int m = i / nblk;
-                if (i < kActRows * nblk) s_dx[(i - m * nblk) * kActRows + m] = v[u];
-            }
+        for (int m = 0; m < kActRows; m++)
+            v[m] = (lane < 2 * np && m < p.m) ? __ldcg(p.xd + (size_t)m * nblk + blk0 + lane) : 0.0f;
+        if (lane < 2 * np) {
+            float4 *d = reinterpret_cast<float4 *>(s_dx + (size_t)(blk0 + lane) * kActRows);
+            d[0] = make_float4(v[0], v[1], v[2], v[3]);
+            d[1] = make_float4(v[4], v[5], v[6], v[7]);
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        __syncwarp();
     }
 #pragma unroll
     for (int q = 0; q < NP; q++) {
         // all 32 lanes take part in the shuffles (q < np is warp-uniform)
         if (q < np) {
+            {
+                // 4 x 4 transpose inside the quad: b[q][j] of lane t = word 4t+j  ->  word 4j+t
+                const bool hi2 = (t & 2) != 0, hi1 = (t & 1) != 0;
+                const uint32_t x0 = hi2 ? b[q][0] : b[q][2], x1 = hi2 ? b[q][1] : b[q][3];
+                const uint32_t y0 = __shfl_xor_sync(0xffffffffu, x0, 2), y1 = __shfl_xor_sync(0xffffffffu, x1, 2);
+                if (hi2) { b[q][0] = y0; b[q][1] = y1; } else { b[q][2] = y0; b[q][3] = y1; }
+                // now b[q][2a+c] = word 4((t&1)+2a) + 2(t>>1)+c; exchange the off-column with lane t^1
+                const uint32_t z0 = __shfl_xor_sync(0xffffffffu, hi1 ? b[q][0] : b[q][1], 1);
+                const uint32_t z1 = __shfl_xor_sync(0xffffffffu, hi1 ? b[q][2] : b[q][3], 1);
+                if (hi1) { b[q][0] = z0; b[q][2] = z1; } else { b[q][1] = z0; b[q][3] = z1; }
+            }
             const uint32_t w_lo = b[q][0], w_hi = b[q][1];
             const int prev = (lane & ~3) | ((t + 3) & 3);                 // lane (g, t-1), wrapping to t = 3
             const uint32_t p_lo = __shfl_sync(0xffffffffu, w_lo, prev);   // word t-1      (t = 0: word 3)
@@ -375,29 +414,49 @@ __global__ void __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const Mma
         if (++c_pbuf == p.rgbuf) c_pbuf = 0;
     }
   }
+    }
+    if (KS > 1) {
+        // Every thread of both CTAs gets here, also after a wait that gave up.  The first barrier
+        // makes both CTAs' sums complete and visible; the second keeps the peer's shared memory
+        // alive until it has been read.
+        cluster_barrier();
+        if (crank == 0) {
+            const int nrows = r_end - r_begin;
+            for (int i = threadIdx.x; i < nrows * p.m; i += blockDim.x) {
+                const int m = i / nrows, r = i - m * nrows;
+                float v = s_out[r * kActRows + m];
+#pragma unroll
+                for (int c = 1; c < KS; c++) v += ld_peer_f32(smem_u32(s_out + r * kActRows + m), (uint32_t)c);
+                p.y[(size_t)m * p.rows + r_begin + r] = v * p.scale;
+            }
+        }
+        cluster_barrier();
+    }
 }
 
 struct MmaPlan {
     int npass = 0, nseg = 0, pitch = 0, stages = 0, rgbuf = 0, max_pairs = 0;
+    int ks = 1, out_rg = 0, grid = 0;
     size_t smem = 0;
 };
 
 constexpr int kMaxPairs = 12;   // block pairs a consumer warp can keep in registers (largest instantiation)
 
-// Ring geometry for `nblk` blocks per row: the fewest passes over K whose K slices fit the
-// registers, then the fewest segments that still give a ring of at least 6 stages (else the
-// deepest ring).  npass = 0 when nothing fits.
-MmaPlan plan_mma(tpb_handle_t h, int nblk) {
-    const size_t limit = (size_t)h->smem_optin - 1024;
-    for (int npass = 1; npass <= 8; npass++) {
-        if (nblk / 8 < npass) break;
+// Ring geometry for `nblk` blocks per row with K split over `ks` CTAs: the fewest passes over a
+// CTA's part of K whose K slices fit the registers, then the fewest segments that still give a
+// ring of at least 6 stages (else the deepest ring).  `extra` bytes of shared memory are kept free.
+// npass = 0 when nothing fits.
+MmaPlan plan_mma_ks(tpb_handle_t h, int nblk, int ks, size_t extra) {
+    const size_t limit = (size_t)h->smem_optin - 1024 - extra;
+    for (int npass = 1; npass <= 8 / ks; npass++) {
+        if (nblk / 8 < npass * ks) break;
         MmaPlan best;
         for (int nseg = 1; nseg <= kConsumers; nseg *= 2) {
             int seg_blocks = 0, max_pairs = 0;
             bool ok = true;
             const int wps = kConsumers / nseg;
-            for (int ps = 0; ps < npass && ok; ps++) {
-                const int pb0 = pass_blk0(nblk, npass, ps), pb1 = pass_blk0(nblk, npass, ps + 1);
+            for (int ps = 0; ps < npass * ks && ok; ps++) {
+                const int pb0 = pass_blk0(nblk, npass * ks, ps), pb1 = pass_blk0(nblk, npass * ks, ps + 1);
                 if ((pb1 - pb0) / 8 < nseg) ok = false;
                 for (int sg = 0; sg < nseg && ok; sg++) {
                     const int nb = seg_blk0(pb0, pb1, nseg, sg + 1) - seg_blk0(pb0, pb1, nseg, sg);
@@ -433,19 +492,43 @@ MmaPlan plan_mma(tpb_handle_t h, int nblk) {
             }
             if (best.npass != 0 && best.stages >= 6) break;
         }
-        if (best.npass != 0) return best;
+        if (best.npass != 0) {
+            best.ks = ks;
+            return best;
+        }
     }
     return MmaPlan();
 }
 
-template <int NP>
-int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, size_t smem) {
-    auto kern = q8_0_gemv_mma_kernel<NP>;
+constexpr int kMaxOutRg = 64;   // K split: row groups a cluster may own (16 KB of sums per CTA)
+
+// One CTA per SM, each with all of K -- unless the rows need several passes over K and splitting K
+// over a pair of CTAs halves them: then pairs of CTAs share twice as many rows.
+MmaPlan plan_mma(tpb_handle_t h, int64_t rows, int nblk) {
+    MmaPlan one = plan_mma_ks(h, nblk, 1, 0);
+    long long grid = (rows + kStageRows - 1) / kStageRows;
+    if (grid > h->sm_count) grid = h->sm_count;
+    one.grid = (int)grid;
+    const char *e = getenv("TPB_GEMV_KSPLIT");   // "0": never split K (measurements; read per launch)
+    if (one.npass == 1 || h->sm_count < 2 || (e && e[0] == '0')) return one;
+    long long owners = (rows + kStageRows - 1) / kStageRows;
+    if (owners > h->sm_count / 2) owners = h->sm_count / 2;
+    const int out_rg = (int)(((rows + owners - 1) / owners + kStageRows - 1) / kStageRows);
+    if (out_rg > kMaxOutRg) return one;
+    MmaPlan two = plan_mma_ks(h, nblk, 2, (size_t)out_rg * kPartFloats * 4);
+    if (two.npass == 0 || (one.npass != 0 && two.npass * 2 > one.npass)) return one;
+    two.out_rg = out_rg;
+    two.smem += (size_t)out_rg * kPartFloats * 4;
+    two.grid = (int)(2 * owners);
+    return two;
+}
+
+template <int NP, int KS>
+int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, const MmaPlan &pl) {
+    auto kern = q8_0_gemv_mma_kernel<NP, KS>;
     static tpb_per_device_once smem_set;
     TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
-    long long grid = ((long long)p.rows + kStageRows - 1) / kStageRows;
-    if (grid > h->sm_count) grid = h->sm_count;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3((unsigned)grid), dim3(kThreadsMma), smem, st, p));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3((unsigned)pl.grid), dim3(kThreadsMma), pl.smem, st, p));
     return TPB_OK;
 }
 
@@ -454,14 +537,14 @@ int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, size_t sm
 // True when the activation-stationary kernel can take this shape.
 bool tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols) {
     if (cols % 256 != 0 || rows < 1) return false;
-    const MmaPlan pl = plan_mma(h, (int)(cols / 32));
+    const MmaPlan pl = plan_mma(h, rows, (int)(cols / 32));
     return pl.npass != 0;
 }
 
 int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale, int64_t rows,
                              int64_t cols, const void *xq, int ng, int row_off, int n_total) {
     const int nblk = (int)(cols / 32);
-    const MmaPlan pl = plan_mma(h, nblk);
+    const MmaPlan pl = plan_mma(h, rows, nblk);
     if (pl.npass == 0)
         return tpb_fail(h, TPB_ERR_INVALID_ARG, "q8_0 gemv: %lld columns do not fit the register-resident kernel",
                         (long long)cols);
@@ -480,7 +563,14 @@ int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const vo
     p.pitch = pl.pitch;
     p.stages = pl.stages;
     p.rgbuf = pl.rgbuf;
+    p.out_rg = pl.out_rg;
     p.status = h->d_status;
-    if (pl.max_pairs <= 6) return launch_np<6>(h, st, p, pl.smem);
-    return launch_np<kMaxPairs>(h, st, p, pl.smem);
+    if (pl.ks == 2) {
+        if (pl.max_pairs <= 6) return launch_np<6, 2>(h, st, p, pl);
+        if (pl.max_pairs <= 9) return launch_np<9, 2>(h, st, p, pl);
+        return launch_np<kMaxPairs, 2>(h, st, p, pl);
+    }
+    if (pl.max_pairs <= 6) return launch_np<6, 1>(h, st, p, pl);
+    if (pl.max_pairs <= 9) return launch_np<9, 1>(h, st, p, pl);
+    return launch_np<kMaxPairs, 1>(h, st, p, pl);
 }
