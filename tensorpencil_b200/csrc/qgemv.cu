@@ -453,19 +453,20 @@ int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, in
 int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total) {
-    // Two kernels.  The dp4a streaming kernel below is the faster one for up to four activation rows
-    // (17.6 us at M = 1, K = 5120 -> N = 17408); its time grows by ~2 us per row, and beyond eight
-    // rows x 12288 columns its activations no longer fit shared memory.  The kernel that keeps the
-    // activations in registers and takes the block sums from mma.sync (qgemv_mma.cu) costs ~24 us
-    // at that shape whatever M is, so it takes over from five rows on, and wherever the dp4a kernel
-    // would have to read its activations from global memory.  TPB_GEMV_KERNEL=dp4a / mma forces one.
+    // Two kernels.  The dp4a streaming kernel below is the faster one for a single activation row
+    // (17.7 us at K = 5120 -> N = 17408); its time grows by ~2 us per row, and beyond eight rows x
+    // 12288 columns its activations no longer fit shared memory.  The kernel that keeps the
+    // activations in registers and takes the block sums from mma.sync (qgemv_mma.cu) costs 19-20 us
+    // at that shape whatever M is (19.3 against 19.2 us at two rows), so it takes every call with two
+    // rows or more, and any the dp4a kernel would have to serve with its activations in global memory.
+    // TPB_GEMV_KERNEL=dp4a / mma forces one.
     {
         const char *e = getenv("TPB_GEMV_KERNEL");
         const bool force_dp4a = e != nullptr && e[0] == 'd', force_mma = e != nullptr && e[0] == 'm';
         const size_t act_bytes = (size_t)ng * (size_t)(cols / 64) * kActPairBytes + (size_t)ng * (size_t)(cols / 32) * 4;
         // the smallest ring the dp4a kernel accepts beside its activations: 8 warps x 2 stages x 2 rows
         const bool acts_fit = act_bytes + 8 * 2 * stage_bytes(2) + 8 * 2 * 8 + 64 <= (size_t)h->smem_optin - 1024;
-        const bool want_mma = force_mma || (!force_dp4a && (ng >= 5 || !acts_fit));
+        const bool want_mma = force_mma || (!force_dp4a && (ng >= 2 || !acts_fit));
         if (want_mma && tpb_q8_0_gemv_mma_fits(h, rows, cols))
             return tpb_launch_q8_0_gemv_mma(h, st, y, w, scale, rows, cols, xq, ng, row_off, n_total);
     }

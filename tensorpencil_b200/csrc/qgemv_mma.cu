@@ -75,6 +75,8 @@ struct MmaGemvParams {
     int npass;         // passes over K (each covers a contiguous range of whole 8-block units)
     int nseg;          // K segments per pass and row group (divides kConsumers)
     int pitch;         // bytes between rows of a stage
+    int grp_rows;      // rows one bulk copy brings in (1, 2, 4 or 8; > 1 only when a stage is whole rows)
+    int grp_shift;     // extra bytes before every further copy's rows (keeps the 8 rows on distinct banks)
     int stages;        // ring depth
     int rgbuf;         // row groups of partial sums kept
     int out_rg;        // K split: row groups of unscaled sums a CTA keeps for the final addition
@@ -93,13 +95,48 @@ __host__ __device__ inline int warp_pair0(int pairs, int wps, int wi) { return p
 // C[8 weight rows][8 activation rows] = A[8 (of 16)][32] * B[32][8], int8 -> int32, C starts at zero.
 // Lane (g = lane / 4, t = lane % 4): a0/a2 = weight row g, k = 4t.. and 16+4t..; a1/a3 (rows 8..15)
 // are zero; b0/b1 = activation row g, same k; c0, c1 = weight row g x activation rows 2t, 2t+1.
+// The accumulators start at the bit pattern of 1.5 * 2^23 (kI2FMagicBits), so that each int32 result, read as a
+// float, is that constant plus the block sum (|sum| <= 32 * 127 * 128 < 2^22): no integer-to-float conversion.
 __device__ __forceinline__ void mma_s8(int &c0, int &c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     int c2, c3;
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%8,%5,%8}, {%6,%7}, {%8,%8,%8,%8};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%8,%5,%8}, {%6,%7}, {%9,%9,%8,%8};"
         : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-        : "r"(a0), "r"(a2), "r"(b0), "r"(b1), "r"(0));
+        : "r"(a0), "r"(a2), "r"(b0), "r"(b1), "r"(0), "r"(kI2FMagicBits));
     (void)c2;
     (void)c3;
+}
+
+// Two packed f32 values; each half rounds like the scalar instruction.
+typedef unsigned long long f2;
+__device__ __forceinline__ f2 pack2(float lo, float hi) {
+    f2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ f2 pack2i(int lo, int hi) {
+    f2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+__device__ __forceinline__ f2 sub2(f2 a, f2 b) {
+    f2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f2 lds_f2x(uint32_t addr) {
+    f2 v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+    return v;
 }
 
 // Shared-memory loads by 32-bit shared address: one address register instead of a generic pointer pair.
@@ -142,7 +179,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
     const int lane = threadIdx.x & 31;
     const int nblk = p.nblk;
     const int S = p.stages;
-    const int stage_bytes = kStageRows * p.pitch;
+    const int stage_bytes = kStageRows * p.pitch + (kStageRows / p.grp_rows) * p.grp_shift;
     const size_t row_bytes = (size_t)nblk * kBlockBytes;
 
     uint8_t *ring = smem;
@@ -167,7 +204,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
     const int wps = kConsumers / p.nseg;  // consumer warps per K segment
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(kProducers));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(kProducers + 1));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(wps));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -187,24 +224,29 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
     if (warp >= kConsumers) {
         // ---------------- producers (the first one also reduces) ----------------
         const int pw = warp - kConsumers;
-        constexpr int kRowsPerProducer = kStageRows / kProducers;
         // the stage the next issue() fills: (pass, row group, segment), ring slot, all advanced by one per call
         int is_pass = 0, is_rg = 0, is_seg = 0, is_slot = 0;
-        auto issue = [&]() {  // whole warp: lane r starts the copy of this warp's r-th row of the next stage
+        auto issue = [&]() {  // whole warp: lane l starts copy number pw + 4 l of the next stage (a copy = grp_rows rows)
             const int row0 = r_begin + is_rg * kStageRows;
             const int nrow = min(kStageRows, r_end - row0);
             const int b0 = s_seg[is_pass * (p.nseg + 1) + is_seg], b1 = s_seg[is_pass * (p.nseg + 1) + is_seg + 1];
-            const uint32_t bytes = (uint32_t)(b1 - b0) * kBlockBytes;
+            const uint32_t bytes = (uint32_t)(b1 - b0) * kBlockBytes;   // per row
             const uint32_t bar = full_bar(is_slot);
-            const int my_rows = max(0, min(kRowsPerProducer, nrow - pw * kRowsPerProducer));
-            if (lane == 0)   // every producer warp arrives, also with nothing to copy (the barrier counts four)
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)my_rows)
+            const int cp = pw + kProducers * lane;                      // this lane's copy
+            const int cp_row0 = cp * p.grp_rows;
+            const int cp_rows = max(0, min(p.grp_rows, nrow - cp_row0));
+            // rows of all this warp's copies (lanes 0 and 1; at most eight copies per stage)
+            const int cp_rows1 = max(0, min(p.grp_rows, nrow - (cp_row0 + kProducers * p.grp_rows)));
+            if (lane == 0)   // every producer warp arrives, also with nothing to copy (the barrier counts them all)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"(bytes * (uint32_t)(cp_rows + cp_rows1))
                              : "memory");
             __syncwarp();
-            const int r = pw * kRowsPerProducer + lane;
             const uint32_t dst = smem_u32(ring) + (uint32_t)(is_slot * stage_bytes);
             const uint8_t *src = p.w + (size_t)row0 * row_bytes + (size_t)b0 * kBlockBytes;
-            if (lane < my_rows) bulk_g2s(dst + (uint32_t)(r * p.pitch), src + (size_t)r * row_bytes, bytes, bar);
+            if (lane < 2 && cp_rows > 0)
+                bulk_g2s(dst + (uint32_t)(cp_row0 * p.pitch + cp * p.grp_shift), src + (size_t)cp_row0 * row_bytes,
+                         bytes * (uint32_t)cp_rows, bar);
             if (++is_slot == S) is_slot = 0;
             if (++is_seg == p.nseg) {
                 is_seg = 0;
@@ -247,7 +289,10 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
             }
         };
         // weights are constants: the ring starts filling before the previous kernel has finished
-        for (int i = 0; i < S && i < total; i++) issue();
+        for (int i = 0; i < S && i < total; i++) {
+            if (pw == 0 && lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_bar(is_slot)) : "memory");
+            issue();
+        }
         asm volatile("griddepcontrol.wait;" ::: "memory");
         bool ok = true;
         // the stage whose release is awaited next: ring slot and phase, segment, row group, pass, partial buffer
@@ -258,14 +303,20 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
             ok = mbar_wait(empty_bar(w_slot), w_par, p.status, (7u << 24) | (uint32_t)w_slot);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // Partial sums are added before this warp's part of the refill goes out, and the refilled
-            // stage is not "full" without it: no consumer can overwrite a partial that is still needed.
-            if (pw == 0 && w_seg == p.nseg - 1) reduce(w_pass, w_rg, w_pbuf);
-            __syncwarp();
+            const uint32_t refill_bar = full_bar(is_slot);
             if (j + S < total) {
                 // order the consumers' generic-proxy reads of the slot before the async-proxy refill
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue();
+            }
+            // The refill is under way; the first producer warp now adds the partial sums of a finished row
+            // group and only then gives the refilled stage its last arrival: the stage is not "full" without
+            // it, so no consumer can overwrite a partial that is still needed, and the copies did not have to
+            // wait for the additions.
+            if (pw == 0) {
+                if (w_seg == p.nseg - 1) reduce(w_pass, w_rg, w_pbuf);
+                __syncwarp();
+                if (lane == 0 && j + S < total) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(refill_bar) : "memory");
             }
             if (++w_slot == S) {
                 w_slot = 0;
@@ -356,7 +407,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
         }
     }
     // shared addresses relative to a stage: this warp's first pair in weight row g, word t
-    const uint32_t ring_u32 = smem_u32(ring) + (uint32_t)(pp0 * kPairBytes) + (uint32_t)(g * p.pitch) + 4u * (uint32_t)t;
+    const uint32_t ring_u32 = smem_u32(ring) + (uint32_t)(pp0 * kPairBytes) + (uint32_t)(g * p.pitch + (g / p.grp_rows) * p.grp_shift) + 4u * (uint32_t)t;
     // activation scales of activation rows 2t and 2t+1, this warp's first block
     const uint32_t dx_u32 = smem_u32(s_dx + (size_t)(sb0 + 2 * pp0) * kActRows + 2 * t);
 
@@ -365,7 +416,8 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t wl = ring_u32 + (uint32_t)(c_slot * stage_bytes);
-        float acc0 = 0.0f, acc1 = 0.0f;
+        f2 acc = 0ull;
+        const f2 magic2 = pack2(kI2FMagic, kI2FMagic);
         // kGroup pairs at a time: first every load and both MMAs of each pair (independent of one
         // another, so the loads and the tensor-core latencies overlap), then the scaling.
 #pragma unroll
@@ -391,19 +443,19 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
                 const int q = q0 + u;
                 if (q < NP && q < np) {
                     // scales of activation rows (2t, 2t+1) for the pair's first and second block
-                    const float2 dx0 = lds_f2(dx_u32 + 64u * q), dx1 = lds_f2(dx_u32 + 64u * q + 32u);
+                    const f2 dx0 = lds_f2x(dx_u32 + 64u * q), dx1 = lds_f2x(dx_u32 + 64u * q + 32u);
                     // weight scales: f16 in the low half of word 0 (first block) and the high half of word 8 (second)
                     const float d0 = f16lo(sc[u][0]), d1 = f16hi(sc[u][1]);
-                    acc0 = fmaf(i2f_small(c[u][0]), d0 * dx0.x, acc0);
-                    acc1 = fmaf(i2f_small(c[u][1]), d0 * dx0.y, acc1);
-                    acc0 = fmaf(i2f_small(c[u][2]), d1 * dx1.x, acc0);
-                    acc1 = fmaf(i2f_small(c[u][3]), d1 * dx1.y, acc1);
+                    // acc += float(sumi) * (d_w * d_x) for both activation rows at once (two-wide f32 instructions,
+                    // each half rounded like the scalar one)
+                    acc = fma2(sub2(pack2i(c[u][0], c[u][1]), magic2), mul2(pack2(d0, d0), dx0), acc);
+                    acc = fma2(sub2(pack2i(c[u][2], c[u][3]), magic2), mul2(pack2(d1, d1), dx1), acc);
                 }
             }
         }
         // this warp's K slice of C[weight row g][activation rows 2t, 2t+1]
         float *part = s_part + ((size_t)c_pbuf * kConsumers + warp) * kPartFloats;
-        *reinterpret_cast<float2 *>(part + g * kActRows + 2 * t) = make_float2(acc0, acc1);
+        *reinterpret_cast<f2 *>(part + g * kActRows + 2 * t) = acc;
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty_bar(c_slot)) : "memory");
         c_slot += p.nseg;
@@ -435,7 +487,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
 }
 
 struct MmaPlan {
-    int npass = 0, nseg = 0, pitch = 0, stages = 0, rgbuf = 0, max_pairs = 0;
+    int npass = 0, nseg = 0, pitch = 0, grp_rows = 1, grp_shift = 0, stages = 0, rgbuf = 0, max_pairs = 0;
     int ks = 1, out_rg = 0, grid = 0;
     size_t smem = 0;
 };
@@ -448,6 +500,8 @@ constexpr int kMaxPairs = 12;   // block pairs a consumer warp can keep in regis
 // npass = 0 when nothing fits.
 MmaPlan plan_mma_ks(tpb_handle_t h, int nblk, int ks, size_t extra) {
     const size_t limit = (size_t)h->smem_optin - 1024 - extra;
+    const char *ms = getenv("TPB_GEMV_MINSTAGES");
+    const int min_stages = ms ? atoi(ms) : 4;
     for (int npass = 1; npass <= 8 / ks; npass++) {
         if (nblk / 8 < npass * ks) break;
         MmaPlan best;
@@ -469,20 +523,39 @@ MmaPlan plan_mma_ks(tpb_handle_t h, int nblk, int ks, size_t extra) {
             }
             if (!ok) break;
             if (max_pairs > kMaxPairs) continue;
-            // rows at 4 words modulo 32 banks, 16-byte aligned
-            int pitch_w = seg_blocks * kBlockBytes / 4;
-            pitch_w += ((4 - pitch_w % 32) + 32) % 32;
-            const int pitch = pitch_w * 4;
-            const size_t stage = (size_t)kStageRows * pitch;
+            // Rows at 4 words modulo 32 banks, 16-byte aligned: by padding the pitch when every row comes
+            // with its own copy.  A stage of whole rows (one pass, one segment, K not split) is contiguous
+            // in the weight: its rows keep their pitch in memory, 4 u words modulo 32 with u = nblk / 8,
+            // and come in copies of as many rows as fall on distinct banks that way (8 / gcd(u, 8)), every
+            // further copy 16 bytes later.  Fewer, larger copies: the producers' issue rate was the limit
+            // of the kernel with one copy per row and 22 KB stages.
+            int pitch, grp_rows = 1, grp_shift = 0;
+            if (npass * ks == 1 && nseg == 1) {
+                const int u = (nblk / 8) % 8;
+                int gcd = 8;
+                while (u % gcd != 0) gcd /= 2;     // gcd(u, 8); u = 0 gives 8
+                grp_rows = 8 / gcd;
+                grp_shift = grp_rows > 1 ? 16 : 0;
+            }
+            if (grp_rows > 1) {
+                pitch = seg_blocks * kBlockBytes;
+            } else {
+                int pitch_w = seg_blocks * kBlockBytes / 4;
+                pitch_w += ((4 - pitch_w % 32) + 32) % 32;
+                pitch = pitch_w * 4;
+            }
+            const size_t stage = (size_t)kStageRows * pitch + (size_t)(kStageRows / grp_rows) * grp_shift;
             const size_t fixed = (size_t)kActRows * nblk * 4 + 64 + 2 * 8 * 16 + 4 * 8 * 17;   // + the segment table
             for (int stages = 12; stages >= 3; stages--) {
                 const int rgbuf = (stages - 1 + nseg - 1) / nseg + 1;
                 const size_t smem = stages * stage + fixed + (size_t)rgbuf * kConsumers * kPartFloats * 4;
                 if (smem > limit) continue;
-                if (best.npass == 0 || (best.stages < 6 && stages > best.stages)) {
+                if (best.npass == 0 || (best.stages < min_stages && stages > best.stages)) {
                     best.npass = npass;
                     best.nseg = nseg;
                     best.pitch = pitch;
+                    best.grp_rows = grp_rows;
+                    best.grp_shift = grp_shift;
                     best.stages = stages;
                     best.rgbuf = rgbuf;
                     best.max_pairs = max_pairs;
@@ -490,7 +563,7 @@ MmaPlan plan_mma_ks(tpb_handle_t h, int nblk, int ks, size_t extra) {
                 }
                 break;
             }
-            if (best.npass != 0 && best.stages >= 6) break;
+            if (best.npass != 0 && best.stages >= min_stages) break;
         }
         if (best.npass != 0) {
             best.ks = ks;
@@ -561,6 +634,8 @@ int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const vo
     p.npass = pl.npass;
     p.nseg = pl.nseg;
     p.pitch = pl.pitch;
+    p.grp_rows = pl.grp_rows;
+    p.grp_shift = pl.grp_shift;
     p.stages = pl.stages;
     p.rgbuf = pl.rgbuf;
     p.out_rg = pl.out_rg;
