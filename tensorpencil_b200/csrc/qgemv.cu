@@ -454,11 +454,13 @@ int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const vo
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total) {
     // Two kernels.  The dp4a streaming kernel below is the faster one for a single activation row
-    // (17.7 us at K = 5120 -> N = 17408); its time grows by ~2 us per row, and beyond eight rows x
-    // 12288 columns its activations no longer fit shared memory.  The kernel that keeps the
-    // activations in registers and takes the block sums from mma.sync (qgemv_mma.cu) costs 19-20 us
-    // at that shape whatever M is (19.3 against 19.2 us at two rows), so it takes every call with two
-    // rows or more, and any the dp4a kernel would have to serve with its activations in global memory.
+    // whose K fits one CTA's registers in the other kernel (17.7 us at K = 5120 -> N = 17408); its
+    // time grows by ~2 us per activation row, and beyond eight rows x 12288 columns its activations no
+    // longer fit shared memory.  The kernel that keeps the activations in registers and takes the block
+    // sums from mma.sync (qgemv_mma.cu) costs 19-20 us at that shape whatever M is (19.3 against
+    // 19.2 us at two rows), so it takes every call with two rows or more; with long rows, where it
+    // splits K over a pair of CTAs (K = 17408 -> N = 5120: 20.6 us against 21.2), also the single row;
+    // and any call the dp4a kernel would have to serve with its activations in global memory.
     // TPB_GEMV_KERNEL=dp4a / mma forces one.
     {
         const char *e = getenv("TPB_GEMV_KERNEL");
@@ -466,8 +468,8 @@ int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const vo
         const size_t act_bytes = (size_t)ng * (size_t)(cols / 64) * kActPairBytes + (size_t)ng * (size_t)(cols / 32) * 4;
         // the smallest ring the dp4a kernel accepts beside its activations: 8 warps x 2 stages x 2 rows
         const bool acts_fit = act_bytes + 8 * 2 * stage_bytes(2) + 8 * 2 * 8 + 64 <= (size_t)h->smem_optin - 1024;
-        const bool want_mma = force_mma || (!force_dp4a && (ng >= 2 || !acts_fit));
-        if (want_mma && tpb_q8_0_gemv_mma_fits(h, rows, cols))
+        const int mma_ks = force_dp4a ? 0 : tpb_q8_0_gemv_mma_fits(h, rows, cols);
+        if (mma_ks != 0 && (force_mma || ng >= 2 || mma_ks >= 2 || !acts_fit))
             return tpb_launch_q8_0_gemv_mma(h, st, y, w, scale, rows, cols, xq, ng, row_off, n_total);
     }
     GemvParams p;

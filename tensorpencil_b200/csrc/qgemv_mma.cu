@@ -13,34 +13,39 @@
 // each Q8_0 block of 8 weight rows is the upper half of an A operand (the lower half is zero):
 // two shared-memory words per lane and one MMA give the 8 x 8 exact int32 block sums that the
 // dp4a kernel needs 8 dp4a per row and activation row for.  (Eight rows, not the sixteen the
-// instruction could take: a stage of the ring is then half as large, there are twice as many
-// of them, and a stage is consumed in half the time -- with sixteen-row stages the round trip
-// "consumed, refill requested, data back" was longer than four stages could cover.)  The per-block scaling stays the reference's
+// instruction could take: a stage of whole rows is then half as large and the ring holds four of
+// them.)  The per-block scaling stays the reference's
 // (src/gpu/cuda/elt.zig:1984-2005):
 //   acc += float(sumi) * (d_w * d_x)   in f32, block after block.
 // Rows too long for the registers (more than 12 block pairs per warp) are taken in several
 // passes over K: a pass streams one K range of all the CTA's rows, and the passes after the
 // first add to the y the first one wrote.  Where that halves the number of passes, K is split
 // across a cluster of two CTAs instead: both stream the same rows (twice as many as a lone CTA
-// would own, so the 8-row stages divide them better), each its own half of K in one pass, and
-// at the end the first CTA adds the second one's sums, read from its shared memory, to its own.
+// would own, so the 8-row stages divide them better), each its own half of K in one pass; the
+// second CTA stores its sums into the first one's shared memory as it goes, and after one cluster
+// barrier at the end the first CTA adds the two parts and writes y.
 //
 // Data path.  One CTA per SM owns a contiguous range of weight rows.  Four producer warps stream
-// them in stages of 8 rows x one K segment with one 1-D bulk copy per row (cp.async.bulk,
-// completion on the stage's "full" mbarrier, no multicast) into a ring that fills most of
-// shared memory; they start before griddepcontrol.wait, so under programmatic dependent launch
-// the ring fills while the previous kernel drains.  (Four warps, two rows each, because a warp
-// gets a bulk copy under way only every ~225 cycles: measured, one warp issuing all sixteen
-// copies of every stage capped the kernel at 3.4 TB/s.  The register file hands out registers
-// to warps in fours, so warps 17..19 cost nothing.)  The warps whose K slice lies in a stage's
-// segment wait for it, multiply, write their 8 x 8 partial sums to a small buffer and arrive
-// on the stage's "empty" mbarrier.  When the last segment of a row group has been released,
-// the first producer warp -- which has to wait for that anyway before it may refill the slot -- adds
-// the partials in warp order (a fixed order: results do not depend on timing), applies
-// `scale`, and stores y.  No warp ever waits for another consumer warp.
+// them in stages of 8 rows x one K segment with 1-D bulk copies (cp.async.bulk, completion on the
+// stage's "full" mbarrier, no multicast) into a ring that fills most of shared memory; they start
+// before griddepcontrol.wait, so under programmatic dependent launch the ring fills while the
+// previous kernel drains.  What bounds this kernel is how fast copies can be issued, not the
+// arithmetic: a warp gets a bulk copy under way only every few hundred cycles (more when memory is
+// busy), and a producer's round "stage released -> fence -> expect -> copies" took 0.6 us per stage
+// with one copy per row and 22 KB stages -- less than the memory system delivers.  Hence few, large
+// copies: the fewest K segments that still leave four stages, and where a stage is whole rows
+// (one pass, one segment, K not split) its rows, which are contiguous in the weight, come with ONE
+// copy per group of rows (see plan_mma_ks for the bank arithmetic).  The warps whose K slice lies
+// in a stage's segment wait for it, multiply, write their 8 x 8 partial sums to a small buffer and
+// arrive on the stage's "empty" mbarrier.  When the last segment of a row group has been released
+// and its refill is under way, the first producer warp adds the partials in warp order (a fixed
+// order: results do not depend on timing), applies `scale` and stores y; the refilled stage counts
+// as full only after that, so partial buffers are never overwritten early.  No warp ever waits for
+// another consumer warp.  (Handing a stage back before the arithmetic, from registers, and letting
+// the last consumer warp add the partials were both measured: slower.)
 //
-// Rows in shared memory sit at a pitch of 4 words modulo 32 banks, so the 8 rows x 4 words an
-// A fragment load touches fall in 32 different banks.
+// Rows in shared memory start 4 words apart modulo 32 banks, so the 8 rows x 4 words an A fragment
+// load touches fall in 32 different banks.
 //
 // Quant bytes of the first block of a pair start 2 bytes into a word (34-byte blocks).  The
 // MMA sums over k, so any order of the 32 positions will do as long as A and B agree: the
@@ -162,13 +167,6 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
-    uint32_t ra;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-    return v;
-}
 
 // 20 warps: 65536 / 640 = 102 registers per thread, 96 after rounding to the allocation unit.
 // KS = CTAs per cluster = parts K is split into (1 or 2).
@@ -199,7 +197,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
         const int gp = crank * p.npass + ps;
         s_seg[e] = seg_blk0(pass_blk0(nblk, npt, gp), pass_blk0(nblk, npt, gp + 1), p.nseg, sg);
     }
-    float *s_out = reinterpret_cast<float *>(s_seg + 8 * 17);   // [out_rg][8 weight rows][8 activation rows], KS > 1 only
+    float *s_out = reinterpret_cast<float *>(s_seg + 8 * 17);   // [KS][out_rg][8 weight rows][8 activation rows], KS > 1 only
 
     const int wps = kConsumers / p.nseg;  // consumer warps per K segment
     if (threadIdx.x == 0) {
@@ -222,7 +220,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
     const int total = p.npass * n_rg * p.nseg;
 
     if (warp >= kConsumers) {
-        // ---------------- producers (the first one also reduces) ----------------
+        // ---------------- producers (the first one also adds the partial sums) ----------------
         const int pw = warp - kConsumers;
         // the stage the next issue() fills: (pass, row group, segment), ring slot, all advanced by one per call
         int is_pass = 0, is_rg = 0, is_seg = 0, is_slot = 0;
@@ -269,14 +267,23 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
             const int row = r_begin + rg * kStageRows + (lane >> 2);
             const int m0 = 2 * (lane & 3);
             if (KS > 1) {
-                // unscaled sums of this CTA's part of K; the cluster's first CTA adds the parts at the end
-                float2 *o = reinterpret_cast<float2 *>(s_out + (size_t)rg * kPartFloats + 2 * lane);
+                // Unscaled sums of this CTA's part of K.  Passes before the last accumulate here; the last one
+                // sends the total to the cluster's first CTA, part `crank` of its s_out (a remote shared-memory
+                // store: nothing waits for it, the cluster barrier at the end makes it visible), which adds
+                // the parts and writes y.
+                float2 *o = reinterpret_cast<float2 *>(s_out + ((size_t)crank * p.out_rg + rg) * kPartFloats + 2 * lane);
                 if (pass != 0) {
                     const float2 prev = *o;
                     sum.x += prev.x;
                     sum.y += prev.y;
                 }
-                *o = sum;
+                if (pass != p.npass - 1 || crank == 0) {
+                    *o = sum;
+                } else {
+                    uint32_t ra;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(o)), "r"(0));
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(ra), "f"(sum.x), "f"(sum.y) : "memory");
+                }
             } else if (row < r_end) {
                 // later passes add to what this same lane stored in the pass before
                 const float v2[2] = {sum.x, sum.y};
@@ -468,9 +475,8 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
   }
     }
     if (KS > 1) {
-        // Every thread of both CTAs gets here, also after a wait that gave up.  The first barrier
-        // makes both CTAs' sums complete and visible; the second keeps the peer's shared memory
-        // alive until it has been read.
+        // Every thread of both CTAs gets here, also after a wait that gave up.  The barrier makes the sums
+        // the other CTAs stored into the first CTA's shared memory complete and visible; they may leave.
         cluster_barrier();
         if (crank == 0) {
             const int nrows = r_end - r_begin;
@@ -478,11 +484,10 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
                 const int m = i / nrows, r = i - m * nrows;
                 float v = s_out[r * kActRows + m];
 #pragma unroll
-                for (int c = 1; c < KS; c++) v += ld_peer_f32(smem_u32(s_out + r * kActRows + m), (uint32_t)c);
+                for (int c = 1; c < KS; c++) v += s_out[(size_t)c * p.out_rg * kPartFloats + r * kActRows + m];
                 p.y[(size_t)m * p.rows + r_begin + r] = v * p.scale;
             }
         }
-        cluster_barrier();
     }
 }
 
@@ -500,8 +505,7 @@ constexpr int kMaxPairs = 12;   // block pairs a consumer warp can keep in regis
 // npass = 0 when nothing fits.
 MmaPlan plan_mma_ks(tpb_handle_t h, int nblk, int ks, size_t extra) {
     const size_t limit = (size_t)h->smem_optin - 1024 - extra;
-    const char *ms = getenv("TPB_GEMV_MINSTAGES");
-    const int min_stages = ms ? atoi(ms) : 4;
+    const int min_stages = 4;
     for (int npass = 1; npass <= 8 / ks; npass++) {
         if (nblk / 8 < npass * ks) break;
         MmaPlan best;
@@ -588,10 +592,10 @@ MmaPlan plan_mma(tpb_handle_t h, int64_t rows, int nblk) {
     if (owners > h->sm_count / 2) owners = h->sm_count / 2;
     const int out_rg = (int)(((rows + owners - 1) / owners + kStageRows - 1) / kStageRows);
     if (out_rg > kMaxOutRg) return one;
-    MmaPlan two = plan_mma_ks(h, nblk, 2, (size_t)out_rg * kPartFloats * 4);
+    MmaPlan two = plan_mma_ks(h, nblk, 2, (size_t)2 * out_rg * kPartFloats * 4);
     if (two.npass == 0 || (one.npass != 0 && two.npass * 2 > one.npass)) return one;
     two.out_rg = out_rg;
-    two.smem += (size_t)out_rg * kPartFloats * 4;
+    two.smem += (size_t)2 * out_rg * kPartFloats * 4;
     two.grid = (int)(2 * owners);
     return two;
 }
@@ -607,11 +611,11 @@ int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, const Mma
 
 }  // namespace
 
-// True when the activation-stationary kernel can take this shape.
-bool tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols) {
-    if (cols % 256 != 0 || rows < 1) return false;
+// 0 when the activation-stationary kernel cannot take this shape, else the number of CTAs K is split over.
+int tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols) {
+    if (cols % 256 != 0 || rows < 1) return 0;
     const MmaPlan pl = plan_mma(h, rows, (int)(cols / 32));
-    return pl.npass != 0;
+    return pl.npass != 0 ? pl.ks : 0;
 }
 
 int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale, int64_t rows,
