@@ -641,6 +641,39 @@ def measure_dit(be, sync, reduce_max, rank, steps, names, agree=_same):
             fn(i)
         ms_of[n] = _events_ms(fn, steps, sync) / steps
     be.status_poll()
+    # What launching from Python costs: the host time to enqueue one step, and the same step
+    # captured once into a CUDA graph and replayed (no host work per launch at all).
+    host_side = {}
+    for n in names:
+        if n not in ("fused_bf16_whole_batch", "fused_bf16_with_attention"):
+            continue
+        fn = _dit_runner(be, harness, w, x_list, mod, attn, DIT_VARIANTS[n][1])
+        entry = {}
+        try:
+            enq = []
+            for i in range(3):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn(i)
+                enq.append((time.perf_counter() - t0) * 1e3)
+            entry["host_enqueue_ms_per_step"] = min(enq)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn(0)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn(0)
+            graph.replay()
+            entry["graph_replay_s_per_step"] = _events_ms(lambda i: graph.replay(), steps, torch.cuda.synchronize) / steps / 1e3   # local sync: a rank whose capture failed must not leave the others in a barrier
+            be.status_poll()
+            del graph
+        except Exception as e:
+            entry["graph"] = f"{type(e).__name__}: {e}"[:200]
+        host_side[n] = entry
     vals = reduce_max([ms_of[n] for n in names])
     ops = harness.dit_linear_ops(T, synth.DIT_BLOCKS, synth.DIT_HIDDEN, synth.DIT_MLP)
     out = {"workload": "config3: INT8 ConvRot DiT step, 28 blocks, hidden 3072, MLP 12288, 4608 tokens, one latent per GPU, "
@@ -650,6 +683,8 @@ def measure_dit(be, sync, reduce_max, rank, steps, names, agree=_same):
                     "stands in for its output); tops counts the linears' 2*M*N*K only",
            "variants": {n: {"s_per_step": v / 1e3, "linear_tops": ops / (v * 1e-3) / 1e12, "what": DIT_VARIANTS[n][0]}
                         for n, v in zip(names, vals)}}
+    for n, entry in host_side.items():
+        out["variants"][n].update(entry)
     w.close()
     return out
 
