@@ -333,6 +333,26 @@ def test_q8_0_gemv_q8n_vs_oracle(be, m, n, k):
     assert np.max(np.abs(y - want_ref)) <= 2e-2
 
 
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("n,k", [(1, 17408), (7, 17408), (100, 24576), (33, 32768), (600, 16384), (9, 49152), (300, 12288)])
+@pytest.mark.parametrize("route", ["default", "mma", "mma, K in one CTA", "dp4a"])
+def test_q8_0_gemv_long_rows(be, monkeypatch, m, n, k, route):
+    """Rows too long for one CTA's registers: K split over a CTA pair, several passes over K, both
+    together, and the same calls forced down the other routes -- every route within a few ulps of
+    the sum of |terms| of the q8_1-emulating reference (src/gpu/cuda/backend.zig:3641-3651)."""
+    if route != "default":
+        monkeypatch.setenv("TPB_GEMV_KERNEL", "dp4a" if route == "dp4a" else "mma")
+    if route == "mma, K in one CTA":
+        monkeypatch.setenv("TPB_GEMV_KSPLIT", "0")
+    g = synth.q8_0_gemv(m, n, k, seed=911 + m)
+    y = be.q8_0_linear(dev(g["x"]), g["w"], n, k, scale=0.25).cpu().numpy()
+    be.status_poll()
+    be.dropWeights()
+    want = oracle.q8_0_gemv_q8(g["w"], n, k, g["x"], scale=0.25, tie_mode=0)
+    tol = gemv_tolerance(g["w"], n, k, g["x"])
+    assert np.max(np.abs(y - want)) <= tol, (np.max(np.abs(y - want)), tol)
+
+
 def test_q8_0_gemv_more_than_8_rows_groups(be):
     g = synth.q8_0_gemv(19, 32, 1024, seed=5)
     y = be.q8_0_linear(dev(g["x"]), g["w"], 32, 1024).cpu().numpy()
