@@ -702,7 +702,17 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
     names = ("fused_bf16_whole_batch", "fused_bf16_with_attention")
     res = {}
     x = mod = attn = None
-    for label, budget in (("streamed", 2 << 30), ("resident", None)):
+    # On several GPUs the default route shares the host link: every rank pulls 1/world of each block
+    # through PCIe and the pieces are exchanged over NVLink (all-gather on the transfer stream), so the
+    # node reads each block from host memory once.  "own_copies" = every GPU pulling every byte itself.
+    group = None
+    routes = [("streamed", 2 << 30, None)]
+    if world > 1:
+        import torch.distributed as dist
+        group = dist.group.WORLD
+        routes = [("streamed", 2 << 30, group), ("own_copies", 2 << 30, None)]
+    routes.append(("resident", None, None))
+    for label, budget, grp in routes:
         w, err = None, None
         try:
             if x is None:
@@ -711,7 +721,7 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
                 mod = harness.dit_modulation(be, synth.DIT_BLOCKS, synth.DIT_HIDDEN)
                 _, _, _, qn, kn, cos, sin = harness.attention_inputs(T, 1, 1, be.device)
                 attn = {"q_norm": qn, "k_norm": kn, "cos": cos, "sin": sin, "heads": synth.DIT_HIDDEN // 128}
-            w = harness.DitWeights(be, 4, stream_budget=budget, distinct_blocks=4)
+            w = harness.DitWeights(be, 4, stream_budget=budget, distinct_blocks=4, stream_group=grp)
         except Exception as e:
             err = f"{type(e).__name__}: {e}"
         if not agree(err is None):
@@ -726,17 +736,20 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
             copied = ((w.streamer.bytes_copied() - c0) / steps) if w.streamer else 0
             res[(label, n)] = (ms, copied)
         be.status_poll()
-        if w.streamer:
+        if w.streamer and label == "streamed":
             res["slots"] = {"slot_bytes": w.block_bytes, "budget_bytes": budget}
         w.close()
         del w
         torch.cuda.empty_cache()
-    keys = [(l, n) for l in ("streamed", "resident") for n in names]
+    labels = [r[0] for r in routes]
+    keys = [(l, n) for l in labels for n in names]
     vals = reduce_max([res[k][0] for k in keys])
     ms = dict(zip(keys, vals))
     out = {"workload": f"config4: INT4 ConvRot DiT step, weights streamed from pinned host memory under a 2 GiB budget, "
                        f"batch of {TOTAL_LATENTS} latents, {L} per GPU on {world} GPU(s); max over ranks",
            "latents_per_gpu": L, "latents_total": L * world, "steps": steps, "unit": "s/step (whole batch)",
+           "route": ("each block crosses the host link once per node: every GPU copies 1/%d of it, the pieces are "
+                     "all-gathered over NVLink on the transfer stream" % world) if world > 1 else "one GPU: every block copied whole",
            "slots": res.get("slots"), "variants": {}}
     for n in names:
         s_ms, r_ms = ms[("streamed", n)], ms[("resident", n)]
@@ -746,6 +759,11 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
                               "streamed_bytes_per_step_per_gpu": copied,
                               "h2d_gbs_per_gpu": copied / (s_ms * 1e-3) / 1e9,
                               "s_per_latent": s_ms / 1e3 / L, "what": DIT_VARIANTS[n][0]}
+        if world > 1:
+            o_ms = ms[("own_copies", n)]
+            out["variants"][n].update({"s_per_step_every_gpu_copies_everything": o_ms / 1e3,
+                                       "overhead_every_gpu_copies_everything": o_ms / r_ms - 1.0,
+                                       "h2d_bytes_per_step_per_gpu_every_gpu_copies_everything": res[("own_copies", n)][1]})
     return out
 
 

@@ -226,6 +226,27 @@ int tpb_stream_release(tpb_streamer_t s, int layer_id, tpb_stream_t compute);
 /* Bytes copied host -> device since open (for the achieved-H2D-bandwidth figure). */
 uint64_t tpb_stream_bytes_copied(tpb_streamer_t s);
 
+/* Sharing the host link between the GPUs of a node (no counterpart in the reference, which
+ * opens one device: src/gpu/cuda/context.zig:111).  When g processes, one per GPU, stream the
+ * same layers in the same order, each can pull 1/g of every layer through PCIe and get the
+ * rest from the others over NVLink:
+ *   tpb_stream_prefetch_part(s, L, r, g, &dev) gives L a slot like prefetch does, copies only
+ *     piece r of g of its image to the same offset in the slot, and returns the slot's device
+ *     address.  Pieces are tpb_stream_piece_bytes(bytes, g) long (the image cut into g equal
+ *     parts, rounded up to 256 bytes; the last is shorter); g * piece must fit a slot.  It
+ *     may be called for several pieces of one layer.  No event is recorded yet.  For a layer
+ *     that is resident (or on its way) already it copies nothing and returns a null address:
+ *     skip the exchange and the commit -- processes that made the same calls all see the same.
+ *   The host then enqueues, on tpb_stream_transfer_stream(s), whatever brings the other
+ *     pieces into the slot (an in-place all-gather over the g slots).
+ *   tpb_stream_commit(s, L) records the layer's "copied" event behind that work; from then on
+ *     acquire / release work as usual.  acquire on a layer with uncommitted pieces and commit
+ *     without pieces return TPB_ERR_STATE. */
+size_t tpb_stream_piece_bytes(size_t bytes, int n_parts);
+int tpb_stream_prefetch_part(tpb_streamer_t s, int layer_id, int part, int n_parts, void **dev_ptr);
+int tpb_stream_commit(tpb_streamer_t s, int layer_id);
+tpb_stream_t tpb_stream_transfer_stream(tpb_streamer_t s);
+
 /* Pinned host memory for weight images (cuMemHostAlloc in src/gpu/cuda/context.zig:151-160). */
 int tpb_host_alloc(tpb_handle_t h, size_t bytes, void **out);
 int tpb_host_free(tpb_handle_t h, void *p);

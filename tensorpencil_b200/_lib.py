@@ -51,6 +51,10 @@ SIGNATURES = {
     "tpb_stream_acquire": (_i, [_vp, _i, _vp, C.POINTER(_vp)]),
     "tpb_stream_release": (_i, [_vp, _i, _vp]),
     "tpb_stream_bytes_copied": (C.c_uint64, [_vp]),
+    "tpb_stream_piece_bytes": (_sz, [_sz, _i]),
+    "tpb_stream_prefetch_part": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
+    "tpb_stream_commit": (_i, [_vp, _i]),
+    "tpb_stream_transfer_stream": (_vp, [_vp]),
     "tpb_host_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tpb_host_free": (_i, [_vp, _vp]),
     "tpb_silu_mul": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i64]),

@@ -14,6 +14,12 @@
 //                L's "copied" event.
 //   acquire(L) : (prefetches on demand) compute stream waits for "copied".
 //   release(L) : records the slot's release event on the compute stream.
+//
+// Several GPUs of a node that stream the same weights share the host link instead of each
+// pulling every byte through it: prefetch_part(L, r, g) copies only piece r of g of the image
+// into the slot, the host then fills in the other pieces from the other GPUs' slots over
+// NVLink (an all-gather enqueued on the transfer stream, whose handle transfer_stream()
+// returns) and commit(L) records the "copied" event behind it.
 #include <new>
 #include <vector>
 
@@ -32,6 +38,7 @@ struct Slot {
     void *dev = nullptr;
     int layer = -1;
     bool in_use = false;        // acquired and not yet released
+    bool filling = false;       // pieces are being copied in; "copied" is recorded by commit()
     bool has_release = false;   // `released` has been recorded at least once
     uint64_t release_seq = 0;   // order of the last release (0 = never used)
     cudaEvent_t copied = nullptr;
@@ -50,30 +57,43 @@ struct tpb_streamer_s {
     uint64_t seq = 0;
 };
 
-static int stream_prefetch_impl(tpb_streamer_t s, int layer_id) {
+// Gives layer L a slot: the free one released longest ago (never-used slots first); the transfer
+// stream waits for that slot's release.  *fresh says whether the slot was assigned by this call.
+static int stream_take_slot(tpb_streamer_t s, int layer_id, const char *who, bool *fresh) {
     tpb_handle_t h = s->h;
     Layer &L = s->layers[layer_id];
+    *fresh = false;
     if (L.slot >= 0) return TPB_OK;  // already resident or on its way
-    // Free slot that was released longest ago (never-used slots first).
     int best = -1;
     for (int i = 0; i < (int)s->slots.size(); i++) {
         const Slot &c = s->slots[i];
-        if (c.in_use) continue;
+        if (c.in_use || c.filling) continue;
         if (best < 0 || c.release_seq < s->slots[best].release_seq) best = i;
     }
     if (best < 0)
         return tpb_fail(h, TPB_ERR_STATE,
-                        "stream_prefetch: every slot holds an acquired layer (release one first, or open more slots)");
+                        "%s: every slot holds an acquired layer (release one first, or open more slots)", who);
     Slot &c = s->slots[best];
     if (c.layer >= 0) s->layers[c.layer].slot = -1;  // evict
     if (c.has_release) TPB_CUDA(h, cudaStreamWaitEvent(s->xfer, c.released, 0));
-    TPB_CUDA(h, cudaMemcpyAsync(c.dev, L.host, L.bytes, cudaMemcpyHostToDevice, s->xfer));
-    TPB_CUDA(h, cudaEventRecord(c.copied, s->xfer));
     c.layer = layer_id;
     // Keep a slot that was just filled from being picked again before it is used:
     // it now counts as the most recently touched one.
     c.release_seq = ++s->seq;
     L.slot = best;
+    *fresh = true;
+    return TPB_OK;
+}
+
+static int stream_prefetch_impl(tpb_streamer_t s, int layer_id) {
+    tpb_handle_t h = s->h;
+    bool fresh = false;
+    const int rc = stream_take_slot(s, layer_id, "stream_prefetch", &fresh);
+    if (rc != TPB_OK || !fresh) return rc;
+    Layer &L = s->layers[layer_id];
+    Slot &c = s->slots[L.slot];
+    TPB_CUDA(h, cudaMemcpyAsync(c.dev, L.host, L.bytes, cudaMemcpyHostToDevice, s->xfer));
+    TPB_CUDA(h, cudaEventRecord(c.copied, s->xfer));
     s->bytes_copied += L.bytes;
     return TPB_OK;
 }
@@ -137,8 +157,8 @@ int tpb_stream_register(tpb_streamer_t s, int layer_id, const void *pinned_host,
     if ((size_t)layer_id >= s->layers.size()) s->layers.resize(layer_id + 1);
     Layer &L = s->layers[layer_id];
     if (L.registered && L.slot >= 0) {
-        if (s->slots[L.slot].in_use)
-            return tpb_fail(h, TPB_ERR_STATE, "stream_register: layer %d is acquired", layer_id);
+        if (s->slots[L.slot].in_use || s->slots[L.slot].filling)
+            return tpb_fail(h, TPB_ERR_STATE, "stream_register: layer %d is acquired or being filled", layer_id);
         s->slots[L.slot].layer = -1;  // drop the stale image
     }
     L.host = pinned_host;
@@ -171,6 +191,8 @@ int tpb_stream_acquire(tpb_streamer_t s, int layer_id, tpb_stream_t compute, voi
     Layer &L = s->layers[layer_id];
     Slot &c = s->slots[L.slot];
     if (c.in_use) return tpb_fail(h, TPB_ERR_STATE, "stream_acquire: layer %d is already acquired", layer_id);
+    if (c.filling)
+        return tpb_fail(h, TPB_ERR_STATE, "stream_acquire: layer %d is being filled piece by piece and was not committed", layer_id);
     TPB_CUDA(h, cudaStreamWaitEvent((cudaStream_t)compute, c.copied, 0));
     c.in_use = true;
     *dev_ptr = c.dev;
@@ -192,6 +214,61 @@ int tpb_stream_release(tpb_streamer_t s, int layer_id, tpb_stream_t compute) {
     c.release_seq = ++s->seq;
     return TPB_OK;
 }
+
+size_t tpb_stream_piece_bytes(size_t bytes, int n_parts) {
+    if (n_parts < 1) return 0;
+    const size_t piece = (bytes + (size_t)n_parts - 1) / (size_t)n_parts;
+    return (piece + 255) / 256 * 256;
+}
+
+int tpb_stream_prefetch_part(tpb_streamer_t s, int layer_id, int part, int n_parts, void **dev_ptr) {
+    if (!s || !dev_ptr) return TPB_ERR_INVALID_ARG;
+    int rc = check_layer(s, layer_id, "stream_prefetch_part");
+    if (rc != TPB_OK) return rc;
+    tpb_handle_t h = s->h;
+    TPB_CHECK_ARG(h, n_parts >= 1 && part >= 0 && part < n_parts, "stream_prefetch_part: part %d of %d", part, n_parts);
+    Layer &L = s->layers[layer_id];
+    const size_t piece = tpb_stream_piece_bytes(L.bytes, n_parts);
+    TPB_CHECK_ARG(h, piece * (size_t)n_parts <= s->slot_bytes,
+                  "stream_prefetch_part: %d pieces of %zu bytes need a slot of %zu bytes, slots have %zu", n_parts, piece,
+                  piece * (size_t)n_parts, s->slot_bytes);
+    if (L.slot >= 0 && !s->slots[L.slot].filling) {
+        // resident or on its way already (every process of the group sees the same, having made the
+        // same calls): nothing to copy, nothing to exchange, nothing to commit
+        *dev_ptr = nullptr;
+        return TPB_OK;
+    }
+    bool fresh = false;
+    rc = stream_take_slot(s, layer_id, "stream_prefetch_part", &fresh);
+    if (rc != TPB_OK) return rc;
+    Slot &c = s->slots[L.slot];
+    c.filling = true;
+    const size_t off = piece * (size_t)part;
+    if (off < L.bytes) {
+        const size_t n = L.bytes - off < piece ? L.bytes - off : piece;
+        TPB_CUDA(h, cudaMemcpyAsync(static_cast<char *>(c.dev) + off, static_cast<const char *>(L.host) + off, n,
+                                    cudaMemcpyHostToDevice, s->xfer));
+        s->bytes_copied += n;
+    }
+    *dev_ptr = c.dev;
+    return TPB_OK;
+}
+
+int tpb_stream_commit(tpb_streamer_t s, int layer_id) {
+    if (!s) return TPB_ERR_INVALID_ARG;
+    const int rc = check_layer(s, layer_id, "stream_commit");
+    if (rc != TPB_OK) return rc;
+    tpb_handle_t h = s->h;
+    Layer &L = s->layers[layer_id];
+    if (L.slot < 0 || !s->slots[L.slot].filling)
+        return tpb_fail(h, TPB_ERR_STATE, "stream_commit: layer %d has no pieces on their way", layer_id);
+    Slot &c = s->slots[L.slot];
+    TPB_CUDA(h, cudaEventRecord(c.copied, s->xfer));
+    c.filling = false;
+    return TPB_OK;
+}
+
+tpb_stream_t tpb_stream_transfer_stream(tpb_streamer_t s) { return s ? (tpb_stream_t)s->xfer : nullptr; }
 
 uint64_t tpb_stream_bytes_copied(tpb_streamer_t s) { return s ? s->bytes_copied : 0; }
 

@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from . import synth
-from .offload import Streamer, packed_size
+from .offload import Streamer, packed_size, slot_size
 
 MLP_TILE = 2048  # src/models/dit_cuda.zig:39
 
@@ -32,7 +32,7 @@ class DitWeights:
 
     def __init__(self, be, bits: int, blocks: int = synth.DIT_BLOCKS, hidden: int = synth.DIT_HIDDEN,
                  mlp: int = synth.DIT_MLP, seed: int = 1003, stream_budget: Optional[int] = None,
-                 distinct_blocks: Optional[int] = None):
+                 distinct_blocks: Optional[int] = None, stream_group=None):
         self.be, self.bits, self.blocks, self.hidden, self.mlp = be, bits, blocks, hidden, mlp
         self.names = [n for n, _, _ in synth.DIT_LINEARS]
         # Generating 28 distinct blocks of random weights on the host takes a while and
@@ -52,11 +52,16 @@ class DitWeights:
             host = [{n: {"w": hb[n]["w"].cpu().numpy(), "w_scale": hb[n]["w_scale"].cpu().numpy()} for n in self.names}
                     for hb in host]
             arrays0 = [a for n in self.names for a in (host[0][n]["w"], host[0][n]["w_scale"])]
-            slot = packed_size(arrays0)
+            world = 1
+            if stream_group is not None:
+                import torch.distributed as dist
+                world = dist.get_world_size(stream_group)
+            slot = slot_size(packed_size(arrays0), world)
             n_slots = max(2, min(4, stream_budget // slot))
             if n_slots * slot > stream_budget:
                 raise ValueError(f"budget {stream_budget} cannot hold two blocks of {slot} bytes")
-            self.streamer = Streamer(be, stream_budget, slot, n_slots)
+            # stream_group: the ranks of a node that hold these same weights share the host link
+            self.streamer = Streamer(be, stream_budget, slot, n_slots, group=stream_group)
             for b in range(blocks):
                 hb = host[b % distinct]
                 self.streamer.register(b, [a for n in self.names for a in (hb[n]["w"], hb[n]["w_scale"])])

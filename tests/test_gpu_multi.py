@@ -1,6 +1,8 @@
 """Two-GPU checks (skipped on a single-GPU box): replicas give the same answer on
-every device, and the N-split GEMM is bit-identical to one GPU both with the NCCL
-all-gather and with the all-gather fused into the GEMM epilogue (peer stores)."""
+every device, the N-split GEMM is bit-identical to one GPU both with the NCCL
+all-gather and with the all-gather fused into the GEMM epilogue (peer stores), and a
+streamed block stack whose ranks share the host link (every rank copies half of each
+block, the halves are exchanged over NVLink) equals the resident run bit for bit."""
 import os
 import socket
 
@@ -92,4 +94,54 @@ def test_two_gpu_replicas_and_nsplit():
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}
+
+
+def _stream_worker(rank, world, port, ret):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+    from tensorpencil_b200 import harness, synth
+    from tensorpencil_b200.backend import Backend
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        be = Backend(rank)
+        blocks, hid, mlp, tokens = 5, 512, 1024, 300
+        res = harness.DitWeights(be, 4, blocks=blocks, hidden=hid, mlp=mlp, seed=77)
+        probe = harness.DitWeights(be, 4, blocks=1, hidden=hid, mlp=mlp, seed=77, stream_budget=1 << 28)
+        slot = probe.block_bytes
+        probe.close()
+        # two slots (plus the rounding the pieces need) for five blocks: slots are reused within a step
+        st = harness.DitWeights(be, 4, blocks=blocks, hidden=hid, mlp=mlp, seed=77, stream_budget=2 * slot + 4096,
+                                stream_group=dist.group.WORLD)
+        mod = harness.dit_modulation(be, blocks, hid, seed=6)
+        x0 = synth.activations(tokens, hid, seed=50 + rank)      # the ranks work on different latents
+        outs = []
+        for w in (res, st, st):                                  # the second streamed step reuses slots
+            x = torch.from_numpy(x0.copy()).cuda()
+            outs.append(harness.dit_step_linears(be, w, x, mode="fused", mod=mod, mlp_tile=tokens).clone())
+            be.status_poll()
+        copied = st.streamer.bytes_copied()
+        ret[rank] = (bool(torch.equal(outs[0], outs[1])), bool(torch.equal(outs[0], outs[2])),
+                     # every rank pulled about half of the ten block images through its own link
+                     0.4 * 2 * blocks * slot <= copied <= 0.6 * 2 * blocks * slot)
+        st.close()
+        res.close()
+        be.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_streaming_with_a_shared_host_link():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_stream_worker, args=(2, port, ret), nprocs=2, join=True)
         assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}

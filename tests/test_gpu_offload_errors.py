@@ -140,3 +140,45 @@ def test_null_arguments(be):
     finally:
         s.close()
     assert TPB_OK == 0
+
+
+def test_a_layer_brought_in_piece_by_piece(be):
+    """The entry points behind the shared host link, on one GPU: both halves of a layer copied by this
+    process, then commit -- the slot holds the image; the misuse around it is reported."""
+    lib = be.lib
+    nbytes = SLOT // 2 - 40                                  # not a multiple of the piece size
+    piece = int(lib.tpb_stream_piece_bytes(nbytes, 2))
+    assert piece % 256 == 0 and 2 * piece >= nbytes
+    s = make(be, n_slots=2, slot=SLOT)
+    try:
+        img = layer(11, nbytes)
+        s.register(0, img)
+        s.register(1, layer(12, nbytes))
+        dev = C.c_void_p()
+        st, msg = status_of(lambda: s._check(lib.tpb_stream_commit(s.s, 0)))
+        assert st == TPB_ERR_STATE and "no pieces" in msg
+        st, _ = status_of(lambda: s._check(lib.tpb_stream_prefetch_part(s.s, 0, 2, 2, C.byref(dev))))
+        assert st == TPB_ERR_INVALID_ARG                      # part out of range
+        st, msg = status_of(lambda: s._check(lib.tpb_stream_prefetch_part(s.s, 0, 0, 512, C.byref(dev))))
+        assert st == TPB_ERR_INVALID_ARG and "need a slot" in msg   # 512 pieces of 256 bytes
+        s._check(lib.tpb_stream_prefetch_part(s.s, 0, 1, 2, C.byref(dev)))
+        first = dev.value
+        assert first
+        st, msg = status_of(lambda: s.acquire(0))             # pieces under way, not committed
+        assert st == TPB_ERR_STATE and "not committed" in msg
+        s._check(lib.tpb_stream_prefetch_part(s.s, 0, 0, 2, C.byref(dev)))
+        assert dev.value == first                             # same slot
+        s._check(lib.tpb_stream_commit(s.s, 0))
+        got = s.acquire(0)[0]
+        assert torch.equal(got.cpu(), torch.from_numpy(img[0]))
+        # resident now: another piece request copies nothing and says so with a null address
+        s._check(lib.tpb_stream_prefetch_part(s.s, 0, 0, 2, C.byref(dev)))
+        assert not dev.value
+        s.release(0)
+        assert s.bytes_copied() == nbytes
+        assert int(lib.tpb_stream_transfer_stream(s.s)) != 0
+        # the whole-layer path still works beside it
+        assert torch.equal(s.acquire(1)[0].cpu(), torch.from_numpy(layer(12, nbytes)[0]))
+        s.release(1)
+    finally:
+        s.close()
