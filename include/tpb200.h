@@ -130,12 +130,29 @@ int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, in
                                const int32_t *act_sum, const void *w, int w_bits,
                                const float *w_scale, int64_t m, int64_t n, int64_t k);
 
+/* The MLP's gate and up projections with the SiLU gate folded into the epilogue: replaces
+ * op{I8,I4}Gemm (mlp.gate), op{I8,I4}Gemm (mlp.up) and Backend.siluMul
+ * (src/models/dit_cuda.zig:508-513; src/gpu/cuda/backend.zig:3294-3315) by one launch:
+ *   g = (float(acc_gate) * act_scale[i]) * w_gate_scale[j],  u = likewise with w_up
+ *   y[i][j] = (g * sigmoid(g)) * u                           f32 arithmetic, then f32 or bf16
+ * Both weights are [n][k] with their own scales; a tile's two halves come from the two weights,
+ * so they are read as they lie in the checkpoint.  With y_dtype f32 the result is bit-identical to
+ * the two GEMMs (f32) followed by tpb_silu_mul; bf16 is its round-to-nearest-even (the separate
+ * route with bf16 GEMM outputs rounds g and u first, so it differs from that one in the last bits).
+ * Always runs the two-CTA kernel.  For w_bits = 4 the reservation (tpb_convrot_w4_reserve) must
+ * cover both weights: 2 n x k elements.  act_sum as for tpb_convrot_gemm. */
+int tpb_convrot_gemm_silu_pair(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, int64_t ldy,
+                               const int8_t *q, const float *act_scale, const int32_t *act_sum,
+                               const void *w_gate, const float *w_gate_scale, const void *w_up,
+                               const float *w_up_scale, int w_bits, int64_t m, int64_t n, int64_t k);
+
 /* INT4 weights run on the int8 tensor-core path: unless TPB_W4_FUSED=1 selects the kernel that
  * unpacks nibbles in shared memory, every int4 GEMM first widens its weight into a scratch
  * buffer the handle owns.  tpb_convrot_w4_reserve sizes that buffer for weights of up to n x k
  * elements (cudaMalloc; it may cudaFree a smaller one, which waits for the device).  Call it
  * once per handle, at set-up, outside any stream capture: the stream-ordered entry points
- * (tpb_convrot_gemm, tpb_convrot_linear, tpb_convrot_gemm_gated_add, the all-gather forms)
+ * (tpb_convrot_gemm, tpb_convrot_linear, tpb_convrot_gemm_gated_add, tpb_convrot_gemm_silu_pair,
+ * the all-gather forms)
  * never allocate, and return TPB_ERR_STATE for an int4 weight larger than the reservation.
  * Replaces the reference's ensureDeviceBuffer growth of its backend scratch
  * (src/gpu/cuda/backend.zig:2457-2470), made explicit. */

@@ -195,6 +195,32 @@ class Backend {
                                          (int64_t)m_, (int64_t)rows, (int64_t)cols_));
     }
 
+    // mlp.gate GEMM + mlp.up GEMM + siluMul in one launch (dit_cuda.zig:508-513):
+    // y[m][rows] = silu(linear_gate(prepped)) * linear_up(prepped), f32
+    void gemmSiluPair(DeviceBuffer y, const void *gate_bytes, const float *gate_scale, const void *up_bytes,
+                      const float *up_scale, size_t rows, int bits = 8) {
+        if (bits_ != bits) throw Error(TPB_ERR_STATE, "gemmSiluPair must follow the matching prep");
+        const size_t w_size = bits == 4 ? rows * cols_ / 2 : rows * cols_;
+        // all four arrays must be resident at once: pin each until the call is enqueued
+        const void *hosts[4] = {gate_bytes, gate_scale, up_bytes, up_scale};
+        const size_t sizes[4] = {w_size, rows * 4, w_size, rows * 4};
+        const void *dev[4] = {nullptr, nullptr, nullptr, nullptr};
+        int pinned = 0;
+        try {
+            for (; pinned < 4; pinned++) dev[pinned] = cachedWeight(hosts[pinned], sizes[pinned], true);
+        } catch (...) {
+            for (int i = 0; i < pinned; i++) unpinWeight(hosts[i]);
+            throw;
+        }
+        for (int i = 0; i < 4; i++) unpinWeight(hosts[i]);
+        if (bits == 4) reserveW4(2 * rows, cols_);
+        check(tpb_convrot_gemm_silu_pair(h_, stream_, y.p, TPB_F32, (int64_t)rows, static_cast<const int8_t *>(i8_x_.p),
+                                         static_cast<const float *>(i8_scale_.p),
+                                         bits == 4 ? static_cast<const int32_t *>(i8_sum_.p) : nullptr, dev[0],
+                                         static_cast<const float *>(dev[1]), dev[2], static_cast<const float *>(dev[3]),
+                                         bits, (int64_t)m_, (int64_t)rows, (int64_t)cols_));
+    }
+
     // ---- attention of the DiT block (dit_cuda.zig:479-489: qkNorm, rope, attn / opAttnTC) ----
     // q [seq][heads*hd], k / v [seq][kv_heads*hd] (f32), freqs = cos table [seq][hd/2] then, sin_off floats
     // later, the sin table; out [seq][heads*hd] f32.  head_dim 128, non-causal.  Unlike the reference's

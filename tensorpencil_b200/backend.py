@@ -321,6 +321,21 @@ class Backend:
         self._check(rc)
         self.launches += 2 if w_bits == 4 else 1
 
+    def gemmSiluPair(self, y: torch.Tensor, w_gate, gate_scale, w_up, up_scale, rows: int, w_bits: int = 8):
+        """mlp.gate GEMM + mlp.up GEMM + siluMul in one kernel: y[m][rows] = silu(linear_gate(prepped)) *
+        linear_up(prepped) (dit_cuda.zig:508-513).  y is f32 or bf16."""
+        assert self.i8_bits == w_bits and y.dtype in (torch.float32, torch.bfloat16) and y.stride(-1) == 1
+        dev = [self.cachedWeight(a) if isinstance(a, np.ndarray) else a for a in (w_gate, gate_scale, w_up, up_scale)]
+        if w_bits == 4:
+            self.reserveW4(2 * rows, self.i8_cols)
+        rc = self.lib.tpb_convrot_gemm_silu_pair(self.h, self._stream(), y.data_ptr(), _TORCH_TO_TPB[y.dtype], y.stride(0),
+                                                 self.i8_x.data_ptr(), self.i8_scale.data_ptr(),
+                                                 self.i8_sum.data_ptr() if w_bits == 4 else None,
+                                                 dev[0].data_ptr(), _ptr(dev[1]), dev[2].data_ptr(), _ptr(dev[3]),
+                                                 w_bits, self.i8_m, rows, self.i8_cols)
+        self._check(rc)
+        self.launches += 3 if w_bits == 4 else 1
+
     def opI8Gemm(self, y: torch.Tensor, w_bytes, weight_scale, rows: int, c_h16: bool = False):
         """y[m][rows] = prepped @ W^T * act_scale[row] * weight_scale[col]
         (backend.zig:2484-2501).  The output type is y.dtype (f32 or bf16; int32

@@ -224,6 +224,23 @@ int tpb_convrot_gemm_gated_add(tpb_handle_t h, tpb_stream_t stream, float *x, in
                            k, nullptr, 0, nullptr, gate);
 }
 
+int tpb_convrot_gemm_silu_pair(tpb_handle_t h, tpb_stream_t stream, void *y, int y_dtype, int64_t ldy, const int8_t *q,
+                               const float *act_scale, const int32_t *act_sum, const void *w_gate,
+                               const float *w_gate_scale, const void *w_up, const float *w_up_scale, int w_bits,
+                               int64_t m, int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, y_dtype == TPB_F32 || y_dtype == TPB_BF16, "gemm_silu_pair: y_dtype must be f32 or bf16");
+    // each weight is checked as for the plain GEMM
+    int rc = tpb_convrot_gemm(h, nullptr, y, y_dtype, ldy, q, act_scale, act_sum, w_gate, w_bits, w_gate_scale, 0, n, k);
+    if (rc != TPB_OK) return rc;
+    rc = tpb_convrot_gemm(h, nullptr, y, y_dtype, ldy, q, act_scale, act_sum, w_up, w_bits, w_up_scale, 0, n, k);
+    if (rc != TPB_OK) return rc;
+    TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "gemm_silu_pair: bad m");
+    if (m == 0) return TPB_OK;
+    return tpb_launch_gemm_silu_pair(h, (cudaStream_t)stream, y, y_dtype, ldy, q, act_scale, w_gate, w_gate_scale, w_up,
+                                     w_up_scale, w_bits, m, n, k);
+}
+
 int tpb_q8_1_quantize(tpb_handle_t h, tpb_stream_t stream, const float *x, int64_t n_elems,
                       void *xq) {
     if (!h) return TPB_ERR_INVALID_ARG;

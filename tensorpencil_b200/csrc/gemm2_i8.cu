@@ -33,10 +33,14 @@ constexpr int kStaging2 = 4 * 2 * 4096;
 constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
 constexpr int kTmemCols2 = 2 * BN2;
 
-template <int OUT, int PEERS>
+// PAIR: the weight tile's two halves come from two different weights (tma_b: the leader's 128 rows,
+// tma_b2: the peer's), both for the same 128 output columns, and the epilogue combines the two
+// projections into silu(first) * second (epilogue_pair).
+template <int OUT, int PEERS, int PAIR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                     const __grid_constant__ CUtensorMap tma_y, const GemmParams p, const int b_unsigned) {
+                     const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_y,
+                     const GemmParams p, const int b_unsigned) {
     constexpr int S = kStages2;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -58,7 +62,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     const int n_pairs = gridDim.x >> 1;
 
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM);  // 256-row tiles
-    const int n_tiles = (p.n + BN2 - 1) / BN2;
+    constexpr int kTileN = PAIR ? BN2 / 2 : BN2;   // output columns per tile
+    const int n_tiles = (p.n + kTileN - 1) / kTileN;
     const int num_tiles = m_tiles * n_tiles;
     const int k_blocks = p.k / BK;
 
@@ -98,7 +103,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
                 const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
-                const int n0 = (tile / m_tiles) * BN2 + (int)rank * (BN2 / 2);
+                const int n0 = PAIR ? (tile / m_tiles) * kTileN : (tile / m_tiles) * BN2 + (int)rank * (BN2 / 2);
+                const CUtensorMap *bmap = (PAIR && rank == 1) ? &tma_b2 : &tma_b;
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
@@ -110,7 +116,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                         mbar_arrive_expect_tx(full_bar(s), 2u * ((load_a ? kStageA : 0) + (load_b ? kStageB : 0)));
                     const uint32_t a_dst = smem_base + s * kStage2;
                     if (load_a) tma_load_2d_pair(a_dst, &tma_a, lead_full, kb * BK, m0);
-                    if (load_b) tma_load_2d_pair(a_dst + kStageA, &tma_b, lead_full, kb * BK, n0);
+                    if (load_b) tma_load_2d_pair(a_dst + kStageA, bmap, lead_full, kb * BK, n0);
                 }
             }
         }
@@ -160,7 +166,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, t_it++) {
             const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
-            const int n0 = (tile / m_tiles) * BN2;
+            const int n0 = (tile / m_tiles) * kTileN;
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
             ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc, true);
@@ -175,8 +181,12 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             if (OUT != OUT_S32 && row_ok) as = __ldcg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldcg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
-            if (!(p.ablate & 4))
+            if (PAIR) {
+                if constexpr (PAIR != 0 && (OUT == OUT_F32 || OUT == OUT_BF16))
+                    epilogue_pair<OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, lane);
+            } else if (!(p.ablate & 4)) {
                 epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
@@ -217,14 +227,37 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
     if (rc != TPB_OK) return rc;
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
-    auto kern = convrot_gemm2_kernel<OUT, PEERS>;
+    auto kern = convrot_gemm2_kernel<OUT, PEERS, 0>;
     static tpb_per_device_once smem_set;   // per instantiation
     TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, my, p, b_unsigned ? 1 : 0));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, b_unsigned ? 1 : 0));
+    return TPB_OK;
+}
+
+template <int OUT>
+int launch_silu_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w_gate,
+                     const void *w_up) {
+    CUtensorMap ma, mb, mb2, my;
+    int rc = make_kmajor_map(h, &ma, q, p.m, p.k, BM);
+    if (rc != TPB_OK) return rc;
+    rc = make_kmajor_map(h, &mb, w_gate, p.n, p.k, BN2 / 2);
+    if (rc != TPB_OK) return rc;
+    rc = make_kmajor_map(h, &mb2, w_up, p.n, p.k, BN2 / 2);
+    if (rc != TPB_OK) return rc;
+    rc = make_out_map<OUT>(h, &my, p);
+    if (rc != TPB_OK) return rc;
+    auto kern = convrot_gemm2_kernel<OUT, 0, 1>;
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
+    const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 / 2 - 1) / (BN2 / 2);
+    const int tiles = m_tiles * n_tiles;
+    const int max_pairs = h->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb2, my, p, 0));
     return TPB_OK;
 }
 
@@ -244,6 +277,13 @@ int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8
 bool tpb_gemm2_wants(tpb_handle_t h, int64_t m, int64_t n) {
     const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
     return tiles >= h->sm_count / 2;
+}
+
+int tpb_launch_gemm2_silu_pair(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
+                               const int8_t *q, const void *w_gate, const void *w_up) {
+    if (y_dtype == TPB_F32) return launch_silu_pair<OUT_F32>(h, st, p, q, w_gate, w_up);
+    if (y_dtype == TPB_BF16) return launch_silu_pair<OUT_BF16>(h, st, p, q, w_gate, w_up);
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm_silu_pair: y_dtype must be f32 or bf16");
 }
 
 int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,

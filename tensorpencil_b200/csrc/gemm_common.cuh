@@ -54,6 +54,9 @@ struct GemmParams {
     // Gated residual (epilogue mode 3, f32 only): y is the residual stream x and the
     // epilogue stores x + gate[col] * (acc * act_scale * w_scale) back into it.
     const float *gate;
+    // Paired weights (two-CTA kernel, PAIR mode): the scales of the second weight; the output is
+    // silu(gate projection) * (up projection), n columns wide.
+    const float *w_scale2 = nullptr;
     // Diagnosis only (TPB_GEMM_ABLATE, two-CTA kernel): bit 0 = issue no loads of q, bit 1 = no loads
     // of w, bit 2 = no epilogue (accumulators are handed back unread), bit 3 = the epilogue only
     // reads the accumulators out of tensor memory, bit 4 = it also converts and stages them in
@@ -403,6 +406,89 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                         }
                     }
                 }
+            }
+            n_store++;
+        }
+    }
+}
+
+// sigmoid with the fast exponential and reciprocal: the same two instructions, in the same order,
+// as the stand-alone SiLU / sigmoid ops (prep_common.cuh), so that fusing changes no bit.
+__device__ __forceinline__ float sigmoid_fast_ep(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
+
+// Epilogue of the paired-weight tile: accumulator columns 0..127 hold the gate projection of
+// output columns n0 .. n0+127, columns 128..255 the up projection of the same ones.  Both are
+// dequantised as in epilogue_tile, out = (g * sigmoid(g)) * u in f32 (the arithmetic of the
+// stand-alone siluMul on f32 operands, src/models/dit_cuda.zig:513), then f32 or bf16, staged
+// and stored like any other tile.
+template <int OUT>
+__device__ __forceinline__ void epilogue_pair(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
+                                              uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
+                                              int row0, int n0, float as, int lane) {
+    static_assert(OUT == OUT_F32 || OUT == OUT_BF16, "paired epilogue writes f32 or bf16");
+    uint32_t rg[32], ru[32];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const int col0 = n0 + c * 32;
+        const int scol = (OUT == OUT_BF16 && (c & 1)) ? col0 - 32 : col0;
+        const bool do_store = row0 < p.m && scol < p.n;   // warp-uniform
+        if (!do_store) continue;
+        tc_ld_32x32(t_row + (uint32_t)(c * 32), rg);
+        tc_ld_32x32(t_row + (uint32_t)(128 + c * 32), ru);
+        tc_wait_ld_dep(rg);
+        tc_wait_ld_dep(ru);
+        const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
+        const uint32_t buf = stg + (n_store & 1u) * 4096u + my_row_off;
+        if (first_piece) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+        }
+        float o[32];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            float4 wg = make_float4(0.f, 0.f, 0.f, 0.f), wu = wg;
+            if (col0 + 4 * g < p.n) {
+                wg = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                wu = __ldg(reinterpret_cast<const float4 *>(p.w_scale2 + col0 + 4 * g));
+            }
+            const float wgs[4] = {wg.x, wg.y, wg.z, wg.w}, wus[4] = {wu.x, wu.y, wu.z, wu.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float vg = __fmul_rn(__fmul_rn(__int2float_rn((int)rg[4 * g + e]), as), wgs[e]);
+                const float vu = __fmul_rn(__fmul_rn(__int2float_rn((int)ru[4 * g + e]), as), wus[e]);
+                o[4 * g + e] = __fmul_rn(__fmul_rn(vg, sigmoid_fast_ep(vg)), vu);
+            }
+        }
+        if (OUT == OUT_F32) {
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+                st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), __float_as_uint(o[4 * g]), __float_as_uint(o[4 * g + 1]),
+                             __float_as_uint(o[4 * g + 2]), __float_as_uint(o[4 * g + 3]));
+        } else {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(o[8 * g + 2 * e], o[8 * g + 2 * e + 1]);
+                    pk[e] = *reinterpret_cast<const uint32_t *>(&b2);
+                }
+                const uint32_t piece = (uint32_t)(4 * (c & 1) + g);
+                st_shared_v4(buf + ((piece ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+        const bool last_piece = OUT != OUT_BF16 || (c & 1) == 1;
+        if (last_piece) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
             n_store++;
         }

@@ -23,6 +23,8 @@
 #include "gemm_common.cuh"
 
 bool tpb_gemm2_wants(tpb_handle_t h, int64_t m, int64_t n);
+int tpb_launch_gemm2_silu_pair(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
+                               const int8_t *q, const void *w_gate, const void *w_up);
 int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
                      const int8_t *q, const void *w8, bool b_unsigned);
 int tpb_launch_gemm_w4(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
@@ -303,4 +305,41 @@ int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64
         case TPB_S32: return launch_out<OUT_S32>(h, st, p, q, w8, false);
     }
     return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm: unsupported y_dtype %d", y_dtype);
+}
+
+// y = silu(gate projection) * (up projection): both weights multiplied in one launch of the two-CTA
+// kernel (each CTA of a pair brings in one weight's half of the tile), combined in its epilogue.
+int tpb_launch_gemm_silu_pair(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy, const int8_t *q,
+                              const float *act_scale, const void *w_gate, const float *w_gate_scale, const void *w_up,
+                              const float *w_up_scale, int w_bits, int64_t m, int64_t n, int64_t k) {
+    GemmParams p;
+    p.mc_y = nullptr;
+    p.gate = nullptr;
+    p.ablate = 0;
+    p.n_peers = 0;
+    for (int i = 0; i < kMaxPeers; i++) p.peer_y[i] = nullptr;
+    p.y = y;
+    p.ldy = ldy;
+    p.act_scale = act_scale;
+    p.w_scale = w_gate_scale;
+    p.w_scale2 = w_up_scale;
+    p.act_sum = nullptr;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.status = h->d_status;
+    const void *g8 = w_gate, *u8 = w_up;
+    if (w_bits == 4) {
+        // both weights widened into the reserved scratch, one after the other
+        int8_t *buf = nullptr;
+        int rc = tpb_w4_scratch(h, 2 * n, k, &buf);
+        if (rc != TPB_OK) return rc;
+        rc = tpb_launch_w4_expand(h, st, w_gate, n, k, buf);
+        if (rc != TPB_OK) return rc;
+        rc = tpb_launch_w4_expand(h, st, w_up, n, k, buf + (size_t)n * (size_t)k);
+        if (rc != TPB_OK) return rc;
+        g8 = buf;
+        u8 = buf + (size_t)n * (size_t)k;
+    }
+    return tpb_launch_gemm2_silu_pair(h, st, p, y_dtype, q, g8, u8);
 }

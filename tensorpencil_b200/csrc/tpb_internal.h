@@ -136,6 +136,9 @@ int tpb_launch_prep(tpb_handle_t h, cudaStream_t st, const void *x, int x_dtype,
                     int64_t k, int bits, int8_t *q, float *act_scale, int32_t *act_sum);
 int tpb_launch_w4_expand(tpb_handle_t h, cudaStream_t st, const void *w4, int64_t n, int64_t k,
                          int8_t *w8);
+int tpb_launch_gemm_silu_pair(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy, const int8_t *q,
+                              const float *act_scale, const void *w_gate, const float *w_gate_scale, const void *w_up,
+                              const float *w_up_scale, int w_bits, int64_t m, int64_t n, int64_t k);
 int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
                     const int8_t *q, const float *act_scale, const int32_t *act_sum,
                     const void *w, int w_bits, const float *w_scale, int64_t m, int64_t n,

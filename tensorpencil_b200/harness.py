@@ -104,7 +104,7 @@ def dit_modulation(be, blocks: int, hidden: int, seed: int = 7) -> torch.Tensor:
 def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
                      mlp_tile: int = MLP_TILE, mode: str = "linears",
                      mod: Optional[torch.Tensor] = None, eps: float = 1e-5,
-                     attn: Optional[dict] = None, latents: int = 1) -> torch.Tensor:
+                     attn: Optional[dict] = None, latents: int = 1, mlp_pair: bool = False) -> torch.Tensor:
     """One step of the block stack on x [latents * tokens][hidden] (f32, updated in place).
 
     mode:
@@ -127,7 +127,11 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
     (the block is acquired, used by every latent, then released); attention runs per latent.
 
     mlp_tile: rows per MLP tile.  The reference tiles by 2048 rows to fit a 24 GB card;
-    with 180 GB of HBM the whole batch can go through at once."""
+    with 180 GB of HBM the whole batch can go through at once.
+
+    mlp_pair (mode "fused"): the MLP's gate and up projections run as one launch whose epilogue
+    applies the SiLU gate (Backend.gemmSiluPair), followed by a plain prep, instead of two GEMMs and
+    the SiLU-gated prep."""
     bits, hid, mlp = w.bits, w.hidden, w.mlp
     prep = be.opI8Prep if bits == 8 else be.opI4Prep
     gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
@@ -210,9 +214,17 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
                 prep(t1, rows, hid)
             else:
                 prep(xt, rows, hid)
-            gemm(tile_gate, wb["mlp_gate"], mlp)
-            gemm(tile_up, wb["mlp_up"], mlp)
-            if mode == "fused":
+            if mode == "fused" and mlp_pair:
+                # gate and up projections with the SiLU gate in the GEMM's epilogue, then a plain prep
+                be.gemmSiluPair(tile_gate[:rows], wb["mlp_gate"][0], wb["mlp_gate"][1], wb["mlp_up"][0], wb["mlp_up"][1],
+                                mlp, bits)
+                prep(tile_gate[:rows], rows, mlp)
+            else:
+                gemm(tile_gate, wb["mlp_gate"], mlp)
+                gemm(tile_up, wb["mlp_up"], mlp)
+            if mode == "fused" and mlp_pair:
+                pass
+            elif mode == "fused":
                 be.prepSiluMul(tile_gate, tile_up, rows, mlp, bits)
             elif mode == "unfused":
                 be.siluMul(tile_gate, tile_up, rows * mlp)

@@ -322,6 +322,27 @@ static void dit_block(tpb::Backend &be, unsigned seed) {
     }
     EXPECT(std::sqrt(fnum / fden) < 1e-4, "dit block, fused against the reference sequence: relative error %g", std::sqrt(fnum / fden));
 
+    // ---- and with the MLP's gate and up projections in one launch, the SiLU gate in its epilogue, then a
+    // plain prep: the bits of the fused block above (f32: the same arithmetic in the same order) ----
+    be.tensorUpload(x_d, x.data(), x.size() * 4);
+    be.prepRmsMod(x_d, mv_d, seq, F, 0, F, eps);
+    lin(q_d, wq);
+    lin(k_d, wk);
+    lin(v_d, wv);
+    lin(g_d, gate);
+    be.attention(q_d, k_d, v_d, attn_d, qn_d, kn_d, freqs_d, sin_off, seq, heads, heads, hd, eps, attn_scale);
+    be.prepSigmoidMul(attn_d, g_d, seq, F);
+    be.gemmGatedAdd(x_d, wo.w.data(), wo.ws.data(), F, mv_d, 2 * F);
+    be.prepRmsMod(x_d, mv_d, seq, F, 3 * F, 4 * F, eps);
+    be.gemmSiluPair(mg_d, mlp_gate.w.data(), mlp_gate.ws.data(), mlp_up.w.data(), mlp_up.ws.data(), MLPD);
+    be.opI8Prep(mg_d, seq, MLPD, false);
+    be.gemmGatedAdd(x_d, mlp_down.w.data(), mlp_down.ws.data(), F, mv_d, 5 * F);
+    std::vector<float> paired(seq * F);
+    be.tensorDownload(x_d, paired.data(), paired.size() * 4);
+    size_t pair_diff = 0;
+    for (size_t i = 0; i < paired.size(); i++) pair_diff += std::memcmp(&paired[i], &fused[i], 4) != 0;
+    EXPECT(pair_diff == 0, "dit block, paired MLP against the fused block: %zu of %zu values differ", pair_diff, paired.size());
+
     double num = 0, den = 0, moved = 0;
     for (size_t i = 0; i < got.size(); i++) {
         num += ((double)got[i] - want[i]) * ((double)got[i] - want[i]);

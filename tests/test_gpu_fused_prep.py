@@ -192,3 +192,58 @@ def test_gemm_with_gated_residual_is_bit_identical_to_two_steps(be, bits, m, n, 
         want = x0.astype(np.float64) + mod.cpu().numpy()[n:2 * n].astype(np.float64) * sim
         err = np.abs(one.cpu().numpy() - want)
         assert (err <= 1e-4 + 1e-3 * np.abs(want)).all()
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,n,k", [(96, 768, 512), (300, 1040, 256), (129, 128, 1024), (4608, 3072, 256), (1100, 12288, 768)])
+def test_gemm_with_silu_pair_is_bit_identical_to_three_steps(be, bits, m, n, k):
+    """silu(gate projection) * (up projection) in one launch == the two f32 GEMMs followed by silu_mul, bit
+    for bit; the bf16 output is that result rounded to nearest even; and the whole agrees with the
+    oracle's integer replica + silu_mul (src/ops/act.zig) to the usual 1e-3 / 1e-4."""
+    from tensorpencil_b200 import synth
+    cg = synth.convrot_linear(m, n, k, bits, seed=51 + m)
+    cu = synth.convrot_linear(m, n, k, bits, seed=52 + m)
+    key = "w_i8" if bits == 8 else "w_packed"
+    wg, wu = dev(cg[key]), dev(cu[key])
+    sg, su = dev(cg["w_scale"]), dev(cu["w_scale"])
+    be._prep(dev(cg["x"]), m, k, bits)
+    g = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    u = torch.empty_like(g)
+    be._gemm(g, wg, sg, n, bits)
+    be._gemm(u, wu, su, n, bits)
+    be.siluMul(g, u, m * n)                                    # in place: g = silu(g) * u
+    one = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    be.gemmSiluPair(one, wg, sg, wu, su, n, bits)
+    one16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    be.gemmSiluPair(one16, wg, sg, wu, su, n, bits)
+    be.status_poll()
+    assert torch.equal(one.view(torch.int32), g.view(torch.int32))
+    assert torch.equal(one16, g.to(torch.bfloat16))
+    if m * n * k <= 300 * 1040 * 256:
+        q = be.i8_x[: m * k].cpu().numpy().reshape(m, k)
+        s = be.i8_scale[:m].cpu().numpy()
+        vg = oracle.dequant_sim(oracle.igemm_s32(q, cg["w_i8"]), s, cg["w_scale"])
+        vu = oracle.dequant_sim(oracle.igemm_s32(q, cu["w_i8"]), s, cu["w_scale"])
+        want = vg / (1.0 + np.exp(-vg)) * vu
+        err = np.abs(one.cpu().numpy() - want)
+        assert (err <= 1e-4 + 1e-3 * np.abs(want)).all()
+
+
+def test_gemm_with_silu_pair_into_a_wider_buffer_and_bad_arguments(be):
+    from tensorpencil_b200 import synth
+    m, n, k = 200, 256, 512
+    cg = synth.convrot_linear(m, n, k, 8, seed=61)
+    cu = synth.convrot_linear(m, n, k, 8, seed=62)
+    wg, wu, sg, su = dev(cg["w_i8"]), dev(cu["w_i8"]), dev(cg["w_scale"]), dev(cu["w_scale"])
+    be._prep(dev(cg["x"]), m, k, 8)
+    wide = torch.full((m, n + 64), -7.0, dtype=torch.float32, device="cuda")
+    be.gemmSiluPair(wide[:, :n], wg, sg, wu, su, n, 8)           # ldy = n + 64
+    tight = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    be.gemmSiluPair(tight, wg, sg, wu, su, n, 8)
+    be.status_poll()
+    assert torch.equal(wide[:, :n], tight) and bool((wide[:, n:] == -7.0).all())
+    L = be.lib
+    args = lambda y_dt, w2: (be.h, None, tight.data_ptr(), y_dt, n, be.i8_x.data_ptr(), be.i8_scale.data_ptr(), None,
+                             wg.data_ptr(), sg.data_ptr(), w2, su.data_ptr(), 8, m, n, k)
+    assert L.tpb_convrot_gemm_silu_pair(*args(_lib.TPB_S32, wu.data_ptr())) == _lib.TPB_ERR_INVALID_ARG   # raw sums make no sense here
+    assert L.tpb_convrot_gemm_silu_pair(*args(_lib.TPB_F32, None)) == _lib.TPB_ERR_INVALID_ARG            # second weight missing
