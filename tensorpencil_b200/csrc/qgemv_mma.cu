@@ -68,7 +68,6 @@ constexpr int kThreadsMma = (kConsumers + kProducers) * 32;
 constexpr int kStageRows = 8;                  // weight rows per stage (rows 0..7 of the MMA's m side)
 constexpr int kActRows = 8;                    // activation rows = n of the MMA
 constexpr int kPartFloats = kStageRows * kActRows;
-constexpr int kGroup = 3;                      // pairs whose loads and MMAs are issued before any of their results is used   // partial sums of one warp for one stage
 
 struct MmaGemvParams {
     float *y;
@@ -172,6 +171,9 @@ __device__ __forceinline__ void cluster_barrier() {
 // KS = CTAs per cluster = parts K is split into (1 or 2).
 template <int NP, int KS>
 __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_0_gemv_mma_kernel(const MmaGemvParams p) {
+    // pairs whose loads and MMAs are issued before any of their results is used: three while the registers
+    // last (short K slices), two beyond -- a spill costs a trip to L2 here, the ring leaves almost no L1
+    constexpr int kGroup = NP <= 6 ? 3 : 2;
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
