@@ -32,16 +32,16 @@ namespace {
 
 enum { FMT_Q4_0 = 1, FMT_Q4_K = 2, FMT_Q5_K = 3, FMT_IQ4_NL = 5 };
 
-constexpr int kUnitsPerLane = 2;                    // 64-element units a lane takes per pipeline stage
-constexpr int kUnitsPerChunk = 32 * kUnitsPerLane;
+// A lane takes U 64-element units per pipeline stage (template parameter: 2, or 3 where that saves iterations
+// per row -- K = 5120 is 80 units: two chunks of 64, the second a quarter full, or one chunk of 96).
 constexpr int kActPairBytes = 80;   // a unit's 64 activation bytes + 16 pad (bank-conflict-free 16-byte reads)
 
 template <int FMT> struct Fmt;
 // bytes of one 64-element unit (a quarter super-block for the k-quants) and of a chunk of one row
-template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
-template <> struct Fmt<FMT_IQ4_NL> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };
-template <> struct Fmt<FMT_Q4_K> { static constexpr int kUnitBytes = 36, kChunkBytes = kUnitsPerChunk * 36; };   // 144 / 4
-template <> struct Fmt<FMT_Q5_K> { static constexpr int kUnitBytes = 44, kChunkBytes = kUnitsPerChunk * 44; };   // 176 / 4
+template <> struct Fmt<FMT_Q4_0> { static constexpr int kUnitBytes = 36; };
+template <> struct Fmt<FMT_IQ4_NL> { static constexpr int kUnitBytes = 36; };
+template <> struct Fmt<FMT_Q4_K> { static constexpr int kUnitBytes = 36; };   // 144 / 4
+template <> struct Fmt<FMT_Q5_K> { static constexpr int kUnitBytes = 44; };   // 176 / 4
 
 struct KGemvParams {
     float *y;
@@ -95,10 +95,12 @@ __device__ __forceinline__ void scale_min_k4(int is, uint32_t s0, uint32_t s1, u
     mn = (float)m;
 }
 
-template <int FMT, int M, int R>
+template <int FMT, int M, int R, int U>
 __global__ void __launch_bounds__(512, 1)
 kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
-    constexpr int kChunkBytes = Fmt<FMT>::kChunkBytes;
+    constexpr int kUnitsPerLane = U;
+    constexpr int kUnitsPerChunk = 32 * U;
+    constexpr int kChunkBytes = kUnitsPerChunk * Fmt<FMT>::kUnitBytes;
     constexpr int kStageBytes = R * kChunkBytes;
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5;
@@ -593,10 +595,10 @@ int launch_q6k(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int ng) {
     return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: ng out of range");
 }
 
-template <int FMT, int M>
-int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
+template <int FMT, int M, int U>
+int launch_fmt_mu(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     constexpr int R = 2;
-    constexpr int kStage = R * Fmt<FMT>::kChunkBytes;
+    constexpr int kStage = R * 32 * U * Fmt<FMT>::kUnitBytes;
     const size_t limit = (size_t)h->smem_optin - 1024;
     const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 8;
     // Warps per CTA: every warp owns a contiguous range of whole rows; among the counts that
@@ -626,11 +628,22 @@ int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     int grid = (int)(((long long)p.rows + (long long)warps * R - 1) / ((long long)warps * R));
     if (grid < 1) grid = 1;
     if (grid > h->sm_count) grid = h->sm_count;
-    auto kern = kquant_gemv_q8n_kernel<FMT, M, R>;
+    auto kern = kquant_gemv_q8n_kernel<FMT, M, R, U>;
     static tpb_per_device_once smem_set;   // the size varies per call: opt in to the device maximum, once
     TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
     TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, st, p, stages));
     return TPB_OK;
+}
+
+template <int FMT, int M>
+int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
+    // three units per lane where that takes fewer chunks per row than two (K = 5120, M = 1: q4_k 17.0 -> 14.6 us,
+    // q4_0 14.6 -> 12.1); with many activation rows the longer unrolled body costs more than it saves
+    // (q5_k, M = 8: 38 -> 45 us), so only up to four
+    const int n_units = p.cols / 64;
+    if constexpr (M <= 4)
+        if ((n_units + 95) / 96 < (n_units + 63) / 64) return launch_fmt_mu<FMT, M, 3>(h, st, p);
+    return launch_fmt_mu<FMT, M, 2>(h, st, p);
 }
 
 template <int FMT>
