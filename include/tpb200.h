@@ -198,7 +198,7 @@ int tpb_q8_0_gemv_f32(tpb_handle_t h, tpb_stream_t stream, float *y, const float
                       const void *w, float scale, int64_t rows, int64_t cols);
 
 /* Decode linear that allocates nothing: quantises x[m][cols] (f32, m <= 8) and runs
- * the grouped dp4a GEMV, y[i*rows + r] as tpb_q8_0_gemv_q8n, keeping the quantised
+ * the Q8_0 GEMV, y[i*rows + r] as tpb_q8_0_gemv_q8n (same kernels, same dispatch), keeping the quantised
  * activations in a fixed array inside the library instead of a buffer somebody has
  * to allocate.  It has no counterpart in the reference, whose backend grows its
  * q8 scratch with ensureDeviceBuffer.  It exists for hosts that cannot let a

@@ -94,3 +94,19 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".h", ".cuh", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower(), (dirpath, f)
+
+
+def test_piece_size_of_the_shared_link_streamer_matches_the_python_slot_size(lib):
+    """tpb_stream_piece_bytes is plain arithmetic (no device): g equal pieces, rounded up to 256 bytes, cover
+    the image; offload.slot_size is g of them."""
+    import random
+    from tensorpencil_b200.offload import slot_size
+    rnd = random.Random(7)
+    for _ in range(200):
+        nbytes, g = rnd.randrange(1, 200_000_000), rnd.choice([1, 2, 3, 4, 8])
+        piece = int(lib.tpb_stream_piece_bytes(nbytes, g))
+        assert piece % 256 == 0 and piece * g >= nbytes and (piece - 256) * g < nbytes
+        if g > 1:
+            assert slot_size(nbytes, g) == piece * g
+    assert slot_size(12345, 1) == 12345
+    assert int(lib.tpb_stream_piece_bytes(1000, 0)) == 0
