@@ -689,6 +689,11 @@ def measure_dit(be, sync, reduce_max, rank, steps, names, agree=_same):
                         for n, v in zip(names, vals)}}
     for n, entry in host_side.items():
         out["variants"][n].update(entry)
+        if "graph_replay_s_per_step" in entry:
+            g = entry["graph_replay_s_per_step"]
+            out["variants"][n + "_cuda_graph"] = {
+                "s_per_step": g, "linear_tops": ops / g / 1e12,
+                "what": DIT_VARIANTS[n][0] + "; the step captured once into a CUDA graph and replayed (rank-local figure)"}
     w.close()
     return out
 
