@@ -362,8 +362,12 @@ convrot_prep_kernel(const PrepParams P) {
                 for (int h = 0; h < 2; h++) {
                     if (g0 + h < n_groups) {
                         const int off = (g0 + h) * 256 + 4 * (l16 + 16 * i);
-                        const float4 pm = __ldcg(reinterpret_cast<const float4 *>(P.premul + off));
-                        const float4 sh = __ldcg(reinterpret_cast<const float4 *>(P.shift + off));
+                        // Plain loads: every row of the launch reads the same two vectors, so they are served
+                        // from L1 after an SM's first row (past L1 they were 24 KB per row from L2, four times
+                        // the bf16 row itself).  Coherent, and issued after griddepcontrol.wait: a kernel of the
+                        // stream may have written them.
+                        const float4 pm = *reinterpret_cast<const float4 *>(P.premul + off);
+                        const float4 sh = *reinterpret_cast<const float4 *>(P.shift + off);
                         x[h][0] = __fmaf_rn(x[h][0] * inv, pm.x, sh.x);
                         x[h][1] = __fmaf_rn(x[h][1] * inv, pm.y, sh.y);
                         x[h][2] = __fmaf_rn(x[h][2] * inv, pm.z, sh.z);
