@@ -1216,7 +1216,8 @@ def run_mode_one_kernel(args, local):
         _, _, _, qn, kn, cos, sin = harness.attention_inputs(T, 1, 1, be.device)
         attn = {"q_norm": qn, "k_norm": kn, "cos": cos, "sin": sin, "heads": synth.DIT_HIDDEN // 128}
         for _ in range(2):
-            harness.dit_step_linears(be, w, x, out_dtype=torch.bfloat16, mode="fused", mod=mod, mlp_tile=T, attn=attn)
+            harness.dit_step_linears(be, w, x, out_dtype=torch.bfloat16, mode="fused", mod=mod, mlp_tile=T, attn=attn,
+                                     mlp_pair=True)
         reps = 2
     elif case == "attn":
         seq, heads = 4608, 24

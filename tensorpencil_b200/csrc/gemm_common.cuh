@@ -293,6 +293,29 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                                               int row0, int n0, float as, int corr, int lane) {
     uint32_t ra[32], rb[32];
     tc_ld_32x32(t_row, ra);
+    // Gated residual: the 32 x 32 pieces of the residual stream this warp updates, read kPre pieces ahead of
+    // their use with whole-line loads (eight lanes per 128-byte row segment, four rows per instruction) and
+    // turned into "one row per lane" through the staging buffer.  A lane reading its own row 16 bytes at a
+    // time touches 32 half-used sectors per warp instruction: K = 3072 took 87 us that way against 38 us for
+    // the plain GEMM (more of those loads in flight made it worse: 102 us).  L2-only loads: the tile is
+    // rewritten below through the TMA (async proxy), which does not update a line such a load would leave in
+    // L1, and a dependent kernel that was launched early on this SM could then read the old values from it.
+    constexpr int kPre = 4;
+    float4 xr[PEERS == 3 ? kPre : 1][8];
+    auto load_residual = [&](int c, float4 (&dst)[8]) {
+        const int col = n0 + c * 32 + 4 * (lane & 7);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int r = row0 + 4 * i + (lane >> 3);
+            dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < p.m && col < p.n)
+                dst[i] = __ldcg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.y) + (size_t)r * (size_t)p.ldy + col));
+        }
+    };
+    if (PEERS == 3) {
+#pragma unroll
+        for (int c = 0; c < kPre && c < BN / 32; c++) load_residual(c, xr[c]);
+    }
 #pragma unroll
     for (int c = 0; c < BN / 32; c++) {
         uint32_t(&cur)[32] = (c & 1) ? rb : ra;
@@ -321,6 +344,25 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), cur[4 * g] - corr, cur[4 * g + 1] - corr,
                              cur[4 * g + 2] - corr, cur[4 * g + 3] - corr);
         } else if (OUT == OUT_F32) {
+            float4 xrow[PEERS == 3 ? 8 : 1];
+            if (PEERS == 3) {
+                // the piece loaded ahead, through the (free) staging buffer: rows x 16-byte chunks in, this lane's row out
+                const uint32_t sbase = stg + (n_store & 1u) * 4096u;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t r = (uint32_t)(4 * i + (lane >> 3));
+                    const float4 v = xr[PEERS == 3 ? c % kPre : 0][i];
+                    st_shared_v4(sbase + r * 128u + ((((uint32_t)lane & 7u) ^ (r & 7u)) << 4), __float_as_uint(v.x),
+                                 __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
+                }
+                __syncwarp();
+#pragma unroll
+                for (int g = 0; g < 8; g++) {
+                    const uint4 v = ld_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4));
+                    xrow[g] = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+                }
+                __syncwarp();   // every lane has its row before anybody overwrites the buffer with results
+            }
 #pragma unroll
             for (int g = 0; g < 8; g++) {
                 float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -330,18 +372,11 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
                 float v3 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 3] - corr), as), ws.w);
                 if (PEERS == 3) {
-                    // this lane's row of the residual stream; the tile is read here and written
+                    // this lane's row of the residual stream (loaded ahead, see above); the tile is written
                     // back by this warp's own TMA store below, nobody else touches it
-                    float4 gt = make_float4(0.f, 0.f, 0.f, 0.f), xv = gt;
-                    if (col0 + 4 * g < p.n) {
-                        gt = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
-                        // L2-only load: the tile is rewritten below through the TMA (async proxy), which
-                        // does not update a line this load would leave in L1, and a dependent kernel that
-                        // was launched early on this SM could then read the old values from it
-                        if (row0 + lane < p.m)
-                            xv = __ldcg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.y) +
-                                                                         (size_t)(row0 + lane) * (size_t)p.ldy + col0 + 4 * g));
-                    }
+                    float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 xv = xrow[PEERS == 3 ? g : 0];
+                    if (col0 + 4 * g < p.n) gt = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
                     v0 = __fmaf_rn(gt.x, v0, xv.x);
                     v1 = __fmaf_rn(gt.y, v1, xv.y);
                     v2 = __fmaf_rn(gt.z, v2, xv.z);
@@ -350,6 +385,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 st_shared_v4(buf + ((((uint32_t)g) ^ sw) << 4), __float_as_uint(v0), __float_as_uint(v1),
                              __float_as_uint(v2), __float_as_uint(v3));
             }
+            if (PEERS == 3 && c + kPre < BN / 32) load_residual(c + kPre, xr[PEERS == 3 ? c % kPre : 0]);
         } else {
             // bf16: 64 columns make one 128-byte row; this chunk fills pieces 4*(c&1) .. +3
 #pragma unroll
