@@ -184,7 +184,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
 
     uint8_t *ring = smem;
     float *s_dx = reinterpret_cast<float *>(smem + (size_t)S * stage_bytes);       // [nblk][8 activation rows]
-    float *s_part = s_dx + (size_t)kActRows * nblk;                                 // [rgbuf][kConsumers][128]
+    float *s_part = s_dx + (size_t)kActRows * nblk;                                 // [rgbuf][kConsumers][8 weight rows x 8 activation rows]
     const uint32_t bars = smem_u32(s_part + (size_t)p.rgbuf * kConsumers * kPartFloats);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
@@ -212,7 +212,7 @@ __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(kThreadsMma, 1) q8_
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // this CTA's rows and its stages: (pass, row group, segment), row groups of 16 rows
+    // this CTA's rows and its stages: (pass, row group, segment), row groups of 8 rows
     // (the CTAs of a cluster share their rows)
     const int n_own = (int)gridDim.x / KS, own = (int)blockIdx.x / KS;
     const int r_base = p.rows / n_own, r_rem = p.rows % n_own;   // the first r_rem owners take one row more
