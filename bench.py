@@ -715,11 +715,13 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
     # through PCIe and the pieces are exchanged over NVLink (all-gather on the transfer stream), so the
     # node reads each block from host memory once.  "own_copies" = every GPU pulling every byte itself.
     group = None
-    routes = [("streamed", 2 << 30, None)]
+    routes = [("own_copies", 2 << 30, None)]
+    share = world >= 4      # the default route: shared host link from four GPUs on (measured: a tie at two)
     if world > 1:
         import torch.distributed as dist
         group = dist.group.WORLD
-        routes = [("streamed", 2 << 30, group), ("own_copies", 2 << 30, None)]
+        routes = [("shared_link", 2 << 30, group), ("own_copies", 2 << 30, None)]
+    default_route = "shared_link" if share else "own_copies"
     routes.append(("resident", None, None))
     for label, budget, grp in routes:
         w, err = None, None
@@ -745,7 +747,7 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
             copied = ((w.streamer.bytes_copied() - c0) / steps) if w.streamer else 0
             res[(label, n)] = (ms, copied)
         be.status_poll()
-        if w.streamer and label == "streamed":
+        if w.streamer and label == default_route:
             res["slots"] = {"slot_bytes": w.block_bytes, "budget_bytes": budget}
         w.close()
         del w
@@ -757,21 +759,23 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
     out = {"workload": f"config4: INT4 ConvRot DiT step, weights streamed from pinned host memory under a 2 GiB budget, "
                        f"batch of {TOTAL_LATENTS} latents, {L} per GPU on {world} GPU(s); max over ranks",
            "latents_per_gpu": L, "latents_total": L * world, "steps": steps, "unit": "s/step (whole batch)",
-           "route": ("each block crosses the host link once per node: every GPU copies 1/%d of it, the pieces are "
-                     "all-gathered over NVLink on the transfer stream" % world) if world > 1 else "one GPU: every block copied whole",
+           "route": (("each block crosses the host link once per node: every GPU copies 1/%d of it, the pieces are "
+                      "all-gathered over NVLink on the transfer stream (default from four GPUs on)" % world) if share else
+                     ("every GPU copies every block through its own link" + (" (default at two GPUs, where the host keeps "
+                      "up and the exchange kernel would only take SMs from the step)" if world > 1 else ""))),
            "slots": res.get("slots"), "variants": {}}
     for n in names:
-        s_ms, r_ms = ms[("streamed", n)], ms[("resident", n)]
-        copied = res[("streamed", n)][1]
+        s_ms, r_ms = ms[(default_route, n)], ms[("resident", n)]
+        copied = res[(default_route, n)][1]
         out["variants"][n] = {"s_per_step": s_ms / 1e3, "s_per_step_weights_resident": r_ms / 1e3,
                               "streaming_overhead": s_ms / r_ms - 1.0,
                               "streamed_bytes_per_step_per_gpu": copied,
                               "h2d_gbs_per_gpu": copied / (s_ms * 1e-3) / 1e9,
                               "s_per_latent": s_ms / 1e3 / L, "what": DIT_VARIANTS[n][0]}
         if world > 1:
-            o_ms = ms[("own_copies", n)]
-            out["variants"][n].update({"s_per_step_every_gpu_copies_everything": o_ms / 1e3,
-                                       "overhead_every_gpu_copies_everything": o_ms / r_ms - 1.0,
+            out["variants"][n].update({"s_per_step_shared_host_link": ms[("shared_link", n)] / 1e3,
+                                       "s_per_step_every_gpu_copies_everything": ms[("own_copies", n)] / 1e3,
+                                       "h2d_bytes_per_step_per_gpu_shared_host_link": res[("shared_link", n)][1],
                                        "h2d_bytes_per_step_per_gpu_every_gpu_copies_everything": res[("own_copies", n)][1]})
     return out
 
