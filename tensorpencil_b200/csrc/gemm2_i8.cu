@@ -169,6 +169,18 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             const int n0 = (tile / m_tiles) * kTileN;
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
+            if (PEERS == 3) {
+                // gated residual: ask for this warp's 32 x 256 piece of the residual stream (a lane's row, eight
+                // lines) to be brought into L2 while the accumulators are still being produced.  Asking a whole
+                // tile earlier was measured slower (m 4608, n 12288, k 3072: 202 us against 180 us).
+                const int prow = m0 + quarter * 32 + lane;
+                if (prow < p.m) {
+                    const float *xp = static_cast<const float *>(p.y) + (size_t)prow * (size_t)p.ldy + n0;
+#pragma unroll
+                    for (int i = 0; i < BN2 / 32; i++)
+                        if (n0 + 32 * i < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(xp + 32 * i));
+                }
+            }
             ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc, true);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;

@@ -300,7 +300,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
     // the plain GEMM (more of those loads in flight made it worse: 102 us).  L2-only loads: the tile is
     // rewritten below through the TMA (async proxy), which does not update a line such a load would leave in
     // L1, and a dependent kernel that was launched early on this SM could then read the old values from it.
-    constexpr int kPre = 4;
+    constexpr int kPre = 2;
     float4 xr[PEERS == 3 ? kPre : 1][8];
     auto load_residual = [&](int c, float4 (&dst)[8]) {
         const int col = n0 + c * 32 + 4 * (lane & 7);
@@ -316,10 +316,38 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
 #pragma unroll
         for (int c = 0; c < kPre && c < BN / 32; c++) load_residual(c, xr[c]);
     }
+    // The 32 per-column scales of a piece (and the gate values in the gated mode), loaded one piece ahead
+    // of their use into two register sets.  Loaded where they were used, inside the conversion loop, each of
+    // the eight loads of a piece stalled its first multiply for an L1 round trip: half the epilogue's time
+    // (measured at K = 256, where the epilogue is all there is).
+    // (The gated mode, which also keeps residual pieces in registers, has room for one set only: it loads a
+    // piece's scales at the top of the piece, ahead of the wait for the accumulators.)
+    constexpr bool kTwoSets = PEERS != 3;
+    float4 wsa[8], wsb[kTwoSets ? 8 : 1], gta[PEERS == 3 ? 8 : 1];
+    auto load_scales = [&](int c, float4 (&w)[8]) {
+        const int col0 = n0 + c * 32;
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            w[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (OUT != OUT_S32 && col0 + 4 * g < p.n) w[g] = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+            if (PEERS == 3) {
+                gta[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (col0 + 4 * g < p.n) gta[g] = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
+            }
+        }
+    };
+    if (kTwoSets) load_scales(0, wsa);
 #pragma unroll
     for (int c = 0; c < BN / 32; c++) {
         uint32_t(&cur)[32] = (c & 1) ? rb : ra;
         uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        float4(&wsc)[8] = (kTwoSets && (c & 1)) ? reinterpret_cast<float4(&)[8]>(wsb) : wsa;
+        float4(&gtc)[PEERS == 3 ? 8 : 1] = gta;
+        if (kTwoSets) {
+            if (c + 1 < BN / 32) load_scales(c + 1, (c & 1) ? wsa : reinterpret_cast<float4(&)[8]>(wsb));
+        } else {
+            load_scales(c, wsa);
+        }
         tc_wait_ld_dep(cur);  // columns 32c.. are in `cur`
         if (c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), nxt);
         const int col0 = n0 + c * 32;
@@ -365,8 +393,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             }
 #pragma unroll
             for (int g = 0; g < 8; g++) {
-                float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (col0 + 4 * g < p.n) ws = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                const float4 ws = wsc[g];
                 float v0 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g] - corr), as), ws.x);
                 float v1 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 1] - corr), as), ws.y);
                 float v2 = __fmul_rn(__fmul_rn(__int2float_rn((int)cur[4 * g + 2] - corr), as), ws.z);
@@ -374,9 +401,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 if (PEERS == 3) {
                     // this lane's row of the residual stream (loaded ahead, see above); the tile is written
                     // back by this warp's own TMA store below, nobody else touches it
-                    float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 gt = gtc[PEERS == 3 ? g : 0];
                     const float4 xv = xrow[PEERS == 3 ? g : 0];
-                    if (col0 + 4 * g < p.n) gt = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));
                     v0 = __fmaf_rn(gt.x, v0, xv.x);
                     v1 = __fmaf_rn(gt.y, v1, xv.y);
                     v2 = __fmaf_rn(gt.z, v2, xv.z);
@@ -390,11 +416,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             // bf16: 64 columns make one 128-byte row; this chunk fills pieces 4*(c&1) .. +3
 #pragma unroll
             for (int g = 0; g < 4; g++) {
-                float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
-                if (col0 + 8 * g < p.n) {
-                    w0 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g));
-                    w1 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 8 * g + 4));
-                }
+                const float4 w0 = wsc[2 * g], w1 = wsc[2 * g + 1];
                 const float wsv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                 uint32_t pk[4];
 #pragma unroll
@@ -476,6 +498,17 @@ __device__ __forceinline__ void epilogue_pair(uint32_t t_row, const GemmParams &
         if (!do_store) continue;
         tc_ld_32x32(t_row + (uint32_t)(c * 32), rg);
         tc_ld_32x32(t_row + (uint32_t)(128 + c * 32), ru);
+        // the piece's scales while the accumulators are on their way (loaded inside the loop below, each
+        // load stalled its first multiply for an L1 round trip)
+        float4 wgv[8], wuv[8];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            wgv[g] = wuv[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col0 + 4 * g < p.n) {
+                wgv[g] = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+                wuv[g] = __ldg(reinterpret_cast<const float4 *>(p.w_scale2 + col0 + 4 * g));
+            }
+        }
         tc_wait_ld_dep(rg);
         tc_wait_ld_dep(ru);
         const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
@@ -487,11 +520,7 @@ __device__ __forceinline__ void epilogue_pair(uint32_t t_row, const GemmParams &
         float o[32];
 #pragma unroll
         for (int g = 0; g < 8; g++) {
-            float4 wg = make_float4(0.f, 0.f, 0.f, 0.f), wu = wg;
-            if (col0 + 4 * g < p.n) {
-                wg = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
-                wu = __ldg(reinterpret_cast<const float4 *>(p.w_scale2 + col0 + 4 * g));
-            }
+            const float4 wg = wgv[g], wu = wuv[g];
             const float wgs[4] = {wg.x, wg.y, wg.z, wg.w}, wus[4] = {wu.x, wu.y, wu.z, wu.w};
 #pragma unroll
             for (int e = 0; e < 4; e++) {
