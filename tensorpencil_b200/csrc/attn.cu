@@ -142,6 +142,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
     auto s_full = [&](int x) { return bars + 8u * (9 + x); };     // x: query tile A = 0, B = 1
     auto p_full = [&](int x) { return bars + 8u * (11 + x); };
     const uint32_t o_done = bars + 8u * 13;
+    auto p_half = [&](int x) { return bars + 8u * (14 + x); };    // the first 32 columns of both halves of P_x
     uint8_t *gen = smem_raw + (smem_base - smem_u32(smem_raw));
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 128);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + kOffBar + 136);
@@ -162,6 +163,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
             mbar_init(p_full(s), 8);
+            mbar_init(p_half(s), 8);
         }
         mbar_init(o_done, 1);
         *abort_flag = 0;
@@ -225,16 +227,20 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
                 }
                 tc_commit(s_full(x));
             };
-            // O_x += P_x V_t: P from tensor memory (8 columns = 16 bf16 per step), V^T from shared memory
-            auto issue_pv = [&](int x, int t) {
+            // O_x += P_x V_t: P from tensor memory (8 columns = 16 bf16 per step), V^T from shared memory.  The
+            // softmax hands P over in two parts -- kv columns 0..31 and 64..95 (the first chunk of each of a row's
+            // two threads), then the rest -- so the product starts while the second chunk is still being computed.
+            auto issue_pv = [&](int x, int t, int part) {
                 const uint32_t va = smem_base + kOffV + (t & 1) * 2 * kAtomBytes;
 #pragma unroll
                 for (int a = 0; a < 2; a++) {
                     const uint64_t vd = make_kmajor_sw128_desc(va + a * kAtomBytes);
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
+                    for (int k2 = 0; k2 < 2; k2++) {
+                        const int kk = 2 * part + k2;
                         tc_mma_bf16_ts(tmem_base + 256u + (uint32_t)(x * 128), tmem_base + (uint32_t)(x * 128 + 8 * (4 * a + kk)),
-                                       vd + 2u * kk, idesc, (t > 0 || a > 0 || kk > 0) ? 1u : 0u);
+                                       vd + 2u * kk, idesc, (t > 0 || part > 0 || a > 0 || k2 > 0) ? 1u : 0u);
+                    }
                 }
             };
             bool ok = mbar_wait(q_full, 0, abort_flag, p.status, (13u << 24) | 1u);
@@ -251,20 +257,28 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
                 const bool more = j + 1 < n_tiles;
                 ok = mbar_wait(v_full(st), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, (13u << 24) | 3u);
                 if (!ok) break;
-                ok = mbar_wait(p_full(0), ph, abort_flag, p.status, (13u << 24) | 4u);
+                ok = mbar_wait(p_half(0), ph, abort_flag, p.status, (13u << 24) | 4u);
                 if (!ok) break;
                 tc_fence_after();
-                issue_pv(0, j);
+                issue_pv(0, j, 0);
+                ok = mbar_wait(p_full(0), ph, abort_flag, p.status, (13u << 24) | 7u);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(0, j, 1);
                 if (more) {
                     ok = mbar_wait(k_full(st ^ 1), (uint32_t)((j + 1) >> 1) & 1u, abort_flag, p.status, (13u << 24) | 5u);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(0, j + 1);
                 }
-                ok = mbar_wait(p_full(1), ph, abort_flag, p.status, (13u << 24) | 6u);
+                ok = mbar_wait(p_half(1), ph, abort_flag, p.status, (13u << 24) | 6u);
                 if (!ok) break;
                 tc_fence_after();
-                issue_pv(1, j);
+                issue_pv(1, j, 0);
+                ok = mbar_wait(p_full(1), ph, abort_flag, p.status, (13u << 24) | 8u);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(1, j, 1);
                 tc_commit(v_empty(st));
                 if (more) {
                     issue_qk(1, j + 1);
@@ -354,6 +368,10 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
                 tc_st_32x16(t_p + (uint32_t)(c * 16), pk);
             };
             exp_chunk(v0, 0);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_half(x));
             exp_chunk(v1, 1);
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m_run = m_new;
