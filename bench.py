@@ -983,7 +983,8 @@ def run_mode_nsplit(args, rank, local, world):
 def measure_gemv(be, peaks, steps, all_formats=True):
     """Config 2: Q8_0 decode GEMV, K=5120 -> N=17408 and the down projection, M in {1,4,8},
     four rotating weight buffers (379 MB > L2) so every launch streams from HBM; then the other
-    GGUF formats at the up-projection shape.  Algorithmic bytes = the weight matrix."""
+    GGUF formats at the up-projection shape and three of them at the down-projection shape.  Algorithmic
+    bytes = the weight matrix."""
     import torch
     from tensorpencil_b200 import harness, synth
     rows_out = []
@@ -1002,13 +1003,15 @@ def measure_gemv(be, peaks, steps, all_formats=True):
                              "frac_of_hbm": gbs / peaks["hbm_gbs"]})
         del ws
     if all_formats:
-        n, k = 17408, 5120
-        for fmt in ("q4_k", "q5_k", "q6_k", "q4_0", "iq4_nl"):
+        # the up projection for every format; the down projection (long rows: the k-quants' second kernel) for three
+        shapes = [(fmt, 17408, 5120, (1, 4, 8)) for fmt in ("q4_k", "q5_k", "q6_k", "q4_0", "iq4_nl")]
+        shapes += [(fmt, 5120, 17408, (1, 2)) for fmt in ("q4_k", "q5_k", "q4_0")]
+        for fmt, n, k, ms_ in shapes:
             base = torch.from_numpy(synth.gguf_weights(fmt, n, k, seed=11)).cuda()
             copies = 8
             ws = [base] + [base.clone() for _ in range(copies - 1)]       # 8 x 50..61 MB > 126 MB of L2
             wbytes = base.numel()
-            for m in (1, 4, 8):
+            for m in ms_:
                 x = torch.randn(m, k, device="cuda")
                 y = torch.empty(m, n, device="cuda")
                 be.opGemvQuantizeX(x, m * k)

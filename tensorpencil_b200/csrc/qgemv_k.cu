@@ -4,6 +4,8 @@
 // private shared-memory ring with 1-D bulk async copies (mbarrier completion, no
 // multicast); q8_1 activations (int8 + per-32-block scale) stay in shared memory for the
 // kernel's life; dp4a for the integer dots, f32 accumulation, warp butterfly, * scale.
+// A second kernel with the same arithmetic behind one CTA-wide ring (kquant_gemv_ring_kernel,
+// further down) takes the calls with one or two activation rows whose rows are long or many.
 //
 // The unit of work of a lane is 64 consecutive elements (two q8_1 activation blocks):
 //   q4_0  a pair of 18-byte blocks (f16 d + 16 nibble bytes each; 36 bytes = 9 aligned
@@ -51,6 +53,7 @@ struct KGemvParams {
     float scale;
     int rows, cols, nblk;  // nblk = cols / 32
     size_t row_bytes;
+    uint32_t chunk_pitch;  // ring kernel: bytes between the rows of a stage
     uint32_t *status;
 };
 
@@ -93,6 +96,143 @@ __device__ __forceinline__ void scale_min_k4(int is, uint32_t s0, uint32_t s1, u
     }
     sc = (float)s;
     mn = (float)m;
+}
+
+// The arithmetic of one pipeline stage: rows 0 .. nrow - 1 of `stage` (pitch bytes apart) hold chunk c of their
+// weight rows; every lane decodes its U units of each row and adds their dot products with the M activation
+// rows into acc.
+template <int FMT, int M, int R, int U>
+__device__ __forceinline__ void kq_stage_dot(const uint8_t *stage, const int pitch, const int nrow, const int c,
+                                             const int n_units, const int lane, const int8_t *s_q, const size_t act_row,
+                                             const float *s_d, const float *s_s, const int nblk, float (&acc)[R][M]) {
+#pragma unroll
+    for (int t = 0; t < U; t++) {
+        const int ul = lane + 32 * t;                 // unit within the chunk
+        const int unit = c * (32 * U) + ul;
+        if (unit >= n_units) continue;
+        // Decode this lane's 64 weights of each row: lo[8] = elements 0..31 as bytes (nibble,
+        // plus the fifth bit for q5_k), hi[8] = elements 32..63 as bytes times 16 (the high
+        // nibbles left where they are: one AND instead of shift + AND; the dot product is
+        // then an exact multiple of 16), and the two (scale, offset) pairs.
+        uint32_t lo[R][8], hi[R][8];
+        float ws0[R], ws1[R], wo0[R], wo1[R];  // acc += ws * (dx * sumi) - wo * S
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (r < nrow) {
+                if (FMT == FMT_IQ4_NL) {
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * pitch + ul * 36);
+                    uint32_t tw[9];
+#pragma unroll
+                    for (int j = 0; j < 9; j++) tw[j] = src[j];
+                    // same 18-byte block pair as q4_0; the nibbles go through the value table and
+                    // come out as signed bytes, so there is no offset term
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t na = __funnelshift_r(tw[j], tw[j + 1], 16), nb = tw[5 + j];
+                        lo[r][j] = iq4nl_lookup(na & 0x0f0f0f0fu);
+                        lo[r][4 + j] = iq4nl_lookup((na >> 4) & 0x0f0f0f0fu);
+                        hi[r][j] = iq4nl_lookup(nb & 0x0f0f0f0fu);
+                        hi[r][4 + j] = iq4nl_lookup((nb >> 4) & 0x0f0f0f0fu);
+                    }
+                    ws0[r] = f16lo(tw[0]);
+                    ws1[r] = f16hi(tw[4]);
+                    wo0[r] = wo1[r] = 0.0f;
+                } else if (FMT == FMT_Q4_0) {
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * pitch + ul * 36);
+                    uint32_t tw[9];
+#pragma unroll
+                    for (int j = 0; j < 9; j++) tw[j] = src[j];
+                    // block A: d = tw[0] low half, nibble bytes 2..17; block B: d = tw[4] high half, bytes 20..35
+                    uint32_t na[4], nb[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) na[j] = __funnelshift_r(tw[j], tw[j + 1], 16);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) nb[j] = tw[5 + j];
+                    // a block's elements 0..15 are its low nibbles, 16..31 its high nibbles; the
+                    // high-nibble words carry a factor 16 that ws/16 below takes back
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        lo[r][j] = (na[j] & 0x0f0f0f0fu) << 4;
+                        lo[r][4 + j] = na[j] & 0xf0f0f0f0u;
+                        hi[r][j] = (nb[j] & 0x0f0f0f0fu) << 4;
+                        hi[r][4 + j] = nb[j] & 0xf0f0f0f0u;
+                    }
+                    ws0[r] = f16lo(tw[0]);
+                    ws1[r] = f16hi(tw[4]);
+                    wo0[r] = 8.0f * ws0[r];
+                    wo1[r] = 8.0f * ws1[r];
+                    ws0[r] *= 0.0625f;
+                    ws1[r] *= 0.0625f;
+                } else {
+                    constexpr int kSb = FMT == FMT_Q5_K ? 176 : 144;
+                    constexpr int kQs = FMT == FMT_Q5_K ? 48 : 16;
+                    const int j = lane & 3;  // quarter of the super-block (32 t is a multiple of 4)
+                    const uint8_t *sb = stage + r * pitch + (ul >> 2) * kSb;
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(sb);
+                    const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j);
+                    const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j + 16);
+                    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                    for (int w = 0; w < 8; w++) {
+                        lo[r][w] = qw[w] & 0x0f0f0f0fu;
+                        hi[r][w] = qw[w] & 0xf0f0f0f0u;
+                    }
+                    if (FMT == FMT_Q5_K) {
+                        // fifth bits: 16 for the low elements; 16 * 16 = 256 does not fit a byte for
+                        // the (x16) high elements, so those go back to plain values
+                        const uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16);
+                        const uint4 h1 = *reinterpret_cast<const uint4 *>(sb + 32);
+                        const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                        for (int w = 0; w < 8; w++) {
+                            lo[r][w] |= ((hw[w] >> (2 * j)) & 0x01010101u) << 4;
+                            hi[r][w] = (hi[r][w] >> 4) | (((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4);
+                        }
+                    }
+                    const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
+                    float sc, mn;
+                    scale_min_k4(2 * j, hdr.y, hdr.z, hdr.w, sc, mn);
+                    ws0[r] = d * sc;
+                    wo0[r] = dmin * mn;
+                    scale_min_k4(2 * j + 1, hdr.y, hdr.z, hdr.w, sc, mn);
+                    ws1[r] = d * sc * (FMT == FMT_Q5_K ? 1.0f : 0.0625f);
+                    wo1[r] = dmin * mn;
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < 8; w++) lo[r][w] = hi[r][w] = 0;
+                ws0[r] = ws1[r] = wo0[r] = wo1[r] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            uint32_t xq[16];
+            const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)unit * kActPairBytes);
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                const int4 tt = a[v];
+                xq[4 * v] = tt.x; xq[4 * v + 1] = tt.y; xq[4 * v + 2] = tt.z; xq[4 * v + 3] = tt.w;
+            }
+            const float2 d2 = *reinterpret_cast<const float2 *>(s_d + (size_t)m * nblk + 2 * unit);
+            const float2 s2 = *reinterpret_cast<const float2 *>(s_s + (size_t)m * nblk + 2 * unit);
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                int i0 = 0, i1 = 0;
+#pragma unroll
+                for (int w = 0; w < 8; w++)
+                    i0 = FMT == FMT_IQ4_NL ? __dp4a((int)lo[r][w], (int)xq[w], i0) : dp4a_us(lo[r][w], xq[w], i0);
+#pragma unroll
+                for (int w = 0; w < 8; w++)
+                    i1 = FMT == FMT_IQ4_NL ? __dp4a((int)hi[r][w], (int)xq[8 + w], i1) : dp4a_us(hi[r][w], xq[8 + w], i1);
+                float tacc = acc[r][m];
+                tacc = fmaf(ws0[r], d2.x * i2f_small(i0), tacc);
+                tacc = fmaf(-wo0[r], s2.x, tacc);
+                tacc = fmaf(ws1[r], d2.y * i2f_small(i1), tacc);
+                tacc = fmaf(-wo1[r], s2.y, tacc);
+                acc[r][m] = tacc;
+            }
+        }
+    }
 }
 
 template <int FMT, int M, int R, int U>
@@ -200,135 +340,8 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         const int c = i % cpr;
         const int row0 = my_r0 + (i / cpr) * R;
         const int nrow = min(R, my_r1 - row0);
-#pragma unroll
-        for (int t = 0; t < kUnitsPerLane; t++) {
-            const int ul = lane + 32 * t;                 // unit within the chunk
-            const int unit = c * kUnitsPerChunk + ul;
-            if (unit >= n_units) continue;
-            // Decode this lane's 64 weights of each row: lo[8] = elements 0..31 as bytes (nibble,
-            // plus the fifth bit for q5_k), hi[8] = elements 32..63 as bytes times 16 (the high
-            // nibbles left where they are: one AND instead of shift + AND; the dot product is
-            // then an exact multiple of 16), and the two (scale, offset) pairs.
-            uint32_t lo[R][8], hi[R][8];
-            float ws0[R], ws1[R], wo0[R], wo1[R];  // acc += ws * (dx * sumi) - wo * S
-            const uint8_t *stage = ring + (size_t)st * kStageBytes;
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                if (r < nrow) {
-                    if (FMT == FMT_IQ4_NL) {
-                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + ul * 36);
-                        uint32_t tw[9];
-#pragma unroll
-                        for (int j = 0; j < 9; j++) tw[j] = src[j];
-                        // same 18-byte block pair as q4_0; the nibbles go through the value table and
-                        // come out as signed bytes, so there is no offset term
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const uint32_t na = __funnelshift_r(tw[j], tw[j + 1], 16), nb = tw[5 + j];
-                            lo[r][j] = iq4nl_lookup(na & 0x0f0f0f0fu);
-                            lo[r][4 + j] = iq4nl_lookup((na >> 4) & 0x0f0f0f0fu);
-                            hi[r][j] = iq4nl_lookup(nb & 0x0f0f0f0fu);
-                            hi[r][4 + j] = iq4nl_lookup((nb >> 4) & 0x0f0f0f0fu);
-                        }
-                        ws0[r] = f16lo(tw[0]);
-                        ws1[r] = f16hi(tw[4]);
-                        wo0[r] = wo1[r] = 0.0f;
-                    } else if (FMT == FMT_Q4_0) {
-                        const uint32_t *src = reinterpret_cast<const uint32_t *>(stage + r * kChunkBytes + ul * 36);
-                        uint32_t tw[9];
-#pragma unroll
-                        for (int j = 0; j < 9; j++) tw[j] = src[j];
-                        // block A: d = tw[0] low half, nibble bytes 2..17; block B: d = tw[4] high half, bytes 20..35
-                        uint32_t na[4], nb[4];
-#pragma unroll
-                        for (int j = 0; j < 4; j++) na[j] = __funnelshift_r(tw[j], tw[j + 1], 16);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) nb[j] = tw[5 + j];
-                        // a block's elements 0..15 are its low nibbles, 16..31 its high nibbles; the
-                        // high-nibble words carry a factor 16 that ws/16 below takes back
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            lo[r][j] = (na[j] & 0x0f0f0f0fu) << 4;
-                            lo[r][4 + j] = na[j] & 0xf0f0f0f0u;
-                            hi[r][j] = (nb[j] & 0x0f0f0f0fu) << 4;
-                            hi[r][4 + j] = nb[j] & 0xf0f0f0f0u;
-                        }
-                        ws0[r] = f16lo(tw[0]);
-                        ws1[r] = f16hi(tw[4]);
-                        wo0[r] = 8.0f * ws0[r];
-                        wo1[r] = 8.0f * ws1[r];
-                        ws0[r] *= 0.0625f;
-                        ws1[r] *= 0.0625f;
-                    } else {
-                        constexpr int kSb = FMT == FMT_Q5_K ? 176 : 144;
-                        constexpr int kQs = FMT == FMT_Q5_K ? 48 : 16;
-                        const int j = lane & 3;  // quarter of the super-block (32 t is a multiple of 4)
-                        const uint8_t *sb = stage + r * kChunkBytes + (ul >> 2) * kSb;
-                        const uint4 hdr = *reinterpret_cast<const uint4 *>(sb);
-                        const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j);
-                        const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + kQs + 32 * j + 16);
-                        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-                        for (int w = 0; w < 8; w++) {
-                            lo[r][w] = qw[w] & 0x0f0f0f0fu;
-                            hi[r][w] = qw[w] & 0xf0f0f0f0u;
-                        }
-                        if (FMT == FMT_Q5_K) {
-                            // fifth bits: 16 for the low elements; 16 * 16 = 256 does not fit a byte for
-                            // the (x16) high elements, so those go back to plain values
-                            const uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16);
-                            const uint4 h1 = *reinterpret_cast<const uint4 *>(sb + 32);
-                            const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-#pragma unroll
-                            for (int w = 0; w < 8; w++) {
-                                lo[r][w] |= ((hw[w] >> (2 * j)) & 0x01010101u) << 4;
-                                hi[r][w] = (hi[r][w] >> 4) | (((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4);
-                            }
-                        }
-                        const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
-                        float sc, mn;
-                        scale_min_k4(2 * j, hdr.y, hdr.z, hdr.w, sc, mn);
-                        ws0[r] = d * sc;
-                        wo0[r] = dmin * mn;
-                        scale_min_k4(2 * j + 1, hdr.y, hdr.z, hdr.w, sc, mn);
-                        ws1[r] = d * sc * (FMT == FMT_Q5_K ? 1.0f : 0.0625f);
-                        wo1[r] = dmin * mn;
-                    }
-                } else {
-#pragma unroll
-                    for (int w = 0; w < 8; w++) lo[r][w] = hi[r][w] = 0;
-                    ws0[r] = ws1[r] = wo0[r] = wo1[r] = 0.0f;
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < M; m++) {
-                uint32_t xq[16];
-                const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)unit * kActPairBytes);
-#pragma unroll
-                for (int v = 0; v < 4; v++) {
-                    const int4 tt = a[v];
-                    xq[4 * v] = tt.x; xq[4 * v + 1] = tt.y; xq[4 * v + 2] = tt.z; xq[4 * v + 3] = tt.w;
-                }
-                const float2 d2 = *reinterpret_cast<const float2 *>(s_d + (size_t)m * nblk + 2 * unit);
-                const float2 s2 = *reinterpret_cast<const float2 *>(s_s + (size_t)m * nblk + 2 * unit);
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    int i0 = 0, i1 = 0;
-#pragma unroll
-                    for (int w = 0; w < 8; w++)
-                        i0 = FMT == FMT_IQ4_NL ? __dp4a((int)lo[r][w], (int)xq[w], i0) : dp4a_us(lo[r][w], xq[w], i0);
-#pragma unroll
-                    for (int w = 0; w < 8; w++)
-                        i1 = FMT == FMT_IQ4_NL ? __dp4a((int)hi[r][w], (int)xq[8 + w], i1) : dp4a_us(hi[r][w], xq[8 + w], i1);
-                    float tacc = acc[r][m];
-                    tacc = fmaf(ws0[r], d2.x * i2f_small(i0), tacc);
-                    tacc = fmaf(-wo0[r], s2.x, tacc);
-                    tacc = fmaf(ws1[r], d2.y * i2f_small(i1), tacc);
-                    tacc = fmaf(-wo1[r], s2.y, tacc);
-                    acc[r][m] = tacc;
-                }
-            }
-        }
+        kq_stage_dot<FMT, M, R, U>(ring + (size_t)st * kStageBytes, kChunkBytes, nrow, c, n_units, lane, s_q, act_row, s_d, s_s,
+                                   nblk, acc);
         __syncwarp();
 
         if (c == cpr - 1) {
@@ -342,6 +355,147 @@ kquant_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                     if (lane == 0 && r < nrow) p.y[(size_t)m * p.rows + row0 + r] = v * p.scale;
                     acc[r][m] = 0.0f;
                 }
+        }
+    }
+}
+
+// ---- the same arithmetic behind a CTA-wide ring ------------------------------------------------
+//
+// With half the bytes per element of Q8_0 a warp of the kernel above has little left in flight: its
+// private ring holds two stages, so every row pair costs it one full trip to HBM.  Here one producer
+// warp streams stages of sixteen rows -- one row per consumer warp -- through a ring that takes all
+// of shared memory, several stages ahead of the arithmetic; where a row is one chunk, a stage is one
+// contiguous piece of the weight and comes with a single bulk copy.  full[s]: the copy's bytes have
+// landed; empty[s]: all sixteen consumer warps are done with the stage.  Same sums in the same order
+// as the kernel above with one row per stage.
+constexpr int kRingRows = 16;
+
+template <int FMT, int M, int U>
+__global__ void __launch_bounds__(32 * (kRingRows + 1), 1)
+kquant_gemv_ring_kernel(const KGemvParams p, const int stages) {
+    constexpr int kUnitsPerChunk = 32 * U;
+    constexpr int kChunkBytes = kUnitsPerChunk * Fmt<FMT>::kUnitBytes;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nblk = p.nblk;
+    const int cols = p.cols;
+    const int n_units = cols / 64;
+    const int pitch = (int)p.chunk_pitch;
+    const int stage_bytes = kRingRows * pitch;
+    const bool whole_rows = (size_t)pitch == p.row_bytes;
+
+    // shared: [act q: M x n_units x 80][act d: M x nblk f32][act S: M x nblk f32][ring][full barriers][empty barriers]
+    const size_t act_row = (size_t)n_units * kActPairBytes;
+    int8_t *s_q = reinterpret_cast<int8_t *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)M * act_row);
+    float *s_s = s_d + (size_t)M * nblk;
+    uint8_t *ring = reinterpret_cast<uint8_t *>(s_s + (size_t)M * nblk);
+    const uint32_t full = smem_u32(ring + (size_t)stages * stage_bytes);
+    const uint32_t empty = full + 8u * (uint32_t)stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full + 8 * s), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty + 8 * s), "r"(kRingRows));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int cpr = (n_units + kUnitsPerChunk - 1) / kUnitsPerChunk;  // chunks per row
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int n_groups = (r1 - r0 + kRingRows - 1) / kRingRows;
+    const int total = n_groups * cpr;
+
+    if (warp == 0) {
+        // ---------------- producer: the weights do not depend on the kernel before this one ----------------
+        if (lane == 0) {
+            for (int i = 0; i < total; i++) {
+                const int st = i % stages;
+                if (i >= stages) {
+                    if (!mbar_wait(empty + 8 * st, (uint32_t)(i / stages - 1) & 1u, p.status, (7u << 24) | (uint32_t)st)) break;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                const int c = i % cpr;
+                const int row0 = r0 + (i / cpr) * kRingRows;
+                const int nrow = min(kRingRows, r1 - row0);
+                const int units = min(kUnitsPerChunk, n_units - c * kUnitsPerChunk);
+                const uint32_t bytes = (uint32_t)units * (uint32_t)Fmt<FMT>::kUnitBytes;
+                const uint32_t bar = full + 8 * st;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)nrow)
+                             : "memory");
+                const uint32_t dst = smem_u32(ring + (size_t)st * stage_bytes);
+                if (whole_rows) {
+                    bulk_g2s(dst, p.w + (size_t)row0 * p.row_bytes, bytes * (uint32_t)nrow, bar);
+                } else {
+                    for (int r = 0; r < nrow; r++)
+                        bulk_g2s(dst + r * pitch, p.w + (size_t)(row0 + r) * p.row_bytes + (size_t)c * kChunkBytes, bytes, bar);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: warp w takes row w of every stage ----------------
+    const int w = warp - 1;
+    const int ctid = threadIdx.x - 32;
+    constexpr int kConsumerThreads = 32 * kRingRows;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        const int per_row = cols / 16;
+        for (int i = ctid; i < M * per_row; i += kConsumerThreads) {
+            const int m = i / per_row, c16 = i - m * per_row;
+            *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
+                __ldcg(gq + i);
+        }
+        for (int i = ctid; i < M * nblk; i += kConsumerThreads) s_d[i] = __ldcg(p.xd + i);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    // S[m][b] = d[m][b] * sum of the block's 32 quants
+    for (int i = ctid; i < M * nblk; i += kConsumerThreads) {
+        const int m = i / nblk, b = i - m * nblk;
+        const int4 *a = reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(b >> 1) * kActPairBytes + (b & 1) * 32);
+        const int4 t0 = a[0], t1 = a[1];
+        int sum = 0;
+        sum = __dp4a(t0.x, 0x01010101, sum); sum = __dp4a(t0.y, 0x01010101, sum);
+        sum = __dp4a(t0.z, 0x01010101, sum); sum = __dp4a(t0.w, 0x01010101, sum);
+        sum = __dp4a(t1.x, 0x01010101, sum); sum = __dp4a(t1.y, 0x01010101, sum);
+        sum = __dp4a(t1.z, 0x01010101, sum); sum = __dp4a(t1.w, 0x01010101, sum);
+        s_s[i] = s_d[i] * (float)sum;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+
+    float acc[1][M];
+#pragma unroll
+    for (int m = 0; m < M; m++) acc[0][m] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < total && ok; i++) {
+        const int st = i % stages;
+        ok = mbar_wait(full + 8 * st, (uint32_t)(i / stages) & 1u, p.status, (8u << 24) | (uint32_t)st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int c = i % cpr;
+        const int row = r0 + (i / cpr) * kRingRows + w;
+        const bool valid = row < r1;
+        if (valid)
+            kq_stage_dot<FMT, M, 1, U>(ring + (size_t)st * stage_bytes + (size_t)w * pitch, pitch, 1, c, n_units, lane, s_q, act_row,
+                                       s_d, s_s, nblk, acc);
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+        if (c == cpr - 1) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                float v = acc[0][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && valid) p.y[(size_t)m * p.rows + row] = v * p.scale;
+                acc[0][m] = 0.0f;
+            }
         }
     }
 }
@@ -635,14 +789,72 @@ int launch_fmt_mu(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     return TPB_OK;
 }
 
+// The ring kernel, where its stages fit at least three deep; 0 stages: does not fit.
+template <int FMT, int U>
+int ring_stages(tpb_handle_t h, const KGemvParams &p, int m, uint32_t *pitch_out) {
+    const int n_units = p.cols / 64;
+    const int cpr = (n_units + 32 * U - 1) / (32 * U);
+    const uint32_t pitch = cpr == 1 ? (uint32_t)p.row_bytes : (uint32_t)(32 * U * Fmt<FMT>::kUnitBytes);
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t act = (size_t)m * n_units * kActPairBytes + (size_t)m * p.nblk * 8;
+    const size_t stage = (size_t)kRingRows * pitch;
+    if (act + 256 >= limit) return 0;
+    int stages = (int)((limit - act - 256) / (stage + 16));
+    if (stages > 12) stages = 12;
+    *pitch_out = pitch;
+    return stages >= 3 ? stages : 0;
+}
+
+template <int FMT, int M, int U>
+int launch_fmt_ring(tpb_handle_t h, cudaStream_t st, KGemvParams p, int stages, uint32_t pitch) {
+    p.chunk_pitch = pitch;
+    const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 8;
+    const size_t smem = act + (size_t)stages * ((size_t)kRingRows * pitch + 16) + 64;
+    int grid = (int)((p.rows + kRingRows - 1) / kRingRows);
+    if (grid > h->sm_count) grid = h->sm_count;
+    auto kern = kquant_gemv_ring_kernel<FMT, M, U>;
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(32 * (kRingRows + 1)), smem, st, p, stages));
+    return TPB_OK;
+}
+
+// TPB_GEMVK_KERNEL=ring|warp forces one of the two kernels (read at every launch, for measurements).
+static int k_kernel_override() {
+    const char *e = getenv("TPB_GEMVK_KERNEL");
+    if (e == nullptr) return 0;
+    return e[0] == 'r' ? 1 : e[0] == 'w' ? 2 : 0;
+}
+
 template <int FMT, int M>
 int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     // three units per lane where that takes fewer chunks per row than two (K = 5120, M = 1: q4_k 17.0 -> 14.6 us,
     // q4_0 14.6 -> 12.1); with many activation rows the longer unrolled body costs more than it saves
     // (q5_k, M = 8: 38 -> 45 us), so only up to four
     const int n_units = p.cols / 64;
+    bool u3 = false;
+    if constexpr (M <= 4) u3 = (n_units + 95) / 96 < (n_units + 63) / 64;
+    // The ring kernel for one or two activation rows where the per-warp rings serialise: rows of several chunks
+    // (K = 17408, M = 1: q4_k 21.5 -> 14.4 us, q4_0 18.2 -> 12.7, q5_k 25.1 -> 18.2) and many rows per warp
+    // (32000 x 4096: q4_k 28.9 -> 19.2 us).  With short rows and few of them per warp the two are within 5 %
+    // either way, and from four activation rows on the dot products set the time in both.
+    if constexpr (M <= 2) {
+        const int force = k_kernel_override();
+        const int cpr = (n_units + (u3 ? 96 : 64) - 1) / (u3 ? 96 : 64);
+        const bool many_rows = p.rows > 10 * 16 * h->sm_count;
+        if (force == 1 || (force == 0 && (cpr > 1 || many_rows))) {
+            uint32_t pitch = 0;
+            if (u3) {
+                const int s = ring_stages<FMT, 3>(h, p, M, &pitch);
+                if (s) return launch_fmt_ring<FMT, M, 3>(h, st, p, s, pitch);
+            } else {
+                const int s = ring_stages<FMT, 2>(h, p, M, &pitch);
+                if (s) return launch_fmt_ring<FMT, M, 2>(h, st, p, s, pitch);
+            }
+        }
+    }
     if constexpr (M <= 4)
-        if ((n_units + 95) / 96 < (n_units + 63) / 64) return launch_fmt_mu<FMT, M, 3>(h, st, p);
+        if (u3) return launch_fmt_mu<FMT, M, 3>(h, st, p);
     return launch_fmt_mu<FMT, M, 2>(h, st, p);
 }
 

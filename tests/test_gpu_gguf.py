@@ -86,6 +86,27 @@ def test_gguf_gemv_config2_size(be, fmt):
     assert (err <= 2e-5 * bound(fmt, w[rows], rows.size, k, x) + 1e-6).all(), f"max err {err.max():.3e}"
 
 
+@pytest.mark.parametrize("fmt", ["q4_0", "iq4_nl", "q4_k", "q5_k"])
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("n,k", [(1, 256), (15, 5120), (16, 17408), (333, 17408), (2500, 1024), (40, 6144)])
+def test_gguf_gemv_ring_kernel_gives_the_per_warp_kernels_bits(be, fmt, m, n, k, monkeypatch):
+    """One or two activation rows take a second kernel (one producer warp, sixteen-row stages) where rows are
+    long or many; it adds the same terms in the same order, so forcing either kernel gives identical bits --
+    ragged row counts, rows of one and of several chunks -- and both match the truth."""
+    w = synth.gguf_weights(fmt, n, k, seed=7 * n + k)
+    x = (np.random.default_rng(m + n).standard_normal((m, k))).astype(np.float32)
+    monkeypatch.setenv("TPB_GEMVK_KERNEL", "ring")
+    ring = run(be, fmt, w, n, k, x)
+    monkeypatch.setenv("TPB_GEMVK_KERNEL", "warp")
+    warp = run(be, fmt, w, n, k, x)
+    monkeypatch.delenv("TPB_GEMVK_KERNEL")
+    auto = run(be, fmt, w, n, k, x)
+    assert np.array_equal(ring, warp) and np.array_equal(auto, warp)
+    want = oracle.gguf_gemv_q8(fmt, w, n, k, x)
+    err = np.abs(ring.astype(np.float64) - want)
+    assert (err <= 2e-5 * bound(fmt, w, n, k, x) + 1e-6).all(), f"max err {err.max():.3e}"
+
+
 def test_gguf_gemv_rejects_bad_arguments(be):
     from tensorpencil_b200 import _lib
     y = torch.zeros(8, device="cuda")
