@@ -1050,6 +1050,75 @@ def run_mode_gemv(args, rank, local, world):
     be.close()
 
 
+def run_mode_gemv_shapes(args, local):
+    """The Q8_0 decode GEMV on ten weight shapes at M = 1 .. 8, as the library dispatches it and with each of its
+    two kernels forced (TPB_GEMV_KERNEL): the table the dispatch rule of tpb_q8_0_gemv_q8n was written from.
+    Also the other GGUF formats' two kernels (TPB_GEMVK_KERNEL) at M = 1, 2."""
+    import torch
+    from tensorpencil_b200 import harness, synth
+    from tensorpencil_b200.backend import Backend
+    torch.cuda.set_device(local)
+    be = Backend(local)
+    peaks = measured_peaks()
+
+    def best_of_3(fn, n=50):
+        for i in range(5):
+            fn(i)
+        return min(_events_ms(fn, n, torch.cuda.synchronize) / n for _ in range(3))
+
+    rows_out = []
+    shapes = ((17408, 5120), (5120, 17408), (32000, 4096), (4096, 14336), (14336, 4096), (8192, 8192), (28672, 8192),
+              (8192, 28672), (6144, 4096), (4096, 11008))
+    for (n, k) in shapes:
+        wbytes = n * (k // 32) * 34
+        copies = max(2, min(8, int(400e6 // wbytes) + 1))
+        ws = harness.rotating_q8_weights(n, k, copies, be.device)
+        for m in (1, 2, 3, 4, 5, 6, 8):
+            x = torch.randn(m, k, device="cuda")
+            y = torch.empty(m, n, device="cuda")
+            be.opGemvQuantizeX(x, m * k)
+            fn = lambda i: be.opGemvQuantQ8N("q8_0", y, ws[i % copies], 1.0, n, k, m, 0, m)
+            row = {"fmt": "q8_0", "n": n, "k": k, "m": m}
+            for name, env in (("auto", None), ("dp4a", "dp4a"), ("mma", "mma")):
+                if env is None:
+                    os.environ.pop("TPB_GEMV_KERNEL", None)
+                else:
+                    os.environ["TPB_GEMV_KERNEL"] = env
+                row[name + "_us"] = best_of_3(fn) * 1e3
+            os.environ.pop("TPB_GEMV_KERNEL", None)
+            row["auto_over_best"] = row["auto_us"] / min(row["dp4a_us"], row["mma_us"])
+            row["auto_frac_of_hbm"] = wbytes / (row["auto_us"] * 1e-6) / 1e9 / peaks["hbm_gbs"]
+            rows_out.append(row)
+        del ws
+    kq = []
+    for fmt in ("q4_k", "q4_0", "q5_k"):
+        for (n, k) in ((17408, 5120), (5120, 17408), (32000, 4096), (4096, 14336), (8192, 8192), (14336, 4096)):
+            base = torch.from_numpy(synth.gguf_weights(fmt, n, k, seed=11)).cuda()
+            ws = [base] + [base.clone() for _ in range(7)]
+            for m in (1, 2):
+                x = torch.randn(m, k, device="cuda")
+                y = torch.empty(m, n, device="cuda")
+                be.opGemvQuantizeX(x, m * k)
+                fn = lambda i: be.opGemvQuantQ8N(fmt, y, ws[i % 8], 1.0, n, k, m, 0, m)
+                row = {"fmt": fmt, "n": n, "k": k, "m": m}
+                for name, env in (("auto", None), ("warp", "warp"), ("ring", "ring")):
+                    if env is None:
+                        os.environ.pop("TPB_GEMVK_KERNEL", None)
+                    else:
+                        os.environ["TPB_GEMVK_KERNEL"] = env
+                    row[name + "_us"] = best_of_3(fn) * 1e3
+                os.environ.pop("TPB_GEMVK_KERNEL", None)
+                row["auto_frac_of_hbm"] = base.numel() / (row["auto_us"] * 1e-6) / 1e9 / peaks["hbm_gbs"]
+                kq.append(row)
+            del ws, base
+    be.status_poll()
+    q = [r["auto_over_best"] for r in rows_out]
+    print(json.dumps({"mode": "gemv-shapes", "what": "best of three 50-launch regions per entry, rotating weight copies larger than L2",
+                      "q8_0_auto_over_best_mean": float(np.mean(q)), "q8_0_auto_over_best_max": float(np.max(q)),
+                      "q8_0": rows_out, "other_formats": kq}), flush=True)
+    be.close()
+
+
 def run_mode_attn(args, local):
     """The attention of one DiT block at config 3's shape (seq 4608, 24 heads x 128, non-causal):
     the prepare pass (qk-norm + RoPE + per-head bf16 layout) and the tcgen05 softmax(q k^T) v
@@ -1266,7 +1335,7 @@ def main():
     ap.add_argument("--secondary-limit", type=float, default=420.0,
                     help="seconds after which the line is printed without the unfinished secondary parts")
     ap.add_argument("--latents", type=int, default=0, help="--mode dit-stream: latents per GPU (default 8 / GPUs)")
-    ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "attn", "one-kernel"], default="linear",
+    ap.add_argument("--mode", choices=["linear", "dit", "dit-stream", "nsplit", "gemv", "gemv-shapes", "attn", "one-kernel"], default="linear",
                     help="linear = the driver's default line (config 1); the others cover configs 2-4")
     ap.add_argument("--case", default="gemm", help="kernel for --mode one-kernel: prep, prep-mlp, gemm, gemm-bf16, "
                     "gemm-small, gemm-w4, gemm-w4-fused, gemm-w4-small, gemm-w4-fused-small, gemm-ablation, gemv1, gemv4, gemv8, gemv1-down, gemv4-down, gemv8-down, gemv1-q4k, gemv1-q6k, gemv8-q4k, prep-silu, attn, dit-blocks")
@@ -1289,6 +1358,8 @@ def main():
         return run_mode_nsplit(args, rank, local, world)
     if args.mode == "gemv":
         return run_mode_gemv(args, rank, local, world)
+    if args.mode == "gemv-shapes":
+        return run_mode_gemv_shapes(args, local)
     if args.mode == "attn":
         return run_mode_attn(args, local)
     if args.mode == "one-kernel":

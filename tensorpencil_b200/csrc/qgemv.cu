@@ -344,6 +344,34 @@ static GemvOverride gemv_override() {
     return v;
 }
 
+// Warps per CTA and stages per warp of the dp4a kernel for one rows-per-stage choice (stage = its bytes); 0 warps:
+// the activations leave no room.  Every warp owns a contiguous range of whole rows, so the slowest warp
+// carries ceil(rows / warps_total) rows.  Among the counts that fit (with >= 2 stages and the activations in
+// shared memory) take the one with the best balance; ties go to more warps.  E.g. 5120 rows on 148 SMs:
+// 16 warps -> 2.16 rows per warp (3 vs 2, 72 %), 12 warps -> 2.88 (96 %).
+static void dp4a_plan(tpb_handle_t h, size_t act, int64_t rows, int stage, int max_warps, int *warps, int *stages) {
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    *warps = 0;
+    *stages = 0;
+    double best_eff = -1.0;
+    for (int w = max_warps; w >= max_warps / 2; w--) {
+        int s_fit = 0;
+        for (int s = 4; s >= 2; s--)
+            if (act + (size_t)w * s * stage + (size_t)w * s * 8 + 64 <= limit) {
+                s_fit = s;
+                break;
+            }
+        if (s_fit == 0) continue;
+        const double per_warp = (double)rows / ((double)h->sm_count * w);
+        const double eff = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : per_warp;
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            *warps = w;
+            *stages = s_fit;
+        }
+    }
+}
+
 template <int M, int R>
 int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max_warps) {
     constexpr int kStage = stage_bytes(R);
@@ -363,32 +391,7 @@ int launch_q8n_cfg(tpb_handle_t h, cudaStream_t st, const GemvParams &p, int max
         TPB_CUDA(h, launch_pdl(kern, grid, ov.warps * 32, need, st, p, ov.stages));
         return TPB_OK;
     }
-    auto fits = [&](int w, int s, bool a) {
-        return (a ? act : 0) + (size_t)w * s * kStage + (size_t)w * s * 8 + 64 <= limit;
-    };
-    // Warps per CTA: every warp owns a contiguous range of whole rows, so the slowest warp
-    // carries ceil(rows / warps_total) rows.  Among the counts that fit (with >= 2 stages and
-    // the activations in shared memory) take the one with the best balance; ties go to more
-    // warps.  E.g. 5120 rows on 148 SMs: 16 warps -> 2.16 rows per warp (3 vs 2, 72 %),
-    // 12 warps -> 2.88 (96 %).
-    const int min_warps = max_warps / 2;
-    double best_eff = -1.0;
-    for (int w = max_warps; w >= min_warps; w--) {
-        int s_fit = 0;
-        for (int s = 4; s >= 2; s--)
-            if (fits(w, s, true)) {
-                s_fit = s;
-                break;
-            }
-        if (s_fit == 0) continue;
-        const double per_warp = (double)p.rows / ((double)h->sm_count * w);
-        const double eff = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : per_warp;
-        if (eff > best_eff + 0.02) {
-            best_eff = eff;
-            warps = w;
-            stages = s_fit;
-        }
-    }
+    dp4a_plan(h, act, p.rows, kStage, max_warps, &warps, &stages);
     if (stages == 0) {
         if (R == 2) return TPB_ERR_STATE;
         act_smem = false;
@@ -453,23 +456,48 @@ int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, in
 int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total) {
-    // Two kernels.  The dp4a streaming kernel below is the faster one for a single activation row
-    // whose K fits one CTA's registers in the other kernel (17.7 us at K = 5120 -> N = 17408); its
-    // time grows by ~2 us per activation row, and beyond eight rows x 12288 columns its activations no
-    // longer fit shared memory.  The kernel that keeps the activations in registers and takes the block
-    // sums from mma.sync (qgemv_mma.cu) costs 19-20 us at that shape whatever M is (19.3 against
-    // 19.2 us at two rows), so it takes every call with two rows or more; with long rows, where it
-    // splits K over a pair of CTAs (K = 17408 -> N = 5120: 20.6 us against 21.2), also the single row;
-    // and any call the dp4a kernel would have to serve with its activations in global memory.
-    // TPB_GEMV_KERNEL=dp4a / mma forces one.
+    // Two kernels.  The dp4a streaming kernel below costs one dp4a per weight word and activation row: the fastest
+    // for one row, 2-10 % slower with each further row, and much slower once its activations crowd the rings out of
+    // shared memory.  The kernel that keeps the activations in registers and takes the block sums from mma.sync
+    // (qgemv_mma.cu) costs the same whatever M is, but 0-4 us more than the dp4a kernel's single row (more where its
+    // per-warp K slices are padded, K = 4096: 4 block pairs in MMAs built for 6, and where it needs two passes
+    // over K).  Measured on ten decode shapes, M = 1 .. 8 (us, dp4a / mma): 17408 x 5120  17.6 19.1 21.0 23.8 /
+    // 19.2-20.0;  5120 x 17408  21.1 22.9 25.4 / 19.9-21.4 (few long rows: the dp4a kernel's warps get 2.9 rows
+    // for two-row stages);  32000 x 4096  22.6 22.7 24.8 26.7 29.9 / 27.1-28.7;  4096 x 14336  11.6 12.7 13.7 15.1
+    // 16.9 26.7 / 15.3-16.2;  8192 x 28672  41.0 42.2 69.6 / 49.8-53.0;  28672 x 8192  41.4 42.4 43.6 47.9 /
+    // 41.4-44.9.  The rule below follows that table.  TPB_GEMV_KERNEL=dp4a / mma forces one.
     {
         const char *e = getenv("TPB_GEMV_KERNEL");
         const bool force_dp4a = e != nullptr && e[0] == 'd', force_mma = e != nullptr && e[0] == 'm';
         const size_t act_bytes = (size_t)ng * (size_t)(cols / 64) * kActPairBytes + (size_t)ng * (size_t)(cols / 32) * 4;
-        // the smallest ring the dp4a kernel accepts beside its activations: 8 warps x 2 stages x 2 rows
-        const bool acts_fit = act_bytes + 8 * 2 * stage_bytes(2) + 8 * 2 * 8 + 64 <= (size_t)h->smem_optin - 1024;
-        const int mma_ks = force_dp4a ? 0 : tpb_q8_0_gemv_mma_fits(h, rows, cols);
-        if (mma_ks != 0 && (force_mma || ng >= 2 || mma_ks >= 2 || !acts_fit))
+        int npass = 1, waste_pct = 100;
+        const int mma_ks = force_dp4a ? 0 : tpb_q8_0_gemv_mma_fits(h, rows, cols, &npass, &waste_pct);
+        bool use_mma = false;
+        if (mma_ks != 0 && !force_mma) {
+            // the dp4a kernel at its best: fourteen warps with two two-row stages each fit beside the activations
+            // (with fewer its time jumps: K = 14336 from the sixth activation row on, K = 28672 from the third)
+            int warps = 0, stages = 0;
+            dp4a_plan(h, act_bytes, rows, stage_bytes(2), 16, &warps, &stages);
+            const bool roomy = warps != 0 && act_bytes + 14 * 2 * (size_t)stage_bytes(2) + 14 * 2 * 8 + 64 <=
+                                                 (size_t)h->smem_optin - 1024;
+            // share of its row slots that hold a row: rows come to a warp two at a time
+            double slots = 1.0;
+            if (roomy) {
+                const double per_warp = (double)rows / ((double)h->sm_count * warps * 2);
+                slots = per_warp >= 1.0 ? per_warp / (double)(long long)(per_warp + 0.999999) : 1.0;
+            }
+            const double mbytes = (double)rows * (double)(cols / 32) * kBlockBytes * 1e-6;
+            const bool padded = waste_pct >= 140;
+            const bool uneven = slots < 0.8 && mbytes >= 50.0;   // below that the fixed costs decide, not the balance
+            if (!roomy) use_mma = true;
+            else if (ng == 1) use_mma = mma_ks >= 2 && uneven;
+            else if (uneven) use_mma = true;
+            else if (ng == 2) use_mma = mbytes >= 200.0 && npass == 1;
+            else if (ng == 3) use_mma = mbytes >= (padded ? 150.0 : 80.0);
+            else if (ng == 4) use_mma = mbytes >= (padded ? 150.0 : 60.0);
+            else use_mma = true;
+        }
+        if (mma_ks != 0 && (force_mma || use_mma))
             return tpb_launch_q8_0_gemv_mma(h, st, y, w, scale, rows, cols, xq, ng, row_off, n_total);
     }
     GemvParams p;

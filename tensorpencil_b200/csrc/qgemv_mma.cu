@@ -613,11 +613,17 @@ int launch_np(tpb_handle_t h, cudaStream_t st, const MmaGemvParams &p, const Mma
 
 }  // namespace
 
-// 0 when the activation-stationary kernel cannot take this shape, else the number of CTAs K is split over.
-int tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols) {
+// 0 when the activation-stationary kernel cannot take this shape, else the number of CTAs K is split over;
+// *npass = its passes over K, *np_waste_pct = block pairs a warp's MMAs cover per pair it needs, in percent
+// (the kernel is instantiated for 6, 9 and 12 pairs per warp).
+int tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols, int *npass, int *np_waste_pct) {
     if (cols % 256 != 0 || rows < 1) return 0;
     const MmaPlan pl = plan_mma(h, rows, (int)(cols / 32));
-    return pl.npass != 0 ? pl.ks : 0;
+    if (pl.npass == 0) return 0;
+    const int np = pl.max_pairs <= 6 ? 6 : pl.max_pairs <= 9 ? 9 : 12;
+    if (npass) *npass = pl.npass;
+    if (np_waste_pct) *np_waste_pct = pl.max_pairs > 0 ? 100 * np / pl.max_pairs : 100;
+    return pl.ks;
 }
 
 int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale, int64_t rows,

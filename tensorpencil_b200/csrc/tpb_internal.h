@@ -154,7 +154,7 @@ int tpb_launch_q8_1_quantize(tpb_handle_t h, cudaStream_t st, const float *x, in
 int tpb_launch_q8_0_gemv_q8n(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale,
                              int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                              int n_total);
-int tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols);   // 0 = no; else CTAs K is split over
+int tpb_q8_0_gemv_mma_fits(tpb_handle_t h, int64_t rows, int64_t cols, int *npass, int *np_waste_pct);   // 0 = no; else CTAs K is split over
 int tpb_launch_q8_0_gemv_mma(tpb_handle_t h, cudaStream_t st, float *y, const void *w, float scale, int64_t rows,
                              int64_t cols, const void *xq, int ng, int row_off, int n_total);
 int tpb_launch_q8_0_gemv_f32(tpb_handle_t h, cudaStream_t st, float *y, const float *x,
