@@ -80,22 +80,24 @@ __device__ __forceinline__ uint32_t iq4nl_lookup(uint32_t idx) {
 }
 __device__ __forceinline__ float f16lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float f16hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
-__device__ __forceinline__ uint32_t byte_of(uint32_t w, int a) { return (w >> (8 * a)) & 0xffu; }
 
-// 6-bit scale and min number `is` (0..7) of a q4_k / q5_k super-block; s0, s1, s2 are the
-// three words of the 12-byte scales field (ggml's get_scale_min_k4).
-__device__ __forceinline__ void scale_min_k4(int is, uint32_t s0, uint32_t s1, uint32_t s2, float &sc, float &mn) {
-    const int a = is & 3;
-    uint32_t s, m;
-    if (is < 4) {
-        s = byte_of(s0, a) & 63u;
-        m = byte_of(s1, a) & 63u;
-    } else {
-        s = (byte_of(s2, a) & 0xFu) | ((byte_of(s0, a) >> 6) << 4);
-        m = (byte_of(s2, a) >> 4) | ((byte_of(s1, a) >> 6) << 4);
-    }
-    sc = (float)s;
-    mn = (float)m;
+// The 6-bit scales and mins of sub-blocks 2j and 2j+1 (j = 0..3) of a q4_k / q5_k super-block, both pairs at
+// once and without a branch; s0, s1, s2 are the three words of the 12-byte scales field.  ggml's
+// get_scale_min_k4 read two sub-blocks at a time: bytes 2j, 2j+1 of the field are one 16-bit word, and
+//   j < 2:  scale = byte & 63 of word j of s0,              min = byte & 63 of word j of s1
+//   j >= 2: scale = (s2 word & 0x0f0f) | (s0 word >> 6 << 4), min = (s2 word >> 4 & 0x0f0f) | (s1 word >> 6 << 4)
+// with "word" the 16-bit half number (j & 1) of each 32-bit word.
+__device__ __forceinline__ void scale_min_k4_pair(int j, uint32_t s0, uint32_t s1, uint32_t s2, float &sc0, float &mn0,
+                                                  float &sc1, float &mn1) {
+    const uint32_t sh = (uint32_t)(j & 1) * 16u;
+    const uint32_t a = (s0 >> sh) & 0xffffu, b = (s1 >> sh) & 0xffffu, c = (s2 >> sh) & 0xffffu;
+    const bool upper = j >= 2;
+    const uint32_t s16 = upper ? ((c & 0x0f0fu) | ((a & 0xc0c0u) >> 2)) : (a & 0x3f3fu);
+    const uint32_t m16 = upper ? (((c >> 4) & 0x0f0fu) | ((b & 0xc0c0u) >> 2)) : (b & 0x3f3fu);
+    sc0 = (float)(s16 & 0xffu);
+    sc1 = (float)(s16 >> 8);
+    mn0 = (float)(m16 & 0xffu);
+    mn1 = (float)(m16 >> 8);
 }
 
 // The arithmetic of one pipeline stage: rows 0 .. nrow - 1 of `stage` (pitch bytes apart) hold chunk c of their
@@ -190,13 +192,12 @@ __device__ __forceinline__ void kq_stage_dot(const uint8_t *stage, const int pit
                         }
                     }
                     const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
-                    float sc, mn;
-                    scale_min_k4(2 * j, hdr.y, hdr.z, hdr.w, sc, mn);
-                    ws0[r] = d * sc;
-                    wo0[r] = dmin * mn;
-                    scale_min_k4(2 * j + 1, hdr.y, hdr.z, hdr.w, sc, mn);
-                    ws1[r] = d * sc * (FMT == FMT_Q5_K ? 1.0f : 0.0625f);
-                    wo1[r] = dmin * mn;
+                    float sc0, mn0, sc1, mn1;
+                    scale_min_k4_pair(j, hdr.y, hdr.z, hdr.w, sc0, mn0, sc1, mn1);
+                    ws0[r] = d * sc0;
+                    wo0[r] = dmin * mn0;
+                    ws1[r] = d * sc1 * (FMT == FMT_Q5_K ? 1.0f : 0.0625f);
+                    wo1[r] = dmin * mn1;
                 }
             } else {
 #pragma unroll
@@ -873,6 +874,22 @@ int launch_fmt(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int ng) {
     return tpb_fail(h, TPB_ERR_INVALID_ARG, "gguf_gemv: ng out of range");
 }
 
+// Whether ng activation rows of `cols` columns leave room for the smallest set of weight rings (four warps, two
+// stages each) of the format's kernel.
+bool kq_group_fits(tpb_handle_t h, int fmt, int ng, int64_t cols) {
+    const size_t limit = (size_t)h->smem_optin - 1024;
+    const size_t n_units = (size_t)(cols / 64), nblk = (size_t)(cols / 32);
+    const size_t act = (size_t)ng * n_units * kActPairBytes + (size_t)ng * nblk * (fmt == TPB_GGUF_Q6_K ? 4 : 8);
+    size_t stage;
+    if (fmt == TPB_GGUF_Q6_K) {
+        stage = 2 * (size_t)kQ6RowStage;
+    } else {
+        const bool u3 = ng <= 4 && (n_units + 95) / 96 < (n_units + 63) / 64;
+        stage = 2 * (size_t)32 * (u3 ? 3 : 2) * (fmt == TPB_GGUF_Q5_K ? 44 : 36);
+    }
+    return act + 4 * 2 * stage + 4 * 2 * 8 + 64 <= limit;
+}
+
 }  // namespace
 
 extern "C" {
@@ -904,6 +921,15 @@ int tpb_gguf_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, int fmt, float *y, co
                   "gguf_gemv: need 1 <= ng <= 8 and row_off + ng <= n_total");
     TPB_CHECK_ARG(h, tpb_aligned16(w) && tpb_aligned16(xq), "gguf_gemv: w and xq must be 16-byte aligned");
     if (rows == 0) return TPB_OK;
+    if (ng > 1 && !kq_group_fits(h, fmt, ng, cols)) {
+        // the group's activations would leave no room for the weight rings (eight rows of 17408 columns are
+        // 209 KB): two launches with half the activation rows each -- a row's result does not depend on its group
+        const int first = ng / 2;
+        const int rc = tpb_gguf_gemv_q8n(h, stream, fmt, y, w, scale, rows, cols, xq, first, row_off, n_total);
+        if (rc != TPB_OK) return rc;
+        return tpb_gguf_gemv_q8n(h, stream, fmt, y + (size_t)first * (size_t)rows, w, scale, rows, cols, xq, ng - first,
+                                 row_off + first, n_total);
+    }
     KGemvParams p;
     const int nblk = (int)(cols / 32);
     p.y = y;

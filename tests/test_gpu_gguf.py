@@ -107,6 +107,21 @@ def test_gguf_gemv_ring_kernel_gives_the_per_warp_kernels_bits(be, fmt, m, n, k,
     assert (err <= 2e-5 * bound(fmt, w, n, k, x) + 1e-6).all(), f"max err {err.max():.3e}"
 
 
+@pytest.mark.parametrize("fmt", ["q4_0", "q4_k", "q5_k", "q6_k"])
+def test_gguf_gemv_group_too_large_for_shared_memory_is_split(be, fmt):
+    """Eight activation rows of 17408 columns take 209 KB of shared memory, more than the kernels can spare; the
+    library then runs the group as two launches.  Same bits as the rows run one at a time, and the truth."""
+    n, k = 48, 17408
+    w = synth.gguf_weights(fmt, n, k, seed=91)
+    x = (np.random.default_rng(92).standard_normal((8, k))).astype(np.float32)
+    got8 = run(be, fmt, w, n, k, x)
+    for r in (0, 3, 7):
+        assert np.array_equal(run(be, fmt, w, n, k, x[r:r + 1])[0], got8[r])
+    want = oracle.gguf_gemv_q8(fmt, w, n, k, x)
+    err = np.abs(got8.astype(np.float64) - want)
+    assert (err <= 2e-5 * bound(fmt, w, n, k, x) + 1e-6).all(), f"max err {err.max():.3e}"
+
+
 def test_gguf_gemv_rejects_bad_arguments(be):
     from tensorpencil_b200 import _lib
     y = torch.zeros(8, device="cuda")
