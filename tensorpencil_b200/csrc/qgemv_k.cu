@@ -187,8 +187,10 @@ __device__ __forceinline__ void kq_stage_dot(const uint8_t *stage, const int pit
                         const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
                         for (int w = 0; w < 8; w++) {
-                            lo[r][w] |= ((hw[w] >> (2 * j)) & 0x01010101u) << 4;
-                            hi[r][w] = (hi[r][w] >> 4) | (((hw[w] >> (2 * j + 1)) & 0x01010101u) << 4);
+                            // bits 2j and 2j+1 of every qh byte, moved to bit 4 of the byte
+                            const uint32_t t = hw[w] >> (2 * j);
+                            lo[r][w] |= (t << 4) & 0x10101010u;
+                            hi[r][w] = ((qw[w] >> 4) & 0x0f0f0f0fu) | ((t << 3) & 0x10101010u);
                         }
                     }
                     const float d = f16lo(hdr.x), dmin = f16hi(hdr.x);
