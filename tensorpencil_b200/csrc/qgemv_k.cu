@@ -508,19 +508,21 @@ kquant_gemv_ring_kernel(const KGemvParams p, const int stages) {
 // 210-byte super-blocks (ql[128] low nibbles, qh[64] two high bits, 16 int8 scales, f16 d;
 // w = d * sc * (q - 32)) are only 2-byte aligned and a row of them is in general not a
 // multiple of 16 bytes, while a bulk copy needs 16-byte aligned addresses and sizes.  A
-// chunk is 8 super-blocks (1680 bytes = 105 x 16), so within a row every chunk starts at
+// chunk is 16 super-blocks (3360 bytes = 210 x 16), so within a row every chunk starts at
 // the same offset `mis` modulo 16: the copy starts `mis` bytes early and is rounded up to
 // 16, and the lanes index from stage + mis.  (The rounding can read up to 14 bytes past a
 // row -- the next row's, or, after the last row, whatever follows the weights in the same
 // allocation; those bytes are never used.)  Fields are fetched as aligned words and funnel-
 // shifted by the (even) byte offset.
 //
-// A lane's unit is 32 elements of one super-block: half n (0/1), eight positions
-// l = 8 lq .. 8 lq + 7 of that half, and the four 32-element strides p -- y[128n + 32p + l].
-// Each of the four 8-element runs lies inside one q8_1 activation block.
+// A lane's unit is 64 elements of one super-block: half n (0/1), sixteen positions
+// l = 16 lh .. 16 lh + 15 of that half (lh = 0/1), and the four 32-element strides p --
+// y[128n + 32p + l].  Each of the four 16-element runs is one scale group of the super-block and half of
+// a q8_1 activation block.  With T = 32 * d_x * (sum of the run's sixteen activation quants), computed once
+// per call into shared memory, a run adds (d * sc) * (d_x * sum(q * x_q)) - (d * sc) * T.
 constexpr int kQ6Sb = 210;
-constexpr int kQ6ChunkSb = 8;
-constexpr int kQ6ChunkBytes = kQ6ChunkSb * kQ6Sb;     // 1680
+constexpr int kQ6ChunkSb = 16;
+constexpr int kQ6ChunkBytes = kQ6ChunkSb * kQ6Sb;     // 3360 = 210 x 16
 constexpr int kQ6RowStage = kQ6ChunkBytes + 16 + 16;  // + alignment slack + words read past the last field
 
 // 8 bytes at byte offset `off` (even) from the 4-byte aligned `base`
@@ -529,6 +531,13 @@ __device__ __forceinline__ uint2 ld8_unaligned(const uint8_t *base, int off) {
     const uint32_t sh = (uint32_t)(off & 3) * 8u;  // 0 or 16
     const uint32_t a = w[0], b = w[1], c = w[2];
     return make_uint2(__funnelshift_r(a, b, sh), __funnelshift_r(b, c, sh));
+}
+// 16 bytes at byte offset `off` (even) from the 4-byte aligned `base`
+__device__ __forceinline__ uint4 ld16_unaligned(const uint8_t *base, int off) {
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(base + (off & ~3));
+    const uint32_t sh = (uint32_t)(off & 3) * 8u;  // 0 or 16
+    const uint32_t a = w[0], b = w[1], c = w[2], d = w[3], e = w[4];
+    return make_uint4(__funnelshift_r(a, b, sh), __funnelshift_r(b, c, sh), __funnelshift_r(c, d, sh), __funnelshift_r(d, e, sh));
 }
 
 template <int M, int R>
@@ -545,9 +554,11 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
     const int n_sb = cols / 256;
 
     const size_t act_row = (size_t)n_units * kActPairBytes;
+    // shared: [act q: M x n_units x 80][act d: M x nblk f32][T: M x 4 n_sb lane-units x 4 runs f32][rings][barriers]
     int8_t *s_q = reinterpret_cast<int8_t *>(smem);
     float *s_d = reinterpret_cast<float *>(smem + (size_t)M * act_row);
-    uint8_t *ring0 = reinterpret_cast<uint8_t *>(s_d + (size_t)M * nblk);
+    float *s_t = s_d + (size_t)M * nblk;
+    uint8_t *ring0 = reinterpret_cast<uint8_t *>(s_t + (size_t)M * 16 * n_sb);
     uint8_t *ring = ring0 + (size_t)warp * stages * kStageBytes;
     const uint32_t bars = smem_u32(ring0 + (size_t)n_warps * stages * kStageBytes) + warp * stages * 8;
 
@@ -604,6 +615,19 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         for (int i = threadIdx.x; i < M * nblk; i += blockDim.x) s_d[i] = __ldcg(p.xd + i);
     }
     __syncthreads();
+    // T[m][lane-unit u = 4 sb + 2 n + lh][run p] = 32 * d_x * sum of activation quants 256 sb + 128 n + 32 p + 16 lh .. + 15
+    for (int i = threadIdx.x; i < M * 16 * n_sb; i += blockDim.x) {
+        const int m = i / (16 * n_sb), j = i - m * 16 * n_sb;
+        const int u = j >> 2, pp = j & 3;
+        const int e = 64 * (u >> 1) * 2 + 32 * pp + 16 * (u & 1);   // 256 sb + 128 n = 128 (u >> 1)
+        const int4 x = *reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
+        int sx = __dp4a(x.x, 0x01010101, 0);
+        sx = __dp4a(x.y, 0x01010101, sx);
+        sx = __dp4a(x.z, 0x01010101, sx);
+        sx = __dp4a(x.w, 0x01010101, sx);
+        s_t[i] = 32.0f * (s_d[(size_t)m * nblk + (e >> 5)] * (float)sx);
+    }
+    __syncthreads();
 
     float acc[R][M];
 #pragma unroll
@@ -627,13 +651,13 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         const int nrow = min(R, my_r1 - row0);
 #pragma unroll
         for (int t = 0; t < 2; t++) {
-            const int ul = lane + 32 * t;              // 64 lane-units per chunk: 8 per super-block
-            const int sb_l = ul >> 3;
+            const int ul = lane + 32 * t;              // 64 lane-units per chunk: 4 per super-block
+            const int sb_l = ul >> 2;
             const int sb = c * kQ6ChunkSb + sb_l;
             if (sb >= n_sb) continue;
-            const int n = (ul >> 2) & 1, lq = ul & 3;
-            // q values of the four runs as unsigned bytes (0..63) and their scales
-            uint32_t qv[R][4][2];
+            const int n = (ul >> 1) & 1, lh = ul & 1;
+            // q values of the four runs as unsigned bytes (0..63), four words each, and their scales
+            uint32_t qv[R][4][4];
             float wsc[R][4];
 #pragma unroll
             for (int r = 0; r < R; r++) {
@@ -641,44 +665,54 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
                     const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
                     const uint8_t *base = ring + (size_t)st * kStageBytes + r * kQ6RowStage;  // 16-byte aligned
                     const int o = (int)mis + sb_l * kQ6Sb;                                    // super-block offset (even)
-                    const uint2 l0 = ld8_unaligned(base, o + 64 * n + 8 * lq);        // low nibbles: run 0, high: run 2
-                    const uint2 l1 = ld8_unaligned(base, o + 64 * n + 32 + 8 * lq);   // low: run 1, high: run 3
-                    const uint2 hb = ld8_unaligned(base, o + 128 + 32 * n + 8 * lq);  // two high bits of runs 0..3
-                    qv[r][0][0] = (l0.x & 0x0f0f0f0fu) | ((hb.x & 0x03030303u) << 4);
-                    qv[r][0][1] = (l0.y & 0x0f0f0f0fu) | ((hb.y & 0x03030303u) << 4);
-                    qv[r][1][0] = (l1.x & 0x0f0f0f0fu) | (((hb.x >> 2) & 0x03030303u) << 4);
-                    qv[r][1][1] = (l1.y & 0x0f0f0f0fu) | (((hb.y >> 2) & 0x03030303u) << 4);
-                    qv[r][2][0] = ((l0.x >> 4) & 0x0f0f0f0fu) | (((hb.x >> 4) & 0x03030303u) << 4);
-                    qv[r][2][1] = ((l0.y >> 4) & 0x0f0f0f0fu) | (((hb.y >> 4) & 0x03030303u) << 4);
-                    qv[r][3][0] = ((l1.x >> 4) & 0x0f0f0f0fu) | (((hb.x >> 6) & 0x03030303u) << 4);
-                    qv[r][3][1] = ((l1.y >> 4) & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
-                    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(base + o + 208)));
-                    const int8_t *sc = reinterpret_cast<const int8_t *>(base + o + 192 + 8 * n + (lq >> 1));
+                    const uint4 la = ld16_unaligned(base, o + 64 * n + 16 * lh);        // low nibbles: run 0, high: run 2
+                    const uint4 lb = ld16_unaligned(base, o + 64 * n + 32 + 16 * lh);   // low: run 1, high: run 3
+                    const uint4 hb = ld16_unaligned(base, o + 128 + 32 * n + 16 * lh);  // two high bits of runs 0..3
+                    const uint32_t a4[4] = {la.x, la.y, la.z, la.w}, b4[4] = {lb.x, lb.y, lb.z, lb.w};
+                    const uint32_t h4[4] = {hb.x, hb.y, hb.z, hb.w};
 #pragma unroll
-                    for (int pp = 0; pp < 4; pp++) wsc[r][pp] = d * (float)sc[2 * pp];
+                    for (int w = 0; w < 4; w++) {
+                        qv[r][0][w] = (a4[w] & 0x0f0f0f0fu) | ((h4[w] << 4) & 0x30303030u);
+                        qv[r][1][w] = (b4[w] & 0x0f0f0f0fu) | ((h4[w] << 2) & 0x30303030u);
+                        qv[r][2][w] = ((a4[w] >> 4) & 0x0f0f0f0fu) | (h4[w] & 0x30303030u);
+                        qv[r][3][w] = ((b4[w] >> 4) & 0x0f0f0f0fu) | ((h4[w] >> 2) & 0x30303030u);
+                    }
+                    // scales 8 n + lh + 0, 2, 4, 6 (one per run) from the eight bytes of this half; d behind them
+                    const uint2 sc8 = ld8_unaligned(base, o + 192 + 8 * n);
+                    const uint32_t sce = lh ? __byte_perm(sc8.x, sc8.y, 0x7531) : __byte_perm(sc8.x, sc8.y, 0x6420);
+                    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(base + o + 208)));
+#pragma unroll
+                    for (int pp = 0; pp < 4; pp++) wsc[r][pp] = d * (float)(int)(int8_t)(sce >> (8 * pp));
                 } else {
 #pragma unroll
                     for (int pp = 0; pp < 4; pp++) {
-                        qv[r][pp][0] = qv[r][pp][1] = 0;
+#pragma unroll
+                        for (int w = 0; w < 4; w++) qv[r][pp][w] = 0;
                         wsc[r][pp] = 0.0f;
                     }
                 }
             }
+            const int u = 4 * sb + 2 * n + lh;     // lane-unit number within the row
 #pragma unroll
             for (int m = 0; m < M; m++) {
+                const float4 dx4 = *reinterpret_cast<const float4 *>(s_d + (size_t)m * nblk + 8 * sb + 4 * n);
+                const float4 t4 = *reinterpret_cast<const float4 *>(s_t + ((size_t)m * 4 * n_sb + u) * 4);
+                const float dxs[4] = {dx4.x, dx4.y, dx4.z, dx4.w}, ts[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
                 for (int pp = 0; pp < 4; pp++) {
-                    // activation elements 256 sb + 128 n + 32 pp + 8 lq .. + 7
-                    const int e = 256 * sb + 128 * n + 32 * pp + 8 * lq;
-                    const int2 xv = *reinterpret_cast<const int2 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
-                    const float dx = s_d[(size_t)m * nblk + (e >> 5)];
-                    int sx = __dp4a(xv.x, 0x01010101, 0);
-                    sx = __dp4a(xv.y, 0x01010101, sx);
+                    // activation elements 256 sb + 128 n + 32 pp + 16 lh .. + 15
+                    const int e = 256 * sb + 128 * n + 32 * pp + 16 * lh;
+                    const int4 xv = *reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
 #pragma unroll
                     for (int r = 0; r < R; r++) {
                         int sq = dp4a_us(qv[r][pp][0], (uint32_t)xv.x, 0);
                         sq = dp4a_us(qv[r][pp][1], (uint32_t)xv.y, sq);
-                        acc[r][m] = fmaf(wsc[r][pp], dx * i2f_small(sq - 32 * sx), acc[r][m]);
+                        sq = dp4a_us(qv[r][pp][2], (uint32_t)xv.z, sq);
+                        sq = dp4a_us(qv[r][pp][3], (uint32_t)xv.w, sq);
+                        float tacc = acc[r][m];
+                        tacc = fmaf(wsc[r][pp], dxs[pp] * i2f_small(sq), tacc);
+                        tacc = fmaf(-wsc[r][pp], ts[pp], tacc);
+                        acc[r][m] = tacc;
                     }
                 }
             }
@@ -705,7 +739,7 @@ int launch_q6k_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     constexpr int R = 2;
     constexpr int kStage = R * kQ6RowStage;
     const size_t limit = (size_t)h->smem_optin - 1024;
-    const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 4;
+    const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 4 + (size_t)M * (p.cols / 16) * 4;
     int warps = 0, stages = 0;
     double best_eff = -1.0;
     for (int w = 16; w >= 4; w--) {
@@ -881,7 +915,7 @@ int launch_fmt(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int ng) {
 bool kq_group_fits(tpb_handle_t h, int fmt, int ng, int64_t cols) {
     const size_t limit = (size_t)h->smem_optin - 1024;
     const size_t n_units = (size_t)(cols / 64), nblk = (size_t)(cols / 32);
-    const size_t act = (size_t)ng * n_units * kActPairBytes + (size_t)ng * nblk * (fmt == TPB_GGUF_Q6_K ? 4 : 8);
+    const size_t act = (size_t)ng * n_units * kActPairBytes + (size_t)ng * nblk * (fmt == TPB_GGUF_Q6_K ? 12 : 8);
     size_t stage;
     if (fmt == TPB_GGUF_Q6_K) {
         stage = 2 * (size_t)kQ6RowStage;
