@@ -540,6 +540,83 @@ __device__ __forceinline__ uint4 ld16_unaligned(const uint8_t *base, int off) {
     return make_uint4(__funnelshift_r(a, b, sh), __funnelshift_r(b, c, sh), __funnelshift_r(c, d, sh), __funnelshift_r(d, e, sh));
 }
 
+// The arithmetic of one q6_k pipeline stage: rows row0 .. row0 + nrow - 1 at `stage` (kQ6RowStage bytes apart, each
+// starting its row's misalignment into its slot) hold chunk c; every lane decodes its two units of each row.
+template <int M, int R>
+__device__ __forceinline__ void q6k_stage_dot(const uint8_t *stage, const int row0, const int nrow, const size_t row_bytes,
+                                              const int c, const int n_sb, const int lane, const int8_t *s_q,
+                                              const size_t act_row, const float *s_d, const float *s_t, const int nblk,
+                                              float (&acc)[R][M]) {
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const int ul = lane + 32 * t;              // 64 lane-units per chunk: 4 per super-block
+        const int sb_l = ul >> 2;
+        const int sb = c * kQ6ChunkSb + sb_l;
+        if (sb >= n_sb) continue;
+        const int n = (ul >> 1) & 1, lh = ul & 1;
+        // q values of the four runs as unsigned bytes (0..63), four words each, and their scales
+        uint32_t qv[R][4][4];
+        float wsc[R][4];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (r < nrow) {
+                const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * row_bytes) & 15u);
+                const uint8_t *base = stage + r * kQ6RowStage;                               // 16-byte aligned
+                const int o = (int)mis + sb_l * kQ6Sb;                                    // super-block offset (even)
+                const uint4 la = ld16_unaligned(base, o + 64 * n + 16 * lh);        // low nibbles: run 0, high: run 2
+                const uint4 lb = ld16_unaligned(base, o + 64 * n + 32 + 16 * lh);   // low: run 1, high: run 3
+                const uint4 hb = ld16_unaligned(base, o + 128 + 32 * n + 16 * lh);  // two high bits of runs 0..3
+                const uint32_t a4[4] = {la.x, la.y, la.z, la.w}, b4[4] = {lb.x, lb.y, lb.z, lb.w};
+                const uint32_t h4[4] = {hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    qv[r][0][w] = (a4[w] & 0x0f0f0f0fu) | ((h4[w] << 4) & 0x30303030u);
+                    qv[r][1][w] = (b4[w] & 0x0f0f0f0fu) | ((h4[w] << 2) & 0x30303030u);
+                    qv[r][2][w] = ((a4[w] >> 4) & 0x0f0f0f0fu) | (h4[w] & 0x30303030u);
+                    qv[r][3][w] = ((b4[w] >> 4) & 0x0f0f0f0fu) | ((h4[w] >> 2) & 0x30303030u);
+                }
+                // scales 8 n + lh + 0, 2, 4, 6 (one per run) from the eight bytes of this half; d behind them
+                const uint2 sc8 = ld8_unaligned(base, o + 192 + 8 * n);
+                const uint32_t sce = lh ? __byte_perm(sc8.x, sc8.y, 0x7531) : __byte_perm(sc8.x, sc8.y, 0x6420);
+                const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(base + o + 208)));
+#pragma unroll
+                for (int pp = 0; pp < 4; pp++) wsc[r][pp] = d * (float)(int)(int8_t)(sce >> (8 * pp));
+            } else {
+#pragma unroll
+                for (int pp = 0; pp < 4; pp++) {
+#pragma unroll
+                    for (int w = 0; w < 4; w++) qv[r][pp][w] = 0;
+                    wsc[r][pp] = 0.0f;
+                }
+            }
+        }
+        const int u = 4 * sb + 2 * n + lh;     // lane-unit number within the row
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            const float4 dx4 = *reinterpret_cast<const float4 *>(s_d + (size_t)m * nblk + 8 * sb + 4 * n);
+            const float4 t4 = *reinterpret_cast<const float4 *>(s_t + ((size_t)m * 4 * n_sb + u) * 4);
+            const float dxs[4] = {dx4.x, dx4.y, dx4.z, dx4.w}, ts[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+            for (int pp = 0; pp < 4; pp++) {
+                // activation elements 256 sb + 128 n + 32 pp + 16 lh .. + 15
+                const int e = 256 * sb + 128 * n + 32 * pp + 16 * lh;
+                const int4 xv = *reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    int sq = dp4a_us(qv[r][pp][0], (uint32_t)xv.x, 0);
+                    sq = dp4a_us(qv[r][pp][1], (uint32_t)xv.y, sq);
+                    sq = dp4a_us(qv[r][pp][2], (uint32_t)xv.z, sq);
+                    sq = dp4a_us(qv[r][pp][3], (uint32_t)xv.w, sq);
+                    float tacc = acc[r][m];
+                    tacc = fmaf(wsc[r][pp], dxs[pp] * i2f_small(sq), tacc);
+                    tacc = fmaf(-wsc[r][pp], ts[pp], tacc);
+                    acc[r][m] = tacc;
+                }
+            }
+        }
+    }
+}
+
 template <int M, int R>
 __global__ void __launch_bounds__(512, 1)
 q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
@@ -649,74 +726,7 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
         const int c = i % cpr;
         const int row0 = my_r0 + (i / cpr) * R;
         const int nrow = min(R, my_r1 - row0);
-#pragma unroll
-        for (int t = 0; t < 2; t++) {
-            const int ul = lane + 32 * t;              // 64 lane-units per chunk: 4 per super-block
-            const int sb_l = ul >> 2;
-            const int sb = c * kQ6ChunkSb + sb_l;
-            if (sb >= n_sb) continue;
-            const int n = (ul >> 1) & 1, lh = ul & 1;
-            // q values of the four runs as unsigned bytes (0..63), four words each, and their scales
-            uint32_t qv[R][4][4];
-            float wsc[R][4];
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                if (r < nrow) {
-                    const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
-                    const uint8_t *base = ring + (size_t)st * kStageBytes + r * kQ6RowStage;  // 16-byte aligned
-                    const int o = (int)mis + sb_l * kQ6Sb;                                    // super-block offset (even)
-                    const uint4 la = ld16_unaligned(base, o + 64 * n + 16 * lh);        // low nibbles: run 0, high: run 2
-                    const uint4 lb = ld16_unaligned(base, o + 64 * n + 32 + 16 * lh);   // low: run 1, high: run 3
-                    const uint4 hb = ld16_unaligned(base, o + 128 + 32 * n + 16 * lh);  // two high bits of runs 0..3
-                    const uint32_t a4[4] = {la.x, la.y, la.z, la.w}, b4[4] = {lb.x, lb.y, lb.z, lb.w};
-                    const uint32_t h4[4] = {hb.x, hb.y, hb.z, hb.w};
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        qv[r][0][w] = (a4[w] & 0x0f0f0f0fu) | ((h4[w] << 4) & 0x30303030u);
-                        qv[r][1][w] = (b4[w] & 0x0f0f0f0fu) | ((h4[w] << 2) & 0x30303030u);
-                        qv[r][2][w] = ((a4[w] >> 4) & 0x0f0f0f0fu) | (h4[w] & 0x30303030u);
-                        qv[r][3][w] = ((b4[w] >> 4) & 0x0f0f0f0fu) | ((h4[w] >> 2) & 0x30303030u);
-                    }
-                    // scales 8 n + lh + 0, 2, 4, 6 (one per run) from the eight bytes of this half; d behind them
-                    const uint2 sc8 = ld8_unaligned(base, o + 192 + 8 * n);
-                    const uint32_t sce = lh ? __byte_perm(sc8.x, sc8.y, 0x7531) : __byte_perm(sc8.x, sc8.y, 0x6420);
-                    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(base + o + 208)));
-#pragma unroll
-                    for (int pp = 0; pp < 4; pp++) wsc[r][pp] = d * (float)(int)(int8_t)(sce >> (8 * pp));
-                } else {
-#pragma unroll
-                    for (int pp = 0; pp < 4; pp++) {
-#pragma unroll
-                        for (int w = 0; w < 4; w++) qv[r][pp][w] = 0;
-                        wsc[r][pp] = 0.0f;
-                    }
-                }
-            }
-            const int u = 4 * sb + 2 * n + lh;     // lane-unit number within the row
-#pragma unroll
-            for (int m = 0; m < M; m++) {
-                const float4 dx4 = *reinterpret_cast<const float4 *>(s_d + (size_t)m * nblk + 8 * sb + 4 * n);
-                const float4 t4 = *reinterpret_cast<const float4 *>(s_t + ((size_t)m * 4 * n_sb + u) * 4);
-                const float dxs[4] = {dx4.x, dx4.y, dx4.z, dx4.w}, ts[4] = {t4.x, t4.y, t4.z, t4.w};
-#pragma unroll
-                for (int pp = 0; pp < 4; pp++) {
-                    // activation elements 256 sb + 128 n + 32 pp + 16 lh .. + 15
-                    const int e = 256 * sb + 128 * n + 32 * pp + 16 * lh;
-                    const int4 xv = *reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        int sq = dp4a_us(qv[r][pp][0], (uint32_t)xv.x, 0);
-                        sq = dp4a_us(qv[r][pp][1], (uint32_t)xv.y, sq);
-                        sq = dp4a_us(qv[r][pp][2], (uint32_t)xv.z, sq);
-                        sq = dp4a_us(qv[r][pp][3], (uint32_t)xv.w, sq);
-                        float tacc = acc[r][m];
-                        tacc = fmaf(wsc[r][pp], dxs[pp] * i2f_small(sq), tacc);
-                        tacc = fmaf(-wsc[r][pp], ts[pp], tacc);
-                        acc[r][m] = tacc;
-                    }
-                }
-            }
-        }
+        q6k_stage_dot<M, R>(ring + (size_t)st * kStageBytes, row0, nrow, p.row_bytes, c, n_sb, lane, s_q, act_row, s_d, s_t, nblk, acc);
         __syncwarp();
 
         if (c == cpr - 1) {
@@ -734,9 +744,170 @@ q6k_gemv_q8n_kernel(const KGemvParams p, const int stages) {
     }
 }
 
+// q6_k behind the CTA-wide ring (see kquant_gemv_ring_kernel): one producer warp, stages of sixteen rows, one row per
+// consumer warp; a row's slot starts 16-byte aligned and the row's chunk sits `mis` bytes into it, as above.
+template <int M>
+__global__ void __launch_bounds__(32 * (kRingRows + 1), 1)
+q6k_gemv_ring_kernel(const KGemvParams p, const int stages) {
+    constexpr int kStageBytes = kRingRows * kQ6RowStage;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nblk = p.nblk;
+    const int cols = p.cols;
+    const int n_units = cols / 64;
+    const int n_sb = cols / 256;
+
+    const size_t act_row = (size_t)n_units * kActPairBytes;
+    int8_t *s_q = reinterpret_cast<int8_t *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)M * act_row);
+    float *s_t = s_d + (size_t)M * nblk;
+    uint8_t *ring = reinterpret_cast<uint8_t *>(s_t + (size_t)M * 16 * n_sb);
+    const uint32_t full = smem_u32(ring + (size_t)stages * kStageBytes);
+    const uint32_t empty = full + 8u * (uint32_t)stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full + 8 * s), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty + 8 * s), "r"(kRingRows));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int cpr = (n_sb + kQ6ChunkSb - 1) / kQ6ChunkSb;
+    const int r0 = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const int n_groups = (r1 - r0 + kRingRows - 1) / kRingRows;
+    const int total = n_groups * cpr;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            for (int i = 0; i < total; i++) {
+                const int st = i % stages;
+                if (i >= stages) {
+                    if (!mbar_wait(empty + 8 * st, (uint32_t)(i / stages - 1) & 1u, p.status, (9u << 24) | (uint32_t)st)) break;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                const int c = i % cpr;
+                const int row0 = r0 + (i / cpr) * kRingRows;
+                const int nrow = min(kRingRows, r1 - row0);
+                const int sbs = min(kQ6ChunkSb, n_sb - c * kQ6ChunkSb);
+                const uint32_t bar = full + 8 * st;
+                uint32_t tx = 0;
+                for (int r = 0; r < nrow; r++) {
+                    const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
+                    tx += (mis + (uint32_t)sbs * kQ6Sb + 15u) & ~15u;
+                }
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tx) : "memory");
+                const uint32_t dst = smem_u32(ring + (size_t)st * kStageBytes);
+                for (int r = 0; r < nrow; r++) {
+                    const size_t goff = (size_t)(row0 + r) * p.row_bytes + (size_t)c * kQ6ChunkBytes;
+                    const uint32_t mis = (uint32_t)(((size_t)(row0 + r) * p.row_bytes) & 15u);
+                    const uint32_t bytes = (mis + (uint32_t)sbs * kQ6Sb + 15u) & ~15u;
+                    bulk_g2s(dst + r * kQ6RowStage, p.w + goff - mis, bytes, bar);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: warp w takes row w of every stage ----------------
+    const int w = warp - 1;
+    const int ctid = threadIdx.x - 32;
+    constexpr int kConsumerThreads = 32 * kRingRows;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const int4 *gq = reinterpret_cast<const int4 *>(p.xq);
+        const int per_row = cols / 16;
+        for (int i = ctid; i < M * per_row; i += kConsumerThreads) {
+            const int m = i / per_row, c16 = i - m * per_row;
+            *reinterpret_cast<int4 *>(s_q + (size_t)m * act_row + (size_t)(c16 >> 2) * kActPairBytes + (c16 & 3) * 16) =
+                __ldcg(gq + i);
+        }
+        for (int i = ctid; i < M * nblk; i += kConsumerThreads) s_d[i] = __ldcg(p.xd + i);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    for (int i = ctid; i < M * 16 * n_sb; i += kConsumerThreads) {
+        const int m = i / (16 * n_sb), j = i - m * 16 * n_sb;
+        const int u = j >> 2, pp = j & 3;
+        const int e = 128 * (u >> 1) + 32 * pp + 16 * (u & 1);
+        const int4 x = *reinterpret_cast<const int4 *>(s_q + (size_t)m * act_row + (size_t)(e >> 6) * kActPairBytes + (e & 63));
+        int sx = __dp4a(x.x, 0x01010101, 0);
+        sx = __dp4a(x.y, 0x01010101, sx);
+        sx = __dp4a(x.z, 0x01010101, sx);
+        sx = __dp4a(x.w, 0x01010101, sx);
+        s_t[i] = 32.0f * (s_d[(size_t)m * nblk + (e >> 5)] * (float)sx);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+
+    float acc[1][M];
+#pragma unroll
+    for (int m = 0; m < M; m++) acc[0][m] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < total && ok; i++) {
+        const int st = i % stages;
+        ok = mbar_wait(full + 8 * st, (uint32_t)(i / stages) & 1u, p.status, (10u << 24) | (uint32_t)st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int c = i % cpr;
+        const int row = r0 + (i / cpr) * kRingRows + w;
+        const bool valid = row < r1;
+        if (valid)
+            q6k_stage_dot<M, 1>(ring + (size_t)st * kStageBytes + (size_t)w * kQ6RowStage, row, 1, p.row_bytes, c, n_sb, lane, s_q,
+                                act_row, s_d, s_t, nblk, acc);
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+        if (c == cpr - 1) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                float v = acc[0][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && valid) p.y[(size_t)m * p.rows + row] = v * p.scale;
+                acc[0][m] = 0.0f;
+            }
+        }
+    }
+}
+
+// TPB_GEMVK_KERNEL=ring|warp forces one of the two kernels (read at every launch, for measurements).
+static int k_kernel_override() {
+    const char *e = getenv("TPB_GEMVK_KERNEL");
+    if (e == nullptr) return 0;
+    return e[0] == 'r' ? 1 : e[0] == 'w' ? 2 : 0;
+}
+
+template <int M>
+int launch_q6k_ring(tpb_handle_t h, cudaStream_t st, const KGemvParams &p, int stages, size_t act) {
+    const size_t smem = act + (size_t)stages * ((size_t)kRingRows * kQ6RowStage + 16) + 64;
+    int grid = (int)((p.rows + kRingRows - 1) / kRingRows);
+    if (grid > h->sm_count) grid = h->sm_count;
+    auto kern = q6k_gemv_ring_kernel<M>;
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, h->smem_optin, smem_set));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(grid), dim3(32 * (kRingRows + 1)), smem, st, p, stages));
+    return TPB_OK;
+}
+
 template <int M>
 int launch_q6k_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {
     constexpr int R = 2;
+    if constexpr (M <= 2) {
+        // the ring kernel for one or two activation rows (see launch_fmt_m), where at least three stages fit
+        const int force = k_kernel_override();
+        const size_t act_r = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 4 + (size_t)M * (p.cols / 16) * 4;
+        const size_t limit_r = (size_t)h->smem_optin - 1024;
+        const int s_r = act_r + 256 < limit_r ? (int)((limit_r - act_r - 256) / ((size_t)kRingRows * kQ6RowStage + 16)) : 0;
+        // measured (us, per-warp rings / ring): K = 17408 -> N = 5120 28.9 / 23.5, 32000 x 4096 34.1 / 27.7, but
+        // 17408 x 5120 22.2 / 27.8 and 8192 x 8192 14.9 / 15.6 at M = 1; at M = 2 4096 x 14336 19.4 / 15.9
+        const bool many_rows = p.rows > 10 * 16 * h->sm_count;
+        const bool pick = many_rows || p.cols >= (M == 1 ? 16384 : 8192);
+        if (s_r >= 3 && (force == 1 || (force == 0 && pick))) return launch_q6k_ring<M>(h, st, p, s_r > 12 ? 12 : s_r, act_r);
+    }
     constexpr int kStage = R * kQ6RowStage;
     const size_t limit = (size_t)h->smem_optin - 1024;
     const size_t act = (size_t)M * (p.cols / 64) * kActPairBytes + (size_t)M * p.nblk * 4 + (size_t)M * (p.cols / 16) * 4;
@@ -856,12 +1027,6 @@ int launch_fmt_ring(tpb_handle_t h, cudaStream_t st, KGemvParams p, int stages, 
     return TPB_OK;
 }
 
-// TPB_GEMVK_KERNEL=ring|warp forces one of the two kernels (read at every launch, for measurements).
-static int k_kernel_override() {
-    const char *e = getenv("TPB_GEMVK_KERNEL");
-    if (e == nullptr) return 0;
-    return e[0] == 'r' ? 1 : e[0] == 'w' ? 2 : 0;
-}
 
 template <int FMT, int M>
 int launch_fmt_m(tpb_handle_t h, cudaStream_t st, const KGemvParams &p) {

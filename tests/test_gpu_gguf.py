@@ -86,7 +86,7 @@ def test_gguf_gemv_config2_size(be, fmt):
     assert (err <= 2e-5 * bound(fmt, w[rows], rows.size, k, x) + 1e-6).all(), f"max err {err.max():.3e}"
 
 
-@pytest.mark.parametrize("fmt", ["q4_0", "iq4_nl", "q4_k", "q5_k"])
+@pytest.mark.parametrize("fmt", ["q4_0", "iq4_nl", "q4_k", "q5_k", "q6_k"])
 @pytest.mark.parametrize("m", [1, 2])
 @pytest.mark.parametrize("n,k", [(1, 256), (15, 5120), (16, 17408), (333, 17408), (2500, 1024), (40, 6144)])
 def test_gguf_gemv_ring_kernel_gives_the_per_warp_kernels_bits(be, fmt, m, n, k, monkeypatch):
