@@ -543,7 +543,8 @@ def run_ours(args, rank: int, local: int, world: int):
         parts = [("gemv", lambda: measure_gemv(be, peaks, 50, all_formats=True)),
                  ("dit", lambda: measure_dit(be, sync_all, reduce_max, rank, steps=8, agree=agree,
                                              names=("unfused_f32", "fused_f32", "fused_bf16_whole_batch",
-                                                    "fused_bf16_paired_mlp", "fused_bf16_with_attention"))),
+                                                    "fused_bf16_paired_mlp", "fused_bf16_grouped",
+                                                    "fused_bf16_with_attention"))),
                  ("dit_stream", lambda: measure_dit_stream(be, sync_all, reduce_max, rank, world, steps=3, agree=agree))]
         if world > 1:
             parts.append(("nsplit", lambda: measure_nsplit(be, args, rank, world, steps=20, agree=agree)))
@@ -593,10 +594,12 @@ DIT_VARIANTS = {
                                dict(mode="fused", bf16=True, whole=True)),
     "fused_bf16_paired_mlp": ("fused_bf16_whole_batch with the MLP's gate and up projections in one launch and the SiLU "
                               "gate in its epilogue", dict(mode="fused", bf16=True, whole=True, pair=True)),
+    "fused_bf16_grouped": ("fused_bf16_paired_mlp with the q, k, v and gate projections of a block in one launch",
+                           dict(mode="fused", bf16=True, whole=True, pair=True, group=True)),
     "linears_only": ("prep + GEMM launches only, one MLP pass over all rows", dict(mode="linears", whole=True)),
-    "fused_bf16_with_attention": ("fused_bf16_paired_mlp plus qk-norm, RoPE and softmax attention (24 heads x 128) in "
+    "fused_bf16_with_attention": ("fused_bf16_grouped plus qk-norm, RoPE and softmax attention (24 heads x 128) in "
                                   "every block: the whole block stack of a step",
-                                  dict(mode="fused", bf16=True, whole=True, attn=True, pair=True)),
+                                  dict(mode="fused", bf16=True, whole=True, attn=True, pair=True, group=True)),
 }
 
 
@@ -612,6 +615,8 @@ def _dit_runner(be, harness, w, x_list, mod, attn, spec, latents=1):
         kw["attn"] = attn
     if spec.get("pair"):
         kw["mlp_pair"] = True
+    if spec.get("group"):
+        kw["qkvg_group"] = True
     return lambda i: harness.dit_step_linears(be, w, x_list[i % len(x_list)], **kw)
 
 
@@ -649,7 +654,7 @@ def measure_dit(be, sync, reduce_max, rank, steps, names, agree=_same):
     # captured once into a CUDA graph and replayed (no host work per launch at all).
     host_side = {}
     for n in names:
-        if n not in ("fused_bf16_paired_mlp", "fused_bf16_with_attention"):
+        if n not in ("fused_bf16_grouped", "fused_bf16_with_attention"):
             continue
         fn = _dit_runner(be, harness, w, x_list, mod, attn, DIT_VARIANTS[n][1])
         entry = {}
@@ -708,7 +713,7 @@ def measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu
     from tensorpencil_b200 import harness, synth
     L = latents_per_gpu if latents_per_gpu else max(1, TOTAL_LATENTS // world)
     T = synth.DIT_TOKENS
-    names = ("fused_bf16_paired_mlp", "fused_bf16_with_attention")
+    names = ("fused_bf16_grouped", "fused_bf16_with_attention")
     res = {}
     x = mod = attn = None
     # On several GPUs the default route shares the host link: every rank pulls 1/world of each block
@@ -808,7 +813,7 @@ def run_mode_dit(args, rank, local, world, streamed: bool):
         out = measure_dit_stream(be, sync, reduce_max, rank, world, steps, latents_per_gpu=args.latents or None)
         if "skipped" in out:
             raise SystemExit(out["skipped"])
-        head = out["variants"]["fused_bf16_paired_mlp"]["s_per_step"]
+        head = out["variants"]["fused_bf16_grouped"]["s_per_step"]
         metric = "dit_int4_streamed_s_per_step"
     else:
         out = measure_dit(be, sync, reduce_max, rank, steps, tuple(DIT_VARIANTS))

@@ -146,12 +146,24 @@ int tpb_convrot_gemm_silu_pair(tpb_handle_t h, tpb_stream_t stream, void *y, int
                                const void *w_gate, const float *w_gate_scale, const void *w_up,
                                const float *w_up_scale, int w_bits, int64_t m, int64_t n, int64_t k);
 
+/* Up to four weights of the same shape multiplied with the same quantised activations in one launch:
+ * replaces the op{I8,I4}Gemm calls that follow one prep -- q, k, v and gate of a DiT block
+ * (src/models/dit_cuda.zig:473-478).  y[g] = dequant(q w[g]^T) exactly as tpb_convrot_gemm computes it, bit for
+ * bit; all outputs share y_dtype (f32 or bf16) and ldy.  The weights' tiles follow one another in one
+ * persistent kernel, so its pipeline fills and drains once instead of count times (4608 x 3072 x 3072, four
+ * weights: 4 x 36 us -> 131 us).  y, w and w_scale are host arrays of `count` device pointers (1 <= count <= 4).
+ * For w_bits = 4 the reservation (tpb_convrot_w4_reserve) must cover all weights: count * n x k elements.
+ * Problems too small for the two-CTA kernel run as `count` ordinary launches. */
+int tpb_convrot_gemm_group(tpb_handle_t h, tpb_stream_t stream, int count, void *const *y, int y_dtype, int64_t ldy,
+                           const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *const *w,
+                           const float *const *w_scale, int w_bits, int64_t m, int64_t n, int64_t k);
+
 /* INT4 weights run on the int8 tensor-core path: unless TPB_W4_FUSED=1 selects the kernel that
  * unpacks nibbles in shared memory, every int4 GEMM first widens its weight into a scratch
  * buffer the handle owns.  tpb_convrot_w4_reserve sizes that buffer for weights of up to n x k
  * elements (cudaMalloc; it may cudaFree a smaller one, which waits for the device).  Call it
  * once per handle, at set-up, outside any stream capture: the stream-ordered entry points
- * (tpb_convrot_gemm, tpb_convrot_linear, tpb_convrot_gemm_gated_add, tpb_convrot_gemm_silu_pair,
+ * (tpb_convrot_gemm, tpb_convrot_linear, tpb_convrot_gemm_gated_add, tpb_convrot_gemm_silu_pair, tpb_convrot_gemm_group,
  * the all-gather forms)
  * never allocate, and return TPB_ERR_STATE for an int4 weight larger than the reservation.
  * Replaces the reference's ensureDeviceBuffer growth of its backend scratch

@@ -221,6 +221,46 @@ class Backend {
                                          bits, (int64_t)m_, (int64_t)rows, (int64_t)cols_));
     }
 
+    // Up to four op{I8,I4}Gemm calls on the same prepped activations in one launch (q, k, v and gate of a block,
+    // dit_cuda.zig:473-478): ys[g][m][rows] = linear_g(prepped), f32, bit-identical to the separate calls.
+    void gemmGroup(int count, const DeviceBuffer *ys, const void *const *w_bytes, const float *const *w_scales, size_t rows,
+                   int bits = 8) {
+        if (bits_ != bits) throw Error(TPB_ERR_STATE, "gemmGroup must follow the matching prep");
+        if (count < 1 || count > 4) throw Error(TPB_ERR_INVALID_ARG, "gemmGroup takes 1 to 4 weights");
+        const size_t w_size = bits == 4 ? rows * cols_ / 2 : rows * cols_;
+        // every array must be resident at once: pin each until the call is enqueued
+        const void *hosts[8];
+        size_t sizes[8];
+        for (int g = 0; g < count; g++) {
+            hosts[2 * g] = w_bytes[g];
+            sizes[2 * g] = w_size;
+            hosts[2 * g + 1] = w_scales[g];
+            sizes[2 * g + 1] = rows * 4;
+        }
+        const void *dev[8];
+        int pinned = 0;
+        try {
+            for (; pinned < 2 * count; pinned++) dev[pinned] = cachedWeight(hosts[pinned], sizes[pinned], true);
+        } catch (...) {
+            for (int i = 0; i < pinned; i++) unpinWeight(hosts[i]);
+            throw;
+        }
+        for (int i = 0; i < 2 * count; i++) unpinWeight(hosts[i]);
+        if (bits == 4) reserveW4((size_t)count * rows, cols_);
+        void *y[4];
+        const void *w[4];
+        const float *sc[4];
+        for (int g = 0; g < count; g++) {
+            y[g] = ys[g].p;
+            w[g] = dev[2 * g];
+            sc[g] = static_cast<const float *>(dev[2 * g + 1]);
+        }
+        check(tpb_convrot_gemm_group(h_, stream_, count, y, TPB_F32, (int64_t)rows, static_cast<const int8_t *>(i8_x_.p),
+                                     static_cast<const float *>(i8_scale_.p),
+                                     bits == 4 ? static_cast<const int32_t *>(i8_sum_.p) : nullptr, w, sc, bits, (int64_t)m_,
+                                     (int64_t)rows, (int64_t)cols_));
+    }
+
     // ---- attention of the DiT block (dit_cuda.zig:479-489: qkNorm, rope, attn / opAttnTC) ----
     // q [seq][heads*hd], k / v [seq][kv_heads*hd] (f32), freqs = cos table [seq][hd/2] then, sin_off floats
     // later, the sin table; out [seq][heads*hd] f32.  head_dim 128, non-causal.  Unlike the reference's

@@ -38,6 +38,7 @@ SIGNATURES = {
     "tpb_convrot_linear": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i64, _i64, _i64]),
     "tpb_convrot_gemm_gated_add": (_i, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i64, _i64, _i64]),
     "tpb_convrot_gemm_silu_pair": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64]),
+    "tpb_convrot_gemm_group": (_i, [_vp, _vp, _i, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64]),
     "tpb_convrot_w4_reserve": (_i, [_vp, _i64, _i64]),
     "tpb_convrot_w4_expanded_bytes": (_sz, [_i64, _i64]),
     "tpb_convrot_w4_expand": (_i, [_vp, _vp, _vp, _i64, _i64, _vp]),

@@ -336,6 +336,26 @@ class Backend:
         self._check(rc)
         self.launches += 3 if w_bits == 4 else 1
 
+    def gemmGroup(self, ys, weights, scales, rows: int, w_bits: int = 8):
+        """Up to four op{I8,I4}Gemm calls on the same prepped activations in one launch (q, k, v and gate of a DiT
+        block, dit_cuda.zig:473-478): ys[g][m][rows] = linear_g(prepped), bit-identical to the separate calls.  The
+        outputs share dtype (f32 or bf16) and row stride."""
+        n = len(ys)
+        assert 1 <= n <= 4 and len(weights) == n and len(scales) == n and self.i8_bits == w_bits
+        assert all(y.dtype == ys[0].dtype and y.stride(-1) == 1 and y.stride(0) == ys[0].stride(0) for y in ys)
+        w_dev = [self.cachedWeight(a) if isinstance(a, np.ndarray) else a for a in weights]
+        s_dev = [self.cachedWeight(a) if isinstance(a, np.ndarray) else a for a in scales]
+        if w_bits == 4:
+            self.reserveW4(n * rows, self.i8_cols)
+        arr = C.c_void_p * n
+        rc = self.lib.tpb_convrot_gemm_group(self.h, self._stream(), n, arr(*[y.data_ptr() for y in ys]),
+                                             _TORCH_TO_TPB[ys[0].dtype], ys[0].stride(0), self.i8_x.data_ptr(),
+                                             self.i8_scale.data_ptr(), self.i8_sum.data_ptr() if w_bits == 4 else None,
+                                             arr(*[w.data_ptr() for w in w_dev]), arr(*[_ptr(a) for a in s_dev]),
+                                             w_bits, self.i8_m, rows, self.i8_cols)
+        self._check(rc)
+        self.launches += n + 1 if w_bits == 4 else 1
+
     def opI8Gemm(self, y: torch.Tensor, w_bytes, weight_scale, rows: int, c_h16: bool = False):
         """y[m][rows] = prepped @ W^T * act_scale[row] * weight_scale[col]
         (backend.zig:2484-2501).  The output type is y.dtype (f32 or bf16; int32

@@ -241,6 +241,23 @@ int tpb_convrot_gemm_silu_pair(tpb_handle_t h, tpb_stream_t stream, void *y, int
                                      w_up_scale, w_bits, m, n, k);
 }
 
+int tpb_convrot_gemm_group(tpb_handle_t h, tpb_stream_t stream, int count, void *const *y, int y_dtype, int64_t ldy,
+                           const int8_t *q, const float *act_scale, const int32_t *act_sum, const void *const *w,
+                           const float *const *w_scale, int w_bits, int64_t m, int64_t n, int64_t k) {
+    if (!h) return TPB_ERR_INVALID_ARG;
+    TPB_CHECK_ARG(h, count >= 1 && count <= 4, "gemm_group: 1 to 4 weights per call (got %d)", count);
+    TPB_CHECK_ARG(h, y && w && w_scale, "gemm_group: null pointer");
+    TPB_CHECK_ARG(h, y_dtype == TPB_F32 || y_dtype == TPB_BF16, "gemm_group: y_dtype must be f32 or bf16");
+    // each weight and output is checked as for the plain GEMM
+    for (int g = 0; g < count; g++) {
+        const int rc = tpb_convrot_gemm(h, nullptr, y[g], y_dtype, ldy, q, act_scale, act_sum, w[g], w_bits, w_scale[g], 0, n, k);
+        if (rc != TPB_OK) return rc;
+    }
+    TPB_CHECK_ARG(h, m >= 0 && m < (1ll << 31), "gemm_group: bad m");
+    if (m == 0) return TPB_OK;
+    return tpb_launch_gemm_group(h, (cudaStream_t)stream, count, y, y_dtype, ldy, q, act_scale, w, w_scale, w_bits, m, n, k);
+}
+
 int tpb_q8_1_quantize(tpb_handle_t h, tpb_stream_t stream, const float *x, int64_t n_elems,
                       void *xq) {
     if (!h) return TPB_ERR_INVALID_ARG;

@@ -33,14 +33,25 @@ constexpr int kStaging2 = 4 * 2 * 4096;
 constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
 constexpr int kTmemCols2 = 2 * BN2;
 
-// PAIR: the weight tile's two halves come from two different weights (tma_b: the leader's 128 rows,
+// Up to four weights of the same shape multiplied with the same activations in one launch (PAIR == 2): the
+// tiles of weight g follow those of weight g - 1 in the persistent loop.  Weight 0 is described by the
+// kernel's own tma_b / tma_y / p.w_scale, weights 1.. by this block.
+struct GemmGroup {
+    CUtensorMap b[3];
+    CUtensorMap y[3];
+    const float *w_scale[3];
+    int count;   // weights in all, 1..4
+};
+
+// PAIR == 1: the weight tile's two halves come from two different weights (tma_b: the leader's 128 rows,
 // tma_b2: the peer's), both for the same 128 output columns, and the epilogue combines the two
-// projections into silu(first) * second (epilogue_pair).
+// projections into silu(first) * second (epilogue_pair).  PAIR == 2: several weights, see GemmGroup.
 template <int OUT, int PEERS, int PAIR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_y,
-                     const GemmParams p, const int b_unsigned) {
+                     const GemmParams p, const int b_unsigned, const __grid_constant__ GemmGroup grp) {
+    constexpr bool MULTI = PAIR == 2;
     constexpr int S = kStages2;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -62,9 +73,10 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     const int n_pairs = gridDim.x >> 1;
 
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM);  // 256-row tiles
-    constexpr int kTileN = PAIR ? BN2 / 2 : BN2;   // output columns per tile
+    constexpr int kTileN = PAIR == 1 ? BN2 / 2 : BN2;   // output columns per tile
     const int n_tiles = (p.n + kTileN - 1) / kTileN;
-    const int num_tiles = m_tiles * n_tiles;
+    const int tiles_per_weight = m_tiles * n_tiles;
+    const int num_tiles = MULTI ? tiles_per_weight * grp.count : tiles_per_weight;
     const int k_blocks = p.k / BK;
 
     if (threadIdx.x == 0) {
@@ -102,9 +114,11 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             uint32_t it = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
-                const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
-                const int n0 = PAIR ? (tile / m_tiles) * kTileN : (tile / m_tiles) * BN2 + (int)rank * (BN2 / 2);
-                const CUtensorMap *bmap = (PAIR && rank == 1) ? &tma_b2 : &tma_b;
+                const int wg = MULTI ? tile / tiles_per_weight : 0;   // which weight
+                const int wt = MULTI ? tile - wg * tiles_per_weight : tile;
+                const int m0 = (wt % m_tiles) * (2 * BM) + (int)rank * BM;
+                const int n0 = PAIR == 1 ? (wt / m_tiles) * kTileN : (wt / m_tiles) * BN2 + (int)rank * (BN2 / 2);
+                const CUtensorMap *bmap = (PAIR == 1 && rank == 1) ? &tma_b2 : (MULTI && wg > 0) ? &grp.b[wg - 1] : &tma_b;
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
@@ -165,8 +179,12 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         uint32_t t_it = 0;
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, t_it++) {
-            const int m0 = (tile % m_tiles) * (2 * BM) + (int)rank * BM;
-            const int n0 = (tile / m_tiles) * kTileN;
+            const int wg = MULTI ? tile / tiles_per_weight : 0;
+            const int wt = MULTI ? tile - wg * tiles_per_weight : tile;
+            const int m0 = (wt % m_tiles) * (2 * BM) + (int)rank * BM;
+            const int n0 = (wt / m_tiles) * kTileN;
+            const CUtensorMap *ymap = (MULTI && wg > 0) ? &grp.y[wg - 1] : &tma_y;
+            const float *w_scale = (MULTI && wg > 0) ? grp.w_scale[wg - 1] : p.w_scale;
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
             if (PEERS == 3) {
@@ -193,11 +211,11 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             if (OUT != OUT_S32 && row_ok) as = __ldcg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldcg(p.act_sum + row);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
-            if (PAIR) {
-                if constexpr (PAIR != 0 && (OUT == OUT_F32 || OUT == OUT_BF16))
+            if (PAIR == 1) {
+                if constexpr (PAIR == 1 && (OUT == OUT_F32 || OUT == OUT_BF16))
                     epilogue_pair<OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, lane);
             } else if (!(p.ablate & 4)) {
-                epilogue_tile<BN2, OUT, PEERS>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane);
+                epilogue_tile<BN2, OUT, PEERS>(t_row, p, ymap, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane, w_scale);
             }
             tc_fence_before();
             __syncwarp();
@@ -229,6 +247,39 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 
 namespace {
 
+const GemmGroup kNoGroup = {};
+
+// Weights w[0 .. count-1] of one shape times the same q, outputs y[0 .. count-1] (same dtype and ldy).
+template <int OUT>
+int launch_group(tpb_handle_t h, cudaStream_t st, const GemmParams &p0, const int8_t *q, int count, const void *const *w8,
+                 const float *const *w_scale, void *const *y) {
+    CUtensorMap ma, mb, my;
+    GemmGroup grp = {};
+    grp.count = count;
+    int rc = make_kmajor_map(h, &ma, q, p0.m, p0.k, BM);
+    if (rc != TPB_OK) return rc;
+    GemmParams p = p0;
+    for (int g = 0; g < count; g++) {
+        p.y = y[g];
+        rc = make_kmajor_map(h, g == 0 ? &mb : &grp.b[g - 1], w8[g], p.n, p.k, BN2 / 2);
+        if (rc != TPB_OK) return rc;
+        rc = make_out_map<OUT>(h, g == 0 ? &my : &grp.y[g - 1], p);
+        if (rc != TPB_OK) return rc;
+        if (g > 0) grp.w_scale[g - 1] = w_scale[g];
+    }
+    p.y = y[0];
+    p.w_scale = w_scale[0];
+    auto kern = convrot_gemm2_kernel<OUT, 0, 2>;
+    static tpb_per_device_once smem_set;
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
+    const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
+    const int tiles = m_tiles * n_tiles * count;
+    const int max_pairs = h->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, 0, grp));
+    return TPB_OK;
+}
+
 template <int OUT, int PEERS>
 int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
@@ -246,7 +297,7 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, b_unsigned ? 1 : 0));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, b_unsigned ? 1 : 0, kNoGroup));
     return TPB_OK;
 }
 
@@ -269,7 +320,7 @@ int launch_silu_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb2, my, p, 0));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb2, my, p, 0, kNoGroup));
     return TPB_OK;
 }
 
@@ -296,6 +347,13 @@ int tpb_launch_gemm2_silu_pair(tpb_handle_t h, cudaStream_t st, const tpb_gemm::
     if (y_dtype == TPB_F32) return launch_silu_pair<OUT_F32>(h, st, p, q, w_gate, w_up);
     if (y_dtype == TPB_BF16) return launch_silu_pair<OUT_BF16>(h, st, p, q, w_gate, w_up);
     return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm_silu_pair: y_dtype must be f32 or bf16");
+}
+
+int tpb_launch_gemm2_group(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype, const int8_t *q,
+                           int count, const void *const *w8, const float *const *w_scale, void *const *y) {
+    if (y_dtype == TPB_F32) return launch_group<OUT_F32>(h, st, p, q, count, w8, w_scale, y);
+    if (y_dtype == TPB_BF16) return launch_group<OUT_BF16>(h, st, p, q, count, w8, w_scale, y);
+    return tpb_fail(h, TPB_ERR_INVALID_ARG, "gemm_group: y_dtype must be f32 or bf16");
 }
 
 int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,

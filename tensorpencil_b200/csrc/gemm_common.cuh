@@ -290,7 +290,9 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 template <int BN, int OUT, int PEERS = 0>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
                                               uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
-                                              int row0, int n0, float as, int corr, int lane) {
+                                              int row0, int n0, float as, int corr, int lane,
+                                              const float *w_scale_in = nullptr) {
+    const float *w_scale = w_scale_in != nullptr ? w_scale_in : p.w_scale;   // the weight's scales (several weights per launch)
     uint32_t ra[32], rb[32];
     tc_ld_32x32(t_row, ra);
     // Gated residual: the 32 x 32 pieces of the residual stream this warp updates, read kPre pieces ahead of
@@ -329,7 +331,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
 #pragma unroll
         for (int g = 0; g < 8; g++) {
             w[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (OUT != OUT_S32 && col0 + 4 * g < p.n) w[g] = __ldg(reinterpret_cast<const float4 *>(p.w_scale + col0 + 4 * g));
+            if (OUT != OUT_S32 && col0 + 4 * g < p.n) w[g] = __ldg(reinterpret_cast<const float4 *>(w_scale + col0 + 4 * g));
             if (PEERS == 3) {
                 gta[g] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (col0 + 4 * g < p.n) gta[g] = __ldcg(reinterpret_cast<const float4 *>(p.gate + col0 + 4 * g));

@@ -23,6 +23,8 @@
 #include "gemm_common.cuh"
 
 bool tpb_gemm2_wants(tpb_handle_t h, int64_t m, int64_t n);
+int tpb_launch_gemm2_group(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype, const int8_t *q,
+                           int count, const void *const *w8, const float *const *w_scale, void *const *y);
 int tpb_launch_gemm2_silu_pair(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
                                const int8_t *q, const void *w_gate, const void *w_up);
 int tpb_launch_gemm2(tpb_handle_t h, cudaStream_t st, const tpb_gemm::GemmParams &p, int y_dtype,
@@ -342,4 +344,50 @@ int tpb_launch_gemm_silu_pair(tpb_handle_t h, cudaStream_t st, void *y, int y_dt
         u8 = buf + (size_t)n * (size_t)k;
     }
     return tpb_launch_gemm2_silu_pair(h, st, p, y_dtype, q, g8, u8);
+}
+
+// Up to four weights of one shape times the same activations in one launch of the two-CTA kernel (the q, k, v and
+// gate projections of a DiT block): their tiles follow one another in its persistent loop, so the pipeline fills
+// and drains once instead of once per weight.  Small problems, which the one-CTA kernel takes, run one by one.
+int tpb_launch_gemm_group(tpb_handle_t h, cudaStream_t st, int count, void *const *y, int y_dtype, int64_t ldy,
+                          const int8_t *q, const float *act_scale, const void *const *w, const float *const *w_scale,
+                          int w_bits, int64_t m, int64_t n, int64_t k) {
+    if (h->opt_gemm_one_cta || !tpb_gemm2_wants(h, m, n)) {
+        for (int g = 0; g < count; g++) {
+            const int rc = tpb_launch_gemm(h, st, y[g], y_dtype, ldy, q, act_scale, nullptr, w[g], w_bits, w_scale[g], m, n, k,
+                                           nullptr, 0, nullptr, nullptr);
+            if (rc != TPB_OK) return rc;
+        }
+        return TPB_OK;
+    }
+    GemmParams p;
+    p.mc_y = nullptr;
+    p.gate = nullptr;
+    p.ablate = 0;
+    p.n_peers = 0;
+    for (int i = 0; i < kMaxPeers; i++) p.peer_y[i] = nullptr;
+    p.y = y[0];
+    p.ldy = ldy;
+    p.act_scale = act_scale;
+    p.w_scale = w_scale[0];
+    p.act_sum = nullptr;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.status = h->d_status;
+    const void *w8[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (int g = 0; g < count; g++) w8[g] = w[g];
+    if (w_bits == 4) {
+        // every weight widened into the reserved scratch, one after the other
+        int8_t *buf = nullptr;
+        int rc = tpb_w4_scratch(h, (int64_t)count * n, k, &buf);
+        if (rc != TPB_OK) return rc;
+        for (int g = 0; g < count; g++) {
+            int8_t *dst = buf + (size_t)g * (size_t)n * (size_t)k;
+            rc = tpb_launch_w4_expand(h, st, w[g], n, k, dst);
+            if (rc != TPB_OK) return rc;
+            w8[g] = dst;
+        }
+    }
+    return tpb_launch_gemm2_group(h, st, p, y_dtype, q, count, w8, w_scale, y);
 }

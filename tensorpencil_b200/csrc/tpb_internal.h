@@ -139,6 +139,9 @@ int tpb_launch_w4_expand(tpb_handle_t h, cudaStream_t st, const void *w4, int64_
 int tpb_launch_gemm_silu_pair(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy, const int8_t *q,
                               const float *act_scale, const void *w_gate, const float *w_gate_scale, const void *w_up,
                               const float *w_up_scale, int w_bits, int64_t m, int64_t n, int64_t k);
+int tpb_launch_gemm_group(tpb_handle_t h, cudaStream_t st, int count, void *const *y, int y_dtype, int64_t ldy,
+                          const int8_t *q, const float *act_scale, const void *const *w, const float *const *w_scale,
+                          int w_bits, int64_t m, int64_t n, int64_t k);
 int tpb_launch_gemm(tpb_handle_t h, cudaStream_t st, void *y, int y_dtype, int64_t ldy,
                     const int8_t *q, const float *act_scale, const int32_t *act_sum,
                     const void *w, int w_bits, const float *w_scale, int64_t m, int64_t n,

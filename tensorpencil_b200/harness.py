@@ -104,7 +104,8 @@ def dit_modulation(be, blocks: int, hidden: int, seed: int = 7) -> torch.Tensor:
 def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32,
                      mlp_tile: int = MLP_TILE, mode: str = "linears",
                      mod: Optional[torch.Tensor] = None, eps: float = 1e-5,
-                     attn: Optional[dict] = None, latents: int = 1, mlp_pair: bool = False) -> torch.Tensor:
+                     attn: Optional[dict] = None, latents: int = 1, mlp_pair: bool = False,
+                     qkvg_group: bool = False) -> torch.Tensor:
     """One step of the block stack on x [latents * tokens][hidden] (f32, updated in place).
 
     mode:
@@ -131,7 +132,8 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
 
     mlp_pair (mode "fused"): the MLP's gate and up projections run as one launch whose epilogue
     applies the SiLU gate (Backend.gemmSiluPair), followed by a plain prep, instead of two GEMMs and
-    the SiLU-gated prep."""
+    the SiLU-gated prep.  qkvg_group: the q, k, v and gate projections of a block in one launch
+    (Backend.gemmGroup) instead of four."""
     bits, hid, mlp = w.bits, w.hidden, w.mlp
     prep = be.opI8Prep if bits == 8 else be.opI4Prep
     gemm = (lambda y, wt, n: be.opI8Gemm(y, wt[0], wt[1], n)) if bits == 8 else \
@@ -179,10 +181,15 @@ def dit_step_linears(be, w: DitWeights, x: torch.Tensor, out_dtype=torch.float32
             prep(t1, m, hid)
         else:
             prep(x, m, hid)
-        gemm(q, wb["wq"], hid)
-        gemm(k, wb["wk"], hid)
-        gemm(v, wb["wv"], hid)
-        gemm(g, wb["gate"], hid)
+        if qkvg_group:
+            # the four projections of one prep in one launch (bit-identical to the four calls)
+            be.gemmGroup([q, k, v, g], [wb[n][0] for n in ("wq", "wk", "wv", "gate")],
+                         [wb[n][1] for n in ("wq", "wk", "wv", "gate")], hid, bits)
+        else:
+            gemm(q, wb["wq"], hid)
+            gemm(k, wb["wk"], hid)
+            gemm(v, wb["wv"], hid)
+            gemm(g, wb["gate"], hid)
         a = v                                              # without attn: v stands in for its output
         if attn is not None and mode != "linears":
             for l in range(latents):

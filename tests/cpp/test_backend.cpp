@@ -323,13 +323,16 @@ static void dit_block(tpb::Backend &be, unsigned seed) {
     EXPECT(std::sqrt(fnum / fden) < 1e-4, "dit block, fused against the reference sequence: relative error %g", std::sqrt(fnum / fden));
 
     // ---- and with the MLP's gate and up projections in one launch, the SiLU gate in its epilogue, then a
-    // plain prep: the bits of the fused block above (f32: the same arithmetic in the same order) ----
+    // plain prep, and q, k, v and gate in one launch too: the bits of the fused block above (f32: the same
+    // arithmetic in the same order) ----
     be.tensorUpload(x_d, x.data(), x.size() * 4);
     be.prepRmsMod(x_d, mv_d, seq, F, 0, F, eps);
-    lin(q_d, wq);
-    lin(k_d, wk);
-    lin(v_d, wv);
-    lin(g_d, gate);
+    {
+        const tpb::DeviceBuffer ys[4] = {q_d, k_d, v_d, g_d};
+        const void *ws[4] = {wq.w.data(), wk.w.data(), wv.w.data(), gate.w.data()};
+        const float *sc[4] = {wq.ws.data(), wk.ws.data(), wv.ws.data(), gate.ws.data()};
+        be.gemmGroup(4, ys, ws, sc, F);
+    }
     be.attention(q_d, k_d, v_d, attn_d, qn_d, kn_d, freqs_d, sin_off, seq, heads, heads, hd, eps, attn_scale);
     be.prepSigmoidMul(attn_d, g_d, seq, F);
     be.gemmGatedAdd(x_d, wo.w.data(), wo.ws.data(), F, mv_d, 2 * F);
@@ -341,7 +344,7 @@ static void dit_block(tpb::Backend &be, unsigned seed) {
     be.tensorDownload(x_d, paired.data(), paired.size() * 4);
     size_t pair_diff = 0;
     for (size_t i = 0; i < paired.size(); i++) pair_diff += std::memcmp(&paired[i], &fused[i], 4) != 0;
-    EXPECT(pair_diff == 0, "dit block, paired MLP against the fused block: %zu of %zu values differ", pair_diff, paired.size());
+    EXPECT(pair_diff == 0, "dit block, paired MLP and grouped projections against the fused block: %zu of %zu values differ", pair_diff, paired.size());
 
     double num = 0, den = 0, moved = 0;
     for (size_t i = 0; i < got.size(); i++) {

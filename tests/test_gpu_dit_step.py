@@ -67,11 +67,11 @@ def rel(a, b):
     return float(np.linalg.norm(a - b) / np.linalg.norm(b))
 
 
-def run(setup, mode, dtype, attn, mlp_tile, mlp_pair=False):
+def run(setup, mode, dtype, attn, mlp_tile, mlp_pair=False, qkvg_group=False):
     be, harness, w, mod, x0, _ = setup
     x = torch.from_numpy(x0.copy()).cuda()
     out = harness.dit_step_linears(be, w, x, out_dtype=dtype, mode=mode, mod=mod, mlp_tile=mlp_tile, attn=attn,
-                                   mlp_pair=mlp_pair)
+                                   mlp_pair=mlp_pair, qkvg_group=qkvg_group)
     be.status_poll()
     return out.float().cpu().numpy()
 
@@ -91,6 +91,10 @@ def test_fused_sequence_matches_reference_sequence(setup):
     # the MLP's gate and up projections in one launch with the SiLU gate in its epilogue
     assert rel(run(setup, "fused", torch.float32, None, 128, mlp_pair=True), ref) < 1e-4
     assert rel(run(setup, "fused", torch.bfloat16, None, TOKENS, mlp_pair=True), ref) < 3e-2
+    # q, k, v and gate in one launch: the same bits as four launches, so the whole step is identical
+    for dt in (torch.float32, torch.bfloat16):
+        assert np.array_equal(run(setup, "fused", dt, None, TOKENS, mlp_pair=True, qkvg_group=True),
+                              run(setup, "fused", dt, None, TOKENS, mlp_pair=True))
 
 
 def test_sequence_with_attention_matches_oracle(setup):

@@ -91,9 +91,10 @@ def test_full_size_block_stack_matches_oracle_on_sampled_rows(be, bits):
     rows = sample_rows(TOKENS)
     want = oracle_stack(w.dev, bits, mod, x0[rows])
 
-    def run(mode, dtype, tile, pair=False):
+    def run(mode, dtype, tile, pair=False, group=False):
         x = torch.from_numpy(x0.copy()).cuda()
-        out = harness.dit_step_linears(be, w, x, out_dtype=dtype, mode=mode, mod=mod, mlp_tile=tile, mlp_pair=pair)
+        out = harness.dit_step_linears(be, w, x, out_dtype=dtype, mode=mode, mod=mod, mlp_tile=tile, mlp_pair=pair,
+                                       qkvg_group=group)
         be.status_poll()
         return out[torch.from_numpy(rows).cuda()].float().cpu().numpy()
 
@@ -107,7 +108,10 @@ def test_full_size_block_stack_matches_oracle_on_sampled_rows(be, bits):
     # gate / up projections and the SiLU gate in one launch (f32: the same bits as three steps up to the
     # quantiser's step function further down the stack; bf16: one rounding fewer than the chain above)
     check_rows(run("fused", torch.float32, TOKENS, pair=True), unfused, 1e-5, overall, "paired MLP, f32, vs unfused")
-    check_rows(run("fused", torch.bfloat16, TOKENS, pair=True), unfused, 6e-2, 6e-2, "paired MLP, bf16, vs f32")
+    paired16 = run("fused", torch.bfloat16, TOKENS, pair=True)
+    check_rows(paired16, unfused, 6e-2, 6e-2, "paired MLP, bf16, vs f32")
+    # q, k, v and gate in one launch: bit-identical to four launches at the full size, both weight widths
+    assert np.array_equal(run("fused", torch.bfloat16, TOKENS, pair=True, group=True), paired16)
     w.close()
 
 

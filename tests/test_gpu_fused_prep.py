@@ -247,3 +247,57 @@ def test_gemm_with_silu_pair_into_a_wider_buffer_and_bad_arguments(be):
                              wg.data_ptr(), sg.data_ptr(), w2, su.data_ptr(), 8, m, n, k)
     assert L.tpb_convrot_gemm_silu_pair(*args(_lib.TPB_S32, wu.data_ptr())) == _lib.TPB_ERR_INVALID_ARG   # raw sums make no sense here
     assert L.tpb_convrot_gemm_silu_pair(*args(_lib.TPB_F32, None)) == _lib.TPB_ERR_INVALID_ARG            # second weight missing
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("count", [1, 2, 3, 4])
+@pytest.mark.parametrize("m,n,k", [(2048, 3072, 512), (2500, 2064, 256), (300, 512, 256)])
+def test_gemm_group_is_bit_identical_to_separate_gemms(be, bits, count, m, n, k):
+    """Several weights of one shape on the same prepped activations in one launch (the q, k, v and gate
+    projections of a block): every output equals the separate GEMM's, bit for bit, f32 and bf16 -- on a
+    problem the two-CTA kernel takes, one with ragged edges, and one small enough for the one-by-one path."""
+    from tensorpencil_b200 import synth
+    cs = [synth.convrot_linear(m, n, k, bits, seed=71 + 3 * g + m) for g in range(count)]
+    key = "w_i8" if bits == 8 else "w_packed"
+    ws = [dev(c[key]) for c in cs]
+    sc = [dev(c["w_scale"]) for c in cs]
+    be._prep(dev(cs[0]["x"]), m, k, bits)
+    for dt in (torch.float32, torch.bfloat16):
+        want = []
+        for g in range(count):
+            y = torch.empty((m, n), dtype=dt, device="cuda")
+            be._gemm(y, ws[g], sc[g], n, bits)
+            want.append(y)
+        got = [torch.full((m, n), 3.0, dtype=dt, device="cuda") for _ in range(count)]
+        be.gemmGroup(got, ws, sc, n, bits)
+        be.status_poll()
+        for g in range(count):
+            assert torch.equal(got[g], want[g]), f"weight {g}, {dt}"
+
+
+def test_gemm_group_into_wider_buffers_and_bad_arguments(be):
+    from tensorpencil_b200 import synth
+    m, n, k = 2048, 3072, 256
+    cs = [synth.convrot_linear(m, n, k, 8, seed=81 + g) for g in range(2)]
+    ws, sc = [dev(c["w_i8"]) for c in cs], [dev(c["w_scale"]) for c in cs]
+    be._prep(dev(cs[0]["x"]), m, k, 8)
+    wide = [torch.full((m, n + 128), -7.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    be.gemmGroup([t[:, :n] for t in wide], ws, sc, n, 8)         # ldy = n + 128
+    tight = [torch.empty((m, n), dtype=torch.float32, device="cuda") for _ in range(2)]
+    be.gemmGroup(tight, ws, sc, n, 8)
+    be.status_poll()
+    for g in range(2):
+        assert torch.equal(wide[g][:, :n], tight[g]) and bool((wide[g][:, n:] == -7.0).all())
+    import ctypes as C
+    L = be.lib
+    arr = C.c_void_p * 2
+    ys, wp, sp = arr(*[t.data_ptr() for t in tight]), arr(*[w.data_ptr() for w in ws]), arr(*[t.data_ptr() for t in sc])
+    call = lambda cnt, y_dt, y_, w_: L.tpb_convrot_gemm_group(be.h, None, cnt, y_, y_dt, n, be.i8_x.data_ptr(),
+                                                              be.i8_scale.data_ptr(), None, w_, sp, 8, m, n, k)
+    assert call(2, _lib.TPB_F32, ys, wp) == _lib.TPB_OK
+    assert call(0, _lib.TPB_F32, ys, wp) == _lib.TPB_ERR_INVALID_ARG
+    assert call(5, _lib.TPB_F32, ys, wp) == _lib.TPB_ERR_INVALID_ARG
+    assert call(2, _lib.TPB_S32, ys, wp) == _lib.TPB_ERR_INVALID_ARG          # dequantised outputs only
+    assert call(2, _lib.TPB_F32, ys, arr(ws[0].data_ptr(), None)) == _lib.TPB_ERR_INVALID_ARG   # a weight missing
+    assert call(2, _lib.TPB_F32, None, wp) == _lib.TPB_ERR_INVALID_ARG
+    be.status_poll()
