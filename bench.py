@@ -1298,7 +1298,7 @@ def run_mode_one_kernel(args, local):
         attn = {"q_norm": qn, "k_norm": kn, "cos": cos, "sin": sin, "heads": synth.DIT_HIDDEN // 128}
         for _ in range(2):
             harness.dit_step_linears(be, w, x, out_dtype=torch.bfloat16, mode="fused", mod=mod, mlp_tile=T, attn=attn,
-                                     mlp_pair=True)
+                                     mlp_pair=True, qkvg_group=True)
         reps = 2
     elif case == "attn":
         seq, heads = 4608, 24
