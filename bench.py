@@ -1182,8 +1182,8 @@ def run_mode_attn(args, local):
 
 
 def run_mode_one_kernel(args, local):
-    """Launches one kernel of the path a few times through the C ABI -- the small,
-    self-ending command the ncu captures under profiles/ are taken from."""
+    """Launches one kernel of the path a few times through the C ABI -- a small,
+    self-ending command to run under a profiler."""
     import torch
     from tensorpencil_b200 import harness
     from tensorpencil_b200.backend import Backend
