@@ -15,7 +15,8 @@
 //           issues every MMA and the tcgen05.commit arrivals, one to its own
 //           barrier and one to the peer's (plain commits to a cluster address,
 //           no multicast qualifier anywhere in this file).
-//   warps 2..5  epilogue for this CTA's 128 rows, as in the one-CTA kernel.
+//   warps 2..5  epilogue for this CTA's 128 rows, as in the one-CTA kernel (warps 2..9 in the gated-residual
+//           mode at short K: see EW below).
 // Every mbarrier wait is bounded; both CTAs always run the same collective
 // steps (cluster barriers, TMEM alloc/dealloc) whatever happened in between.
 #include "gemm_common.cuh"
@@ -28,9 +29,15 @@ constexpr int BN2 = 256;                       // tile width (UMMA N)
 constexpr int kStageA = BM * BK;               // 16 KB: this CTA's 128 rows of q
 constexpr int kStageB = (BN2 / 2) * BK;        // 16 KB: this CTA's half of the weight tile
 constexpr int kStage2 = kStageA + kStageB;
-constexpr int kStages2 = 6;
-constexpr int kStaging2 = 4 * 2 * 4096;
-constexpr int kSmem2 = kStages2 * kStage2 + kStaging2 + 1024 + 256;
+// Epilogue warps per CTA (template parameter EW): four (one per 32-lane quarter of tensor memory, all 256 columns
+// each), or eight -- two warps per quarter, 128 columns each -- for the gated-residual mode at short K, where the
+// epilogue, which reads the residual tile it updates, sets the pace (K = 3072: 56 -> 51 us).  Their staging
+// buffers take the place of one operand stage, which costs a long-K GEMM more than the epilogue gains
+// (K = 12288: 131 -> 141 us), so those keep four.
+constexpr int stages2(int ew) { return ew == 8 ? 5 : 6; }
+constexpr int staging2(int ew) { return ew * 2 * 4096; }
+constexpr int smem2(int ew) { return stages2(ew) * kStage2 + staging2(ew) + 1024 + 256; }
+constexpr int threads2(int ew) { return 64 + 32 * ew; }
 constexpr int kTmemCols2 = 2 * BN2;
 
 // Up to four weights of the same shape multiplied with the same activations in one launch (PAIR == 2): the
@@ -46,13 +53,16 @@ struct GemmGroup {
 // PAIR == 1: the weight tile's two halves come from two different weights (tma_b: the leader's 128 rows,
 // tma_b2: the peer's), both for the same 128 output columns, and the epilogue combines the two
 // projections into silu(first) * second (epilogue_pair).  PAIR == 2: several weights, see GemmGroup.
-template <int OUT, int PEERS, int PAIR>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <int OUT, int PEERS, int PAIR, int EW = 4>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads2(EW), 1)
 convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_y,
                      const GemmParams p, const int b_unsigned, const __grid_constant__ GemmGroup grp) {
     constexpr bool MULTI = PAIR == 2;
-    constexpr int S = kStages2;
+    constexpr int S = stages2(EW);
+    constexpr int kEpiWarps = EW;
+    constexpr int kStaging2 = staging2(EW);
+    constexpr int kEpiCols = BN2 * 4 / kEpiWarps;   // columns of a tile one epilogue warp handles
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -86,7 +96,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+            mbar_init(tempty_bar(a), 2 * kEpiWarps);  // the epilogue warps of both CTAs of the pair
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -172,6 +182,8 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     } else {
         // ---------------- epilogue (both CTAs, own 128 rows) ----------------
         const int quarter = warp & 3;
+        const int chalf = (kEpiWarps == 8) ? (warp - 2) >> 2 : 0;   // which 128 columns of the tile (eight warps)
+        const int c_off = chalf * kEpiCols;
         const uint32_t stg = stg_base + (uint32_t)(warp - 2) * 8192u;
         const uint32_t my_row_off = (uint32_t)lane * 128u;
         const uint32_t sw = (uint32_t)(lane & 7);
@@ -188,15 +200,15 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             const int acc = t_it & 1;
             const uint32_t acc_ph = (t_it >> 1) & 1u;
             if (PEERS == 3) {
-                // gated residual: ask for this warp's 32 x 256 piece of the residual stream (a lane's row, eight
+                // gated residual: ask for this warp's 32 rows x 128 columns of the residual stream (a lane's row, four
                 // lines) to be brought into L2 while the accumulators are still being produced.  Asking a whole
                 // tile earlier was measured slower (m 4608, n 12288, k 3072: 202 us against 180 us).
                 const int prow = m0 + quarter * 32 + lane;
                 if (prow < p.m) {
-                    const float *xp = static_cast<const float *>(p.y) + (size_t)prow * (size_t)p.ldy + n0;
+                    const float *xp = static_cast<const float *>(p.y) + (size_t)prow * (size_t)p.ldy + n0 + c_off;
 #pragma unroll
-                    for (int i = 0; i < BN2 / 32; i++)
-                        if (n0 + 32 * i < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(xp + 32 * i));
+                    for (int i = 0; i < kEpiCols / 32; i++)
+                        if (n0 + c_off + 32 * i < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(xp + 32 * i));
                 }
             }
             ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, (3u << 24) | (rank << 8) | acc, true);
@@ -210,12 +222,12 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             int corr = 0;
             if (OUT != OUT_S32 && row_ok) as = __ldcg(p.act_scale + row);
             if (p.act_sum != nullptr && row_ok) corr = 8 * __ldcg(p.act_sum + row);
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2 + c_off);
             if (PAIR == 1) {
                 if constexpr (PAIR == 1 && (OUT == OUT_F32 || OUT == OUT_BF16))
                     epilogue_pair<OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, lane);
             } else if (!(p.ablate & 4)) {
-                epilogue_tile<BN2, OUT, PEERS>(t_row, p, ymap, stg, my_row_off, sw, n_store, row0, n0, as, corr, lane, w_scale);
+                epilogue_tile<kEpiCols, OUT, PEERS, EW == 8>(t_row, p, ymap, stg, my_row_off, sw, n_store, row0, n0 + c_off, as, corr, lane, w_scale);
             }
             tc_fence_before();
             __syncwarp();
@@ -271,16 +283,16 @@ int launch_group(tpb_handle_t h, cudaStream_t st, const GemmParams &p0, const in
     p.w_scale = w_scale[0];
     auto kern = convrot_gemm2_kernel<OUT, 0, 2>;
     static tpb_per_device_once smem_set;
-    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, smem2(4), smem_set));
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
     const int tiles = m_tiles * n_tiles * count;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, 0, grp));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(threads2(4)), smem2(4), st, ma, mb, mb, my, p, 0, grp));
     return TPB_OK;
 }
 
-template <int OUT, int PEERS>
+template <int OUT, int PEERS, int EW = 4>
 int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
     CUtensorMap ma, mb, my;
@@ -290,14 +302,14 @@ int launch_pair_p(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const in
     if (rc != TPB_OK) return rc;
     rc = make_out_map<OUT>(h, &my, p);
     if (rc != TPB_OK) return rc;
-    auto kern = convrot_gemm2_kernel<OUT, PEERS, 0>;
+    auto kern = convrot_gemm2_kernel<OUT, PEERS, 0, EW>;
     static tpb_per_device_once smem_set;   // per instantiation
-    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, smem2(EW), smem_set));
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 - 1) / BN2;
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb, my, p, b_unsigned ? 1 : 0, kNoGroup));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(threads2(EW)), smem2(EW), st, ma, mb, mb, my, p, b_unsigned ? 1 : 0, kNoGroup));
     return TPB_OK;
 }
 
@@ -315,19 +327,21 @@ int launch_silu_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const
     if (rc != TPB_OK) return rc;
     auto kern = convrot_gemm2_kernel<OUT, 0, 1>;
     static tpb_per_device_once smem_set;
-    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, kSmem2, smem_set));
+    TPB_CUDA(h, tpb_set_max_smem_once(h, kern, smem2(4), smem_set));
     const int m_tiles = (p.m + 2 * BM - 1) / (2 * BM), n_tiles = (p.n + BN2 / 2 - 1) / (BN2 / 2);
     const int tiles = m_tiles * n_tiles;
     const int max_pairs = h->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), kSmem2, st, ma, mb, mb2, my, p, 0, kNoGroup));
+    TPB_CUDA(h, tpb_launch_pdl(kern, dim3(2 * pairs), dim3(threads2(4)), smem2(4), st, ma, mb, mb2, my, p, 0, kNoGroup));
     return TPB_OK;
 }
 
 template <int OUT>
 int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
-    if (p.gate != nullptr) return launch_pair_p<OUT_F32, 3>(h, st, p, q, w8, b_unsigned);
+    if (p.gate != nullptr)
+        return p.k <= 6144 ? launch_pair_p<OUT_F32, 3, 8>(h, st, p, q, w8, b_unsigned)
+                           : launch_pair_p<OUT_F32, 3, 4>(h, st, p, q, w8, b_unsigned);
     if (p.mc_y != nullptr) return launch_pair_p<OUT, 2>(h, st, p, q, w8, b_unsigned);
     return p.n_peers > 0 ? launch_pair_p<OUT, 1>(h, st, p, q, w8, b_unsigned)
                          : launch_pair_p<OUT, 0>(h, st, p, q, w8, b_unsigned);

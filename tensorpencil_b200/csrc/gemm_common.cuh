@@ -287,12 +287,15 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 // 1 = also write every piece to GemmParams::peer_y with plain
 // stores; 2 = write every piece once, to the multicast address GemmParams::mc_y, instead of
 // the local TMA store.  A template parameter so that the ordinary kernels carry none of it.
-template <int BN, int OUT, int PEERS = 0>
+template <int BN, int OUT, int PEERS = 0, bool LEAN = false>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
                                               uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
                                               int row0, int n0, float as, int corr, int lane,
                                               const float *w_scale_in = nullptr) {
     const float *w_scale = w_scale_in != nullptr ? w_scale_in : p.w_scale;   // the weight's scales (several weights per launch)
+    // LEAN (the gated mode with eight epilogue warps, 168 registers per thread): the accumulators are read through
+    // one buffer instead of two and the residual one piece ahead instead of two.
+    constexpr bool kOneTmemBuf = LEAN;
     uint32_t ra[32], rb[32];
     tc_ld_32x32(t_row, ra);
     // Gated residual: the 32 x 32 pieces of the residual stream this warp updates, read kPre pieces ahead of
@@ -302,7 +305,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
     // the plain GEMM (more of those loads in flight made it worse: 102 us).  L2-only loads: the tile is
     // rewritten below through the TMA (async proxy), which does not update a line such a load would leave in
     // L1, and a dependent kernel that was launched early on this SM could then read the old values from it.
-    constexpr int kPre = 2;
+    constexpr int kPre = LEAN ? 1 : 2;
     float4 xr[PEERS == 3 ? kPre : 1][8];
     auto load_residual = [&](int c, float4 (&dst)[8]) {
         const int col = n0 + c * 32 + 4 * (lane & 7);
@@ -341,7 +344,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
     if (kTwoSets) load_scales(0, wsa);
 #pragma unroll
     for (int c = 0; c < BN / 32; c++) {
-        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&cur)[32] = (!kOneTmemBuf && (c & 1)) ? rb : ra;
         uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
         float4(&wsc)[8] = (kTwoSets && (c & 1)) ? reinterpret_cast<float4(&)[8]>(wsb) : wsa;
         float4(&gtc)[PEERS == 3 ? 8 : 1] = gta;
@@ -351,7 +354,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             load_scales(c, wsa);
         }
         tc_wait_ld_dep(cur);  // columns 32c.. are in `cur`
-        if (c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), nxt);
+        if (!kOneTmemBuf && c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), nxt);
         const int col0 = n0 + c * 32;
         // first piece of a 128-byte staging row: make sure the TMA store that last
         // read this buffer (two stores ago) is done with it
@@ -363,7 +366,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
         // other buffer's store".
         const int scol = (OUT == OUT_BF16 && (c & 1)) ? col0 - 32 : col0;
         const bool do_store = row0 < p.m && scol < p.n && !(p.ablate & 8);
-        if (!do_store) continue;
+        if (!do_store) {
+            if (kOneTmemBuf && c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), ra);
+            continue;
+        }
         if (first_piece) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
@@ -432,6 +438,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 st_shared_v4(buf + ((piece ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
             }
         }
+        // one accumulator buffer: the next piece is requested now that this one's values are used up
+        if (kOneTmemBuf && c + 1 < BN / 32) tc_ld_32x32(t_row + (uint32_t)((c + 1) * 32), ra);
         const bool last_piece = OUT != OUT_BF16 || (c & 1) == 1;
         if (last_piece) {
             // generic-proxy writes -> visible to the async proxy, then one lane stores
