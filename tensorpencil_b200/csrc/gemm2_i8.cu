@@ -30,12 +30,11 @@ constexpr int kStageA = BM * BK;               // 16 KB: this CTA's 128 rows of 
 constexpr int kStageB = (BN2 / 2) * BK;        // 16 KB: this CTA's half of the weight tile
 constexpr int kStage2 = kStageA + kStageB;
 // Epilogue warps per CTA (template parameter EW): four (one per 32-lane quarter of tensor memory, all 256 columns
-// each), or eight -- two warps per quarter, 128 columns each -- for the gated-residual mode at short K, where the
-// epilogue, which reads the residual tile it updates, sets the pace (K = 3072: 56 -> 51 us).  Their staging
-// buffers take the place of one operand stage, which costs a long-K GEMM more than the epilogue gains
-// (K = 12288: 131 -> 141 us), so those keep four.
-constexpr int stages2(int ew) { return ew == 8 ? 5 : 6; }
-constexpr int staging2(int ew) { return ew * 2 * 4096; }
+// each, two 4 KB staging buffers per warp), or eight -- two warps per quarter, 128 columns each, one staging buffer
+// per warp -- for the gated-residual mode, whose epilogue reads the residual tile it updates and sets the pace at
+// short K (K = 3072: 56 -> 48 us; K = 12288: 134 -> 130 us).  The operand ring is the same either way.
+constexpr int stages2(int) { return 6; }
+constexpr int staging2(int) { return 4 * 2 * 4096; }   // two 4 KB buffers per warp (four warps) or one each (eight)
 constexpr int smem2(int ew) { return stages2(ew) * kStage2 + staging2(ew) + 1024 + 256; }
 constexpr int threads2(int ew) { return 64 + 32 * ew; }
 constexpr int kTmemCols2 = 2 * BN2;
@@ -184,7 +183,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         const int quarter = warp & 3;
         const int chalf = (kEpiWarps == 8) ? (warp - 2) >> 2 : 0;   // which 128 columns of the tile (eight warps)
         const int c_off = chalf * kEpiCols;
-        const uint32_t stg = stg_base + (uint32_t)(warp - 2) * 8192u;
+        const uint32_t stg = stg_base + (uint32_t)(warp - 2) * (kEpiWarps == 8 ? 4096u : 8192u);
         const uint32_t my_row_off = (uint32_t)lane * 128u;
         const uint32_t sw = (uint32_t)(lane & 7);
         uint32_t n_store = 0;
@@ -227,7 +226,7 @@ convrot_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 if constexpr (PAIR == 1 && (OUT == OUT_F32 || OUT == OUT_BF16))
                     epilogue_pair<OUT>(t_row, p, &tma_y, stg, my_row_off, sw, n_store, row0, n0, as, lane);
             } else if (!(p.ablate & 4)) {
-                epilogue_tile<kEpiCols, OUT, PEERS, EW == 8>(t_row, p, ymap, stg, my_row_off, sw, n_store, row0, n0 + c_off, as, corr, lane, w_scale);
+                epilogue_tile<kEpiCols, OUT, PEERS, EW == 8 && PEERS == 3, EW == 8>(t_row, p, ymap, stg, my_row_off, sw, n_store, row0, n0 + c_off, as, corr, lane, w_scale);
             }
             tc_fence_before();
             __syncwarp();
@@ -339,12 +338,12 @@ int launch_silu_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const
 template <int OUT>
 int launch_pair(tpb_handle_t h, cudaStream_t st, const GemmParams &p, const int8_t *q, const void *w8,
                 bool b_unsigned) {
-    if (p.gate != nullptr)
-        return p.k <= 6144 ? launch_pair_p<OUT_F32, 3, 8>(h, st, p, q, w8, b_unsigned)
-                           : launch_pair_p<OUT_F32, 3, 4>(h, st, p, q, w8, b_unsigned);
+    if (p.gate != nullptr) return launch_pair_p<OUT_F32, 3, 8>(h, st, p, q, w8, b_unsigned);
     if (p.mc_y != nullptr) return launch_pair_p<OUT, 2>(h, st, p, q, w8, b_unsigned);
-    return p.n_peers > 0 ? launch_pair_p<OUT, 1>(h, st, p, q, w8, b_unsigned)
-                         : launch_pair_p<OUT, 0>(h, st, p, q, w8, b_unsigned);
+    if (p.n_peers > 0) return launch_pair_p<OUT, 1>(h, st, p, q, w8, b_unsigned);
+    // (eight epilogue warps in the plain modes: the epilogue alone gets faster -- n = 12288, k = 256: 77 -> 54 us --
+    // but a GEMM bound by its main loop does not: k = 3072, n = 12288: 129 -> 134 us)
+    return launch_pair_p<OUT, 0>(h, st, p, q, w8, b_unsigned);
 }
 
 }  // namespace

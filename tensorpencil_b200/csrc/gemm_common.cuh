@@ -287,14 +287,15 @@ __device__ __forceinline__ uint32_t make_idesc2_i8(bool b_unsigned) {
 // 1 = also write every piece to GemmParams::peer_y with plain
 // stores; 2 = write every piece once, to the multicast address GemmParams::mc_y, instead of
 // the local TMA store.  A template parameter so that the ordinary kernels carry none of it.
-template <int BN, int OUT, int PEERS = 0, bool LEAN = false>
+template <int BN, int OUT, int PEERS = 0, bool LEAN = false, bool ONE_STG = LEAN>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &p, const CUtensorMap *tma_y,
                                               uint32_t stg, uint32_t my_row_off, uint32_t sw, uint32_t &n_store,
                                               int row0, int n0, float as, int corr, int lane,
                                               const float *w_scale_in = nullptr) {
     const float *w_scale = w_scale_in != nullptr ? w_scale_in : p.w_scale;   // the weight's scales (several weights per launch)
     // LEAN (the gated mode with eight epilogue warps, 168 registers per thread): the accumulators are read through
-    // one buffer instead of two and the residual one piece ahead instead of two.
+    // one register buffer instead of two and the residual one piece ahead instead of two.  ONE_STG (eight epilogue
+    // warps, 4 KB of staging each): a piece is staged in one buffer, whose previous store must have been read out first.
     constexpr bool kOneTmemBuf = LEAN;
     uint32_t ra[32], rb[32];
     tc_ld_32x32(t_row, ra);
@@ -359,7 +360,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
         // first piece of a 128-byte staging row: make sure the TMA store that last
         // read this buffer (two stores ago) is done with it
         const bool first_piece = OUT != OUT_BF16 || (c & 1) == 0;
-        const uint32_t buf = stg + (n_store & 1u) * 4096u + my_row_off;
+        const uint32_t buf = stg + (ONE_STG ? 0u : (n_store & 1u) * 4096u) + my_row_off;
         // Warp-uniform: does this 128-byte-wide piece reach into the tensor at all?
         // Skipped pieces touch neither the staging buffers nor the buffer counter,
         // so "all but the latest store have finished reading" keeps meaning "the
@@ -371,7 +372,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             continue;
         }
         if (first_piece) {
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (lane == 0) {
+                if (ONE_STG) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // one staging buffer
+                else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
             __syncwarp();
         }
         if (OUT == OUT_S32) {
@@ -383,7 +387,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             float4 xrow[PEERS == 3 ? 8 : 1];
             if (PEERS == 3) {
                 // the piece loaded ahead, through the (free) staging buffer: rows x 16-byte chunks in, this lane's row out
-                const uint32_t sbase = stg + (n_store & 1u) * 4096u;
+                const uint32_t sbase = stg + (ONE_STG ? 0u : (n_store & 1u) * 4096u);
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const uint32_t r = (uint32_t)(4 * i + (lane >> 3));
@@ -446,7 +450,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (PEERS != 2 && lane == 0 && !(p.ablate & 16)) {
-                tma_store_2d(tma_y, stg + (n_store & 1u) * 4096u, scol, row0);
+                tma_store_2d(tma_y, stg + (ONE_STG ? 0u : (n_store & 1u) * 4096u), scol, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
             if (PEERS == 1 || PEERS == 2) {
@@ -455,7 +459,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const GemmParams &
                 // instruction writes four whole rows' segments.
                 constexpr int kElemsPerChunk = OUT == OUT_BF16 ? 8 : 4;
                 constexpr int kElemBytes = OUT == OUT_BF16 ? 2 : 4;
-                const uint32_t sbase = stg + (n_store & 1u) * 4096u;
+                const uint32_t sbase = stg + (ONE_STG ? 0u : (n_store & 1u) * 4096u);
                 const int chunk = lane & 7;
                 const int gcol = scol + chunk * kElemsPerChunk;
 #pragma unroll
