@@ -197,7 +197,15 @@ int tpb_q8_1_quantize(tpb_handle_t h, tpb_stream_t stream, const float *x, int64
  *   y[i*rows + r] = scale * sum_b float(sum_e qw*qx) * (d_w * d_x),  i < ng <= 8
  * against activation rows row_off .. row_off+ng-1 of an xq buffer that holds
  * n_total rows of `cols` elements.  The weight streams from HBM once for all
- * ng rows.  cols % 32 == 0; w 16-byte aligned. */
+ * ng rows.  cols % 32 == 0; w 16-byte aligned.
+ *
+ * Ordering: the GEMV kernels (this one, tpb_q8_0_gemv, tpb_q8_0_gemv_static and tpb_gguf_gemv_q8n) are launched
+ * with programmatic stream serialisation and begin streaming the WEIGHT while the kernel before them in the
+ * stream is still finishing; everything else (xq, y) is ordered as usual.  A weight is a constant of the model,
+ * so this is invisible -- except to a host that produces `w` with a kernel launched on the same stream directly
+ * before the call (a conversion or a copy kernel): put anything between the two (another kernel, an event), or
+ * set TPB_NO_PDL=1, which launches every kernel of the library fully serialised.  Copies enqueued with
+ * cudaMemcpyAsync and work ordered through events, as the weight streamer does it, are not affected. */
 int tpb_q8_0_gemv_q8n(tpb_handle_t h, tpb_stream_t stream, float *y, const void *w, float scale,
                       int64_t rows, int64_t cols, const void *xq, int ng, int row_off,
                       int n_total);

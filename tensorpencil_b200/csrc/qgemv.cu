@@ -319,17 +319,7 @@ q8_0_gemv_f32_kernel(float *__restrict__ y, const float *__restrict__ x, const u
 template <typename Kern>
 cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t st, const GemvParams &p,
                        int stages) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)block);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, p, stages);
+    return tpb_launch_pdl(kern, dim3((unsigned)grid), dim3((unsigned)block), smem, st, p, stages);
 }
 
 // One (M, R) instantiation: fit activations + per-warp rings into the opt-in shared
